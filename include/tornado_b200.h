@@ -1,0 +1,161 @@
+/*
+ * tornado_b200.h -- C ABI of libtornado_b200.so
+ *
+ * Hand-written sm_100a kernels for the dense / quantised matrix-vector and
+ * matrix-matrix products that TornadoVM runs through its library-task API.
+ * The library plays the role that tornado-drivers/cublas-jni and
+ * tornado-drivers/cutlass-jni play for cuBLAS and CUTLASS, but exposes a plain
+ * C ABI (no jni.h) so that Java binds it with java.lang.foreign downcalls.
+ *
+ * Calling convention (same discipline as tornado-drivers/cutlass-jni/src/main/
+ * cpp/source/tornado-cutlass.cu:176-259 and cublas-jni/.../tornado-cublas.cpp:
+ * 131-198):
+ *   - every device pointer is a raw CUdeviceptr that already points at element
+ *     0 of a TornadoVM off-heap array, i.e. buffer base + array header
+ *     (tornado-runtime/.../interpreter/TornadoVMInterpreter.java:1260-1266);
+ *     the header is 16 or 24 bytes, so 8-byte alignment is all that is
+ *     guaranteed; 16-byte aligned pointers take the fast path;
+ *   - scalars are passed by value; `stream` is the CUstream / cudaStream_t of
+ *     the execution plan (TornadoNativeStreamSupport.getNativeStream);
+ *   - the CUDA context of the plan must be current on the calling thread;
+ *   - every call only enqueues work: it never allocates, frees, synchronises
+ *     or copies, so it may be issued while the stream is being captured;
+ *   - the return value is a status: 0 success, < 0 argument / library error
+ *     (tb200_status below), > 0 a cudaError_t.  Nothing throws or aborts.
+ *
+ * Layouts (all row-major, little-endian):
+ *   FloatArray      float32
+ *   HalfFloatArray  IEEE binary16 bit patterns in 16-bit words
+ *   Int8Array       int8
+ *   Q8_0 split      Int8Array q[rows*cols] + HalfFloatArray scale[rows*cols/32]
+ *   Q8_0 blocks     ByteArray of 34-byte blocks: fp16 scale, 32 x int8
+ *                   (tornado-examples/.../MatrixVectorRowMajor.java:363-407)
+ *   Q4_0 blocks     ByteArray of 18-byte blocks: fp16 scale, 16 bytes; byte i
+ *                   holds element i in its low nibble and element i+16 in its
+ *                   high nibble; value = nibble - 8
+ *   batched GEMV    x is [batch][cols], y is [batch][rows]
+ */
+#ifndef TORNADO_B200_H
+#define TORNADO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TB200_VERSION 100
+
+typedef void *tb200_stream_t; /* CUstream / cudaStream_t */
+
+enum tb200_status {
+    TB200_OK = 0,
+    TB200_ERR_INVALID_ARG = -1,  /* null pointer, non-positive or unsupported shape */
+    TB200_ERR_ALIGNMENT = -2,    /* pointer below the guaranteed alignment */
+    TB200_ERR_WORKSPACE = -3,    /* workspace missing or too small */
+    TB200_ERR_UNSUPPORTED = -4,  /* device is not sm_100 */
+    TB200_ERR_DRIVER = -5,       /* a driver entry point could not be resolved */
+    TB200_ERR_TIMEOUT = -6       /* a bounded device-side wait expired */
+};
+
+/* Replaces Java_..._CutlassNativeLib_statusString
+ * (tornado-cutlass.cu:474-478) / CuBlasNativeLib.statusName
+ * (tornado-cublas/.../provider/CuBlasNativeLib.java:80-100). */
+const char *tb200_status_string(int status);
+int tb200_version(void);
+
+/* Non-zero once any kernel of this library on the current device gave up a
+ * bounded wait (value = TB200_ERR_TIMEOUT).  Synchronises the device; meant
+ * for tests and diagnostics, not for the launch path. */
+int tb200_device_status(int *status_out);
+
+/* Device scratch owned by the provider's context (grow-only workspace of the
+ * integer path).  Replaces CutlassNativeLib.allocateDeviceMemory /
+ * freeDeviceMemory (tornado-cutlass.cu:455-472; CutlassLibraryProvider.java:
+ * 51-66).  Called from createContext / prepare / destroyContext only, never
+ * between launches. */
+int tb200_device_malloc(size_t bytes, void **out);
+int tb200_device_free(void *ptr);
+
+/* ---- FP32 matrix-vector ---------------------------------------------------
+ * out[i] = sum_j m[i*cols + j] * v[j]
+ * Replaces the JIT-compiled README mxv kernel (README.md:35-47),
+ * LinearAlgebraArrays.sgemv (tornado-benchmarks/.../LinearAlgebraArrays.java:
+ * 34-42) and matrixVectorGeneric (MatrixVectorRowMajor.java:108-158); same
+ * operands as CuBlas.cublasSgemv for a row-major matrix
+ * (tornado-cublas.cpp:131-140). */
+int tb200_sgemv(int rows, int cols, const float *m, const float *v, float *out, tb200_stream_t stream);
+
+/* ---- Q8_0 matrix-vector, fp32 activations ("float mode") -------------------
+ * y[b][r] = sum_j ((float) q[r][j] * scale[r][j/32]) * x[b][j]
+ * Replaces matrixVectorGenericFinal (MatrixVectorRowMajor.java:409-423,
+ * :530-578) for the split layout and matrixVectorGenericQ8Byte (:428-524) for
+ * the 34-byte block layout.  cols % 32 == 0, 1 <= batch <= 16. */
+int tb200_q8_gemv(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x, float *y,
+                  tb200_stream_t stream);
+int tb200_q8b_gemv(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
+                   tb200_stream_t stream);
+
+/* ---- Q4_0 matrix-vector, fp32 activations ----------------------------------
+ * y[b][r] = sum_blk scale[r][blk] * sum_i (nibble[r][blk][i] - 8) * x[b][32 blk + i]
+ * No counterpart in the reference (Q4_0 is only on its roadmap,
+ * NVIDIA_ROADMAP.md:18); the operand discipline is that of tb200_q8b_gemv. */
+int tb200_q4b_gemv(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
+                   tb200_stream_t stream);
+
+/* ---- integer path ("exact-int mode") ----------------------------------------
+ * Activations are quantised on the device to int8 with one fp32 scale per
+ * 32-element block, scale = max|x|/127 (1 when the block is all zero),
+ * q = (int8) floor(x * (1/scale) + 0.5): the rule of reductionCalculateMax +
+ * quantizeKernelContext (MatrixVectorRowMajor.java:308-354) applied per block.
+ * Each weight block then contributes an exact int32 dot (dp4a, the device form
+ * of QuantizationUtils.dp4a, tornado-api/.../utils/QuantizationUtils.java:29-39)
+ * and y[b][r] = sum_blk (float) dot * wscale * xscale
+ * (dequantizeFusedResult, QuantizationUtils.java:53-55).
+ *
+ * The quantised activations live in caller-provided scratch memory:
+ *   workspace layout  int8 xq[batch][cols], then float xs[batch][cols/32]
+ *   (xs starts at the next multiple of 16 bytes after xq). */
+size_t tb200_qx_workspace_bytes(int cols, int batch);
+int tb200_quantize_x(int cols, int batch, const float *x, void *workspace, size_t workspace_bytes,
+                     tb200_stream_t stream);
+int tb200_q8_gemv_i8(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x,
+                     float *y, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+int tb200_q8b_gemv_i8(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
+                      void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+int tb200_q4b_gemv_i8(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
+                      void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+
+/* Test entry points: the raw int32 block dots, dots[r][blk], for one
+ * already-quantised activation vector xq[cols].  Device form of the unit test
+ * QuantizationTests.testDP4A (tornado-unittests/.../quantization/
+ * QuantizationTests.java:517-549). */
+int tb200_q8_blockdots_i32(int rows, int cols, const int8_t *q, const int8_t *xq, int32_t *dots,
+                           tb200_stream_t stream);
+int tb200_q8b_blockdots_i32(int rows, int cols, const uint8_t *blocks, const int8_t *xq, int32_t *dots,
+                            tb200_stream_t stream);
+int tb200_q4b_blockdots_i32(int rows, int cols, const uint8_t *blocks, const int8_t *xq, int32_t *dots,
+                            tb200_stream_t stream);
+
+/* ---- FP32 SGEMM -------------------------------------------------------------
+ * C = alpha * A * B + beta * C, A[m][k], B[k][n], C[m][n] row-major.
+ * Replaces MatrixMultiplication2D.matrixMultiplication
+ * (tornado-examples/.../MatrixMultiplication2D.java:48-58) and has the
+ * signature of Java_..._CutlassNativeLib_sgemm (tornado-cutlass.cu:176-199). */
+int tb200_sgemm(int m, int n, int k, float alpha, const float *a, const float *b, float beta, float *c,
+                tb200_stream_t stream);
+
+/* ---- FP16 GEMM, fp32 accumulate and output ---------------------------------
+ * C(fp32)[m][n] = A(fp16)[m][k] * B(fp16)[k][n], row-major.
+ * Replaces the tile-API kernels gemmMMA ... gemmMMASwizzled
+ * (tornado-examples/.../MatrixMultiplicationMMA.java:100-613) and the operands
+ * of CuBlas.cublasGemmExFP16FP32 (tornado-cublas/.../CuBlas.java:261-279).
+ * Runs on tcgen05 tensor cores when k % 8 == 0, n % 8 == 0 and A, B are
+ * 16-byte aligned; any other case takes a CUDA-core kernel. */
+int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c, tb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TORNADO_B200_H */

@@ -1,0 +1,92 @@
+"""Factories of the ``b200/linalg`` library tasks.
+
+Python twin of the Java class ``B200``; same shape as ``Cutlass``
+(tornado-cutlass/.../Cutlass.java:44-191) and ``CuBlas``
+(tornado-cublas/.../CuBlas.java:97-305): each factory validates shapes early
+with a clear message and returns a LibraryTaskDescriptor whose parameter list
+is what the provider later receives positionally.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from .arrays import ByteArray, FloatArray, HalfFloatArray, Int8Array
+from .descriptor import Access, LibraryTaskDescriptor
+
+LIBRARY_NAME = "b200/linalg"
+MAX_BATCH = 16
+
+
+@dataclass
+class B200Options:
+    """Per-call tuning object (LibraryTaskDescriptor.withTuning):
+    ``exact_int`` selects the int8-activation / int32 block-dot arithmetic for
+    the quantised mat-vec tasks."""
+    exact_int: bool = False
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError("[ERROR] " + msg)
+
+
+def _desc(function, params, out_index, read_write=False, tuning=None):
+    access = [Access.READ_ONLY] * len(params)
+    access[out_index] = Access.READ_WRITE if read_write else Access.WRITE_ONLY
+    d = LibraryTaskDescriptor().withLibrary(LIBRARY_NAME).withFunction(function).withParameters(params).withAccess(access)
+    if tuning is not None:
+        d.withTuning(tuning)
+    return d
+
+
+class B200:
+    LIBRARY_NAME = LIBRARY_NAME
+
+    @staticmethod
+    def sgemv(rows: int, cols: int, m: FloatArray, v: FloatArray, out: FloatArray):
+        """out[i] = sum_j m[i*cols+j] * v[j] (README mxv, README.md:35-47)."""
+        _check(rows >= 0 and cols >= 0, f"B200 sgemv requires non-negative sizes; got rows={rows}, cols={cols}")
+        _check(m.getSize() >= rows * cols and v.getSize() >= cols and out.getSize() >= rows,
+               "B200 sgemv: array smaller than rows x cols")
+        return _desc("sgemv", [rows, cols, m, v, out], 4)
+
+    @staticmethod
+    def _check_q(name, rows, cols, batch, x, y):
+        _check(cols % 32 == 0, f"B200 {name} requires cols to be a multiple of the 32-element block; got cols={cols}")
+        _check(1 <= batch <= MAX_BATCH, f"B200 {name} requires 1 <= batch <= {MAX_BATCH}; got {batch}")
+        _check(x.getSize() >= batch * cols and y.getSize() >= batch * rows, f"B200 {name}: x or y too small")
+
+    @staticmethod
+    def q8Gemv(rows, cols, batch, q: Int8Array, scales: HalfFloatArray, x: FloatArray, y: FloatArray, options=None):  # noqa: N802
+        """Q8_0 mat-vec, split layout (matrixVectorGenericFinal, MatrixVectorRowMajor.java:409-423)."""
+        B200._check_q("q8Gemv", rows, cols, batch, x, y)
+        _check(q.getSize() >= rows * cols and scales.getSize() >= rows * cols // 32, "B200 q8Gemv: weights too small")
+        return _desc("q8Gemv", [rows, cols, batch, q, scales, x, y], 6, tuning=options)
+
+    @staticmethod
+    def q8GemvBytes(rows, cols, batch, blocks: ByteArray, x: FloatArray, y: FloatArray, options=None):  # noqa: N802
+        """Q8_0 mat-vec, 34-byte blocks (matrixVectorGenericQ8Byte, MatrixVectorRowMajor.java:428-524)."""
+        B200._check_q("q8GemvBytes", rows, cols, batch, x, y)
+        _check(blocks.getSize() >= rows * (cols // 32) * 34, "B200 q8GemvBytes: weights too small")
+        return _desc("q8GemvBytes", [rows, cols, batch, blocks, x, y], 5, tuning=options)
+
+    @staticmethod
+    def q4GemvBytes(rows, cols, batch, blocks: ByteArray, x: FloatArray, y: FloatArray, options=None):  # noqa: N802
+        """Q4_0 mat-vec, 18-byte blocks."""
+        B200._check_q("q4GemvBytes", rows, cols, batch, x, y)
+        _check(blocks.getSize() >= rows * (cols // 32) * 18, "B200 q4GemvBytes: weights too small")
+        return _desc("q4GemvBytes", [rows, cols, batch, blocks, x, y], 5, tuning=options)
+
+    @staticmethod
+    def sgemm(m, n, k, alpha, a: FloatArray, b: FloatArray, beta, c: FloatArray):
+        """C = alpha*A*B + beta*C, row-major; signature of Cutlass.cutlassSgemm (Cutlass.java:57-66)."""
+        _check(m >= 0 and n >= 0 and k >= 0, f"B200 sgemm requires non-negative sizes; got m={m}, n={n}, k={k}")
+        _check(a.getSize() >= m * k and b.getSize() >= k * n and c.getSize() >= m * n, "B200 sgemm: array too small")
+        return _desc("sgemm", [m, n, k, float(alpha), a, b, float(beta), c], 7, read_write=(beta != 0.0))
+
+    @staticmethod
+    def hgemmF32(m, n, k, a: HalfFloatArray, b: HalfFloatArray, c: FloatArray):  # noqa: N802
+        """C(fp32) = A(fp16) * B(fp16), row-major (operands of CuBlas.cublasGemmExFP16FP32, CuBlas.java:261-279)."""
+        _check(m >= 0 and n >= 0 and k >= 0, f"B200 hgemmF32 requires non-negative sizes; got m={m}, n={n}, k={k}")
+        _check(a.getSize() >= m * k and b.getSize() >= k * n and c.getSize() >= m * n, "B200 hgemmF32: array too small")
+        return _desc("hgemmF32", [m, n, k, a, b, c], 5)

@@ -1,0 +1,130 @@
+"""``B200LibraryProvider`` -- Python twin of the Java provider of the same name.
+
+Implements the reference's provider SPI method for method
+(tornado-runtime/.../library/spi/TornadoLibraryProvider.java:42-85) with the
+structure of CutlassLibraryProvider (tornado-cutlass/.../provider/
+CutlassLibraryProvider.java:40-169): a per-(device, plan) context that holds
+the plan's stream and a grow-only device workspace, ``prepare`` that sizes the
+workspace before any launch (and before stream capture), and ``dispatch`` that
+marshals positional arguments into one native call and checks its status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from .b200 import LIBRARY_NAME, B200Options
+from .native import B200Native
+
+
+class LibraryInvocation:
+    """spi/LibraryInvocation.java:54-97."""
+
+    def __init__(self, args, device_pointers, context, tuning=None, device=None, plan_id=0):
+        self._args, self._ptrs, self._ctx = list(args), list(device_pointers), context
+        self._tuning, self._device, self._plan = tuning, device, plan_id
+
+    def getArg(self, i):  # noqa: N802
+        return self._args[i]
+
+    def getDevicePointer(self, i):  # noqa: N802
+        p = self._ptrs[i]
+        if p is None:
+            raise RuntimeError(f"[ERROR] argument {i} is not a device reference")
+        return p
+
+    def isReference(self, i):  # noqa: N802
+        return self._ptrs[i] is not None
+
+    def getContext(self):  # noqa: N802
+        return self._ctx
+
+    def getTuning(self):  # noqa: N802
+        return self._tuning
+
+    def getDevice(self):  # noqa: N802
+        return self._device
+
+    def getExecutionPlanId(self):  # noqa: N802
+        return self._plan
+
+
+class B200Context:
+    """LibraryContext: stream of the plan + grow-only workspace."""
+
+    def __init__(self, stream: int):
+        self.stream = stream
+        self.workspace_ptr = 0
+        self.workspace_bytes = 0
+
+    def grow_workspace(self, required: int) -> None:
+        if required > self.workspace_bytes:
+            if self.workspace_ptr:
+                B200Native.call("tb200_device_free", C.c_void_p(self.workspace_ptr))
+                self.workspace_ptr, self.workspace_bytes = 0, 0
+            out = C.c_void_p()
+            B200Native.call("tb200_device_malloc", required, C.byref(out))
+            if not out.value:
+                raise RuntimeError(f"[ERROR] Unable to allocate B200 workspace of {required} bytes")
+            self.workspace_ptr, self.workspace_bytes = out.value, required
+
+
+_QUANT_FUNCTIONS = {"q8Gemv", "q8GemvBytes", "q4GemvBytes"}
+
+
+class B200LibraryProvider:
+    def libraryName(self) -> str:  # noqa: N802
+        return LIBRARY_NAME
+
+    def canHandle(self, device) -> bool:  # noqa: N802
+        # only devices that expose their native stream (TornadoNativeStreamSupport)
+        return hasattr(device, "getNativeStream")
+
+    def createContext(self, device, executionPlanId: int) -> B200Context:  # noqa: N802
+        B200Native.load()
+        return B200Context(device.getNativeStream(executionPlanId))
+
+    def prepare(self, descriptor, context: B200Context) -> None:
+        fn = descriptor.getFunctionName()
+        tuning = descriptor.getTuning()
+        if fn in _QUANT_FUNCTIONS and isinstance(tuning, B200Options) and tuning.exact_int:
+            p = descriptor.getParameters()
+            need = B200Native.load().tb200_qx_workspace_bytes(int(p[1]), int(p[2]))
+            context.grow_workspace(int(need))
+
+    def dispatch(self, functionName: str, inv: LibraryInvocation) -> None:  # noqa: N802
+        ctx: B200Context = inv.getContext()
+        lib = B200Native.load()
+        tuning = inv.getTuning()
+        exact = isinstance(tuning, B200Options) and tuning.exact_int
+        P = inv.getDevicePointer
+        A = inv.getArg
+        ws = (ctx.workspace_ptr, ctx.workspace_bytes)
+        if functionName == "sgemv":  # (rows, cols, m, v, out)
+            st = lib.tb200_sgemv(A(0), A(1), P(2), P(3), P(4), ctx.stream)
+        elif functionName == "q8Gemv":  # (rows, cols, batch, q, scales, x, y)
+            if exact:
+                st = lib.tb200_q8_gemv_i8(A(0), A(1), A(2), P(3), P(4), P(5), P(6), *ws, ctx.stream)
+            else:
+                st = lib.tb200_q8_gemv(A(0), A(1), A(2), P(3), P(4), P(5), P(6), ctx.stream)
+        elif functionName == "q8GemvBytes":  # (rows, cols, batch, blocks, x, y)
+            if exact:
+                st = lib.tb200_q8b_gemv_i8(A(0), A(1), A(2), P(3), P(4), P(5), *ws, ctx.stream)
+            else:
+                st = lib.tb200_q8b_gemv(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
+        elif functionName == "q4GemvBytes":
+            if exact:
+                st = lib.tb200_q4b_gemv_i8(A(0), A(1), A(2), P(3), P(4), P(5), *ws, ctx.stream)
+            else:
+                st = lib.tb200_q4b_gemv(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
+        elif functionName == "sgemm":  # (m, n, k, alpha, a, b, beta, c)
+            st = lib.tb200_sgemm(A(0), A(1), A(2), A(3), P(4), P(5), A(6), P(7), ctx.stream)
+        elif functionName == "hgemmF32":  # (m, n, k, a, b, c)
+            st = lib.tb200_hgemm_f32(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
+        else:
+            raise RuntimeError(f"[ERROR] B200 function not supported: {functionName}")
+        B200Native.check_status(st, functionName)
+
+    def destroyContext(self, context: B200Context) -> None:  # noqa: N802
+        if context.workspace_ptr:
+            B200Native.call("tb200_device_free", C.c_void_p(context.workspace_ptr))
+            context.workspace_ptr, context.workspace_bytes = 0, 0

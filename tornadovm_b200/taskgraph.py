@@ -1,0 +1,187 @@
+"""A small stand-in for the part of TornadoVM that surrounds a library task.
+
+No JVM exists where this package is built and tested, so this module plays the
+role of ``TaskGraph`` / ``TornadoExecutionPlan`` and of the interpreter's
+``executeLibraryLaunch`` (tornado-runtime/.../interpreter/
+TornadoVMInterpreter.java:1245-1328) for graphs made of library tasks:
+
+* device buffers are ``header + payload`` bytes and tasks receive
+  ``base + header`` (:1260-1266);
+* one non-blocking stream per plan (cuda-jni/.../CUDAContext.cpp:83);
+* ``prepare`` for every task before the first launch and before capture
+  (:1036-1055); ``withCUDAGraph()`` captures the launches of one execution and
+  replays them (HYBRID_API_GUIDE.md:317-334);
+* contexts are destroyed when the plan closes (TornadoTaskGraph.java:1277).
+
+Device memory, streams and copies are PyTorch's; nothing here computes.
+"""
+from __future__ import annotations
+
+import enum
+import itertools
+
+import torch
+
+from .arrays import TornadoNativeArray
+from .provider import B200LibraryProvider, LibraryInvocation
+
+
+class DataTransferMode(enum.Enum):
+    FIRST_EXECUTION = 1
+    EVERY_EXECUTION = 2
+
+
+class CudaDevice:
+    """What a provider sees of a device: TornadoNativeStreamSupport
+    (spi/TornadoNativeStreamSupport.java:34-63)."""
+
+    def __init__(self, index: int = 0):
+        if not torch.cuda.is_available():
+            raise RuntimeError("[ERROR] no CUDA device: the b200/linalg tasks have no CPU path")
+        self.index = index
+        self.torch_device = torch.device("cuda", index)
+        self._streams = {}
+
+    def torch_stream(self, plan_id: int) -> torch.cuda.Stream:
+        if plan_id not in self._streams:
+            with torch.cuda.device(self.index):
+                self._streams[plan_id] = torch.cuda.Stream(device=self.torch_device)
+        return self._streams[plan_id]
+
+    def getNativeStream(self, plan_id: int) -> int:  # noqa: N802
+        return self.torch_stream(plan_id).cuda_stream
+
+    def getNativeContext(self, plan_id: int) -> int:  # noqa: N802
+        return 0  # primary context, current once torch has selected the device
+
+
+class _LibraryTask:
+    def __init__(self, task_id, descriptor):
+        self.id, self.descriptor = task_id, descriptor
+
+
+class TaskGraph:
+    def __init__(self, name: str):
+        self.name = name
+        self.to_device = []  # (mode, array)
+        self.to_host = []
+        self.tasks = []
+
+    def transferToDevice(self, mode: DataTransferMode, *arrays):  # noqa: N802
+        self.to_device += [(mode, a) for a in arrays]
+        return self
+
+    def libraryTask(self, task_id: str, factory, *args):  # noqa: N802
+        # the factory runs immediately and its descriptor is what the runtime keeps (TaskGraph.java:737-739)
+        self.tasks.append(_LibraryTask(task_id, factory(*args)))
+        return self
+
+    def transferToHost(self, mode: DataTransferMode, *arrays):  # noqa: N802
+        self.to_host += [(mode, a) for a in arrays]
+        return self
+
+    def snapshot(self):
+        return self
+
+
+class TornadoExecutionPlan:
+    _ids = itertools.count(1)
+
+    def __init__(self, graph: TaskGraph, device: CudaDevice | None = None, provider=None):
+        self.graph = graph
+        self.device = device or CudaDevice(0)
+        self.provider = provider or B200LibraryProvider()
+        if not self.provider.canHandle(self.device):
+            raise RuntimeError("[ERROR] device does not expose a native stream")
+        self.plan_id = next(self._ids)
+        self.stream = self.device.torch_stream(self.plan_id)
+        self.context = self.provider.createContext(self.device, self.plan_id)
+        self._buffers = {}  # id(array) -> (device uint8 tensor, pinned host tensor)
+        self._executions = 0
+        self._use_graph = False
+        self._cuda_graph = None
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+
+    # -- plan options -------------------------------------------------------
+    def withCUDAGraph(self):  # noqa: N802
+        self._use_graph = True
+        return self
+
+    # -- internals ------------------------------------------------------------
+    def _buffer(self, arr: TornadoNativeArray):
+        key = id(arr)
+        if key not in self._buffers:
+            n = arr.nbytes_with_header
+            dev = torch.empty(n, dtype=torch.uint8, device=self.device.torch_device)
+            host = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+            self._buffers[key] = (dev, host)
+        return self._buffers[key]
+
+    def _device_pointer(self, arr: TornadoNativeArray) -> int:
+        return self._buffer(arr)[0].data_ptr() + arr.header
+
+    def _launch_all(self):
+        for t in self.graph.tasks:
+            d = t.descriptor
+            params = d.getParameters()
+            ptrs = [self._device_pointer(p) if isinstance(p, TornadoNativeArray) else None for p in params]
+            inv = LibraryInvocation(params, ptrs, self.context, d.getTuning(), self.device, self.plan_id)
+            self.provider.dispatch(d.getFunctionName(), inv)
+
+    def execute(self):
+        g = self.graph
+        first = self._executions == 0
+        with torch.cuda.device(self.device.index), torch.cuda.stream(self.stream):
+            if first:
+                # allocate every buffer a task touches, then the pre-launch prepare pass
+                for t in g.tasks:
+                    for p in t.descriptor.getParameters():
+                        if isinstance(p, TornadoNativeArray):
+                            self._buffer(p)
+                    self.provider.prepare(t.descriptor, self.context)
+            h2d = 0
+            for mode, arr in g.to_device:
+                if first or mode is DataTransferMode.EVERY_EXECUTION:
+                    dev, host = self._buffer(arr)
+                    host.numpy()[:] = arr.segment
+                    dev.copy_(host, non_blocking=True)
+                    h2d += arr.nbytes_with_header
+            if self._use_graph:
+                if self._cuda_graph is None:
+                    self._launch_all()  # warm run: module load and attribute calls happen outside capture
+                    self.stream.synchronize()
+                    self._cuda_graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(self._cuda_graph, stream=self.stream):
+                        self._launch_all()
+                self._cuda_graph.replay()
+            else:
+                self._launch_all()
+            d2h = 0
+            for mode, arr in g.to_host:
+                dev, host = self._buffer(arr)
+                host.copy_(dev, non_blocking=True)
+                d2h += arr.nbytes_with_header
+            self.stream.synchronize()
+            for mode, arr in g.to_host:
+                host = self._buffer(arr)[1]
+                arr.segment[arr.header:] = host.numpy()[arr.header:]
+        self.h2d_bytes_last, self.d2h_bytes_last = h2d, d2h
+        self._executions += 1
+        return self
+
+    def close(self):
+        if self.context is not None:
+            with torch.cuda.device(self.device.index):
+                self.stream.synchronize()
+                self.provider.destroyContext(self.context)
+            self.context = None
+        self._buffers.clear()
+        self._cuda_graph = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+        return False
