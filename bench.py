@@ -1,0 +1,418 @@
+#!/usr/bin/env python
+"""Benchmark of the b200/linalg hot path.
+
+Headline workload (BASELINE.json configs[3]): Q8_0 quantised GEMV, decode style,
+W[14336 x 4096] as 32-element int8 blocks with one fp16 scale each, fp32
+activations, batch 1.  One "step" is one pass over LAYERS distinct weight
+matrices (LAYERS * 62.4 MB > the 126 MB L2, so every pass streams from HBM).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Prints one JSON line (rank 0).  `value` is device-resident throughput in GB/s of
+algorithmic bytes (34*rows*cols/32 + 4*batch*(cols+rows) per GEMV); `e2e` is the
+same metric through the public task-graph API with host buffers (activation
+host->device and result device->host inside every step); `roofline` compares
+the GEMV kernel with the measured HBM copy bandwidth; `cpu_baseline` times the
+CPU restatement of the reference's sequential / multi-core loop on the host.
+With N > 1 the weight rows are sharded over the ranks and the outputs are
+all-gathered over NCCL (strong scaling: the total work is fixed).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS, BATCH = 14336, 4096, 1
+LAYERS = 8  # distinct weight matrices per step: 8 * 62.4 MB = 499 MB footprint
+METRIC = "q8_0_gemv_hbm_throughput"
+UNIT = "GB/s"
+
+
+def algorithmic_bytes(rows, cols, batch, block_bytes=34):
+    return block_bytes * rows * cols // 32 + 4 * batch * (cols + rows)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+# ------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()  # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------- CPU baseline / reference arm
+def cpu_reference(seconds_target=8.0, threads=True):
+    """Times the CPU restatement of the reference's Q8_0 mat-vec loop
+    (MatrixVectorRowMajor.java:530-578 arithmetic, rows split over host threads the
+    way TornadoVM's multi-core CPU device splits the outer loop) on the full
+    14336 x 4096 matrix.  The only place this benchmark touches oracle/."""
+    import numpy as np
+    import oracle as o
+    rng = np.random.default_rng(42)
+    q = rng.integers(-127, 128, ROWS * COLS, dtype=np.int8)
+    s = (np.abs(rng.standard_normal(ROWS * COLS // 32)) * 0.02).astype(np.float16).view(np.uint16)
+    x = rng.standard_normal(COLS).astype(np.float32)
+    o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=threads)  # warm-up
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=threads)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds_target:
+            break
+    per = dt / n
+    cores = o.num_threads() if threads else 1
+    return {"value": algorithmic_bytes(ROWS, COLS, 1) / per / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} full {ROWS}x{COLS} batch-1 mat-vecs in {dt:.1f} s ({'OpenMP rows over host threads' if threads else 'single thread'})",
+            "ms_per_matvec": per * 1e3}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # K steps of LAYERS mat-vecs each would take minutes on a CPU: each step is a bounded sample (one mat-vec)
+    import numpy as np
+    import oracle as o
+    rng = np.random.default_rng(42)
+    q = rng.integers(-127, 128, ROWS * COLS, dtype=np.int8)
+    s = (np.abs(rng.standard_normal(ROWS * COLS // 32)) * 0.02).astype(np.float16).view(np.uint16)
+    x = rng.standard_normal(COLS).astype(np.float32)
+    for _ in range(args.warmup):
+        o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=True)
+    dt = time.perf_counter() - t0
+    per = dt / args.steps
+    val = algorithmic_bytes(ROWS, COLS, 1) / per / 1e9
+    sample = f"each step = one full {ROWS}x{COLS} batch-1 mat-vec (of the {LAYERS} per GPU step) on {o.num_threads()} host threads"
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"Q8_0 GEMV {ROWS}x{COLS} batch {BATCH}, CPU restatement of the reference loop"},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": o.num_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------- GPU arm
+def make_weights(torch, dev, rows, layers, seed):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q = torch.randint(-127, 128, (layers, rows, COLS), dtype=torch.int8, device=dev, generator=g)
+    sc = (torch.randn((layers, rows, COLS // 32), device=dev, generator=g).abs() * 0.02).half()
+    return q, sc
+
+
+def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak):
+    """Short device-resident timings of the other kernels on the path (not the headline)."""
+    out = {}
+    P = lambda t: C.c_void_p(t.data_ptr())
+    S = C.c_void_p(stream.cuda_stream)
+    dev = torch.device("cuda", torch.cuda.current_device())
+
+    def timeit(fn, reps, flush=None):
+        for _ in range(3):
+            fn(0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        stream.synchronize()
+        e0.record(stream)
+        for i in range(reps):
+            fn(i)
+        e1.record(stream)
+        stream.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    with torch.cuda.stream(stream):
+        # FP32 GEMV 8192 x 8192 (configs[0]); two matrices alternate (537 MB > L2)
+        m = torch.rand((2, 8192, 8192), device=dev) * 2 - 1
+        v = torch.rand(8192, device=dev) * 2 - 1
+        y = torch.empty(8192, device=dev)
+        t = timeit(lambda i: lib.tb200_sgemv(8192, 8192, P(m[i & 1]), P(v), P(y), S), 20)
+        b = 4 * (8192 * 8192 + 2 * 8192)
+        out["sgemv_8192"] = {"GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / hbm_peak, "us": t * 1e6}
+        del m
+        # Q8_0 variants on the headline shape
+        q, sc = make_weights(torch, dev, ROWS, 4, 7)
+        blocks = torch.empty((4, ROWS, COLS // 32, 34), dtype=torch.uint8, device=dev)
+        blocks[..., :2] = sc.view(torch.uint8).view(4, ROWS, COLS // 32, 2)
+        blocks[..., 2:] = q.view(torch.uint8).view(4, ROWS, COLS // 32, 32)
+        for batch in (1, 8):
+            x = torch.randn((batch, COLS), device=dev)
+            yb = torch.empty((batch, ROWS), device=dev)
+            ws_n = lib.tb200_qx_workspace_bytes(COLS, batch)
+            ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+            by = algorithmic_bytes(ROWS, COLS, batch)
+            runs = {
+                f"q8_split_f32_b{batch}": lambda i: lib.tb200_q8_gemv(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), S),
+                f"q8_blocks_f32_b{batch}": lambda i: lib.tb200_q8b_gemv(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), S),
+                f"q8_split_int_b{batch}": lambda i: lib.tb200_q8_gemv_i8(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), P(ws), ws_n, S),
+                f"q8_blocks_int_b{batch}": lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), P(ws), ws_n, S),
+            }
+            for name, fn in runs.items():
+                t = timeit(fn, 40)
+                out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
+        del q, sc, blocks
+        # Q4_0 Llama-3-8B-shaped layer sweep (configs[4]): 7 projections + the output projection
+        shapes = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336), (128256, 4096)]
+        g = torch.Generator(device=dev).manual_seed(3)
+        # two sets of weights alternate so that a pass never finds its matrices in L2 (2 x 418 MB)
+        wsets = [[torch.randint(0, 256, (r * (c // 32) * 18,), dtype=torch.uint8, device=dev, generator=g) for r, c in shapes] for _ in range(2)]
+        for batch in (1, 4, 16):
+            xs = {c: torch.randn((batch, c), device=dev) for c in (4096, 14336)}
+            ys = {r: torch.empty((batch, r), device=dev) for r in (4096, 1024, 14336, 128256)}
+            ws_n = lib.tb200_qx_workspace_bytes(14336, batch)
+            ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+            by = sum(algorithmic_bytes(r, c, batch, 18) for r, c in shapes)
+
+            def sweep_f(i):
+                for (r, c), w in zip(shapes, wsets[i & 1]):
+                    lib.tb200_q4b_gemv(r, c, batch, P(w), P(xs[c]), P(ys[r]), S)
+
+            def sweep_i(i):
+                for (r, c), w in zip(shapes, wsets[i & 1]):
+                    lib.tb200_q4b_gemv_i8(r, c, batch, P(w), P(xs[c]), P(ys[r]), P(ws), ws_n, S)
+            for name, fn in ((f"q4_layer_sweep_f32_b{batch}", sweep_f), (f"q4_layer_sweep_int_b{batch}", sweep_i)):
+                t = timeit(fn, 6)
+                out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
+        del wsets
+        # FP32 SGEMM 4096^3 (configs[1])
+        a = torch.rand((4096, 4096), device=dev)
+        bm = torch.rand((4096, 4096), device=dev)
+        c = torch.empty((4096, 4096), device=dev)
+        t = timeit(lambda i: lib.tb200_sgemm(4096, 4096, 4096, C.c_float(1.0), P(a), P(bm), C.c_float(0.0), P(c), S), 5)
+        out["sgemm_4096"] = {"TFLOP/s": 2 * 4096**3 / t / 1e12, "ms": t * 1e3}
+        # FP16 GEMM sweep (configs[2])
+        for n in (2048, 4096, 8192):
+            ah = (torch.randn((n, n), device=dev) / n**0.5).half()
+            bh = (torch.randn((n, n), device=dev) / n**0.5).half()
+            ch = torch.empty((n, n), device=dev)
+            t = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, P(ah), P(bh), P(ch), S), 5 if n < 8192 else 2)
+            out[f"hgemm_{n}"] = {"TFLOP/s": 2 * n**3 / t / 1e12, "frac_tensor": 2 * n**3 / t / 1e12 / tensor_peak, "ms": t * 1e3}
+    return out
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from tornadovm_b200.native import B200Native
+    from tornadovm_b200.sharding import ShardedQ8Gemv, gather_rows, shard_range, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the b200/linalg kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = B200Native.load()  # raises if libtornado_b200.so is missing
+    hbm_peak, tensor_peak, peak_kind = measured_peaks()
+
+    # ---- device-resident workload: rank r owns rows [r0, r1) of every layer -------------------------------
+    per = shard_rows(ROWS, world)
+    r0, r1 = shard_range(ROWS, world, rank)
+    lrows = r1 - r0
+    q, sc = make_weights(torch, dev, lrows, LAYERS, 1234 + rank)
+    x = torch.randn((BATCH, COLS), device=dev, generator=torch.Generator(device=dev).manual_seed(99))
+    y_local = torch.zeros((LAYERS, BATCH, per), device=dev)  # [layer][batch][per]: one gather per step
+    gather_buf = torch.empty((world, LAYERS * BATCH, per), device=dev) if world > 1 else None
+    stream = torch.cuda.Stream(device=dev)
+    S = C.c_void_p(stream.cuda_stream)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    launches = 0
+
+    def step():
+        nonlocal launches
+        for l in range(LAYERS):
+            st = lib.tb200_q8_gemv(lrows, COLS, BATCH, P(q[l]), P(sc[l]), P(x), P(y_local[l]), S)
+            if st:
+                B200Native.check_status(st, "tb200_q8_gemv")
+            launches += 1
+        if world > 1:
+            gather_rows(y_local.view(LAYERS * BATCH, per), ROWS, None, gather_buf)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        barrier()
+        launches = 0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            e0.record(stream)
+            for _ in range(args.steps):
+                step()
+            e1.record(stream)
+            barrier()
+        elapsed = e0.elapsed_time(e1) * 1e-3
+        # kernel-only duration for the roofline: the same launches without the gather, events on the launch stream
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(args.steps, 10)
+        k0.record(stream)
+        for _ in range(reps):
+            for l in range(LAYERS):
+                lib.tb200_q8_gemv(lrows, COLS, BATCH, P(q[l]), P(sc[l]), P(x), P(y_local[l]), S)
+        k1.record(stream)
+        stream.synchronize()
+        kernel_s = k0.elapsed_time(k1) * 1e-3 / (reps * LAYERS)
+    gpu_launches = launches
+    if world > 1:
+        t = torch.tensor([elapsed], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed = t.item()
+    total_bytes = LAYERS * algorithmic_bytes(ROWS, COLS, BATCH)  # whole job, all ranks
+    value = total_bytes * args.steps / elapsed / 1e9
+    launch_bytes = algorithmic_bytes(lrows, COLS, BATCH)
+    achieved = launch_bytes / kernel_s / 1e9
+
+    # ---- end to end through the public API, host buffers ---------------------------------------------------
+    e2e_steps = args.steps
+    if world == 1:
+        from tornadovm_b200.arrays import FloatArray, HalfFloatArray, Int8Array
+        from tornadovm_b200.b200 import B200
+        from tornadovm_b200.taskgraph import CudaDevice, DataTransferMode, TaskGraph, TornadoExecutionPlan
+        qa = [Int8Array(q[l].cpu().numpy()) for l in range(LAYERS)]
+        sa = [HalfFloatArray(sc[l].cpu().numpy().view("uint16")) for l in range(LAYERS)]
+        xa = FloatArray(x.cpu().numpy())
+        ya = [FloatArray(ROWS * BATCH) for _ in range(LAYERS)]
+        tg = TaskGraph("q8decode").transferToDevice(DataTransferMode.FIRST_EXECUTION, *qa, *sa) \
+            .transferToDevice(DataTransferMode.EVERY_EXECUTION, xa)
+        for l in range(LAYERS):
+            tg.libraryTask(f"l{l}", B200.q8Gemv, ROWS, COLS, BATCH, qa[l], sa[l], xa, ya[l])
+        tg.transferToHost(DataTransferMode.EVERY_EXECUTION, *ya)
+        with TornadoExecutionPlan(tg, CudaDevice(local)).withCUDAGraph() as plan:
+            for _ in range(max(args.warmup, 3)):
+                plan.execute()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                plan.execute()
+            torch.cuda.synchronize()
+            e2e_s = time.perf_counter() - t0
+            h2d, d2h = plan.h2d_bytes_last, plan.d2h_bytes_last
+        gpu_launches += e2e_steps * LAYERS
+    else:
+        ops = [ShardedQ8Gemv(ROWS, COLS, BATCH, q[l], sc[l]) for l in range(LAYERS)]
+        xh = torch.randn((BATCH, COLS)).pin_memory()
+        for _ in range(max(args.warmup, 3)):
+            for op in ops:
+                op.run(xh)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for op in ops:
+                op.run(xh)
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = t.item()
+        h2d, d2h = LAYERS * BATCH * COLS * 4, LAYERS * BATCH * ROWS * 4
+        gpu_launches += e2e_steps * LAYERS
+    e2e_value = total_bytes * e2e_steps / e2e_s / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"Q8_0 GEMV W[{ROWS}x{COLS}] int8 blocks of 32 + fp16 scale (split layout), fp32 x, batch {BATCH}",
+                   "layers_per_step": LAYERS, "l2_policy": f"{LAYERS} distinct weight matrices per step ({LAYERS * 62.4:.0f} MB > 126 MB L2)",
+                   "parallelism": f"rows sharded over {world} GPU(s), outputs all-gathered once per step" if world > 1 else "single GPU",
+                   "mode": "float (fp32 activations, reference arithmetic)"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s / e2e_steps * 1e3,
+                "api": "TaskGraph.libraryTask(B200.q8Gemv) + TornadoExecutionPlan.withCUDAGraph().execute()" if world == 1 else "ShardedQ8Gemv.run"},
+        "gpu_launches": gpu_launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "traffic": None, "peak_source": f"{peak_kind} copy bandwidth", "kernel": "q8s_gemv_kernel",
+                     "bytes_per_launch": launch_bytes, "us_per_launch": kernel_s * 1e6},
+        "clocks": clocks.summary(),
+    }
+    if rank == 0:
+        if world == 1:
+            line["cpu_baseline"] = cpu_reference(seconds_target=args.cpu_seconds)
+            if not args.no_secondary:
+                line["secondary"] = secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=8.0)
+    ap.add_argument("--no-secondary", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,120 @@
+"""GPU parity: FP32 SGEMM and FP16 GEMM through the C ABI against the CPU oracle."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle as o
+from harness import DevBuf, out_buf, stream_ptr, sync_and_check
+from kat import build as build_kat
+
+pytestmark = pytest.mark.gpu
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")))
+
+REL_L2_FP32 = 1e-5   # FP32 SGEMM vs fp64-accumulated oracle
+REL_L2_FP16 = 2e-3   # FP16 GEMM vs the fp32-accumulated reference loop
+
+
+def _ok(st, lib):
+    assert st == 0, lib.tb200_status_string(st).decode()
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 512), (128, 128, 128), (256, 384, 64), (200, 136, 100), (64, 64, 4),
+                                   (17, 19, 23), (1, 1, 1), (130, 260, 36)])
+@pytest.mark.parametrize("header", [16, 24])
+def test_sgemm_matches_oracle(lib, m, n, k, header):
+    r = o.JavaRandom(42)
+    a, b = r.uniform_f32(m * k, 0, 1), r.uniform_f32(k * n, 0, 1)
+    da, db, dc = DevBuf(a, header), DevBuf(b, header), out_buf(m * n, header=header)
+    _ok(lib.tb200_sgemm(m, n, k, 1.0, da.ptr, db.ptr, 0.0, dc.ptr, stream_ptr()), lib)
+    sync_and_check(lib)
+    got = dc.numpy().reshape(m, n)
+    c64 = o.sgemm_f64(a, b, m, n, k)
+    cref = o.sgemm_seq(a, b, m, n, k)
+    err = o.rel_l2(got, c64)
+    assert err <= REL_L2_FP32 and err <= max(o.rel_l2(cref, c64), 2e-7)
+    assert np.abs(got - cref).max() <= GOLD["tolerances"]["sgemm_abs"]["value"]
+    assert dc.guard_intact()
+
+
+def test_sgemm_alpha_beta_and_identity(lib):
+    n = 256
+    b = o.JavaRandom(3).uniform_f32(n * n, 0, 1)
+    eye = np.eye(n, dtype=np.float32).ravel()
+    c0 = o.JavaRandom(4).uniform_f32(n * n, 0, 1)
+    da, db, dc = DevBuf(eye), DevBuf(b), DevBuf(c0.copy())
+    _ok(lib.tb200_sgemm(n, n, n, 2.0, da.ptr, db.ptr, 0.5, dc.ptr, stream_ptr()), lib)
+    sync_and_check(lib)
+    assert np.allclose(dc.numpy(), 2.0 * b + 0.5 * c0, rtol=1e-6, atol=1e-6)
+    # SgemmTornado.java:116-134: A = identity gives C == B exactly
+    dc2 = out_buf(n * n)
+    _ok(lib.tb200_sgemm(n, n, n, 1.0, da.ptr, db.ptr, 0.0, dc2.ptr, stream_ptr()), lib)
+    sync_and_check(lib)
+    assert np.array_equal(dc2.numpy(), b)
+
+
+def test_sgemm_benchmark_shape_rows_sampled(lib):
+    """M=N=K=4096 (MatrixMultiplication2D shape): a band of rows against the oracle, the rest by linearity."""
+    import torch
+    n = 4096
+    a, b = o.make_sgemm(n, n, n)
+    ta, tb = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    tc = torch.full((n, n), float("nan"), device="cuda")
+    P = lambda t: C.c_void_p(t.data_ptr())
+    _ok(lib.tb200_sgemm(n, n, n, 1.0, P(ta), P(tb), 0.0, P(tc), stream_ptr()), lib)
+    sync_and_check(lib)
+    c = tc.cpu().numpy()
+    assert not np.isnan(c).any()
+    for r0 in (0, 2047, 4088):
+        want = o.sgemm_f64(a, b, n, n, n, r0, r0 + 8)
+        assert o.rel_l2(c[r0:r0 + 8], want) <= REL_L2_FP32
+    # checksum of checksums: (1^T A) B 1 == 1^T C 1 in double
+    lhs = (a.reshape(n, n).astype(np.float64).sum(0) * b.reshape(n, n).astype(np.float64).sum(1)).sum()
+    assert abs(c.astype(np.float64).sum() - lhs) / lhs < 1e-6
+
+
+@pytest.mark.parametrize("case", GOLD["mma_gemm"], ids=lambda c: c["source"].split()[-1])
+@pytest.mark.parametrize("header", [16, 24])
+def test_hgemm_reference_known_answers(lib, case, header):
+    a, b, exp = build_kat(case)
+    m, n, k = case["m"], case["n"], case["k"]
+    da, db, dc = DevBuf(a, header), DevBuf(b, header), out_buf(m * n, header=header)
+    _ok(lib.tb200_hgemm_f32(m, n, k, da.ptr, db.ptr, dc.ptr, stream_ptr()), lib)
+    sync_and_check(lib)
+    assert np.abs(dc.numpy().reshape(m, n) - exp).max() <= case["tol"]
+    assert dc.guard_intact()
+
+
+HGEMM_SHAPES = [tuple(s) for s in GOLD["mma_random_shapes"]["shapes"]] + [
+    (128, 128, 64), (256, 256, 256), (128, 256, 512), (384, 640, 192), (1024, 1024, 1024),
+    (200, 264, 72), (130, 136, 40), (100, 100, 100), (1, 8, 8), (2048, 2048, 2048)]
+
+
+@pytest.mark.parametrize("m,n,k", HGEMM_SHAPES)
+@pytest.mark.parametrize("header", [16, 24])
+def test_hgemm_matches_reference_loop(lib, m, n, k, header):
+    if m * n * k > 2**28 and header == 24:
+        pytest.skip("large case runs once")
+    r = o.JavaRandom(42)
+    mul = 1.0 / np.sqrt(k)
+    a, b = r.gaussian_f16(m * k, mul), r.gaussian_f16(k * n, mul)
+    da, db, dc = DevBuf(a, header), DevBuf(b, header), out_buf(m * n, header=header)
+    _ok(lib.tb200_hgemm_f32(m, n, k, da.ptr, db.ptr, dc.ptr, stream_ptr()), lib)
+    sync_and_check(lib)
+    got = dc.numpy().reshape(m, n)
+    rows = m if m * n * k <= 2**27 else 64
+    ref = o.hgemm_ref(a, b, m, n, k, 0, rows)
+    assert o.rel_l2(got[:rows], ref) <= REL_L2_FP16
+    # the reference's own acceptance tests: abs 0.01 (unit tests), rel 2e-2 / max(|ref|,1) (example)
+    assert np.abs(got[:rows] - ref).max() <= GOLD["mma_random_shapes"]["abs_tol"]
+    assert not np.isnan(got).any() and dc.guard_intact()
+
+
+def test_gemm_argument_errors(lib):
+    d = DevBuf(np.zeros(64, np.float32))
+    assert lib.tb200_sgemm(-1, 2, 2, 1.0, d.ptr, d.ptr, 0.0, d.ptr, stream_ptr()) == -1
+    assert lib.tb200_sgemm(2, 2, 2, 1.0, None, d.ptr, 0.0, d.ptr, stream_ptr()) == -1
+    assert lib.tb200_hgemm_f32(2, 2, 2, C.c_void_p(d.ptr.value + 1), d.ptr, d.ptr, stream_ptr()) == -2
+    assert lib.tb200_hgemm_f32(0, 2, 2, d.ptr, d.ptr, d.ptr, stream_ptr()) == 0

@@ -1,0 +1,95 @@
+"""Row / column sharding of the mat-vec and mat-mul tasks over the GPUs of one box.
+
+One process per GPU (torch.distributed, NCCL over NVLink).  A GEMV shards by
+rows: rank r owns a contiguous block of rows of W (whole Q8_0/Q4_0 block runs,
+so any row split is byte-exact), the activation is replicated and the output
+shards are all-gathered.  A GEMM shards B and C by N-columns the same way.
+The reference has no counterpart: its multi-device mode runs independent tasks
+on different devices with host round trips (docs/source/multi-device.rst:9-14).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .native import B200Native
+
+
+def shard_rows(rows: int, world: int) -> int:
+    """Rows per rank: equal blocks of ceil(rows / world); the last ranks may own fewer real rows."""
+    return (rows + world - 1) // world
+
+
+def shard_range(rows: int, world: int, rank: int) -> tuple[int, int]:
+    per = shard_rows(rows, world)
+    r0 = min(rank * per, rows)
+    return r0, min(r0 + per, rows)
+
+
+def gather_rows(y_local: torch.Tensor, rows: int, group=None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gather per-rank output blocks ``[batch][per]`` into ``[batch][rows]``.
+
+    ``y_local`` always has ``per = shard_rows(rows, world)`` columns (ranks that
+    own fewer rows leave the tail unused) so that the collective is one
+    equal-sized all-gather.
+    """
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return y_local[:, :rows]
+    batch, per = y_local.shape
+    if out is None:
+        out = torch.empty((world, batch, per), dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(out.view(-1), y_local.reshape(-1), group=group)
+    # [world][batch][per] -> [batch][world*per] -> trim the padding of the last ranks
+    return out.permute(1, 0, 2).reshape(batch, world * per)[:, :rows]
+
+
+class ShardedQ8Gemv:
+    """Q8_0 (split layout) mat-vec whose weight rows are sharded over the ranks.
+
+    ``run(x_host)`` is the end-to-end call: activation host->device, the local
+    shard's GEMV through the C ABI, all-gather of the output shards over NCCL,
+    gathered result device->host.
+    """
+
+    def __init__(self, rows: int, cols: int, batch: int, q_shard: torch.Tensor, scales_shard: torch.Tensor, group=None):
+        self.rows, self.cols, self.batch, self.group = rows, cols, batch, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.per = shard_rows(rows, self.world)
+        r0, r1 = shard_range(rows, self.world, self.rank)
+        self.local_rows = r1 - r0
+        assert q_shard.is_cuda and q_shard.numel() == self.local_rows * cols
+        self.q, self.scales = q_shard, scales_shard
+        dev = q_shard.device
+        self.lib = B200Native.load()
+        self.stream = torch.cuda.Stream(device=dev)
+        self.x_dev = torch.empty((batch, cols), dtype=torch.float32, device=dev)
+        self.y_local = torch.zeros((batch, self.per), dtype=torch.float32, device=dev)
+        self.y_tmp = torch.empty((batch, max(self.local_rows, 1)), dtype=torch.float32, device=dev)
+        self.gather_buf = torch.empty((self.world, batch, self.per), dtype=torch.float32, device=dev) if self.world > 1 else None
+        self.y_host = torch.empty((batch, rows), dtype=torch.float32, pin_memory=True)
+
+    def launch(self) -> torch.Tensor:
+        """Enqueue GEMV + gather on this object's stream; returns the gathered device tensor."""
+        with torch.cuda.stream(self.stream):
+            if self.local_rows > 0:
+                # y of the shard is [batch][local_rows]; it lands in the padded [batch][per] block
+                tgt = self.y_local if self.local_rows == self.per else self.y_tmp
+                B200Native.check_status(
+                    self.lib.tb200_q8_gemv(self.local_rows, self.cols, self.batch, C.c_void_p(self.q.data_ptr()),
+                                           C.c_void_p(self.scales.data_ptr()), C.c_void_p(self.x_dev.data_ptr()),
+                                           C.c_void_p(tgt.data_ptr()), C.c_void_p(self.stream.cuda_stream)), "tb200_q8_gemv")
+                if tgt is self.y_tmp:
+                    self.y_local[:, :self.local_rows].copy_(self.y_tmp)
+            return gather_rows(self.y_local, self.rows, self.group, self.gather_buf)
+
+    def run(self, x_host: torch.Tensor) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            self.x_dev.copy_(x_host, non_blocking=True)
+            y = self.launch()
+            self.y_host.copy_(y, non_blocking=True)
+        self.stream.synchronize()
+        return self.y_host
