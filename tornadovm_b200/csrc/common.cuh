@@ -42,11 +42,16 @@ constexpr int kMaxDevices = 64;
 // Opt a kernel in to the device's full dynamic shared memory, once per device
 // and kernel.  The first call for a kernel should come from a warm-up launch or
 // a prepare step, outside any stream capture.
-template <typename K>
-static int ensure_smem_optin(K kernel, const DeviceInfo *di) {
+template <auto kernel>
+static int ensure_smem_optin(const DeviceInfo *di) {
     static bool done[kMaxDevices];
     if (!done[di->device]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin);
+        // the opt-in limit covers static + dynamic shared memory of the kernel
+        cudaFuncAttributes attr;
+        cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 di->max_smem_optin - (int)attr.sharedSizeBytes);
         if (e != cudaSuccess) return (int)e;
         done[di->device] = true;
     }

@@ -126,7 +126,7 @@ extern "C" int tb200_sgemv(int rows, int cols, const float *m, const float *v, f
         int head = (int)(((16 - ((uintptr_t)m & 15)) & 15) >> 2);
         if (head > cols) head = cols;
         int bulk_ok = (((uintptr_t)m & 15) == ((uintptr_t)v & 15)) && (cols - head) >= 4;
-        st = ensure_smem_optin(sgemv_rows_kernel, di);
+        st = ensure_smem_optin<sgemv_rows_kernel>(di);
         if (st) return st;
         int ctas_per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
         int grid = di->sm_count * ctas_per_sm;

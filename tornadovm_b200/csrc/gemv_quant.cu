@@ -13,14 +13,14 @@
 //          (dp4a), one fp32 multiply-add per block for the two scales
 //
 // Kernel families:
-//   q8s_gemv_kernel   split layout; each lane streams 16 quants per row with one
-//                     128-bit load that bypasses L1; R rows share every
-//                     activation read from shared memory.
-//   qblk_gemv_kernel  block layouts; rows are 2-byte aligned records, so each
-//                     warp runs its own bulk-async-copy (TMA) pipeline that
-//                     lands row chunks of 64 blocks in shared memory; a lane
-//                     decodes one pair of blocks (a 4-byte aligned 68 / 36 byte
-//                     record) per row.
+//   qring_gemv_kernel every format when cols % 256 == 0 and the weights are 16-byte
+//                     aligned: each warp runs its own bulk-async-copy (TMA)
+//                     ring that lands row chunks of 64 blocks in shared memory,
+//                     so the bytes in flight are bounded by shared memory and
+//                     not by registers; the integer mode can quantise the
+//                     activations in its own prologue.
+//   q8s_gemv_kernel   split layout with other column counts; each lane streams
+//                     16 quants per row with one 128-bit load that bypasses L1.
 //   q*_generic_kernel any alignment and any cols % 32 == 0; byte loads.
 //
 // Activations are staged once per CTA in shared memory in a lane-interleaved
@@ -312,27 +312,44 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-// Family 2: block layouts (Q8B, Q4B) through a per-warp bulk-copy pipeline.
+// Family 2: every format through a per-warp bulk-async-copy (TMA) ring.
+//
+// A CTA owns a contiguous range of rows; its warps take groups of R rows from a
+// shared-memory counter.  Each warp keeps STAGES row chunks (64 blocks = 2048
+// columns of R rows) in flight in its own ring: lane 0 arms an mbarrier with the
+// byte count and issues one bulk copy per row (two for the split layout: quants
+// and scales); all lanes wait on the barrier, pull their part of the chunk into
+// registers, and the stage is refilled at once.  Bytes in flight are bounded by
+// shared memory, not by registers.
+//
+// Chunk record in shared memory, per row:
+//   Q8S  [2048 quant bytes][64 fp16 scales]            2176 bytes
+//   Q8B  64 x 34-byte blocks                           2176 bytes
+//   Q4B  64 x 18-byte blocks                           1152 bytes
+// Lane ownership inside a chunk:
+//   Q8S  the four 16-byte pieces j*32 + lane (half a block each)
+//   Q8B / Q4B  the block pair `lane` (a 4-byte aligned 68 / 36 byte record)
 // ---------------------------------------------------------------------------
-constexpr int kBlkWarps = 8;
-constexpr int kBlkThreads = kBlkWarps * 32;
-constexpr int kBlkStages = 2;
 constexpr int kChunkBlocks = 64;  // blocks per row chunk = 2048 columns
+constexpr int MODE_FLOAT = 0;     // fp32 activations
+constexpr int MODE_INT = 1;       // int8 activations read from the workspace
+constexpr int MODE_INT_FUSED = 2; // int8 activations quantised in the prologue of this kernel
 
 template <int FMT>
-struct BlkTraits {
-    static constexpr int BB = FMT == FMT_Q8B ? 34 : 18;  // bytes per block
-    static constexpr int PW = BB / 2;                    // 32-bit words per block pair
-    static constexpr int CB = kChunkBlocks * BB;         // bytes per full row chunk
-    static constexpr int QW = FMT == FMT_Q8B ? 8 : 4;    // quant words per block
+struct RingTraits {
+    static constexpr int BB = FMT == FMT_Q4B ? 18 : 34;         // bytes per block (split: 32 + 2)
+    static constexpr int PW = BB / 2;                           // 32-bit words per block pair
+    static constexpr int CB = kChunkBlocks * BB;                // bytes per full row chunk
+    static constexpr int QW = FMT == FMT_Q4B ? 4 : 8;           // quant words per block
+    static constexpr int CPL = FMT == FMT_Q8S ? 16 : 64;        // contiguous columns per lane
 };
 
 // Pull one block pair (PW words, 4-byte aligned) out of shared memory and
 // split it into the two scales and the realigned quant words of each block.
 template <int FMT>
-__device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], uint32_t (&qa)[BlkTraits<FMT>::QW],
-                                          uint32_t (&qb)[BlkTraits<FMT>::QW]) {
-    constexpr int PW = BlkTraits<FMT>::PW, QW = BlkTraits<FMT>::QW;
+__device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], uint32_t (&qa)[RingTraits<FMT>::QW],
+                                          uint32_t (&qb)[RingTraits<FMT>::QW]) {
+    constexpr int PW = RingTraits<FMT>::PW, QW = RingTraits<FMT>::QW;
     uint32_t wds[PW];
 #pragma unroll
     for (int i = 0; i < PW; ++i) wds[i] = p[i];
@@ -346,72 +363,144 @@ __device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], 
     for (int i = 0; i < QW; ++i) qb[i] = wds[QW + 1 + i];
 }
 
-template <int FMT, int B, int R, bool INT, bool DOTS>
-__global__ void __launch_bounds__(kBlkThreads) qblk_gemv_kernel(QGemvArgs a) {
-    using T = BlkTraits<FMT>;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[kBlkWarps][kBlkStages];
+// Integer activations into shared memory, one warp per 32-element block:
+// quantise on the fly (QUANTIZE) or copy the workspace's int8 values; write
+// each byte to its lane-interleaved slot, the block's fp32 scale, and the
+// block's int32 sum (Q4_0 needs sum(xq) for the "- 8" of its nibbles).
+template <int CPL, bool QUANTIZE, bool WANT_SUM>
+__device__ __forceinline__ void stage_x_blocks(unsigned char *xq_smem, float *xs_smem, int *xsum_smem,
+                                               const QGemvArgs &a, int batch, int slots_per_vec, bool want_scales) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int bpr = a.cols / 32;
+    for (int i = warp; i < batch * bpr; i += nwarps) {
+        const int b = i / bpr, blk = i - b * bpr;
+        const int col = blk * 32 + lane;
+        int qv;
+        float scale = 1.0f;
+        if (QUANTIZE) {
+            const float v = __ldg(a.x + (size_t)b * a.cols + col);
+            float m = fabsf(v);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            scale = (m == 0.0f) ? 1.0f : __fdiv_rn(m, 127.0f);
+            const float inv = __fdiv_rn(1.0f, scale);
+            qv = (int)(int8_t)(int)floorf(__fadd_rn(__fmul_rn(v, inv), 0.5f));
+        } else {
+            qv = (int)a.xq[(size_t)b * a.cols + col];
+            if (want_scales && lane == 0) scale = a.xs[(size_t)b * bpr + blk];
+        }
+        xq_smem[((size_t)b * slots_per_vec + permuted_slot<CPL, 16>(col)) * 16 + (col & 15)] = (unsigned char)(int8_t)qv;
+        if (WANT_SUM) {
+            int s = qv;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (lane == 0) xsum_smem[i] = s;
+        }
+        if (lane == 0 && want_scales) xs_smem[i] = scale;
+    }
+}
 
-    const int cols = a.cols, rows = a.rows;
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) qring_gemv_kernel(QGemvArgs a) {
+    using T = RingTraits<FMT>;
+    constexpr bool INT = MODE != MODE_FLOAT;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
+    __shared__ int group_of_stage[WARPS][STAGES];
+    __shared__ int next_group;
+
+    const int cols = a.cols;
     const int bpr = cols / 32;
     const int nch = (bpr + kChunkBlocks - 1) / kChunkBlocks;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const size_t row_bytes = (size_t)bpr * T::BB;
 
-    // ---- shared memory carve-up ---------------------------------------------
-    // [ weight pipeline: warps x stages x R x CB ][ activations ][ activation scales ]
-    unsigned char *wbuf = smem_raw + (size_t)warp * kBlkStages * R * T::CB;
-    unsigned char *xbase = smem_raw + (size_t)kBlkWarps * kBlkStages * R * T::CB;
-    const int slots = nch * (INT ? 128 : 512);  // 16-byte slots per activation vector
-    float *xs_scales = nullptr;
-    if (INT) {
-        xs_scales = reinterpret_cast<float *>(xbase + (size_t)B * slots * 16);
-        stage_x_int<64>(reinterpret_cast<uint4 *>(xbase), a.xq, cols, B, slots);
-        if (!DOTS)
-            for (int i = threadIdx.x; i < B * bpr; i += blockDim.x) xs_scales[i] = a.xs[i];
-    } else {
-        stage_x_float<64>(reinterpret_cast<float4 *>(xbase), a.x, cols, B, slots);
-    }
+    // rows of this CTA and its groups of R rows
+    const int row_begin = (int)((long long)a.rows * blockIdx.x / gridDim.x);
+    const int row_end = (int)((long long)a.rows * (blockIdx.x + 1) / gridDim.x);
+    const int ngroups = (row_end - row_begin + R - 1) / R;
+
+    // ---- shared memory carve-up -----------------------------------------------
+    // [ ring: warps x stages x R x CB ][ activations ][ activation scales ][ activation block sums ]
+    unsigned char *wbuf = smem_raw + (size_t)warp * STAGES * R * T::CB;
+    unsigned char *xbase = smem_raw + (size_t)WARPS * STAGES * R * T::CB;
+    const int slots = (cols + 32 * T::CPL - 1) / (32 * T::CPL) * (32 * T::CPL) / (INT ? 16 : 4);  // 16-byte slots per vector
+    float *xs_scales = reinterpret_cast<float *>(xbase + (size_t)B * slots * 16);
+    int *xsum = reinterpret_cast<int *>(xs_scales + B * bpr);
+
+    if (threadIdx.x == 0) next_group = 0;
     if (lane == 0) {
 #pragma unroll
-        for (int s = 0; s < kBlkStages; ++s) mbar_init(&bars[warp][s], 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
         mbar_fence_init();
     }
     __syncthreads();
 
-    const int ngroups = (rows + R - 1) / R;
-    const int gw = blockIdx.x * kBlkWarps + warp;
-    const int gstride = gridDim.x * kBlkWarps;
-    const int mine = gw < ngroups ? (ngroups - gw + gstride - 1) / gstride : 0;
-    const int total = mine * nch;  // pipeline steps of this warp
-
-    // issue step t: R bulk copies (one per row) of chunk c of group g
-    auto issue = [&](int t) {
-        const int gi = t / nch, c = t - gi * nch;
-        const int g = gw + gi * gstride;
-        const int nblk = min(kChunkBlocks, bpr - c * kChunkBlocks);
-        const uint32_t bytes = (uint32_t)nblk * T::BB;
-        const int st = t % kBlkStages;
+    // ---- issue side of the ring (all lanes run it in lock step) -------------------
+    int issued = 0, issue_group = -1, issue_chunk = 0;
+    bool more = true;
+    auto issue = [&]() {
+        const int st = issued % STAGES;
+        ++issued;
+        if (more && issue_chunk == 0) {
+            int g = 0;
+            if (lane == 0) g = atomicAdd(&next_group, 1);
+            g = __shfl_sync(0xffffffffu, g, 0);
+            if (g >= ngroups) more = false;
+            issue_group = g;
+        }
+        if (!more) {
+            if (lane == 0) group_of_stage[warp][st] = -1;
+            return;
+        }
+        const int c = issue_chunk;
+        issue_chunk = (c + 1 == nch) ? 0 : c + 1;
         if (lane == 0) {
+            group_of_stage[warp][st] = issue_group;
+            const int nblk = min(kChunkBlocks, bpr - c * kChunkBlocks);
+            // the block-dot test entry of the split layout passes no scales: copy quants only
+            const bool with_scales = FMT != FMT_Q8S || a.scales != nullptr;
+            const uint32_t bytes = (uint32_t)nblk * (with_scales ? T::BB : 32);
             mbar_expect_tx(&bars[warp][st], bytes * R);
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const size_t row = (size_t)min(g * R + r, rows - 1);
-                bulk_g2s_stream(wbuf + ((size_t)st * R + r) * T::CB, a.w + row * row_bytes + (size_t)c * T::CB, bytes,
-                                &bars[warp][st]);
+                const size_t row = (size_t)min(row_begin + issue_group * R + r, row_end - 1);
+                unsigned char *dst = wbuf + ((size_t)st * R + r) * T::CB;
+                if (FMT == FMT_Q8S) {
+                    bulk_g2s_stream(dst, a.w + row * cols + (size_t)c * 2048, (uint32_t)nblk * 32, &bars[warp][st]);
+                    if (with_scales)
+                        bulk_g2s_stream(dst + 2048, a.scales + row * bpr + (size_t)c * kChunkBlocks, (uint32_t)nblk * 2,
+                                        &bars[warp][st]);
+                } else {
+                    bulk_g2s_stream(dst, a.w + (row * bpr + (size_t)c * kChunkBlocks) * T::BB, bytes, &bars[warp][st]);
+                }
             }
         }
     };
+#pragma unroll 1
+    for (int s = 0; s < STAGES; ++s) issue();  // weights start streaming before the activations are staged
 
-    for (int t = 0; t < kBlkStages && t < total; ++t) issue(t);
+    // ---- activations ------------------------------------------------------------
+    if (MODE == MODE_FLOAT) {
+        stage_x_float<T::CPL>(reinterpret_cast<float4 *>(xbase), a.x, cols, B, slots);
+    } else if (MODE == MODE_INT_FUSED) {
+        stage_x_blocks<T::CPL, true, FMT == FMT_Q4B>(xbase, xs_scales, xsum, a, B, slots, true);
+    } else {
+        stage_x_blocks<T::CPL, false, FMT == FMT_Q4B>(xbase, xs_scales, xsum, a, B, slots, !DOTS);
+    }
+    __syncthreads();
 
+    // ---- consume ------------------------------------------------------------------
     float acc[R][B];
-    bool alive = true;
-    for (int t = 0; t < total && alive; ++t) {
-        const int gi = t / nch, c = t - gi * nch;
-        const int g = gw + gi * gstride;
-        const int st = t % kBlkStages;
+    int chunk = 0;
+#pragma unroll 1
+    for (int t = 0;; ++t) {
+        const int st = t % STAGES;
+        __syncwarp();
+        const int g = group_of_stage[warp][st];
+        if (g < 0) break;
+        const int c = chunk;
+        chunk = (c + 1 == nch) ? 0 : c + 1;
         const int nblk = min(kChunkBlocks, bpr - c * kChunkBlocks);
         if (c == 0) {
 #pragma unroll
@@ -419,107 +508,177 @@ __global__ void __launch_bounds__(kBlkThreads) qblk_gemv_kernel(QGemvArgs a) {
 #pragma unroll
                 for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
         }
-        alive = __all_sync(0xffffffffu, mbar_wait(&bars[warp][st], (uint32_t)((t / kBlkStages) & 1)));
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars[warp][st], (uint32_t)((t / STAGES) & 1)))) break;
+        const int row0 = row_begin + g * R;
 
-        const bool active = 2 * lane < nblk;
-        float scale[R][2];
-        uint32_t qa[R][T::QW], qb[R][T::QW];
-        if (active) {
+        if constexpr (FMT == FMT_Q8S) {
+            // ---------------- split layout: four 16-byte pieces per lane and row
+            uint4 w[R][4];
+            float sc[R][4];
+            bool valid[4];
 #pragma unroll
-            for (int r = 0; r < R; ++r)
-                load_pair<FMT>(reinterpret_cast<const uint32_t *>(wbuf + ((size_t)st * R + r) * T::CB) + lane * T::PW,
-                               scale[r], qa[r], qb[r]);
-        }
-        __syncwarp();
-        if (t + kBlkStages < total) issue(t + kBlkStages);  // the stage is free again
-
-        if (active) {
-            const int blk0 = c * kChunkBlocks + 2 * lane;
-            if (INT) {
-                const uint4 *xq16 = reinterpret_cast<const uint4 *>(xbase);
+            for (int j = 0; j < 4; ++j) {
+                const int piece = j * 32 + lane;
+                valid[j] = piece < 2 * nblk;
 #pragma unroll
-                for (int b = 0; b < B; ++b) {
-                    // 64 activation bytes of this lane: pieces k = 0..3
-                    uint32_t xw[16];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint4 v = xq16[(size_t)b * slots + c * 128 + k * 32 + lane];
-                        xw[4 * k] = v.x, xw[4 * k + 1] = v.y, xw[4 * k + 2] = v.z, xw[4 * k + 3] = v.w;
-                    }
-                    const float2 xsc = DOTS ? make_float2(1.f, 1.f) : *reinterpret_cast<const float2 *>(xs_scales + b * bpr + blk0);
-                    int xsum[2] = {0, 0};
-                    if (FMT == FMT_Q4B) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            xsum[0] = dp4a_s8(0x01010101u, xw[i], xsum[0]);
-                            xsum[1] = dp4a_s8(0x01010101u, xw[8 + i], xsum[1]);
-                        }
-                    }
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        int d0 = 0, d1 = 0;
-                        if (FMT == FMT_Q8B) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                d0 = dp4a_s8(qa[r][i], xw[i], d0);
-                                d1 = dp4a_s8(qb[r][i], xw[8 + i], d1);
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                d0 = dp4a_s8(qa[r][i] & 0x0F0F0F0Fu, xw[i], d0);
-                                d0 = dp4a_s8((qa[r][i] >> 4) & 0x0F0F0F0Fu, xw[4 + i], d0);
-                                d1 = dp4a_s8(qb[r][i] & 0x0F0F0F0Fu, xw[8 + i], d1);
-                                d1 = dp4a_s8((qb[r][i] >> 4) & 0x0F0F0F0Fu, xw[12 + i], d1);
-                            }
-                            d0 -= 8 * xsum[0];
-                            d1 -= 8 * xsum[1];
-                        }
-                        if (DOTS && b == 0 && g * R + r < rows) {
-                            int32_t *dp = a.dots + (size_t)(g * R + r) * bpr + blk0;
-                            dp[0] = d0;
-                            dp[1] = d1;
-                        }
-                        acc[r][b] = fmaf((float)d0, scale[r][0] * xsc.x, acc[r][b]);
-                        acc[r][b] = fmaf((float)d1, scale[r][1] * xsc.y, acc[r][b]);
-                    }
+                for (int r = 0; r < R; ++r) {
+                    const unsigned char *rec = wbuf + ((size_t)st * R + r) * T::CB;
+                    w[r][j] = *reinterpret_cast<const uint4 *>(rec + piece * 16);
+                    sc[r][j] = DOTS ? 1.0f
+                                    : half_bits_to_float(*reinterpret_cast<const uint16_t *>(rec + 2048 + (piece >> 1) * 2));
                 }
-            } else {
-                const float4 *xs4 = reinterpret_cast<const float4 *>(xbase);
-                float part[R][B];
-                // k indexes the lane's sixteen float4 activation pieces: 0..7 block A, 8..15 block B
+            }
+            __syncwarp();
+            issue();  // the stage is free again
 #pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                    float wf[R][4];
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        if (FMT == FMT_Q8B) {
-                            const uint32_t word = k < 8 ? qa[r][k] : qb[r][k - 8];
-                            s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
-                        } else {
-                            // elements 4j..4j+3 are the low nibbles of word j, 16+4j.. the high nibbles
-                            const int kk = k & 7;
-                            const uint32_t word = k < 8 ? qa[r][kk & 3] : qb[r][kk & 3];
-                            const uint32_t nib = (kk < 4 ? word : (word >> 4)) & 0x0F0F0F0Fu;
-                            u8x4_to_f32(nib, 8388616.0f, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
-                        }
-                    }
+            for (int j = 0; j < 4; ++j) {
+                const unsigned vmask = __ballot_sync(0xffffffffu, valid[j]);
+                if (!valid[j]) continue;
+                const int piece = j * 32 + lane;
+                const int blk = c * kChunkBlocks + (piece >> 1);
+                if (INT) {
+                    const uint4 *xq16 = reinterpret_cast<const uint4 *>(xbase);
 #pragma unroll
                     for (int b = 0; b < B; ++b) {
-                        const float4 xv = xs4[(size_t)b * slots + c * 512 + k * 32 + lane];
+                        const uint4 xv = xq16[(size_t)b * slots + c * 128 + piece];
+                        const float xscale = DOTS ? 1.0f : xs_scales[b * bpr + blk];
 #pragma unroll
                         for (int r = 0; r < R; ++r) {
-                            float p = (k & 7) == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, part[r][b]);
-                            p = fmaf(wf[r][1], xv.y, p);
-                            p = fmaf(wf[r][2], xv.z, p);
-                            part[r][b] = fmaf(wf[r][3], xv.w, p);
+                            int isum = dp4a_s8(w[r][j].x, xv.x, 0);
+                            isum = dp4a_s8(w[r][j].y, xv.y, isum);
+                            isum = dp4a_s8(w[r][j].z, xv.z, isum);
+                            isum = dp4a_s8(w[r][j].w, xv.w, isum);
+                            if (DOTS) {
+                                const int full = isum + __shfl_xor_sync(vmask, isum, 1);  // a block spans two lanes
+                                if ((lane & 1) == 0 && b == 0 && row0 + r < row_end) a.dots[(size_t)(row0 + r) * bpr + blk] = full;
+                            }
+                            acc[r][b] = fmaf((float)isum, sc[r][j] * xscale, acc[r][b]);
                         }
                     }
-                    if ((k & 7) == 7) {
+                } else {
+                    const float4 *xs4 = reinterpret_cast<const float4 *>(xbase);
+                    float part[R][B];
 #pragma unroll
-                        for (int r = 0; r < R; ++r)
+                    for (int k = 0; k < 4; ++k) {
+                        float wf[R][4];
 #pragma unroll
-                            for (int b = 0; b < B; ++b) acc[r][b] = fmaf(scale[r][k >> 3], part[r][b], acc[r][b]);
+                        for (int r = 0; r < R; ++r) {
+                            const uint32_t word = k == 0 ? w[r][j].x : k == 1 ? w[r][j].y : k == 2 ? w[r][j].z : w[r][j].w;
+                            s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
+                        }
+#pragma unroll
+                        for (int b = 0; b < B; ++b) {
+                            // float4 slot of columns 16*piece + 4k: segment (c*4 + j), piece-in-lane k
+                            const float4 xv = xs4[(size_t)b * slots + (c * 4 + j) * 128 + k * 32 + lane];
+#pragma unroll
+                            for (int r = 0; r < R; ++r) {
+                                float p = k == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, part[r][b]);
+                                p = fmaf(wf[r][1], xv.y, p);
+                                p = fmaf(wf[r][2], xv.z, p);
+                                part[r][b] = fmaf(wf[r][3], xv.w, p);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r)
+#pragma unroll
+                        for (int b = 0; b < B; ++b) acc[r][b] = fmaf(sc[r][j], part[r][b], acc[r][b]);
+                }
+            }
+        } else {
+            // ---------------- block layouts: one block pair per lane and row
+            const bool active = 2 * lane < nblk;
+            float scale[R][2];
+            uint32_t qa[R][T::QW], qb[R][T::QW];
+            if (active) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    load_pair<FMT>(reinterpret_cast<const uint32_t *>(wbuf + ((size_t)st * R + r) * T::CB) + lane * T::PW,
+                                   scale[r], qa[r], qb[r]);
+            }
+            __syncwarp();
+            issue();  // the stage is free again
+            if (active) {
+                const int blk0 = c * kChunkBlocks + 2 * lane;
+                if (INT) {
+                    const uint4 *xq16 = reinterpret_cast<const uint4 *>(xbase);
+#pragma unroll
+                    for (int b = 0; b < B; ++b) {
+                        uint32_t xw[16];  // the lane's 64 activation bytes: pieces k = 0..3
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint4 v = xq16[(size_t)b * slots + c * 128 + k * 32 + lane];
+                            xw[4 * k] = v.x, xw[4 * k + 1] = v.y, xw[4 * k + 2] = v.z, xw[4 * k + 3] = v.w;
+                        }
+                        const float2 xsc = DOTS ? make_float2(1.f, 1.f) : *reinterpret_cast<const float2 *>(xs_scales + b * bpr + blk0);
+                        int2 xsm = make_int2(0, 0);
+                        if (FMT == FMT_Q4B) xsm = *reinterpret_cast<const int2 *>(xsum + b * bpr + blk0);
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            int d0 = 0, d1 = 0;
+                            if (FMT == FMT_Q8B) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    d0 = dp4a_s8(qa[r][i], xw[i], d0);
+                                    d1 = dp4a_s8(qb[r][i], xw[8 + i], d1);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    d0 = dp4a_s8(qa[r][i] & 0x0F0F0F0Fu, xw[i], d0);
+                                    d0 = dp4a_s8((qa[r][i] >> 4) & 0x0F0F0F0Fu, xw[4 + i], d0);
+                                    d1 = dp4a_s8(qb[r][i] & 0x0F0F0F0Fu, xw[8 + i], d1);
+                                    d1 = dp4a_s8((qb[r][i] >> 4) & 0x0F0F0F0Fu, xw[12 + i], d1);
+                                }
+                                d0 -= 8 * xsm.x;
+                                d1 -= 8 * xsm.y;
+                            }
+                            if (DOTS && b == 0 && row0 + r < row_end) {
+                                int32_t *dp = a.dots + (size_t)(row0 + r) * bpr + blk0;
+                                dp[0] = d0;
+                                dp[1] = d1;
+                            }
+                            acc[r][b] = fmaf((float)d0, scale[r][0] * xsc.x, acc[r][b]);
+                            acc[r][b] = fmaf((float)d1, scale[r][1] * xsc.y, acc[r][b]);
+                        }
+                    }
+                } else {
+                    const float4 *xs4 = reinterpret_cast<const float4 *>(xbase);
+                    float part[R][B];
+                    // k indexes the lane's sixteen float4 activation pieces: 0..7 block A, 8..15 block B
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        float wf[R][4];
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            if (FMT == FMT_Q8B) {
+                                const uint32_t word = k < 8 ? qa[r][k & 7] : qb[r][k & 7];
+                                s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
+                            } else {
+                                // elements 4j..4j+3 are the low nibbles of word j, 16+4j.. the high nibbles
+                                const int kk = k & 7;
+                                const uint32_t word = k < 8 ? qa[r][kk & 3] : qb[r][kk & 3];
+                                const uint32_t nib = (kk < 4 ? word : (word >> 4)) & 0x0F0F0F0Fu;
+                                u8x4_to_f32(nib, 8388616.0f, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
+                            }
+                        }
+#pragma unroll
+                        for (int b = 0; b < B; ++b) {
+                            const float4 xv = xs4[(size_t)b * slots + c * 512 + k * 32 + lane];
+#pragma unroll
+                            for (int r = 0; r < R; ++r) {
+                                float p = (k & 7) == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, part[r][b]);
+                                p = fmaf(wf[r][1], xv.y, p);
+                                p = fmaf(wf[r][2], xv.z, p);
+                                part[r][b] = fmaf(wf[r][3], xv.w, p);
+                            }
+                        }
+                        if ((k & 7) == 7) {
+#pragma unroll
+                            for (int r = 0; r < R; ++r)
+#pragma unroll
+                                for (int b = 0; b < B; ++b) acc[r][b] = fmaf(scale[r][k >> 3], part[r][b], acc[r][b]);
+                        }
                     }
                 }
             }
@@ -529,8 +688,8 @@ __global__ void __launch_bounds__(kBlkThreads) qblk_gemv_kernel(QGemvArgs a) {
             for (int r = 0; r < R; ++r)
 #pragma unroll
                 for (int b = 0; b < B; ++b) {
-                    float s = warp_sum(acc[r][b]);
-                    if (lane == 0 && g * R + r < rows) a.y[(size_t)b * rows + g * R + r] = s;
+                    const float s = warp_sum(acc[r][b]);
+                    if (lane == 0 && row0 + r < row_end) a.y[(size_t)b * a.rows + row0 + r] = s;
                 }
         }
     }
@@ -560,6 +719,18 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float *__restrict
 // Host side
 // ---------------------------------------------------------------------------
 
+// Resident CTAs per SM of a kernel at a given dynamic shared memory size,
+// cached per (kernel, device, size class).  Host-side query, no device work.
+template <auto kernel>
+static int resident_ctas(const DeviceInfo *di, int threads, size_t smem) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess) {
+        cudaGetLastError();
+        n = 1;
+    }
+    return n < 1 ? 1 : n;
+}
+
 // Pick a CTA count <= max_ctas that wastes the fewest warp slots in the last
 // round of a grid-stride loop over `units` (row groups).
 static int balanced_grid(int units, int warps_per_cta, int max_ctas) {
@@ -579,41 +750,57 @@ static int balanced_grid(int units, int warps_per_cta, int max_ctas) {
     return best;
 }
 
-static int occupancy_ctas(const DeviceInfo *di, size_t smem, int cap) {
-    // shared memory per SM is 228 KB, 1 KB of it reserved per resident CTA
-    int by_smem = (int)((size_t)(di->max_smem_optin + 1024) / (smem + 1024));
-    if (by_smem < 1) by_smem = 1;
-    return by_smem < cap ? by_smem : cap;
-}
-
 template <int B, int R, bool INT, bool DOTS>
 static int launch_q8s(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     const int nseg = (a.cols + 511) / 512;
     size_t smem = INT ? (size_t)B * nseg * 32 * 16 + (size_t)B * (a.cols / 32) * 4 : (size_t)B * nseg * 128 * 16;
     if (smem + 256 > (size_t)di->max_smem_optin) return TB200_ERR_INVALID_ARG;
-    auto kernel = q8s_gemv_kernel<B, R, INT, DOTS>;
-    int st = ensure_smem_optin(kernel, di);
+    constexpr auto kernel = q8s_gemv_kernel<B, R, INT, DOTS>;
+    int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
-    int ctas = occupancy_ctas(di, smem, 4);
+    int ctas = resident_ctas<kernel>(di, kQ8SThreads, smem);
     int grid = balanced_grid((a.rows + R - 1) / R, kQ8SThreads / 32, di->sm_count * ctas);
     kernel<<<grid, kQ8SThreads, smem, s>>>(a);
     return check_launch();
 }
 
-template <int FMT, int B, int R, bool INT, bool DOTS>
-static int launch_qblk(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
-    using T = BlkTraits<FMT>;
-    const int bpr = a.cols / 32;
-    const int nch = (bpr + kChunkBlocks - 1) / kChunkBlocks;
-    size_t smem = (size_t)kBlkWarps * kBlkStages * R * T::CB;
-    smem += INT ? (size_t)B * nch * 128 * 16 + (size_t)B * bpr * 4 : (size_t)B * nch * 512 * 16;
-    if (smem + 256 > (size_t)di->max_smem_optin) return TB200_ERR_INVALID_ARG;
-    auto kernel = qblk_gemv_kernel<FMT, B, R, INT, DOTS>;
-    int st = ensure_smem_optin(kernel, di);
+template <int FMT, int B, int MODE>
+struct RingConfig {
+    static constexpr bool INT = MODE != MODE_FLOAT;
+    // rows per group: more rows share each activation read; the integer path reads
+    // one activation byte per weight byte and needs that only for larger batches
+    static constexpr int R = INT ? (B <= 2 ? 1 : (B <= 4 ? 2 : 4)) : (FMT == FMT_Q4B ? (B <= 4 ? 4 : 2) : 2);
+    static constexpr int WARPS = 8;
+    // about 17 KB of ring per warp whatever the group size
+    static constexpr int STAGES = (FMT == FMT_Q4B ? 16 : 8) / R;
+};
+
+template <int FMT, int B, int MODE>
+static size_t ring_smem_bytes(int cols) {
+    using T = RingTraits<FMT>;
+    using Cfg = RingConfig<FMT, B, MODE>;
+    const int seg = 32 * T::CPL;
+    const size_t slots = (size_t)((cols + seg - 1) / seg) * seg / (Cfg::INT ? 16 : 4);
+    size_t smem = (size_t)Cfg::WARPS * Cfg::STAGES * Cfg::R * T::CB + (size_t)B * slots * 16;
+    if (Cfg::INT) smem += (size_t)B * (cols / 32) * 8;  // scales + block sums
+    return smem;
+}
+
+template <int FMT, int B, int MODE, bool DOTS>
+static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+    using Cfg = RingConfig<FMT, B, MODE>;
+    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols);
+    constexpr auto kernel = qring_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES, Cfg::WARPS>;
+    int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
-    int ctas = occupancy_ctas(di, smem, 2);
-    int grid = balanced_grid((a.rows + R - 1) / R, kBlkWarps, di->sm_count * ctas);
-    kernel<<<grid, kBlkThreads, smem, s>>>(a);
+    const int ctas = resident_ctas<kernel>(di, Cfg::WARPS * 32, smem);
+    // every CTA should have at least a couple of groups per warp; small matrices use fewer CTAs
+    int grid = di->sm_count * ctas;
+    const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
+    const int need = (groups + Cfg::WARPS - 1) / Cfg::WARPS;
+    if (grid > need) grid = need;
+    if (grid > a.rows) grid = a.rows;
+    kernel<<<grid, Cfg::WARPS * 32, smem, s>>>(a);
     return check_launch();
 }
 
@@ -625,95 +812,138 @@ static int launch_generic(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t
     return check_launch();
 }
 
-// Largest batch the fast kernels can hold in shared memory next to the weight
-// pipeline, for one launch.
-template <int FMT, bool INT>
-static int max_fast_batch(int cols, const DeviceInfo *di) {
-    size_t per_vec, fixed = 0;
-    if (FMT == FMT_Q8S) {
-        const int nseg = (cols + 511) / 512;
-        per_vec = INT ? (size_t)nseg * 512 + (size_t)(cols / 32) * 4 : (size_t)nseg * 2048;
-    } else {
-        const int nch = (cols / 32 + kChunkBlocks - 1) / kChunkBlocks;
-        per_vec = INT ? (size_t)nch * 2048 + (size_t)(cols / 32) * 4 : (size_t)nch * 8192;
-        fixed = (size_t)kBlkWarps * kBlkStages * 4 * BlkTraits<FMT == FMT_Q8S ? FMT_Q8B : FMT>::CB;
+enum Path { PATH_GENERIC, PATH_Q8S_DIRECT, PATH_RING };
+
+// Does one fast launch with `batch` activation vectors fit in shared memory?
+template <int FMT, int MODE>
+static bool fast_batch_fits(int cols, int batch, Path path, const DeviceInfo *di) {
+    const size_t limit = (size_t)di->max_smem_optin - 1024;
+    if (path == PATH_RING) {
+        switch (batch) {
+            case 1: return ring_smem_bytes<FMT, 1, MODE>(cols) <= limit;
+            case 2: return ring_smem_bytes<FMT, 2, MODE>(cols) <= limit;
+            case 3: return ring_smem_bytes<FMT, 3, MODE>(cols) <= limit;
+            case 4: return ring_smem_bytes<FMT, 4, MODE>(cols) <= limit;
+            case 5: return ring_smem_bytes<FMT, 5, MODE>(cols) <= limit;
+            case 6: return ring_smem_bytes<FMT, 6, MODE>(cols) <= limit;
+            case 7: return ring_smem_bytes<FMT, 7, MODE>(cols) <= limit;
+            case 8: return ring_smem_bytes<FMT, 8, MODE>(cols) <= limit;
+            default: return false;
+        }
     }
-    size_t room = (size_t)di->max_smem_optin > fixed + 256 ? (size_t)di->max_smem_optin - fixed - 256 : 0;
-    int b = (int)(room / per_vec);
-    return b > 8 ? 8 : b;
+    const int nseg = (cols + 511) / 512;
+    const size_t per = MODE != MODE_FLOAT ? (size_t)nseg * 512 + (size_t)(cols / 32) * 4 : (size_t)nseg * 2048;
+    return batch >= 1 && batch <= 8 && per * batch <= limit;
 }
 
-template <int FMT, bool INT, bool DOTS, int B>
-static int launch_fast_b(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+// Fewest passes over the weights such that each pass's share of the batch fits;
+// returns the per-pass batch, 0 if not even one vector fits.
+template <int FMT, int MODE>
+static int batch_per_pass(int cols, int batch, Path path, const DeviceInfo *di) {
+    for (int passes = 1; passes <= batch; ++passes) {
+        const int per = (batch + passes - 1) / passes;
+        if (fast_batch_fits<FMT, MODE>(cols, per, path, di)) return per;
+    }
+    return 0;
+}
+
+template <int FMT, int MODE, bool DOTS, int B>
+static int launch_fast_b(const QGemvArgs &a, Path path, const DeviceInfo *di, cudaStream_t s) {
     if constexpr (FMT == FMT_Q8S) {
-        return launch_q8s<B, (B <= 2 ? 4 : 2), INT, DOTS>(a, di, s);
-    } else if constexpr (FMT == FMT_Q8B) {
-        return launch_qblk<FMT_Q8B, B, 2, INT, DOTS>(a, di, s);
-    } else {
-        return launch_qblk<FMT_Q4B, B, (B <= 4 ? 4 : 2), INT, DOTS>(a, di, s);
+        if (path == PATH_Q8S_DIRECT) return launch_q8s<B, (B <= 2 ? 4 : 2), MODE != MODE_FLOAT, DOTS>(a, di, s);
     }
+    return launch_ring<FMT, B, MODE, DOTS>(a, di, s);
 }
 
-template <int FMT, bool INT, bool DOTS>
-static int launch_fast(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+template <int FMT, int MODE, bool DOTS>
+static int launch_fast(const QGemvArgs &a, Path path, const DeviceInfo *di, cudaStream_t s) {
     switch (a.batch) {
-        case 1: return launch_fast_b<FMT, INT, DOTS, 1>(a, di, s);
-        case 2: return launch_fast_b<FMT, INT, false, 2>(a, di, s);
-        case 3: return launch_fast_b<FMT, INT, false, 3>(a, di, s);
-        case 4: return launch_fast_b<FMT, INT, false, 4>(a, di, s);
-        case 5: return launch_fast_b<FMT, INT, false, 5>(a, di, s);
-        case 6: return launch_fast_b<FMT, INT, false, 6>(a, di, s);
-        case 7: return launch_fast_b<FMT, INT, false, 7>(a, di, s);
-        case 8: return launch_fast_b<FMT, INT, false, 8>(a, di, s);
+        case 1: return launch_fast_b<FMT, MODE, DOTS, 1>(a, path, di, s);
+        case 2: return launch_fast_b<FMT, MODE, false, 2>(a, path, di, s);
+        case 3: return launch_fast_b<FMT, MODE, false, 3>(a, path, di, s);
+        case 4: return launch_fast_b<FMT, MODE, false, 4>(a, path, di, s);
+        case 5: return launch_fast_b<FMT, MODE, false, 5>(a, path, di, s);
+        case 6: return launch_fast_b<FMT, MODE, false, 6>(a, path, di, s);
+        case 7: return launch_fast_b<FMT, MODE, false, 7>(a, path, di, s);
+        case 8: return launch_fast_b<FMT, MODE, false, 8>(a, path, di, s);
         default: return TB200_ERR_INVALID_ARG;
     }
 }
 
+// Fusing the activation quantiser into the GEMV prologue repeats it in every
+// CTA; beyond this many activation elements the separate quantiser kernel and
+// the workspace are cheaper.
+constexpr int kFusedQuantMaxElems = 16384;
+
 // Shared front end: validation, path choice, batch splitting.
-template <int FMT, bool INT, bool DOTS>
-static int qgemv_dispatch(QGemvArgs a, tb200_stream_t stream) {
+//   MODE_FLOAT      a.x set
+//   MODE_INT        a.xq / a.xs set (already quantised)
+//   MODE_INT_FUSED  a.x set, quantised inside the kernel; falls back to
+//                   quantiser kernel + workspace (xq_ws / xs_ws) when the fast
+//                   path is not taken or the batch is large
+template <int FMT, int MODE, bool DOTS>
+static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream_t stream);
+
+static int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s);
+
+template <int FMT, int MODE, bool DOTS>
+static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream_t stream) {
+    constexpr bool INT = MODE != MODE_FLOAT;
     if (a.rows < 0 || a.cols < 0 || a.batch < 1 || a.batch > kMaxBatch) return TB200_ERR_INVALID_ARG;
     if (a.cols % 32 != 0) return TB200_ERR_INVALID_ARG;
     if (a.rows == 0) return TB200_OK;
     if (!a.w || (FMT == FMT_Q8S && !DOTS && !a.scales) || (!DOTS && !a.y)) return TB200_ERR_INVALID_ARG;
-    if (INT ? (!a.xq || (!DOTS && !a.xs)) : !a.x) return TB200_ERR_INVALID_ARG;
+    if (MODE == MODE_INT ? (!a.xq || (!DOTS && !a.xs)) : !a.x) return TB200_ERR_INVALID_ARG;
     if (DOTS && !a.dots) return TB200_ERR_INVALID_ARG;
     if (FMT == FMT_Q8S && a.scales && !aligned_to(a.scales, 2)) return TB200_ERR_ALIGNMENT;
-    if ((a.y && !aligned_to(a.y, 4)) || (!INT && !aligned_to(a.x, 4))) return TB200_ERR_ALIGNMENT;
+    if ((a.y && !aligned_to(a.y, 4)) || (MODE != MODE_INT && !aligned_to(a.x, 4))) return TB200_ERR_ALIGNMENT;
     int st;
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
     cudaStream_t s = (cudaStream_t)stream;
     if (a.cols == 0) {
-        if (a.y) {
-            cudaError_t e = cudaMemsetAsync(a.y, 0, sizeof(float) * (size_t)a.rows * a.batch, s);
-            return (int)e;
+        if (a.y) return (int)cudaMemsetAsync(a.y, 0, sizeof(float) * (size_t)a.rows * a.batch, s);
+        return TB200_OK;
+    }
+    // ring: every row chunk starts on a 16-byte boundary and is a whole number of 16-byte units
+    Path path = PATH_GENERIC;
+    if (aligned_to(a.w, 16)) {
+        if (a.cols % 256 == 0 && (FMT != FMT_Q8S || DOTS || aligned_to(a.scales, 16))) path = PATH_RING;
+        else if (FMT == FMT_Q8S) path = PATH_Q8S_DIRECT;
+    }
+    const int per = path == PATH_GENERIC
+                        ? 0
+                        : batch_per_pass<FMT, MODE == MODE_INT_FUSED ? MODE_INT : MODE>(a.cols, a.batch, path, di);
+    if (per < 1) path = PATH_GENERIC;
+
+    if (MODE == MODE_INT_FUSED) {
+        const bool fuse = path == PATH_RING && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per;
+        if (fuse) return launch_fast<FMT, MODE_INT_FUSED, false>(a, path, di, s);
+        // separate quantiser into the workspace, then the MODE_INT kernels
+        st = quantize_x(a.cols, a.batch, a.x, xq_ws, xs_ws, s);
+        if (st) return st;
+        QGemvArgs b = a;
+        b.x = nullptr, b.xq = xq_ws, b.xs = xs_ws;
+        return qgemv_dispatch<FMT, MODE_INT, false>(b, nullptr, nullptr, stream);
+    } else {
+        if (path == PATH_Q8S_DIRECT && INT && !aligned_to(a.xq, 16)) path = PATH_GENERIC;
+        if (path == PATH_GENERIC) return launch_generic<FMT, INT>(a, di, s);
+        // more activation vectors than fit next to the ring: several passes over the weights
+        for (int b0 = 0; b0 < a.batch; b0 += per) {
+            QGemvArgs p = a;
+            p.batch = a.batch - b0 < per ? a.batch - b0 : per;
+            if (INT) {
+                p.xq = a.xq + (size_t)b0 * a.cols;
+                if (a.xs) p.xs = a.xs + (size_t)b0 * (a.cols / 32);
+            } else {
+                p.x = a.x + (size_t)b0 * a.cols;
+            }
+            if (a.y) p.y = a.y + (size_t)b0 * a.rows;
+            st = launch_fast<FMT, MODE, DOTS>(p, path, di, s);
+            if (st) return st;
         }
         return TB200_OK;
     }
-    // fast path: rows of a whole number of 16-byte units starting on a 16-byte boundary
-    const bool fast = aligned_to(a.w, 16) && (FMT == FMT_Q8S ? true : (a.cols % 256 == 0)) &&
-                      (!INT || aligned_to(a.xq, 16));
-    if (!fast) return launch_generic<FMT, INT>(a, di, s);
-    const int maxb = max_fast_batch<FMT, INT>(a.cols, di);
-    if (maxb < 1) return launch_generic<FMT, INT>(a, di, s);
-    // more activation vectors than fit next to the pipeline: several passes over the weights
-    int passes = (a.batch + maxb - 1) / maxb;
-    int per = (a.batch + passes - 1) / passes;
-    for (int b0 = 0; b0 < a.batch; b0 += per) {
-        QGemvArgs p = a;
-        p.batch = a.batch - b0 < per ? a.batch - b0 : per;
-        if (INT) {
-            p.xq = a.xq + (size_t)b0 * a.cols;
-            p.xs = a.xs + (size_t)b0 * (a.cols / 32);
-        } else {
-            p.x = a.x + (size_t)b0 * a.cols;
-        }
-        if (a.y) p.y = a.y + (size_t)b0 * a.rows;
-        st = launch_fast<FMT, INT, DOTS>(p, di, s);
-        if (st) return st;
-    }
-    return TB200_OK;
 }
 
 static int split_workspace(int cols, int batch, void *workspace, size_t workspace_bytes, int8_t **xq, float **xs) {
@@ -747,11 +977,8 @@ static int qgemv_i8(int rows, int cols, int batch, const void *w, const uint16_t
     int st = split_workspace(cols, batch, workspace, workspace_bytes, &xq, &xs);
     if (st) return st;
     if (rows < 0) return TB200_ERR_INVALID_ARG;
-    if (rows == 0) return TB200_OK;
-    st = quantize_x(cols, batch, x, xq, xs, (cudaStream_t)stream);
-    if (st) return st;
-    QGemvArgs a{reinterpret_cast<const uint8_t *>(w), scales, nullptr, xq, xs, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT, true, false>(a, stream);
+    QGemvArgs a{reinterpret_cast<const uint8_t *>(w), scales, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
+    return qgemv_dispatch<FMT, MODE_INT_FUSED, false>(a, xq, xs, stream);
 }
 
 }  // namespace tb200
@@ -761,21 +988,21 @@ using namespace tb200;
 extern "C" int tb200_q8_gemv(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x,
                              float *y, tb200_stream_t stream) {
     QGemvArgs a{reinterpret_cast<const uint8_t *>(q), scales, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT_Q8S, false, false>(a, stream);
+    return qgemv_dispatch<FMT_Q8S, MODE_FLOAT, false>(a, nullptr, nullptr, stream);
 }
 
 extern "C" int tb200_q8b_gemv(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
                               tb200_stream_t stream) {
     if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
     QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT_Q8B, false, false>(a, stream);
+    return qgemv_dispatch<FMT_Q8B, MODE_FLOAT, false>(a, nullptr, nullptr, stream);
 }
 
 extern "C" int tb200_q4b_gemv(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
                               tb200_stream_t stream) {
     if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
     QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT_Q4B, false, false>(a, stream);
+    return qgemv_dispatch<FMT_Q4B, MODE_FLOAT, false>(a, nullptr, nullptr, stream);
 }
 
 extern "C" size_t tb200_qx_workspace_bytes(int cols, int batch) {
@@ -815,7 +1042,7 @@ extern "C" int tb200_q4b_gemv_i8(int rows, int cols, int batch, const uint8_t *b
 template <int FMT>
 static int blockdots(int rows, int cols, const void *w, const int8_t *xq, int32_t *dots, tb200_stream_t stream) {
     QGemvArgs a{reinterpret_cast<const uint8_t *>(w), nullptr, nullptr, xq, nullptr, nullptr, dots, rows, cols, 1};
-    return qgemv_dispatch<FMT, true, true>(a, stream);
+    return qgemv_dispatch<FMT, MODE_INT, true>(a, nullptr, nullptr, stream);
 }
 
 extern "C" int tb200_q8_blockdots_i32(int rows, int cols, const int8_t *q, const int8_t *xq, int32_t *dots,
