@@ -70,6 +70,21 @@ int tb200_version(void);
  * for tests and diagnostics, not for the launch path. */
 int tb200_device_status(int *status_out);
 
+/* Process-wide options; the provider sets them from its tuning object
+ * (LibraryTaskDescriptor.withTuning, tornado-api/.../common/LibraryTaskDescriptor.java:79-86;
+ * applied like CuBlasOptions in CuBlasLibraryProvider.java:124-151).
+ *
+ * TB200_OPT_OVERLAP_LAUNCHES (default 0): the mat-vec kernels are launched with
+ * programmatic stream serialization.  A kernel may then start while the kernel
+ * enqueued before it on the same stream is still finishing: it prefetches its
+ * WEIGHT operand at once, and waits for the predecessor to complete before it
+ * reads activations or writes outputs.  Contract when on: a weight operand must
+ * not be written by the kernel enqueued immediately before the mat-vec on the
+ * same stream (copies and earlier kernels are fine). */
+enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1 };
+int tb200_set_option(int option, int value);
+int tb200_get_option(int option, int *value);
+
 /* Device scratch owned by the provider's context (grow-only workspace of the
  * integer path).  Replaces CutlassNativeLib.allocateDeviceMemory /
  * freeDeviceMemory (tornado-cutlass.cu:455-472; CutlassLibraryProvider.java:

@@ -5,6 +5,8 @@
 
 namespace tb200 {
 
+int g_overlap_launches = 0;
+
 static DeviceInfo g_info[kMaxDevices];
 static bool g_info_valid[kMaxDevices];
 static std::mutex g_info_mutex;
@@ -85,4 +87,25 @@ extern "C" int tb200_device_malloc(size_t bytes, void **out) {
 extern "C" int tb200_device_free(void *ptr) {
     if (!ptr) return TB200_OK;
     return (int)cudaFree(ptr);
+}
+
+extern "C" int tb200_set_option(int option, int value) {
+    switch (option) {
+        case TB200_OPT_OVERLAP_LAUNCHES:
+            tb200::g_overlap_launches = value != 0;
+            return TB200_OK;
+        default:
+            return TB200_ERR_INVALID_ARG;
+    }
+}
+
+extern "C" int tb200_get_option(int option, int *value) {
+    if (!value) return TB200_ERR_INVALID_ARG;
+    switch (option) {
+        case TB200_OPT_OVERLAP_LAUNCHES:
+            *value = tb200::g_overlap_launches;
+            return TB200_OK;
+        default:
+            return TB200_ERR_INVALID_ARG;
+    }
 }

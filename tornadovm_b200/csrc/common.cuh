@@ -58,9 +58,43 @@ static int ensure_smem_optin(const DeviceInfo *di) {
     return TB200_OK;
 }
 
+// Process-wide options (tb200_set_option).
+extern int g_overlap_launches;
+
+// Launch through cudaLaunchKernelEx so that a kernel can carry the programmatic
+// stream serialization attribute: it may then begin while its predecessor in
+// the stream is still draining.  Such kernels call pdl_wait() before they touch
+// anything the predecessor may have produced.
+template <typename... KArgs, typename... Args>
+static int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool overlap,
+                         Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (overlap) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return (int)e;
+    }
+    return check_launch();
+}
+
 // --------------------------------------------------------------------------
 // PTX wrappers
 // --------------------------------------------------------------------------
+// Programmatic dependent launch: both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {

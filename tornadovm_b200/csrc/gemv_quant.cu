@@ -30,6 +30,8 @@
 // Algorithmic bytes per launch:
 //   Q8: 34 * rows*cols/32 + 4*batch*(cols + rows)
 //   Q4: 18 * rows*cols/32 + 4*batch*(cols + rows)
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace tb200 {
@@ -165,148 +167,286 @@ __device__ __forceinline__ void stage_x_float(float4 *xs4, const float *x, int c
     }
 }
 
-// int mode: xq16[b * slots_per_vec + slot] (16 int8 per slot); xq is 16-byte
-// aligned by construction of the workspace.
-template <int CPL>
-__device__ __forceinline__ void stage_x_int(uint4 *xq16, const int8_t *xq, int cols, int batch, int slots_per_vec) {
-    const int n16 = cols / 16;
-    for (int b = 0; b < batch; ++b) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(xq + (size_t)b * cols);
-        for (int i = threadIdx.x; i < n16; i += blockDim.x)
-            xq16[(size_t)b * slots_per_vec + permuted_slot<CPL, 16>(16 * i)] = __ldg(src + i);
+constexpr int MODE_FLOAT = 0;     // fp32 activations
+constexpr int MODE_INT = 1;       // int8 activations read from the workspace
+constexpr int MODE_INT_FUSED = 2; // int8 activations quantised in the prologue of this kernel
+
+// Integer activations into shared memory.  Eight consecutive threads share a
+// 32-element block, four elements each: quantise on the fly (QUANTIZE) or copy
+// the workspace's int8 values; write the four bytes to their lane-interleaved
+// slot, the block's fp32 scale, and the block's int32 sum (Q4_0 needs sum(xq)
+// for the "- 8" of its nibbles).
+template <int CPL, bool QUANTIZE, bool WANT_SUM>
+__device__ __forceinline__ void stage_x_blocks(unsigned char *xq_smem, float *xs_smem, int *xsum_smem,
+                                               const QGemvArgs &a, int batch, int slots_per_vec, bool want_scales) {
+    const int total4 = batch * a.cols / 4;  // groups of four elements, all vectors back to back
+    const bool x_vec = QUANTIZE && (((uintptr_t)a.x & 15) == 0);
+    const bool q_vec = !QUANTIZE && (((uintptr_t)a.xq & 3) == 0);
+    const int lane = threadIdx.x & 31;
+    constexpr int T = 4;  // trips whose global loads are issued together
+    // blockDim.x is a multiple of 32 and a.cols of 32: the eight threads of a block sit in one warp and
+    // take the same trips; trip counts are warp-uniform
+    for (int base = threadIdx.x & ~31; base < total4; base += T * blockDim.x) {
+        float4 v[T];
+        uint32_t qw[T];
+        float sc[T];
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+            const int i4 = base + t * blockDim.x + lane;
+            v[t] = make_float4(0.f, 0.f, 0.f, 0.f), qw[t] = 0, sc[t] = 1.0f;
+            if (i4 < total4) {
+                const int flat = i4 * 4;
+                if (QUANTIZE) {
+                    if (x_vec) {
+                        v[t] = __ldg(reinterpret_cast<const float4 *>(a.x + flat));
+                    } else {
+                        v[t].x = __ldg(a.x + flat), v[t].y = __ldg(a.x + flat + 1);
+                        v[t].z = __ldg(a.x + flat + 2), v[t].w = __ldg(a.x + flat + 3);
+                    }
+                } else {
+                    if (q_vec) {
+                        qw[t] = __ldg(reinterpret_cast<const uint32_t *>(a.xq + flat));
+                    } else {
+                        qw[t] = (uint32_t)(uint8_t)a.xq[flat] | ((uint32_t)(uint8_t)a.xq[flat + 1] << 8) |
+                                ((uint32_t)(uint8_t)a.xq[flat + 2] << 16) | ((uint32_t)(uint8_t)a.xq[flat + 3] << 24);
+                    }
+                    if (want_scales) sc[t] = a.xs[flat >> 5];
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+            const int i4 = base + t * blockDim.x + lane;
+            const unsigned mask = __ballot_sync(0xffffffffu, i4 < total4);  // whole groups of eight lanes
+            if (i4 >= total4) continue;
+            const int flat = i4 * 4;
+            const int b = flat / a.cols, col = flat - b * a.cols;
+            const int blk_flat = flat >> 5;  // == b * (cols / 32) + col / 32
+            uint32_t packed = qw[t];
+            float scale = sc[t];
+            if (QUANTIZE) {
+                float m = fmaxf(fmaxf(fabsf(v[t].x), fabsf(v[t].y)), fmaxf(fabsf(v[t].z), fabsf(v[t].w)));
+                m = fmaxf(m, __shfl_xor_sync(mask, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(mask, m, 2));
+                m = fmaxf(m, __shfl_xor_sync(mask, m, 4));
+                scale = (m == 0.0f) ? 1.0f : __fdiv_rn(m, 127.0f);
+                const float inv = __fdiv_rn(1.0f, scale);
+                const int q0 = (int)floorf(__fadd_rn(__fmul_rn(v[t].x, inv), 0.5f));
+                const int q1 = (int)floorf(__fadd_rn(__fmul_rn(v[t].y, inv), 0.5f));
+                const int q2 = (int)floorf(__fadd_rn(__fmul_rn(v[t].z, inv), 0.5f));
+                const int q3 = (int)floorf(__fadd_rn(__fmul_rn(v[t].w, inv), 0.5f));
+                packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+                         ((uint32_t)(q3 & 0xFF) << 24);
+            }
+            *reinterpret_cast<uint32_t *>(xq_smem + ((size_t)b * slots_per_vec + permuted_slot<CPL, 16>(col)) * 16 + (col & 15)) = packed;
+            if (WANT_SUM) {
+                int sum = dp4a_s8(packed, 0x01010101u, 0);
+                sum += __shfl_xor_sync(mask, sum, 1);
+                sum += __shfl_xor_sync(mask, sum, 2);
+                sum += __shfl_xor_sync(mask, sum, 4);
+                if ((lane & 7) == 0) xsum_smem[blk_flat] = sum;
+            }
+            if (want_scales && (lane & 7) == 0) xs_smem[blk_flat] = scale;
+        }
     }
 }
 
 // ---------------------------------------------------------------------------
-// Family 1: split Q8_0.
-// Tile = R rows x one 512-column segment per lane load (16 quants per lane).
+// Family 1: split Q8_0 through per-lane cp.async rings.
+//
+// A CTA owns a contiguous range of rows.  Its work items are (group of R rows,
+// trip of U 512-column segments); warp w takes items w, w + 8, ...  For each
+// item a lane copies its R*U 16-byte pieces (16 quants each) into its own slots
+// of the warp's shared-memory ring with cp.async (no registers held while the
+// bytes are in flight, no cross-lane synchronisation: a lane reads back only
+// what it copied) and keeps STAGES items in flight.  The fp16 scales ride in
+// registers.  Per-item sums go to a small shared table and are added per row in
+// a fixed order at the end, so results do not depend on warp timing.
 // ---------------------------------------------------------------------------
 constexpr int kQ8SThreads = 256;
+constexpr int kQ8SWarps = kQ8SThreads / 32;
 
-template <int B, int R, bool INT, bool DOTS>
-__global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
+__device__ __forceinline__ void cp_async_16(void *dst_smem, const void *src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int B, int R, int U, int MODE, bool DOTS, int STAGES>
+__global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int max_rows_per_cta) {
+    constexpr bool INT = MODE != MODE_FLOAT;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int cols = a.cols, rows = a.rows;
+    const int cols = a.cols;
     const int bpr = cols / 32;
     const int nseg = (cols + 511) / 512;
-    const int lane = threadIdx.x & 31;
+    const int ntrips = (nseg + U - 1) / U;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int8_t *q = reinterpret_cast<const int8_t *>(a.w);
 
-    // ---- stage activations -------------------------------------------------
+    const int row_begin = (int)((long long)a.rows * blockIdx.x / gridDim.x);
+    const int row_end = (int)((long long)a.rows * (blockIdx.x + 1) / gridDim.x);
+    const int ngroups = (row_end - row_begin + R - 1) / R;
+    const int nitems = ngroups * ntrips;
+
+    // ---- shared memory carve-up -------------------------------------------------
+    // [ activations ][ activation scales ][ per-item sums ][ rings: warps x stages x R x U x 512 ]
     const int slots = nseg * (INT ? 32 : 128);  // 16-byte slots per activation vector
-    float *xs_scales = nullptr;
-    if (INT) {
-        uint4 *xq16 = reinterpret_cast<uint4 *>(smem_raw);
-        xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
-        stage_x_int<16>(xq16, a.xq, cols, B, slots);
-        if (!DOTS)
-            for (int i = threadIdx.x; i < B * bpr; i += blockDim.x) xs_scales[i] = a.xs[i];
-    } else {
+    float *xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
+    float *part = xs_scales + (INT ? B * bpr : 0);  // [row_local][trip][b]
+    size_t ring_off = (size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 4 + (size_t)max_rows_per_cta * ntrips * B * 4;
+    ring_off = (ring_off + 127) & ~(size_t)127;
+    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * U * 512 + lane * 16;
+
+    uint16_t sc[STAGES][R][U];
+    auto issue = [&](auto stage_c, int item) {
+        constexpr int st = decltype(stage_c)::value;
+        if (item < nitems) {
+            const int g = item / ntrips, trip = item - g * ntrips;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const size_t row = (size_t)min(row_begin + g * R + r, row_end - 1);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int col0 = (trip * U + u) * 512 + lane * 16;
+                    if (col0 < cols) {
+                        cp_async_16(ring + ((st * R + r) * U + u) * 512, q + row * cols + col0);
+                        if (!DOTS) sc[st][r][u] = __ldg(a.scales + row * bpr + (col0 >> 5));
+                    }
+                }
+            }
+        }
+        cp_async_commit();
+    };
+
+    // ring primed before the activations are staged
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) {
+        if (st == 0) issue(std::integral_constant<int, 0>{}, warp);
+        if (st == 1) issue(std::integral_constant<int, 1 % STAGES>{}, warp + kQ8SWarps);
+        if (st == 2) issue(std::integral_constant<int, 2 % STAGES>{}, warp + 2 * kQ8SWarps);
+        if (st == 3) issue(std::integral_constant<int, 3 % STAGES>{}, warp + 3 * kQ8SWarps);
+    }
+
+    // weights are on their way; dependents may start, and nothing else is touched before the predecessor is done
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (MODE == MODE_FLOAT) {
         stage_x_float<16>(reinterpret_cast<float4 *>(smem_raw), a.x, cols, B, slots);
+    } else if (MODE == MODE_INT_FUSED) {
+        stage_x_blocks<16, true, false>(smem_raw, xs_scales, nullptr, a, B, slots, true);
+    } else {
+        stage_x_blocks<16, false, false>(smem_raw, xs_scales, nullptr, a, B, slots, !DOTS);
     }
     __syncthreads();
 
-    const int wpc = kQ8SThreads / 32;
-    const int ngroups = (rows + R - 1) / R;
-    const int8_t *q = reinterpret_cast<const int8_t *>(a.w);
-
-    for (int g = blockIdx.x * wpc + (threadIdx.x >> 5); g < ngroups; g += gridDim.x * wpc) {
-        size_t rowi[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) rowi[r] = (size_t)min(g * R + r, rows - 1);
+    auto consume = [&](auto stage_c, int item) {
+        constexpr int st = decltype(stage_c)::value;
+        const int g = item / ntrips, trip = item - g * ntrips;
+        const int row0 = row_begin + g * R;
         float acc[R][B];
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
-
-        // two segments per trip: 2*R independent 128-bit loads in flight per lane
-        for (int seg = 0; seg < nseg; seg += 2) {
-            uint4 w[2][R];
-            float sc[2][R];
-            bool valid[2];
-            unsigned vmask[2];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int col0 = (seg + u) * 512 + lane * 16;
-                valid[u] = (seg + u) < nseg && col0 < cols;
-                vmask[u] = __ballot_sync(0xffffffffu, valid[u]);  // lanes come in whole pairs per block
-                if (valid[u]) {
+        for (int u = 0; u < U; ++u) {
+            const int s = trip * U + u;
+            const int col0 = s * 512 + lane * 16;
+            const bool valid = col0 < cols;
+            const unsigned vmask = __ballot_sync(0xffffffffu, valid);  // lanes come in whole pairs per block
+            if (!valid) continue;
+            const int blk = col0 >> 5;
+            uint4 w[R];
 #pragma unroll
-                    for (int r = 0; r < R; ++r) w[u][r] = ldg_stream_v4(q + rowi[r] * cols + col0);
+            for (int r = 0; r < R; ++r) w[r] = *reinterpret_cast<const uint4 *>(ring + ((st * R + r) * U + u) * 512);
+            if (INT) {
+                const uint4 *xq16 = reinterpret_cast<const uint4 *>(smem_raw);
+#pragma unroll
+                for (int b = 0; b < B; ++b) {
+                    const uint4 xv = xq16[(size_t)b * slots + s * 32 + lane];
+                    const float xscale = DOTS ? 1.0f : xs_scales[b * bpr + blk];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        int isum = dp4a_s8(w[r].x, xv.x, 0);
+                        isum = dp4a_s8(w[r].y, xv.y, isum);
+                        isum = dp4a_s8(w[r].z, xv.z, isum);
+                        isum = dp4a_s8(w[r].w, xv.w, isum);
+                        if (DOTS) {
+                            const int full = isum + __shfl_xor_sync(vmask, isum, 1);  // a block spans two lanes
+                            if ((lane & 1) == 0 && b == 0 && row0 + r < row_end) a.dots[(size_t)(row0 + r) * bpr + blk] = full;
+                        }
+                        const float wscale = DOTS ? 1.0f : half_bits_to_float(sc[st][r][u]);
+                        acc[r][b] = fmaf((float)isum, wscale * xscale, acc[r][b]);
+                    }
                 }
-            }
+            } else {
+                const float4 *xs4 = reinterpret_cast<const float4 *>(smem_raw);
+                float p[R][B];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int col0 = (seg + u) * 512 + lane * 16;
-                if (valid[u]) {
+                for (int k = 0; k < 4; ++k) {
+                    float wf[R][4];
 #pragma unroll
-                    for (int r = 0; r < R; ++r)
-                        sc[u][r] = DOTS ? 1.0f : half_bits_to_float(__ldg(a.scales + rowi[r] * bpr + (col0 >> 5)));
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (!valid[u]) continue;
-                const int s = seg + u;
-                const int blk = (s * 512 + lane * 16) >> 5;
-                if (INT) {
-                    const uint4 *xq16 = reinterpret_cast<const uint4 *>(smem_raw);
+                    for (int r = 0; r < R; ++r) {
+                        const uint32_t word = k == 0 ? w[r].x : k == 1 ? w[r].y : k == 2 ? w[r].z : w[r].w;
+                        s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
+                    }
 #pragma unroll
                     for (int b = 0; b < B; ++b) {
-                        const uint4 xv = xq16[(size_t)b * slots + s * 32 + lane];
-                        const float xscale = DOTS ? 1.0f : xs_scales[b * bpr + blk];
+                        const float4 xv = xs4[(size_t)b * slots + s * 128 + k * 32 + lane];
 #pragma unroll
                         for (int r = 0; r < R; ++r) {
-                            int isum = dp4a_s8(w[u][r].x, xv.x, 0);
-                            isum = dp4a_s8(w[u][r].y, xv.y, isum);
-                            isum = dp4a_s8(w[u][r].z, xv.z, isum);
-                            isum = dp4a_s8(w[u][r].w, xv.w, isum);
-                            if (DOTS) {
-                                // a block is shared by two neighbouring lanes
-                                int full = isum + __shfl_xor_sync(vmask[u], isum, 1);
-                                if ((lane & 1) == 0 && b == 0 && g * R + r < rows) a.dots[rowi[r] * bpr + blk] = full;
-                            }
-                            acc[r][b] = fmaf((float)isum, sc[u][r] * xscale, acc[r][b]);
+                            float t = k == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, p[r][b]);
+                            t = fmaf(wf[r][1], xv.y, t);
+                            t = fmaf(wf[r][2], xv.z, t);
+                            p[r][b] = fmaf(wf[r][3], xv.w, t);
                         }
                     }
-                } else {
-                    const float4 *xs4 = reinterpret_cast<const float4 *>(smem_raw);
-                    float part[R][B];
+                }
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        float wf[R][4];
+                for (int r = 0; r < R; ++r) {
+                    const float wscale = half_bits_to_float(sc[st][r][u]);
 #pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            const uint32_t word = k == 0 ? w[u][r].x : k == 1 ? w[u][r].y : k == 2 ? w[u][r].z : w[u][r].w;
-                            s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
-                        }
-#pragma unroll
-                        for (int b = 0; b < B; ++b) {
-                            const float4 xv = xs4[(size_t)b * slots + s * 128 + k * 32 + lane];
-#pragma unroll
-                            for (int r = 0; r < R; ++r) {
-                                float p = k == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, part[r][b]);
-                                p = fmaf(wf[r][1], xv.y, p);
-                                p = fmaf(wf[r][2], xv.z, p);
-                                part[r][b] = fmaf(wf[r][3], xv.w, p);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int r = 0; r < R; ++r)
-#pragma unroll
-                        for (int b = 0; b < B; ++b) acc[r][b] = fmaf(sc[u][r], part[r][b], acc[r][b]);
+                    for (int b = 0; b < B; ++b) acc[r][b] = fmaf(wscale, p[r][b], acc[r][b]);
                 }
             }
         }
-        if (a.y) {
+        if (!DOTS) {
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
                 for (int b = 0; b < B; ++b) {
-                    float s = warp_sum(acc[r][b]);
-                    if (lane == 0 && g * R + r < rows) a.y[(size_t)b * rows + g * R + r] = s;
+                    const float s = warp_sum(acc[r][b]);
+                    if (lane == 0 && row0 + r < row_end) part[((size_t)(g * R + r) * ntrips + trip) * B + b] = s;
                 }
+        }
+    };
+
+    for (int base = warp; base < nitems; base += STAGES * kQ8SWarps) {
+#pragma unroll
+        for (int st = 0; st < STAGES; ++st) {
+            const int item = base + st * kQ8SWarps;
+            if (item >= nitems) break;  // uniform across the warp
+            cp_async_wait<STAGES - 1>();
+            if (st == 0) { consume(std::integral_constant<int, 0>{}, item); issue(std::integral_constant<int, 0>{}, item + STAGES * kQ8SWarps); }
+            if (st == 1) { consume(std::integral_constant<int, 1 % STAGES>{}, item); issue(std::integral_constant<int, 1 % STAGES>{}, item + STAGES * kQ8SWarps); }
+            if (st == 2) { consume(std::integral_constant<int, 2 % STAGES>{}, item); issue(std::integral_constant<int, 2 % STAGES>{}, item + STAGES * kQ8SWarps); }
+            if (st == 3) { consume(std::integral_constant<int, 3 % STAGES>{}, item); issue(std::integral_constant<int, 3 % STAGES>{}, item + STAGES * kQ8SWarps); }
+        }
+    }
+    cp_async_wait<0>();
+
+    if (!DOTS && a.y) {
+        __syncthreads();
+        const int nrows = row_end - row_begin;
+        for (int i = threadIdx.x; i < nrows * B; i += kQ8SThreads) {
+            const int rl = i / B, b = i - rl * B;
+            float s = 0.f;
+            for (int t = 0; t < ntrips; ++t) s += part[((size_t)rl * ntrips + t) * B + b];
+            a.y[(size_t)b * a.rows + row_begin + rl] = s;
         }
     }
 }
@@ -331,9 +471,6 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
 //   Q8B / Q4B  the block pair `lane` (a 4-byte aligned 68 / 36 byte record)
 // ---------------------------------------------------------------------------
 constexpr int kChunkBlocks = 64;  // blocks per row chunk = 2048 columns
-constexpr int MODE_FLOAT = 0;     // fp32 activations
-constexpr int MODE_INT = 1;       // int8 activations read from the workspace
-constexpr int MODE_INT_FUSED = 2; // int8 activations quantised in the prologue of this kernel
 
 template <int FMT>
 struct RingTraits {
@@ -361,43 +498,6 @@ __device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], 
     scale[1] = half_bits_to_float((uint16_t)(wds[QW] >> 16));
 #pragma unroll
     for (int i = 0; i < QW; ++i) qb[i] = wds[QW + 1 + i];
-}
-
-// Integer activations into shared memory, one warp per 32-element block:
-// quantise on the fly (QUANTIZE) or copy the workspace's int8 values; write
-// each byte to its lane-interleaved slot, the block's fp32 scale, and the
-// block's int32 sum (Q4_0 needs sum(xq) for the "- 8" of its nibbles).
-template <int CPL, bool QUANTIZE, bool WANT_SUM>
-__device__ __forceinline__ void stage_x_blocks(unsigned char *xq_smem, float *xs_smem, int *xsum_smem,
-                                               const QGemvArgs &a, int batch, int slots_per_vec, bool want_scales) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const int bpr = a.cols / 32;
-    for (int i = warp; i < batch * bpr; i += nwarps) {
-        const int b = i / bpr, blk = i - b * bpr;
-        const int col = blk * 32 + lane;
-        int qv;
-        float scale = 1.0f;
-        if (QUANTIZE) {
-            const float v = __ldg(a.x + (size_t)b * a.cols + col);
-            float m = fabsf(v);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            scale = (m == 0.0f) ? 1.0f : __fdiv_rn(m, 127.0f);
-            const float inv = __fdiv_rn(1.0f, scale);
-            qv = (int)(int8_t)(int)floorf(__fadd_rn(__fmul_rn(v, inv), 0.5f));
-        } else {
-            qv = (int)a.xq[(size_t)b * a.cols + col];
-            if (want_scales && lane == 0) scale = a.xs[(size_t)b * bpr + blk];
-        }
-        xq_smem[((size_t)b * slots_per_vec + permuted_slot<CPL, 16>(col)) * 16 + (col & 15)] = (unsigned char)(int8_t)qv;
-        if (WANT_SUM) {
-            int s = qv;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (lane == 0) xsum_smem[i] = s;
-        }
-        if (lane == 0 && want_scales) xs_smem[i] = scale;
-    }
 }
 
 template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, int WARPS>
@@ -481,6 +581,8 @@ __global__ void __launch_bounds__(WARPS * 32) qring_gemv_kernel(QGemvArgs a) {
     for (int s = 0; s < STAGES; ++s) issue();  // weights start streaming before the activations are staged
 
     // ---- activations ------------------------------------------------------------
+    pdl_launch_dependents();
+    pdl_wait();  // weights were prefetched above; activations and outputs wait for the predecessor
     if (MODE == MODE_FLOAT) {
         stage_x_float<T::CPL>(reinterpret_cast<float4 *>(xbase), a.x, cols, B, slots);
     } else if (MODE == MODE_INT_FUSED) {
@@ -750,18 +852,51 @@ static int balanced_grid(int units, int warps_per_cta, int max_ctas) {
     return best;
 }
 
-template <int B, int R, bool INT, bool DOTS>
+template <int B, int MODE>
+struct Q8SConfig {
+    // rows per item x segments per trip: R*U 16-byte pieces per lane and item
+    static constexpr int R = B <= 2 ? 1 : 2;
+    static constexpr int U = B <= 2 ? 4 : 2;
+    static constexpr int STAGES = 4;
+};
+
+// dynamic shared memory of the split-layout kernel for a given grid
+template <int B, int MODE>
+static size_t q8s_smem_bytes(int rows, int cols, int grid) {
+    using Cfg = Q8SConfig<B, MODE>;
+    const bool is_int = MODE != MODE_FLOAT;
+    const int nseg = (cols + 511) / 512;
+    const int ntrips = (nseg + Cfg::U - 1) / Cfg::U;
+    const int max_rows = rows / grid + 1;
+    size_t off = (size_t)B * nseg * (is_int ? 512 : 2048) + (is_int ? (size_t)B * (cols / 32) * 4 : 0) +
+                 (size_t)max_rows * ntrips * B * 4;
+    off = (off + 127) & ~(size_t)127;
+    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * Cfg::U * 512;
+}
+
+template <int B, int MODE, bool DOTS>
 static int launch_q8s(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
-    const int nseg = (a.cols + 511) / 512;
-    size_t smem = INT ? (size_t)B * nseg * 32 * 16 + (size_t)B * (a.cols / 32) * 4 : (size_t)B * nseg * 128 * 16;
-    if (smem + 256 > (size_t)di->max_smem_optin) return TB200_ERR_INVALID_ARG;
-    constexpr auto kernel = q8s_gemv_kernel<B, R, INT, DOTS>;
+    using Cfg = Q8SConfig<B, MODE>;
+    constexpr auto kernel = q8s_gemv_kernel<B, Cfg::R, Cfg::U, MODE, DOTS, Cfg::STAGES>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
-    int ctas = resident_ctas<kernel>(di, kQ8SThreads, smem);
-    int grid = balanced_grid((a.rows + R - 1) / R, kQ8SThreads / 32, di->sm_count * ctas);
-    kernel<<<grid, kQ8SThreads, smem, s>>>(a);
-    return check_launch();
+    // As many CTAs as stay resident at once (a multiple of the SM count, so that every SM streams the
+    // same number of rows); more waves only when the per-row table of one CTA would grow past 16 KB.
+    const int nseg = (a.cols + 511) / 512;
+    const int ntrips = (nseg + Cfg::U - 1) / Cfg::U;
+    int grid = 0;
+    for (int per_sm = 4; per_sm >= 1 && grid == 0; --per_sm) {
+        int g = di->sm_count * per_sm;
+        while ((size_t)(a.rows / g + 1) * ntrips * B * 4 > 16384) g *= 2;
+        const size_t need = q8s_smem_bytes<B, MODE>(a.rows, a.cols, g);
+        if (need + 1024 > (size_t)di->max_smem_optin) continue;
+        if (resident_ctas<kernel>(di, kQ8SThreads, need) >= per_sm) grid = g;
+    }
+    if (grid == 0) return TB200_ERR_INVALID_ARG;
+    const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
+    if (grid > groups) grid = groups;
+    const size_t smem = q8s_smem_bytes<B, MODE>(a.rows, a.cols, grid);
+    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a, a.rows / grid + 1);
 }
 
 template <int FMT, int B, int MODE>
@@ -800,8 +935,7 @@ static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s)
     const int need = (groups + Cfg::WARPS - 1) / Cfg::WARPS;
     if (grid > need) grid = need;
     if (grid > a.rows) grid = a.rows;
-    kernel<<<grid, Cfg::WARPS * 32, smem, s>>>(a);
-    return check_launch();
+    return launch_kernel(kernel, dim3(grid), dim3(Cfg::WARPS * 32), smem, s, g_overlap_launches != 0, a);
 }
 
 template <int FMT, bool INT>
@@ -831,9 +965,10 @@ static bool fast_batch_fits(int cols, int batch, Path path, const DeviceInfo *di
             default: return false;
         }
     }
+    // split layout, one CTA per SM as the worst case for the per-row table (rows are not known here: bound it)
     const int nseg = (cols + 511) / 512;
-    const size_t per = MODE != MODE_FLOAT ? (size_t)nseg * 512 + (size_t)(cols / 32) * 4 : (size_t)nseg * 2048;
-    return batch >= 1 && batch <= 8 && per * batch <= limit;
+    const size_t x_bytes = (size_t)batch * nseg * (MODE != MODE_FLOAT ? 512 : 2048) + (size_t)batch * (cols / 32) * 4;
+    return batch >= 1 && batch <= 8 && x_bytes + (64 + 16 + 1) * 1024 <= limit;  // + rings + per-row table
 }
 
 // Fewest passes over the weights such that each pass's share of the batch fits;
@@ -850,9 +985,10 @@ static int batch_per_pass(int cols, int batch, Path path, const DeviceInfo *di) 
 template <int FMT, int MODE, bool DOTS, int B>
 static int launch_fast_b(const QGemvArgs &a, Path path, const DeviceInfo *di, cudaStream_t s) {
     if constexpr (FMT == FMT_Q8S) {
-        if (path == PATH_Q8S_DIRECT) return launch_q8s<B, (B <= 2 ? 4 : 2), MODE != MODE_FLOAT, DOTS>(a, di, s);
+        return launch_q8s<B, MODE, DOTS>(a, di, s);
+    } else {
+        return launch_ring<FMT, B, MODE, DOTS>(a, di, s);
     }
-    return launch_ring<FMT, B, MODE, DOTS>(a, di, s);
 }
 
 template <int FMT, int MODE, bool DOTS>
@@ -906,10 +1042,11 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
         return TB200_OK;
     }
     // ring: every row chunk starts on a 16-byte boundary and is a whole number of 16-byte units
+    // split layout: 128-bit loads need 16-byte aligned rows (cols % 32 == 0 keeps the phase)
     Path path = PATH_GENERIC;
     if (aligned_to(a.w, 16)) {
-        if (a.cols % 256 == 0 && (FMT != FMT_Q8S || DOTS || aligned_to(a.scales, 16))) path = PATH_RING;
-        else if (FMT == FMT_Q8S) path = PATH_Q8S_DIRECT;
+        if (FMT == FMT_Q8S) path = PATH_Q8S_DIRECT;
+        else if (a.cols % 256 == 0) path = PATH_RING;
     }
     const int per = path == PATH_GENERIC
                         ? 0
@@ -917,7 +1054,7 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     if (per < 1) path = PATH_GENERIC;
 
     if (MODE == MODE_INT_FUSED) {
-        const bool fuse = path == PATH_RING && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per;
+        const bool fuse = path != PATH_GENERIC && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per;
         if (fuse) return launch_fast<FMT, MODE_INT_FUSED, false>(a, path, di, s);
         // separate quantiser into the workspace, then the MODE_INT kernels
         st = quantize_x(a.cols, a.batch, a.x, xq_ws, xs_ws, s);
@@ -926,7 +1063,6 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
         b.x = nullptr, b.xq = xq_ws, b.xs = xs_ws;
         return qgemv_dispatch<FMT, MODE_INT, false>(b, nullptr, nullptr, stream);
     } else {
-        if (path == PATH_Q8S_DIRECT && INT && !aligned_to(a.xq, 16)) path = PATH_GENERIC;
         if (path == PATH_GENERIC) return launch_generic<FMT, INT>(a, di, s);
         // more activation vectors than fit next to the ring: several passes over the weights
         for (int b0 = 0; b0 < a.batch; b0 += per) {

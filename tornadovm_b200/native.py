@@ -20,6 +20,8 @@ SIGNATURES = {
     "tb200_status_string": (C.c_char_p, [_I]),
     "tb200_version": (_I, []),
     "tb200_device_status": (_I, [C.POINTER(_I)]),
+    "tb200_set_option": (_I, [_I, _I]),
+    "tb200_get_option": (_I, [_I, C.POINTER(_I)]),
     "tb200_device_malloc": (_I, [_Z, C.POINTER(_P)]),
     "tb200_device_free": (_I, [_P]),
     "tb200_sgemv": (_I, [_I, _I, _P, _P, _P, _P]),
