@@ -43,7 +43,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-I", CSRC]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", LIB_PATH, os.path.join(CSRC, "libtornado_b200.cu"), "-lcuda"]
+    cmd += ["-o", LIB_PATH, os.path.join(CSRC, "libtornado_b200.cu")]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
