@@ -158,91 +158,103 @@ def make_weights(torch, dev, rows, layers, seed):
     return q, sc
 
 
-def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak):
+def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgemv", "q8", "q4", "sgemm", "hgemm"), hgemm_sizes=(2048, 4096, 8192, 16384)):
     """Short device-resident timings of the other kernels on the path (not the headline)."""
     out = {}
     P = lambda t: C.c_void_p(t.data_ptr())
     S = C.c_void_p(stream.cuda_stream)
     dev = torch.device("cuda", torch.cuda.current_device())
 
-    def timeit(fn, reps, flush=None):
-        for _ in range(3):
-            fn(0)
+    def timeit(fn, reps, period=4):
+        """Average seconds per call; `period` consecutive calls (distinct operands) are captured in a CUDA graph."""
+        for i in range(period):
+            fn(i)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(period):
+                fn(i)
+        g.replay()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         stream.synchronize()
         e0.record(stream)
-        for i in range(reps):
-            fn(i)
+        for _ in range(reps):
+            g.replay()
         e1.record(stream)
         stream.synchronize()
-        return e0.elapsed_time(e1) / reps * 1e-3
+        return e0.elapsed_time(e1) / (reps * period) * 1e-3
 
     with torch.cuda.stream(stream):
-        # FP32 GEMV 8192 x 8192 (configs[0]); two matrices alternate (537 MB > L2)
-        m = torch.rand((2, 8192, 8192), device=dev) * 2 - 1
-        v = torch.rand(8192, device=dev) * 2 - 1
-        y = torch.empty(8192, device=dev)
-        t = timeit(lambda i: lib.tb200_sgemv(8192, 8192, P(m[i & 1]), P(v), P(y), S), 20)
-        b = 4 * (8192 * 8192 + 2 * 8192)
-        out["sgemv_8192"] = {"GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / hbm_peak, "us": t * 1e6}
-        del m
-        # Q8_0 variants on the headline shape
-        q, sc = make_weights(torch, dev, ROWS, 4, 7)
-        blocks = torch.empty((4, ROWS, COLS // 32, 34), dtype=torch.uint8, device=dev)
-        blocks[..., :2] = sc.view(torch.uint8).view(4, ROWS, COLS // 32, 2)
-        blocks[..., 2:] = q.view(torch.uint8).view(4, ROWS, COLS // 32, 32)
-        for batch in (1, 8):
-            x = torch.randn((batch, COLS), device=dev)
-            yb = torch.empty((batch, ROWS), device=dev)
-            ws_n = lib.tb200_qx_workspace_bytes(COLS, batch)
-            ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
-            by = algorithmic_bytes(ROWS, COLS, batch)
-            runs = {
-                f"q8_split_f32_b{batch}": lambda i: lib.tb200_q8_gemv(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), S),
-                f"q8_blocks_f32_b{batch}": lambda i: lib.tb200_q8b_gemv(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), S),
-                f"q8_split_int_b{batch}": lambda i: lib.tb200_q8_gemv_i8(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), P(ws), ws_n, S),
-                f"q8_blocks_int_b{batch}": lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), P(ws), ws_n, S),
-            }
-            for name, fn in runs.items():
-                t = timeit(fn, 40)
-                out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
-        del q, sc, blocks
-        # Q4_0 Llama-3-8B-shaped layer sweep (configs[4]): 7 projections + the output projection
-        shapes = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336), (128256, 4096)]
-        g = torch.Generator(device=dev).manual_seed(3)
-        # two sets of weights alternate so that a pass never finds its matrices in L2 (2 x 418 MB)
-        wsets = [[torch.randint(0, 256, (r * (c // 32) * 18,), dtype=torch.uint8, device=dev, generator=g) for r, c in shapes] for _ in range(2)]
-        for batch in (1, 4, 16):
-            xs = {c: torch.randn((batch, c), device=dev) for c in (4096, 14336)}
-            ys = {r: torch.empty((batch, r), device=dev) for r in (4096, 1024, 14336, 128256)}
-            ws_n = lib.tb200_qx_workspace_bytes(14336, batch)
-            ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
-            by = sum(algorithmic_bytes(r, c, batch, 18) for r, c in shapes)
+        if "sgemv" in sections:
+            # FP32 GEMV 8192 x 8192 (configs[0]); two matrices alternate (537 MB > L2)
+            m = torch.rand((2, 8192, 8192), device=dev) * 2 - 1
+            v = torch.rand(8192, device=dev) * 2 - 1
+            y = torch.empty(8192, device=dev)
+            t = timeit(lambda i: lib.tb200_sgemv(8192, 8192, P(m[i & 1]), P(v), P(y), S), 10)
+            b = 4 * (8192 * 8192 + 2 * 8192)
+            out["sgemv_8192"] = {"GB/s": b / t / 1e9, "frac_hbm": b / t / 1e9 / hbm_peak, "us": t * 1e6}
+            del m
+        if "q8" in sections:
+            # Q8_0 variants on the headline shape
+            q, sc = make_weights(torch, dev, ROWS, 4, 7)
+            blocks = torch.empty((4, ROWS, COLS // 32, 34), dtype=torch.uint8, device=dev)
+            blocks[..., :2] = sc.view(torch.uint8).view(4, ROWS, COLS // 32, 2)
+            blocks[..., 2:] = q.view(torch.uint8).view(4, ROWS, COLS // 32, 32)
+            for batch in (1, 8):
+                x = torch.randn((batch, COLS), device=dev)
+                yb = torch.empty((batch, ROWS), device=dev)
+                ws_n = lib.tb200_qx_workspace_bytes(COLS, batch)
+                ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+                by = algorithmic_bytes(ROWS, COLS, batch)
+                runs = {
+                    f"q8_split_f32_b{batch}": lambda i: lib.tb200_q8_gemv(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), S),
+                    f"q8_blocks_f32_b{batch}": lambda i: lib.tb200_q8b_gemv(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), S),
+                    f"q8_split_int_b{batch}": lambda i: lib.tb200_q8_gemv_i8(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), P(ws), ws_n, S),
+                    f"q8_blocks_int_b{batch}": lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), P(ws), ws_n, S),
+                }
+                for name, fn in runs.items():
+                    t = timeit(fn, 10)
+                    out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
+            del q, sc, blocks
+        if "q4" in sections:
+            # Q4_0 Llama-3-8B-shaped layer sweep (configs[4]): 7 projections + the output projection
+            shapes = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336), (128256, 4096)]
+            g = torch.Generator(device=dev).manual_seed(3)
+            # two sets of weights alternate so that a pass never finds its matrices in L2 (2 x 418 MB)
+            wsets = [[torch.randint(0, 256, (r * (c // 32) * 18,), dtype=torch.uint8, device=dev, generator=g) for r, c in shapes] for _ in range(2)]
+            for batch in (1, 4, 16):
+                xs = {c: torch.randn((batch, c), device=dev) for c in (4096, 14336)}
+                ys = {r: torch.empty((batch, r), device=dev) for r in (4096, 1024, 14336, 128256)}
+                ws_n = lib.tb200_qx_workspace_bytes(14336, batch)
+                ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+                by = sum(algorithmic_bytes(r, c, batch, 18) for r, c in shapes)
 
-            def sweep_f(i):
-                for (r, c), w in zip(shapes, wsets[i & 1]):
-                    lib.tb200_q4b_gemv(r, c, batch, P(w), P(xs[c]), P(ys[r]), S)
+                def sweep_f(i):
+                    for (r, c), w in zip(shapes, wsets[i & 1]):
+                        lib.tb200_q4b_gemv(r, c, batch, P(w), P(xs[c]), P(ys[r]), S)
 
-            def sweep_i(i):
-                for (r, c), w in zip(shapes, wsets[i & 1]):
-                    lib.tb200_q4b_gemv_i8(r, c, batch, P(w), P(xs[c]), P(ys[r]), P(ws), ws_n, S)
-            for name, fn in ((f"q4_layer_sweep_f32_b{batch}", sweep_f), (f"q4_layer_sweep_int_b{batch}", sweep_i)):
-                t = timeit(fn, 6)
-                out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
-        del wsets
-        # FP32 SGEMM 4096^3 (configs[1])
-        a = torch.rand((4096, 4096), device=dev)
-        bm = torch.rand((4096, 4096), device=dev)
-        c = torch.empty((4096, 4096), device=dev)
-        t = timeit(lambda i: lib.tb200_sgemm(4096, 4096, 4096, C.c_float(1.0), P(a), P(bm), C.c_float(0.0), P(c), S), 5)
-        out["sgemm_4096"] = {"TFLOP/s": 2 * 4096**3 / t / 1e12, "ms": t * 1e3}
-        # FP16 GEMM sweep (configs[2])
-        for n in (2048, 4096, 8192):
-            ah = (torch.randn((n, n), device=dev) / n**0.5).half()
-            bh = (torch.randn((n, n), device=dev) / n**0.5).half()
-            ch = torch.empty((n, n), device=dev)
-            t = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, P(ah), P(bh), P(ch), S), 5 if n < 8192 else 2)
-            out[f"hgemm_{n}"] = {"TFLOP/s": 2 * n**3 / t / 1e12, "frac_tensor": 2 * n**3 / t / 1e12 / tensor_peak, "ms": t * 1e3}
+                def sweep_i(i):
+                    for (r, c), w in zip(shapes, wsets[i & 1]):
+                        lib.tb200_q4b_gemv_i8(r, c, batch, P(w), P(xs[c]), P(ys[r]), P(ws), ws_n, S)
+                for name, fn in ((f"q4_layer_sweep_f32_b{batch}", sweep_f), (f"q4_layer_sweep_int_b{batch}", sweep_i)):
+                    t = timeit(fn, 3, period=2)
+                    out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
+            del wsets
+        if "sgemm" in sections:
+            # FP32 SGEMM 4096^3 (configs[1])
+            a = torch.rand((4096, 4096), device=dev)
+            bm = torch.rand((4096, 4096), device=dev)
+            c = torch.empty((4096, 4096), device=dev)
+            t = timeit(lambda i: lib.tb200_sgemm(4096, 4096, 4096, C.c_float(1.0), P(a), P(bm), C.c_float(0.0), P(c), S), 3, period=2)
+            out["sgemm_4096"] = {"TFLOP/s": 2 * 4096**3 / t / 1e12, "ms": t * 1e3}
+        if "hgemm" in sections:
+            # FP16 GEMM sweep (configs[2])
+            for n in hgemm_sizes:
+                ah = (torch.randn((n, n), device=dev) / n**0.5).half()
+                bh = (torch.randn((n, n), device=dev) / n**0.5).half()
+                ch = torch.empty((n, n), device=dev)
+                t = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, P(ah), P(bh), P(ch), S), 3, period=2)
+                out[f"hgemm_{n}"] = {"TFLOP/s": 2 * n**3 / t / 1e12, "frac_tensor": 2 * n**3 / t / 1e12 / tensor_peak, "ms": t * 1e3}
     return out
 
 
@@ -276,14 +288,29 @@ def run_gpu_arm(args):
     S = C.c_void_p(stream.cuda_stream)
     P = lambda t: C.c_void_p(t.data_ptr())
     launches = 0
+    ws_n = lib.tb200_qx_workspace_bytes(COLS, BATCH)
+    ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+    # consecutive mat-vecs may overlap: each prefetches its weights while its predecessor drains
+    B200Native.call("tb200_set_option", 1, 1)
+
+    def enqueue_layers():
+        for l in range(LAYERS):
+            st = lib.tb200_q8_gemv_i8(lrows, COLS, BATCH, P(q[l]), P(sc[l]), P(x), P(y_local[l]), P(ws), ws_n, S)
+            if st:
+                B200Native.check_status(st, "tb200_q8_gemv_i8")
+
+    # one step = LAYERS launches, captured once and replayed (how TornadoVM runs a plan withCUDAGraph)
+    with torch.cuda.stream(stream):
+        enqueue_layers()
+        stream.synchronize()
+        layer_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(layer_graph, stream=stream):
+            enqueue_layers()
 
     def step():
         nonlocal launches
-        for l in range(LAYERS):
-            st = lib.tb200_q8_gemv(lrows, COLS, BATCH, P(q[l]), P(sc[l]), P(x), P(y_local[l]), S)
-            if st:
-                B200Native.check_status(st, "tb200_q8_gemv")
-            launches += 1
+        layer_graph.replay()
+        launches += LAYERS
         if world > 1:
             gather_rows(y_local.view(LAYERS * BATCH, per), ROWS, None, gather_buf)
 
@@ -310,8 +337,7 @@ def run_gpu_arm(args):
         reps = max(args.steps, 10)
         k0.record(stream)
         for _ in range(reps):
-            for l in range(LAYERS):
-                lib.tb200_q8_gemv(lrows, COLS, BATCH, P(q[l]), P(sc[l]), P(x), P(y_local[l]), S)
+            layer_graph.replay()
         k1.record(stream)
         stream.synchronize()
         kernel_s = k0.elapsed_time(k1) * 1e-3 / (reps * LAYERS)
@@ -335,10 +361,12 @@ def run_gpu_arm(args):
         sa = [HalfFloatArray(sc[l].cpu().numpy().view("uint16")) for l in range(LAYERS)]
         xa = FloatArray(x.cpu().numpy())
         ya = [FloatArray(ROWS * BATCH) for _ in range(LAYERS)]
+        from tornadovm_b200.b200 import B200Options
+        opts = B200Options(exact_int=True, overlap_launches=True)
         tg = TaskGraph("q8decode").transferToDevice(DataTransferMode.FIRST_EXECUTION, *qa, *sa) \
             .transferToDevice(DataTransferMode.EVERY_EXECUTION, xa)
         for l in range(LAYERS):
-            tg.libraryTask(f"l{l}", B200.q8Gemv, ROWS, COLS, BATCH, qa[l], sa[l], xa, ya[l])
+            tg.libraryTask(f"l{l}", B200.q8Gemv, ROWS, COLS, BATCH, qa[l], sa[l], xa, ya[l], opts)
         tg.transferToHost(DataTransferMode.EVERY_EXECUTION, *ya)
         with TornadoExecutionPlan(tg, CudaDevice(local)).withCUDAGraph() as plan:
             for _ in range(max(args.warmup, 3)):
@@ -374,11 +402,12 @@ def run_gpu_arm(args):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic",
+        "dtype": "s8", "data": "synthetic",
         "config": {"workload": f"Q8_0 GEMV W[{ROWS}x{COLS}] int8 blocks of 32 + fp16 scale (split layout), fp32 x, batch {BATCH}",
                    "layers_per_step": LAYERS, "l2_policy": f"{LAYERS} distinct weight matrices per step ({LAYERS * 62.4:.0f} MB > 126 MB L2)",
                    "parallelism": f"rows sharded over {world} GPU(s), outputs all-gathered once per step" if world > 1 else "single GPU",
-                   "mode": "float (fp32 activations, reference arithmetic)"},
+                   "mode": "int (fp32 activations quantised to int8 per 32-block inside the kernel, exact int32 block dots)",
+                   "launch": "CUDA-graph replay, programmatic dependent launches"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / e2e_steps * 1e3,
                 "api": "TaskGraph.libraryTask(B200.q8Gemv) + TornadoExecutionPlan.withCUDAGraph().execute()" if world == 1 else "ShardedQ8Gemv.run"},
@@ -407,8 +436,18 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=8.0)
     ap.add_argument("--no-secondary", action="store_true")
+    ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q4,sgemm,hgemm) and print their timings; for profiling")
+    ap.add_argument("--hgemm-sizes", default="2048,4096,8192,16384")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sections:
+        import torch
+        from tornadovm_b200.native import B200Native
+        torch.cuda.set_device(0)
+        hbm_peak, tensor_peak, _ = measured_peaks()
+        res = secondary_metrics(torch, B200Native.load(), torch.cuda.Stream(), hbm_peak, tensor_peak,
+                                tuple(args.sections.split(",")), tuple(int(v) for v in args.hgemm_sizes.split(",")))
+        print(json.dumps({"sections": res}))
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -21,8 +21,12 @@ MAX_BATCH = 16
 class B200Options:
     """Per-call tuning object (LibraryTaskDescriptor.withTuning):
     ``exact_int`` selects the int8-activation / int32 block-dot arithmetic for
-    the quantised mat-vec tasks."""
+    the quantised mat-vec tasks; ``overlap_launches`` lets consecutive mat-vec
+    kernels of the plan overlap (each prefetches its weights while the kernel
+    before it drains), which requires that no task writes a weight array
+    immediately before the mat-vec that reads it."""
     exact_int: bool = False
+    overlap_launches: bool = False
 
 
 def _check(cond: bool, msg: str) -> None:

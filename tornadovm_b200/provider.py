@@ -86,6 +86,8 @@ class B200LibraryProvider:
     def prepare(self, descriptor, context: B200Context) -> None:
         fn = descriptor.getFunctionName()
         tuning = descriptor.getTuning()
+        if isinstance(tuning, B200Options) and tuning.overlap_launches:
+            B200Native.call("tb200_set_option", 1, 1)  # TB200_OPT_OVERLAP_LAUNCHES
         if fn in _QUANT_FUNCTIONS and isinstance(tuning, B200Options) and tuning.exact_int:
             p = descriptor.getParameters()
             need = B200Native.load().tb200_qx_workspace_bytes(int(p[1]), int(p[2]))
