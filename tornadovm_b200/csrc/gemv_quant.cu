@@ -30,6 +30,7 @@
 // Algorithmic bytes per launch:
 //   Q8: 34 * rows*cols/32 + 4*batch*(cols + rows)
 //   Q4: 18 * rows*cols/32 + 4*batch*(cols + rows)
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -254,20 +255,21 @@ __device__ __forceinline__ void stage_x_blocks(unsigned char *xq_smem, float *xs
 // ---------------------------------------------------------------------------
 // Family 1: split Q8_0 through per-lane cp.async rings.
 //
-// A CTA owns a contiguous range of rows.  Its work items are (group of R rows,
-// trip of U 512-column segments); warp w takes items w, w + 8, ...  For each
-// item a lane copies its R*U 16-byte pieces (16 quants each) into its own slots
-// of the warp's shared-memory ring with cp.async (no registers held while the
-// bytes are in flight, no cross-lane synchronisation: a lane reads back only
-// what it copied) and keeps STAGES items in flight.  The fp16 scales ride in
-// registers.  Per-item sums go to a small shared table and are added per row in
-// a fixed order at the end, so results do not depend on warp timing.
+// A CTA owns a contiguous range of rows and each of its warps a contiguous run
+// of row groups (R rows).  A ring stage holds one trip of one group: U segments
+// of 512 columns, i.e. R*U 16-byte pieces (16 quants each) per lane.  A lane
+// copies its pieces into its own slots of the warp's shared-memory ring with
+// cp.async and keeps STAGES stages in flight: no registers are held while the
+// bytes travel and no cross-lane synchronisation is needed, because a lane
+// reads back only what it copied.  The fp16 scales ride in registers.  Rows
+// longer than one trip are accumulated in registers by the same warp, so a
+// row's sum never depends on warp timing.
 // ---------------------------------------------------------------------------
 constexpr int kQ8SThreads = 256;
 constexpr int kQ8SWarps = kQ8SThreads / 32;
 
-__device__ __forceinline__ void cp_async_16(void *dst_smem, const void *src_gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src_gmem) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -276,8 +278,9 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 template <int B, int R, int U, int MODE, bool DOTS, int STAGES>
-__global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int max_rows_per_cta) {
+__global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
     constexpr bool INT = MODE != MODE_FLOAT;
+    static_assert(STAGES >= 2 && STAGES <= 4, "ring depth");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int cols = a.cols;
     const int bpr = cols / 32;
@@ -286,51 +289,51 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int8_t *q = reinterpret_cast<const int8_t *>(a.w);
 
+    // rows of the CTA, row groups of the warp
     const int row_begin = (int)((long long)a.rows * blockIdx.x / gridDim.x);
     const int row_end = (int)((long long)a.rows * (blockIdx.x + 1) / gridDim.x);
     const int ngroups = (row_end - row_begin + R - 1) / R;
-    const int nitems = ngroups * ntrips;
+    const int g_begin = ngroups * warp / kQ8SWarps, g_end = ngroups * (warp + 1) / kQ8SWarps;
 
-    // ---- shared memory carve-up -------------------------------------------------
-    // [ activations ][ activation scales ][ per-item sums ][ rings: warps x stages x R x U x 512 ]
+    // ---- shared memory: [ activations ][ activation scales ][ rings: warps x stages x R x U x 512 ] ----
     const int slots = nseg * (INT ? 32 : 128);  // 16-byte slots per activation vector
     float *xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
-    float *part = xs_scales + (INT ? B * bpr : 0);  // [row_local][trip][b]
-    size_t ring_off = (size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 4 + (size_t)max_rows_per_cta * ntrips * B * 4;
-    ring_off = (ring_off + 127) & ~(size_t)127;
+    const uint32_t ring_off = (uint32_t)(((size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 4 + 127) & ~(size_t)127);
     unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * U * 512 + lane * 16;
+    const uint32_t ring_s = smem_u32(ring);
 
+    // ---- issue side ----------------------------------------------------------------
     uint16_t sc[STAGES][R][U];
-    auto issue = [&](auto stage_c, int item) {
+    int ig = g_begin, itrip = 0;  // next (group, trip) to request
+    auto issue = [&](auto stage_c) {
         constexpr int st = decltype(stage_c)::value;
-        if (item < nitems) {
-            const int g = item / ntrips, trip = item - g * ntrips;
+        if (ig < g_end) {
+            const int colbase = itrip * (U * 512) + lane * 16;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const size_t row = (size_t)min(row_begin + g * R + r, row_end - 1);
+                const size_t row = (size_t)min(row_begin + ig * R + r, row_end - 1);
+                const int8_t *qrow = q + row * cols + colbase;
+                const uint16_t *srow = a.scales + row * bpr + (colbase >> 5);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const int col0 = (trip * U + u) * 512 + lane * 16;
-                    if (col0 < cols) {
-                        cp_async_16(ring + ((st * R + r) * U + u) * 512, q + row * cols + col0);
-                        if (!DOTS) sc[st][r][u] = __ldg(a.scales + row * bpr + (col0 >> 5));
+                    if (colbase + u * 512 < cols) {
+                        cp_async_16(ring_s + ((st * R + r) * U + u) * 512, qrow + u * 512);
+                        if (!DOTS) sc[st][r][u] = __ldg(srow + u * 16);
                     }
                 }
             }
+            if (++itrip == ntrips) itrip = 0, ++ig;
         }
         cp_async_commit();
     };
 
-    // ring primed before the activations are staged
-#pragma unroll
-    for (int st = 0; st < STAGES; ++st) {
-        if (st == 0) issue(std::integral_constant<int, 0>{}, warp);
-        if (st == 1) issue(std::integral_constant<int, 1 % STAGES>{}, warp + kQ8SWarps);
-        if (st == 2) issue(std::integral_constant<int, 2 % STAGES>{}, warp + 2 * kQ8SWarps);
-        if (st == 3) issue(std::integral_constant<int, 3 % STAGES>{}, warp + 3 * kQ8SWarps);
-    }
+    // ring primed before anything else: weights do not depend on the predecessor kernel
+    issue(std::integral_constant<int, 0>{});
+    issue(std::integral_constant<int, 1>{});
+    if (STAGES > 2) issue(std::integral_constant<int, 2 % STAGES>{});
+    if (STAGES > 3) issue(std::integral_constant<int, 3 % STAGES>{});
 
-    // weights are on their way; dependents may start, and nothing else is touched before the predecessor is done
+    // dependents may start (they only prefetch weights); activations and outputs wait for the predecessor
     pdl_launch_dependents();
     pdl_wait();
 
@@ -343,23 +346,26 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int 
     }
     __syncthreads();
 
-    auto consume = [&](auto stage_c, int item) {
+    // ---- consume side ----------------------------------------------------------------
+    float acc[R][B];
+    int cg = g_begin, ctrip = 0;
+    auto consume = [&](auto stage_c) {
         constexpr int st = decltype(stage_c)::value;
-        const int g = item / ntrips, trip = item - g * ntrips;
-        const int row0 = row_begin + g * R;
-        float acc[R][B];
+        const int row0 = row_begin + cg * R;
+        if (ctrip == 0) {
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+            for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+                for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+        }
+        const int colbase = ctrip * (U * 512) + lane * 16;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int s = trip * U + u;
-            const int col0 = s * 512 + lane * 16;
+            const int col0 = colbase + u * 512;
             const bool valid = col0 < cols;
             const unsigned vmask = __ballot_sync(0xffffffffu, valid);  // lanes come in whole pairs per block
             if (!valid) continue;
-            const int blk = col0 >> 5;
+            const int piece = col0 >> 4;  // 16-column piece index within the row
             uint4 w[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) w[r] = *reinterpret_cast<const uint4 *>(ring + ((st * R + r) * U + u) * 512);
@@ -367,8 +373,8 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int 
                 const uint4 *xq16 = reinterpret_cast<const uint4 *>(smem_raw);
 #pragma unroll
                 for (int b = 0; b < B; ++b) {
-                    const uint4 xv = xq16[(size_t)b * slots + s * 32 + lane];
-                    const float xscale = DOTS ? 1.0f : xs_scales[b * bpr + blk];
+                    const uint4 xv = xq16[b * slots + piece];
+                    const float xscale = DOTS ? 1.0f : xs_scales[b * bpr + (piece >> 1)];
 #pragma unroll
                     for (int r = 0; r < R; ++r) {
                         int isum = dp4a_s8(w[r].x, xv.x, 0);
@@ -377,7 +383,8 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int 
                         isum = dp4a_s8(w[r].w, xv.w, isum);
                         if (DOTS) {
                             const int full = isum + __shfl_xor_sync(vmask, isum, 1);  // a block spans two lanes
-                            if ((lane & 1) == 0 && b == 0 && row0 + r < row_end) a.dots[(size_t)(row0 + r) * bpr + blk] = full;
+                            if ((lane & 1) == 0 && b == 0 && row0 + r < row_end)
+                                a.dots[(size_t)(row0 + r) * bpr + (piece >> 1)] = full;
                         }
                         const float wscale = DOTS ? 1.0f : half_bits_to_float(sc[st][r][u]);
                         acc[r][b] = fmaf((float)isum, wscale * xscale, acc[r][b]);
@@ -385,6 +392,7 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int 
                 }
             } else {
                 const float4 *xs4 = reinterpret_cast<const float4 *>(smem_raw);
+                const int seg = piece >> 5;  // 512-column segment
                 float p[R][B];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -396,7 +404,7 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int 
                     }
 #pragma unroll
                     for (int b = 0; b < B; ++b) {
-                        const float4 xv = xs4[(size_t)b * slots + s * 128 + k * 32 + lane];
+                        const float4 xv = xs4[b * slots + seg * 128 + k * 32 + lane];
 #pragma unroll
                         for (int r = 0; r < R; ++r) {
                             float t = k == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, p[r][b]);
@@ -414,41 +422,43 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a, int 
                 }
             }
         }
-        if (!DOTS) {
+        if (++ctrip == ntrips) {
+            ctrip = 0;
+            if (!DOTS) {
 #pragma unroll
-            for (int r = 0; r < R; ++r)
+                for (int r = 0; r < R; ++r)
 #pragma unroll
-                for (int b = 0; b < B; ++b) {
-                    const float s = warp_sum(acc[r][b]);
-                    if (lane == 0 && row0 + r < row_end) part[((size_t)(g * R + r) * ntrips + trip) * B + b] = s;
-                }
+                    for (int b = 0; b < B; ++b) {
+                        const float s = warp_sum(acc[r][b]);
+                        if (lane == 0 && row0 + r < row_end) a.y[(size_t)b * a.rows + row0 + r] = s;
+                    }
+            }
+            ++cg;
         }
     };
 
-    for (int base = warp; base < nitems; base += STAGES * kQ8SWarps) {
-#pragma unroll
-        for (int st = 0; st < STAGES; ++st) {
-            const int item = base + st * kQ8SWarps;
-            if (item >= nitems) break;  // uniform across the warp
+    while (cg < g_end) {
+        cp_async_wait<STAGES - 1>();
+        consume(std::integral_constant<int, 0>{});
+        issue(std::integral_constant<int, 0>{});
+        if (cg >= g_end) break;
+        cp_async_wait<STAGES - 1>();
+        consume(std::integral_constant<int, 1>{});
+        issue(std::integral_constant<int, 1>{});
+        if (STAGES > 2) {
+            if (cg >= g_end) break;
             cp_async_wait<STAGES - 1>();
-            if (st == 0) { consume(std::integral_constant<int, 0>{}, item); issue(std::integral_constant<int, 0>{}, item + STAGES * kQ8SWarps); }
-            if (st == 1) { consume(std::integral_constant<int, 1 % STAGES>{}, item); issue(std::integral_constant<int, 1 % STAGES>{}, item + STAGES * kQ8SWarps); }
-            if (st == 2) { consume(std::integral_constant<int, 2 % STAGES>{}, item); issue(std::integral_constant<int, 2 % STAGES>{}, item + STAGES * kQ8SWarps); }
-            if (st == 3) { consume(std::integral_constant<int, 3 % STAGES>{}, item); issue(std::integral_constant<int, 3 % STAGES>{}, item + STAGES * kQ8SWarps); }
+            consume(std::integral_constant<int, 2 % STAGES>{});
+            issue(std::integral_constant<int, 2 % STAGES>{});
+        }
+        if (STAGES > 3) {
+            if (cg >= g_end) break;
+            cp_async_wait<STAGES - 1>();
+            consume(std::integral_constant<int, 3 % STAGES>{});
+            issue(std::integral_constant<int, 3 % STAGES>{});
         }
     }
     cp_async_wait<0>();
-
-    if (!DOTS && a.y) {
-        __syncthreads();
-        const int nrows = row_end - row_begin;
-        for (int i = threadIdx.x; i < nrows * B; i += kQ8SThreads) {
-            const int rl = i / B, b = i - rl * B;
-            float s = 0.f;
-            for (int t = 0; t < ntrips; ++t) s += part[((size_t)rl * ntrips + t) * B + b];
-            a.y[(size_t)b * a.rows + row_begin + rl] = s;
-        }
-    }
 }
 
 // ---------------------------------------------------------------------------
@@ -854,22 +864,19 @@ static int balanced_grid(int units, int warps_per_cta, int max_ctas) {
 
 template <int B, int MODE>
 struct Q8SConfig {
-    // rows per item x segments per trip: R*U 16-byte pieces per lane and item
+    // rows per group x segments per trip: R*U 16-byte pieces (4 KB per warp) per ring stage
     static constexpr int R = B <= 2 ? 1 : 2;
-    static constexpr int U = B <= 2 ? 4 : 2;
-    static constexpr int STAGES = 4;
+    static constexpr int U = B <= 2 ? 8 : 4;
+    static constexpr int STAGES = 3;
 };
 
-// dynamic shared memory of the split-layout kernel for a given grid
+// dynamic shared memory of the split-layout kernel
 template <int B, int MODE>
-static size_t q8s_smem_bytes(int rows, int cols, int grid) {
+static size_t q8s_smem_bytes(int cols) {
     using Cfg = Q8SConfig<B, MODE>;
     const bool is_int = MODE != MODE_FLOAT;
     const int nseg = (cols + 511) / 512;
-    const int ntrips = (nseg + Cfg::U - 1) / Cfg::U;
-    const int max_rows = rows / grid + 1;
-    size_t off = (size_t)B * nseg * (is_int ? 512 : 2048) + (is_int ? (size_t)B * (cols / 32) * 4 : 0) +
-                 (size_t)max_rows * ntrips * B * 4;
+    size_t off = (size_t)B * nseg * (is_int ? 512 : 2048) + (is_int ? (size_t)B * (cols / 32) * 4 : 0);
     off = (off + 127) & ~(size_t)127;
     return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * Cfg::U * 512;
 }
@@ -880,23 +887,14 @@ static int launch_q8s(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) 
     constexpr auto kernel = q8s_gemv_kernel<B, Cfg::R, Cfg::U, MODE, DOTS, Cfg::STAGES>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
-    // As many CTAs as stay resident at once (a multiple of the SM count, so that every SM streams the
-    // same number of rows); more waves only when the per-row table of one CTA would grow past 16 KB.
-    const int nseg = (a.cols + 511) / 512;
-    const int ntrips = (nseg + Cfg::U - 1) / Cfg::U;
-    int grid = 0;
-    for (int per_sm = 4; per_sm >= 1 && grid == 0; --per_sm) {
-        int g = di->sm_count * per_sm;
-        while ((size_t)(a.rows / g + 1) * ntrips * B * 4 > 16384) g *= 2;
-        const size_t need = q8s_smem_bytes<B, MODE>(a.rows, a.cols, g);
-        if (need + 1024 > (size_t)di->max_smem_optin) continue;
-        if (resident_ctas<kernel>(di, kQ8SThreads, need) >= per_sm) grid = g;
-    }
-    if (grid == 0) return TB200_ERR_INVALID_ARG;
+    const size_t smem = q8s_smem_bytes<B, MODE>(a.cols);
+    if (smem + 1024 > (size_t)di->max_smem_optin) return TB200_ERR_INVALID_ARG;
+    // one resident wave: a multiple of the SM count, so that every SM streams the same number of rows
+    int grid = di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem);
     const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
-    if (grid > groups) grid = groups;
-    const size_t smem = q8s_smem_bytes<B, MODE>(a.rows, a.cols, grid);
-    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a, a.rows / grid + 1);
+    const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;  // at least one group per warp
+    if (grid > want) grid = want;
+    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a);
 }
 
 template <int FMT, int B, int MODE>
@@ -965,10 +963,17 @@ static bool fast_batch_fits(int cols, int batch, Path path, const DeviceInfo *di
             default: return false;
         }
     }
-    // split layout, one CTA per SM as the worst case for the per-row table (rows are not known here: bound it)
-    const int nseg = (cols + 511) / 512;
-    const size_t x_bytes = (size_t)batch * nseg * (MODE != MODE_FLOAT ? 512 : 2048) + (size_t)batch * (cols / 32) * 4;
-    return batch >= 1 && batch <= 8 && x_bytes + (64 + 16 + 1) * 1024 <= limit;  // + rings + per-row table
+    switch (batch) {
+        case 1: return q8s_smem_bytes<1, MODE>(cols) <= limit;
+        case 2: return q8s_smem_bytes<2, MODE>(cols) <= limit;
+        case 3: return q8s_smem_bytes<3, MODE>(cols) <= limit;
+        case 4: return q8s_smem_bytes<4, MODE>(cols) <= limit;
+        case 5: return q8s_smem_bytes<5, MODE>(cols) <= limit;
+        case 6: return q8s_smem_bytes<6, MODE>(cols) <= limit;
+        case 7: return q8s_smem_bytes<7, MODE>(cols) <= limit;
+        case 8: return q8s_smem_bytes<8, MODE>(cols) <= limit;
+        default: return false;
+    }
 }
 
 // Fewest passes over the weights such that each pass's share of the batch fits;
