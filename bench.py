@@ -34,6 +34,9 @@ sys.path.insert(0, ROOT)
 
 ROWS, COLS, BATCH = 14336, 4096, 1
 LAYERS = 8  # distinct weight matrices per step: 8 * 62.4 MB = 499 MB footprint
+# dram__bytes_read.sum + dram__bytes_write.sum of one 14336 x 4096 integer-mode launch, from the ncu capture
+# summarised in profiles/q8s_gemv_int_14336x4096.md (62.45 MB read + ~0.15 MB written)
+NCU_TRAFFIC_BYTES_PER_GEMV = 62_600_000
 METRIC = "q8_0_gemv_hbm_throughput"
 UNIT = "GB/s"
 
@@ -413,7 +416,7 @@ def run_gpu_arm(args):
                 "api": "TaskGraph.libraryTask(B200.q8Gemv) + TornadoExecutionPlan.withCUDAGraph().execute()" if world == 1 else "ShardedQ8Gemv.run"},
         "gpu_launches": gpu_launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_source": f"{peak_kind} copy bandwidth", "kernel": "q8s_gemv_kernel",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_GEMV * lrows // ROWS if world == 1 else None, "peak_source": f"{peak_kind} copy bandwidth", "kernel": "q8s_gemv_kernel",
                      "bytes_per_launch": launch_bytes, "us_per_launch": kernel_s * 1e6},
         "clocks": clocks.summary(),
     }
