@@ -142,6 +142,28 @@ int tb200_q8b_gemv_i8(int rows, int cols, int batch, const uint8_t *blocks, cons
 int tb200_q4b_gemv_i8(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
                       void *workspace, size_t workspace_bytes, tb200_stream_t stream);
 
+/* Integer-path Q8_0 mat-vec (split layout) for callers that cannot hand over
+ * scratch memory.  It has no counterpart in the reference.
+ *
+ * Same arithmetic and results as tb200_q8_gemv_i8, but the quantised
+ * activations are kept in a fixed TB200_STATIC_SCRATCH_BYTES array inside the
+ * library image (present on every GPU that loads the library, until the process
+ * exits) instead of a workspace argument.  Meant for code that may not allocate
+ * device memory where it calls from: a provider whose only hook is the launch
+ * itself (TornadoVM owns the plan's device memory and forbids allocation in
+ * dispatch), or a caller already inside a stream capture.
+ *   - Shapes whose tb200_qx_workspace_bytes(cols, batch) exceeds
+ *     TB200_STATIC_SCRATCH_BYTES are rejected with TB200_ERR_WORKSPACE.
+ *   - The first call on a device looks up the array's device address; make that
+ *     first call before any stream capture begins.  No call allocates or frees.
+ *   - All calls on a device share the one array and each call overwrites every
+ *     byte it later reads, so nothing needs clearing between calls; two calls
+ *     whose kernels can run at the same time on one GPU (different streams)
+ *     race on it and must be ordered by the caller. */
+#define TB200_STATIC_SCRATCH_BYTES 147456 /* enough for cols * batch <= 131072, e.g. 16384 x 8 */
+int tb200_q8_gemv_i8_static(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x,
+                            float *y, tb200_stream_t stream);
+
 /* Test entry points: the raw int32 block dots, dots[r][blk], for one
  * already-quantised activation vector xq[cols].  Device form of the unit test
  * QuantizationTests.testDP4A (tornado-unittests/.../quantization/

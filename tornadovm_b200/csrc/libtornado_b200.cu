@@ -6,3 +6,4 @@
 #include "gemv_quant.cu"
 #include "sgemm.cu"
 #include "hgemm.cu"
+#include "gemv_static.cu"
