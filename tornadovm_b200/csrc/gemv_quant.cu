@@ -13,14 +13,13 @@
 //          (dp4a), one fp32 multiply-add per block for the two scales
 //
 // Kernel families:
-//   qring_gemv_kernel every format when cols % 256 == 0 and the weights are 16-byte
-//                     aligned: each warp runs its own bulk-async-copy (TMA)
-//                     ring that lands row chunks of 64 blocks in shared memory,
-//                     so the bytes in flight are bounded by shared memory and
-//                     not by registers; the integer mode can quantise the
-//                     activations in its own prologue.
-//   q8s_gemv_kernel   split layout with other column counts; each lane streams
-//                     16 quants per row with one 128-bit load that bypasses L1.
+//   q8s_gemv_kernel   split layout, 16-byte aligned weights: per-lane cp.async rings.
+//   qblk_gemv_kernel  block layouts when cols % 256 == 0 and the weights are
+//                     16-byte aligned: per-warp cp.async rings, block pairs
+//                     decoded from shared memory.
+//                     Both keep the bytes in flight in shared memory, not in
+//                     registers, and the integer mode can quantise the
+//                     activations in the kernel's own prologue.
 //   q*_generic_kernel any alignment and any cols % 32 == 0; byte loads.
 //
 // Activations are staged once per CTA in shared memory in a lane-interleaved
@@ -462,33 +461,28 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
 }
 
 // ---------------------------------------------------------------------------
-// Family 2: every format through a per-warp bulk-async-copy (TMA) ring.
+// Family 2: block layouts (Q8B 34-byte, Q4B 18-byte blocks) through per-warp
+// cp.async rings.
 //
-// A CTA owns a contiguous range of rows; its warps take groups of R rows from a
-// shared-memory counter.  Each warp keeps STAGES row chunks (64 blocks = 2048
-// columns of R rows) in flight in its own ring: lane 0 arms an mbarrier with the
-// byte count and issues one bulk copy per row (two for the split layout: quants
-// and scales); all lanes wait on the barrier, pull their part of the chunk into
-// registers, and the stage is refilled at once.  Bytes in flight are bounded by
-// shared memory, not by registers.
-//
-// Chunk record in shared memory, per row:
-//   Q8S  [2048 quant bytes][64 fp16 scales]            2176 bytes
-//   Q8B  64 x 34-byte blocks                           2176 bytes
-//   Q4B  64 x 18-byte blocks                           1152 bytes
-// Lane ownership inside a chunk:
-//   Q8S  the four 16-byte pieces j*32 + lane (half a block each)
-//   Q8B / Q4B  the block pair `lane` (a 4-byte aligned 68 / 36 byte record)
+// A CTA owns a contiguous range of rows and each of its warps a contiguous run
+// of row groups (R rows).  A ring stage holds one chunk of 128 blocks (4096
+// columns) of the R rows: the lanes copy it as consecutive 16-byte pieces
+// (coalesced cp.async, no registers held while the bytes travel), STAGES chunks
+// are in flight per warp.  Blocks are 2-byte aligned records, so after the
+// copies of a stage have landed (cp.async.wait_group + __syncwarp) a lane
+// decodes whole block *pairs* -- 4-byte aligned records of 68 / 36 bytes read
+// with conflict-free 32-bit shared loads -- pairs `lane` and `lane + 32`.
 // ---------------------------------------------------------------------------
-constexpr int kChunkBlocks = 64;  // blocks per row chunk = 2048 columns
+constexpr int kChunkBlocks = 128;  // blocks per row chunk = 4096 columns
 
 template <int FMT>
 struct RingTraits {
-    static constexpr int BB = FMT == FMT_Q4B ? 18 : 34;         // bytes per block (split: 32 + 2)
-    static constexpr int PW = BB / 2;                           // 32-bit words per block pair
-    static constexpr int CB = kChunkBlocks * BB;                // bytes per full row chunk
-    static constexpr int QW = FMT == FMT_Q4B ? 4 : 8;           // quant words per block
-    static constexpr int CPL = FMT == FMT_Q8S ? 16 : 64;        // contiguous columns per lane
+    static constexpr int BB = FMT == FMT_Q4B ? 18 : 34;   // bytes per block
+    static constexpr int PW = BB / 2;                     // 32-bit words per block pair
+    static constexpr int CB = kChunkBlocks * BB;          // bytes per full row chunk (4352 / 2304)
+    static constexpr int QW = FMT == FMT_Q4B ? 4 : 8;     // quant words per block
+    static constexpr int CPL = 64;                        // contiguous columns per lane and pair
+    static constexpr int PIECES = (CB / 16 + 31) / 32;    // 16-byte pieces per lane and row chunk (9 / 5)
 };
 
 // Pull one block pair (PW words, 4-byte aligned) out of shared memory and
@@ -510,301 +504,191 @@ __device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], 
     for (int i = 0; i < QW; ++i) qb[i] = wds[QW + 1 + i];
 }
 
-template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) qring_gemv_kernel(QGemvArgs a) {
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES>
+__global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
     using T = RingTraits<FMT>;
     constexpr bool INT = MODE != MODE_FLOAT;
+    static_assert(STAGES >= 2 && STAGES <= 4, "ring depth");
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bars[WARPS][STAGES];
-    __shared__ int group_of_stage[WARPS][STAGES];
-    __shared__ int next_group;
-
     const int cols = a.cols;
     const int bpr = cols / 32;
     const int nch = (bpr + kChunkBlocks - 1) / kChunkBlocks;
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t row_bytes = (size_t)bpr * T::BB;
 
-    // rows of this CTA and its groups of R rows
     const int row_begin = (int)((long long)a.rows * blockIdx.x / gridDim.x);
     const int row_end = (int)((long long)a.rows * (blockIdx.x + 1) / gridDim.x);
     const int ngroups = (row_end - row_begin + R - 1) / R;
+    const int g_begin = ngroups * warp / kQ8SWarps, g_end = ngroups * (warp + 1) / kQ8SWarps;
 
-    // ---- shared memory carve-up -----------------------------------------------
-    // [ ring: warps x stages x R x CB ][ activations ][ activation scales ][ activation block sums ]
-    unsigned char *wbuf = smem_raw + (size_t)warp * STAGES * R * T::CB;
-    unsigned char *xbase = smem_raw + (size_t)WARPS * STAGES * R * T::CB;
-    const int slots = (cols + 32 * T::CPL - 1) / (32 * T::CPL) * (32 * T::CPL) / (INT ? 16 : 4);  // 16-byte slots per vector
-    float *xs_scales = reinterpret_cast<float *>(xbase + (size_t)B * slots * 16);
+    // ---- shared memory: [ activations ][ scales ][ block sums ][ rings: warps x stages x R x CB ] ----
+    const int slots = (cols + 2047) / 2048 * 2048 / (INT ? 16 : 4);  // 16-byte slots per activation vector
+    float *xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
     int *xsum = reinterpret_cast<int *>(xs_scales + B * bpr);
+    const uint32_t ring_off = (uint32_t)(((size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 8 + 127) & ~(size_t)127);
+    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * T::CB;
+    const uint32_t ring_s = smem_u32(ring);
 
-    if (threadIdx.x == 0) next_group = 0;
-    if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[warp][s], 1);
-        mbar_fence_init();
-    }
-    __syncthreads();
-
-    // ---- issue side of the ring (all lanes run it in lock step) -------------------
-    int issued = 0, issue_group = -1, issue_chunk = 0;
-    bool more = true;
-    auto issue = [&]() {
-        const int st = issued % STAGES;
-        ++issued;
-        if (more && issue_chunk == 0) {
-            int g = 0;
-            if (lane == 0) g = atomicAdd(&next_group, 1);
-            g = __shfl_sync(0xffffffffu, g, 0);
-            if (g >= ngroups) more = false;
-            issue_group = g;
-        }
-        if (!more) {
-            if (lane == 0) group_of_stage[warp][st] = -1;
-            return;
-        }
-        const int c = issue_chunk;
-        issue_chunk = (c + 1 == nch) ? 0 : c + 1;
-        if (lane == 0) {
-            group_of_stage[warp][st] = issue_group;
-            const int nblk = min(kChunkBlocks, bpr - c * kChunkBlocks);
-            // the block-dot test entry of the split layout passes no scales: copy quants only
-            const bool with_scales = FMT != FMT_Q8S || a.scales != nullptr;
-            const uint32_t bytes = (uint32_t)nblk * (with_scales ? T::BB : 32);
-            mbar_expect_tx(&bars[warp][st], bytes * R);
+    // ---- issue side ------------------------------------------------------------------
+    int ig = g_begin, ich = 0;
+    auto issue = [&](int st) {
+        if (ig < g_end) {
+            const int nblk = min(kChunkBlocks, bpr - ich * kChunkBlocks);
+            const int npieces = nblk * T::BB / 16;  // nblk is a multiple of 8: whole 16-byte pieces
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const size_t row = (size_t)min(row_begin + issue_group * R + r, row_end - 1);
-                unsigned char *dst = wbuf + ((size_t)st * R + r) * T::CB;
-                if (FMT == FMT_Q8S) {
-                    bulk_g2s_stream(dst, a.w + row * cols + (size_t)c * 2048, (uint32_t)nblk * 32, &bars[warp][st]);
-                    if (with_scales)
-                        bulk_g2s_stream(dst + 2048, a.scales + row * bpr + (size_t)c * kChunkBlocks, (uint32_t)nblk * 2,
-                                        &bars[warp][st]);
-                } else {
-                    bulk_g2s_stream(dst, a.w + (row * bpr + (size_t)c * kChunkBlocks) * T::BB, bytes, &bars[warp][st]);
-                }
+                const size_t row = (size_t)min(row_begin + ig * R + r, row_end - 1);
+                const unsigned char *src = a.w + row * row_bytes + (size_t)ich * T::CB + lane * 16;
+                const uint32_t dst = ring_s + (st * R + r) * T::CB + lane * 16;
+#pragma unroll
+                for (int i = 0; i < T::PIECES; ++i)
+                    if (lane + 32 * i < npieces) cp_async_16(dst + i * 512, src + i * 512);
             }
+            if (++ich == nch) ich = 0, ++ig;
         }
+        cp_async_commit();
     };
-#pragma unroll 1
-    for (int s = 0; s < STAGES; ++s) issue();  // weights start streaming before the activations are staged
+#pragma unroll
+    for (int st = 0; st < STAGES; ++st) issue(st);
 
-    // ---- activations ------------------------------------------------------------
     pdl_launch_dependents();
-    pdl_wait();  // weights were prefetched above; activations and outputs wait for the predecessor
+    pdl_wait();  // weights were requested above; activations and outputs wait for the predecessor
+
     if (MODE == MODE_FLOAT) {
-        stage_x_float<T::CPL>(reinterpret_cast<float4 *>(xbase), a.x, cols, B, slots);
+        stage_x_float<T::CPL>(reinterpret_cast<float4 *>(smem_raw), a.x, cols, B, slots);
     } else if (MODE == MODE_INT_FUSED) {
-        stage_x_blocks<T::CPL, true, FMT == FMT_Q4B>(xbase, xs_scales, xsum, a, B, slots, true);
+        stage_x_blocks<T::CPL, true, FMT == FMT_Q4B>(smem_raw, xs_scales, xsum, a, B, slots, true);
     } else {
-        stage_x_blocks<T::CPL, false, FMT == FMT_Q4B>(xbase, xs_scales, xsum, a, B, slots, !DOTS);
+        stage_x_blocks<T::CPL, false, FMT == FMT_Q4B>(smem_raw, xs_scales, xsum, a, B, slots, !DOTS);
     }
     __syncthreads();
 
-    // ---- consume ------------------------------------------------------------------
+    // ---- consume side ------------------------------------------------------------------
     float acc[R][B];
-    int chunk = 0;
-#pragma unroll 1
-    for (int t = 0;; ++t) {
-        const int st = t % STAGES;
-        __syncwarp();
-        const int g = group_of_stage[warp][st];
-        if (g < 0) break;
-        const int c = chunk;
-        chunk = (c + 1 == nch) ? 0 : c + 1;
+    int cg = g_begin, cch = 0, st = 0;
+    while (cg < g_end) {
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();  // every lane's pieces of this stage have landed
+        const int c = cch;
         const int nblk = min(kChunkBlocks, bpr - c * kChunkBlocks);
+        const int row0 = row_begin + cg * R;
         if (c == 0) {
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
                 for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
         }
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars[warp][st], (uint32_t)((t / STAGES) & 1)))) break;
-        const int row0 = row_begin + g * R;
-
-        if constexpr (FMT == FMT_Q8S) {
-            // ---------------- split layout: four 16-byte pieces per lane and row
-            uint4 w[R][4];
-            float sc[R][4];
-            bool valid[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int piece = j * 32 + lane;
-                valid[j] = piece < 2 * nblk;
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const unsigned char *rec = wbuf + ((size_t)st * R + r) * T::CB;
-                    w[r][j] = *reinterpret_cast<const uint4 *>(rec + piece * 16);
-                    sc[r][j] = DOTS ? 1.0f
-                                    : half_bits_to_float(*reinterpret_cast<const uint16_t *>(rec + 2048 + (piece >> 1) * 2));
-                }
-            }
-            __syncwarp();
-            issue();  // the stage is free again
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const unsigned vmask = __ballot_sync(0xffffffffu, valid[j]);
-                if (!valid[j]) continue;
-                const int piece = j * 32 + lane;
-                const int blk = c * kChunkBlocks + (piece >> 1);
-                if (INT) {
-                    const uint4 *xq16 = reinterpret_cast<const uint4 *>(xbase);
-#pragma unroll
-                    for (int b = 0; b < B; ++b) {
-                        const uint4 xv = xq16[(size_t)b * slots + c * 128 + piece];
-                        const float xscale = DOTS ? 1.0f : xs_scales[b * bpr + blk];
-#pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            int isum = dp4a_s8(w[r][j].x, xv.x, 0);
-                            isum = dp4a_s8(w[r][j].y, xv.y, isum);
-                            isum = dp4a_s8(w[r][j].z, xv.z, isum);
-                            isum = dp4a_s8(w[r][j].w, xv.w, isum);
-                            if (DOTS) {
-                                const int full = isum + __shfl_xor_sync(vmask, isum, 1);  // a block spans two lanes
-                                if ((lane & 1) == 0 && b == 0 && row0 + r < row_end) a.dots[(size_t)(row0 + r) * bpr + blk] = full;
-                            }
-                            acc[r][b] = fmaf((float)isum, sc[r][j] * xscale, acc[r][b]);
-                        }
-                    }
-                } else {
-                    const float4 *xs4 = reinterpret_cast<const float4 *>(xbase);
-                    float part[R][B];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        float wf[R][4];
-#pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            const uint32_t word = k == 0 ? w[r][j].x : k == 1 ? w[r][j].y : k == 2 ? w[r][j].z : w[r][j].w;
-                            s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
-                        }
-#pragma unroll
-                        for (int b = 0; b < B; ++b) {
-                            // float4 slot of columns 16*piece + 4k: segment (c*4 + j), piece-in-lane k
-                            const float4 xv = xs4[(size_t)b * slots + (c * 4 + j) * 128 + k * 32 + lane];
-#pragma unroll
-                            for (int r = 0; r < R; ++r) {
-                                float p = k == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, part[r][b]);
-                                p = fmaf(wf[r][1], xv.y, p);
-                                p = fmaf(wf[r][2], xv.z, p);
-                                part[r][b] = fmaf(wf[r][3], xv.w, p);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int r = 0; r < R; ++r)
-#pragma unroll
-                        for (int b = 0; b < B; ++b) acc[r][b] = fmaf(sc[r][j], part[r][b], acc[r][b]);
-                }
-            }
-        } else {
-            // ---------------- block layouts: one block pair per lane and row
-            const bool active = 2 * lane < nblk;
+        for (int j = 0; j < 2; ++j) {
+            const int pair = lane + 32 * j;
+            if (2 * pair >= nblk) continue;
+            const int blk0 = c * kChunkBlocks + 2 * pair;
+            const int seg = c * 2 + j;  // 2048-column activation segment of this pair
             float scale[R][2];
             uint32_t qa[R][T::QW], qb[R][T::QW];
-            if (active) {
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-                    load_pair<FMT>(reinterpret_cast<const uint32_t *>(wbuf + ((size_t)st * R + r) * T::CB) + lane * T::PW,
-                                   scale[r], qa[r], qb[r]);
-            }
-            __syncwarp();
-            issue();  // the stage is free again
-            if (active) {
-                const int blk0 = c * kChunkBlocks + 2 * lane;
-                if (INT) {
-                    const uint4 *xq16 = reinterpret_cast<const uint4 *>(xbase);
-#pragma unroll
-                    for (int b = 0; b < B; ++b) {
-                        uint32_t xw[16];  // the lane's 64 activation bytes: pieces k = 0..3
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint4 v = xq16[(size_t)b * slots + c * 128 + k * 32 + lane];
-                            xw[4 * k] = v.x, xw[4 * k + 1] = v.y, xw[4 * k + 2] = v.z, xw[4 * k + 3] = v.w;
-                        }
-                        const float2 xsc = DOTS ? make_float2(1.f, 1.f) : *reinterpret_cast<const float2 *>(xs_scales + b * bpr + blk0);
-                        int2 xsm = make_int2(0, 0);
-                        if (FMT == FMT_Q4B) xsm = *reinterpret_cast<const int2 *>(xsum + b * bpr + blk0);
-#pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            int d0 = 0, d1 = 0;
-                            if (FMT == FMT_Q8B) {
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    d0 = dp4a_s8(qa[r][i], xw[i], d0);
-                                    d1 = dp4a_s8(qb[r][i], xw[8 + i], d1);
-                                }
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    d0 = dp4a_s8(qa[r][i] & 0x0F0F0F0Fu, xw[i], d0);
-                                    d0 = dp4a_s8((qa[r][i] >> 4) & 0x0F0F0F0Fu, xw[4 + i], d0);
-                                    d1 = dp4a_s8(qb[r][i] & 0x0F0F0F0Fu, xw[8 + i], d1);
-                                    d1 = dp4a_s8((qb[r][i] >> 4) & 0x0F0F0F0Fu, xw[12 + i], d1);
-                                }
-                                d0 -= 8 * xsm.x;
-                                d1 -= 8 * xsm.y;
-                            }
-                            if (DOTS && b == 0 && row0 + r < row_end) {
-                                int32_t *dp = a.dots + (size_t)(row0 + r) * bpr + blk0;
-                                dp[0] = d0;
-                                dp[1] = d1;
-                            }
-                            acc[r][b] = fmaf((float)d0, scale[r][0] * xsc.x, acc[r][b]);
-                            acc[r][b] = fmaf((float)d1, scale[r][1] * xsc.y, acc[r][b]);
-                        }
-                    }
-                } else {
-                    const float4 *xs4 = reinterpret_cast<const float4 *>(xbase);
-                    float part[R][B];
-                    // k indexes the lane's sixteen float4 activation pieces: 0..7 block A, 8..15 block B
-#pragma unroll
-                    for (int k = 0; k < 16; ++k) {
-                        float wf[R][4];
-#pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            if (FMT == FMT_Q8B) {
-                                const uint32_t word = k < 8 ? qa[r][k & 7] : qb[r][k & 7];
-                                s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
-                            } else {
-                                // elements 4j..4j+3 are the low nibbles of word j, 16+4j.. the high nibbles
-                                const int kk = k & 7;
-                                const uint32_t word = k < 8 ? qa[r][kk & 3] : qb[r][kk & 3];
-                                const uint32_t nib = (kk < 4 ? word : (word >> 4)) & 0x0F0F0F0Fu;
-                                u8x4_to_f32(nib, 8388616.0f, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
-                            }
-                        }
-#pragma unroll
-                        for (int b = 0; b < B; ++b) {
-                            const float4 xv = xs4[(size_t)b * slots + c * 512 + k * 32 + lane];
-#pragma unroll
-                            for (int r = 0; r < R; ++r) {
-                                float p = (k & 7) == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, part[r][b]);
-                                p = fmaf(wf[r][1], xv.y, p);
-                                p = fmaf(wf[r][2], xv.z, p);
-                                part[r][b] = fmaf(wf[r][3], xv.w, p);
-                            }
-                        }
-                        if ((k & 7) == 7) {
-#pragma unroll
-                            for (int r = 0; r < R; ++r)
-#pragma unroll
-                                for (int b = 0; b < B; ++b) acc[r][b] = fmaf(scale[r][k >> 3], part[r][b], acc[r][b]);
-                        }
-                    }
-                }
-            }
-        }
-        if (c == nch - 1 && a.y) {
 #pragma unroll
             for (int r = 0; r < R; ++r)
+                load_pair<FMT>(reinterpret_cast<const uint32_t *>(ring + (st * R + r) * T::CB) + pair * T::PW, scale[r], qa[r], qb[r]);
+            if (INT) {
+                const uint4 *xq16 = reinterpret_cast<const uint4 *>(smem_raw);
 #pragma unroll
                 for (int b = 0; b < B; ++b) {
-                    const float s = warp_sum(acc[r][b]);
-                    if (lane == 0 && row0 + r < row_end) a.y[(size_t)b * a.rows + row0 + r] = s;
+                    uint32_t xw[16];  // the pair's 64 activation bytes: pieces k = 0..3
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint4 v = xq16[b * slots + seg * 128 + k * 32 + lane];
+                        xw[4 * k] = v.x, xw[4 * k + 1] = v.y, xw[4 * k + 2] = v.z, xw[4 * k + 3] = v.w;
+                    }
+                    const float2 xsc = DOTS ? make_float2(1.f, 1.f) : *reinterpret_cast<const float2 *>(xs_scales + b * bpr + blk0);
+                    int2 xsm = make_int2(0, 0);
+                    if (FMT == FMT_Q4B) xsm = *reinterpret_cast<const int2 *>(xsum + b * bpr + blk0);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        int d0 = 0, d1 = 0;
+                        if (FMT == FMT_Q8B) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                d0 = dp4a_s8(qa[r][i], xw[i], d0);
+                                d1 = dp4a_s8(qb[r][i], xw[8 + i], d1);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                d0 = dp4a_s8(qa[r][i] & 0x0F0F0F0Fu, xw[i], d0);
+                                d0 = dp4a_s8((qa[r][i] >> 4) & 0x0F0F0F0Fu, xw[4 + i], d0);
+                                d1 = dp4a_s8(qb[r][i] & 0x0F0F0F0Fu, xw[8 + i], d1);
+                                d1 = dp4a_s8((qb[r][i] >> 4) & 0x0F0F0F0Fu, xw[12 + i], d1);
+                            }
+                            d0 -= 8 * xsm.x;
+                            d1 -= 8 * xsm.y;
+                        }
+                        if (DOTS && b == 0 && row0 + r < row_end) {
+                            int32_t *dp = a.dots + (size_t)(row0 + r) * bpr + blk0;
+                            dp[0] = d0;
+                            dp[1] = d1;
+                        }
+                        acc[r][b] = fmaf((float)d0, scale[r][0] * xsc.x, acc[r][b]);
+                        acc[r][b] = fmaf((float)d1, scale[r][1] * xsc.y, acc[r][b]);
+                    }
                 }
+            } else {
+                const float4 *xs4 = reinterpret_cast<const float4 *>(smem_raw);
+                float part[R][B];
+                // k indexes the pair's sixteen float4 activation pieces: 0..7 block A, 8..15 block B
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    float wf[R][4];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        if (FMT == FMT_Q8B) {
+                            const uint32_t word = k < 8 ? qa[r][k & 7] : qb[r][k & 7];
+                            s8x4_to_f32(word, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
+                        } else {
+                            // elements 4i..4i+3 are the low nibbles of word i, 16+4i.. the high nibbles
+                            const int kk = k & 7;
+                            const uint32_t word = k < 8 ? qa[r][kk & 3] : qb[r][kk & 3];
+                            const uint32_t nib = (kk < 4 ? word : (word >> 4)) & 0x0F0F0F0Fu;
+                            u8x4_to_f32(nib, 8388616.0f, wf[r][0], wf[r][1], wf[r][2], wf[r][3]);
+                        }
+                    }
+#pragma unroll
+                    for (int b = 0; b < B; ++b) {
+                        const float4 xv = xs4[b * slots + seg * 512 + k * 32 + lane];
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            float p = (k & 7) == 0 ? wf[r][0] * xv.x : fmaf(wf[r][0], xv.x, part[r][b]);
+                            p = fmaf(wf[r][1], xv.y, p);
+                            p = fmaf(wf[r][2], xv.z, p);
+                            part[r][b] = fmaf(wf[r][3], xv.w, p);
+                        }
+                    }
+                    if ((k & 7) == 7) {
+#pragma unroll
+                        for (int r = 0; r < R; ++r)
+#pragma unroll
+                            for (int b = 0; b < B; ++b) acc[r][b] = fmaf(scale[r][k >> 3], part[r][b], acc[r][b]);
+                    }
+                }
+            }
+        }
+        __syncwarp();  // every lane is done with this stage before it is refilled
+        issue(st);
+        st = st + 1 == STAGES ? 0 : st + 1;
+        if (++cch == nch) {
+            cch = 0;
+            if (a.y) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int b = 0; b < B; ++b) {
+                        const float s = warp_sum(acc[r][b]);
+                        if (lane == 0 && row0 + r < row_end) a.y[(size_t)b * a.rows + row0 + r] = s;
+                    }
+            }
+            ++cg;
         }
     }
+    cp_async_wait<0>();
 }
 
 // ---------------------------------------------------------------------------
@@ -900,40 +784,35 @@ static int launch_q8s(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) 
 template <int FMT, int B, int MODE>
 struct RingConfig {
     static constexpr bool INT = MODE != MODE_FLOAT;
-    // rows per group: more rows share each activation read; the integer path reads
-    // one activation byte per weight byte and needs that only for larger batches
-    static constexpr int R = INT ? (B <= 2 ? 1 : (B <= 4 ? 2 : 4)) : (FMT == FMT_Q4B ? (B <= 4 ? 4 : 2) : 2);
-    static constexpr int WARPS = 8;
-    // about 17 KB of ring per warp whatever the group size
-    static constexpr int STAGES = (FMT == FMT_Q4B ? 16 : 8) / R;
+    // rows per group: more rows share each activation read from shared memory
+    static constexpr int R = INT ? (B <= 2 ? 1 : 2) : (B <= 2 ? 2 : 1);
+    // about 13 KB (Q8_0) / 14 KB (Q4_0) of ring per warp
+    static constexpr int STAGES = FMT == FMT_Q4B ? (R == 1 ? 4 : 3) : (R == 1 ? 3 : 2);
 };
 
 template <int FMT, int B, int MODE>
 static size_t ring_smem_bytes(int cols) {
     using T = RingTraits<FMT>;
     using Cfg = RingConfig<FMT, B, MODE>;
-    const int seg = 32 * T::CPL;
-    const size_t slots = (size_t)((cols + seg - 1) / seg) * seg / (Cfg::INT ? 16 : 4);
-    size_t smem = (size_t)Cfg::WARPS * Cfg::STAGES * Cfg::R * T::CB + (size_t)B * slots * 16;
-    if (Cfg::INT) smem += (size_t)B * (cols / 32) * 8;  // scales + block sums
-    return smem;
+    const size_t slots = (size_t)((cols + 2047) / 2048) * 2048 / (Cfg::INT ? 16 : 4);
+    size_t off = (size_t)B * slots * 16 + (Cfg::INT ? (size_t)B * (cols / 32) * 8 : 0);  // + scales + block sums
+    off = (off + 127) & ~(size_t)127;
+    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * T::CB;
 }
 
 template <int FMT, int B, int MODE, bool DOTS>
 static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     using Cfg = RingConfig<FMT, B, MODE>;
     const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols);
-    constexpr auto kernel = qring_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES, Cfg::WARPS>;
+    constexpr auto kernel = qblk_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
-    const int ctas = resident_ctas<kernel>(di, Cfg::WARPS * 32, smem);
-    // every CTA should have at least a couple of groups per warp; small matrices use fewer CTAs
-    int grid = di->sm_count * ctas;
+    // one resident wave, a multiple of the SM count; small matrices use fewer CTAs (one group per warp at least)
+    int grid = di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem);
     const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
-    const int need = (groups + Cfg::WARPS - 1) / Cfg::WARPS;
-    if (grid > need) grid = need;
-    if (grid > a.rows) grid = a.rows;
-    return launch_kernel(kernel, dim3(grid), dim3(Cfg::WARPS * 32), smem, s, g_overlap_launches != 0, a);
+    const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;
+    if (grid > want) grid = want;
+    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a);
 }
 
 template <int FMT, bool INT>
