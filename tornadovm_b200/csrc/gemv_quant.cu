@@ -276,7 +276,9 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-template <int B, int R, int U, int MODE, bool DOTS, int STAGES>
+// SA: the scales of a trip are 16-byte aligned runs and travel through the ring as well (cols % 256 == 0,
+// 16-byte aligned scale array); otherwise they are loaded into registers when the trip is requested.
+template <int B, int R, int U, int MODE, bool DOTS, int STAGES, bool SA>
 __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
     constexpr bool INT = MODE != MODE_FLOAT;
     static_assert(STAGES >= 2 && STAGES <= 4, "ring depth");
@@ -298,11 +300,12 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
     const int slots = nseg * (INT ? 32 : 128);  // 16-byte slots per activation vector
     float *xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
     const uint32_t ring_off = (uint32_t)(((size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 4 + 127) & ~(size_t)127);
-    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * U * 512 + lane * 16;
+    constexpr int REC = U * 512 + (SA ? U * 32 : 0);  // bytes per row and stage: quants, then the trip's scales
+    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * REC + lane * 16;
     const uint32_t ring_s = smem_u32(ring);
 
     // ---- issue side ----------------------------------------------------------------
-    uint16_t sc[STAGES][R][U];
+    uint16_t sc[SA ? 1 : STAGES][R][U];
     int ig = g_begin, itrip = 0;  // next (group, trip) to request
     auto issue = [&](auto stage_c) {
         constexpr int st = decltype(stage_c)::value;
@@ -316,9 +319,15 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     if (colbase + u * 512 < cols) {
-                        cp_async_16(ring_s + ((st * R + r) * U + u) * 512, qrow + u * 512);
-                        if (!DOTS) sc[st][r][u] = __ldg(srow + u * 16);
+                        cp_async_16(ring_s + (st * R + r) * REC + u * 512, qrow + u * 512);
+                        if (!DOTS && !SA) sc[SA ? 0 : st][r][u] = __ldg(srow + u * 16);
                     }
+                }
+                if (SA && !DOTS) {
+                    // the trip's U*16 scales: 16-byte pieces of eight, copied by the first lanes
+                    const int blk = itrip * (U * 16) + lane * 8;
+                    if (lane < U * 2 && blk < bpr)
+                        cp_async_16(ring_s + (st * R + r) * REC + U * 512, a.scales + row * bpr + blk);
                 }
             }
             if (++itrip == ntrips) itrip = 0, ++ig;
@@ -367,7 +376,15 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
             const int piece = col0 >> 4;  // 16-column piece index within the row
             uint4 w[R];
 #pragma unroll
-            for (int r = 0; r < R; ++r) w[r] = *reinterpret_cast<const uint4 *>(ring + ((st * R + r) * U + u) * 512);
+            for (int r = 0; r < R; ++r) w[r] = *reinterpret_cast<const uint4 *>(ring + (st * R + r) * REC + u * 512);
+            float wsc[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                if (DOTS) wsc[r] = 1.0f;
+                else if (SA) wsc[r] = half_bits_to_float(*reinterpret_cast<const uint16_t *>(
+                    ring - lane * 16 + (st * R + r) * REC + U * 512 + (u * 16 + (lane >> 1)) * 2));
+                else wsc[r] = half_bits_to_float(sc[SA ? 0 : st][r][u]);
+            }
             if (INT) {
                 const uint4 *xq16 = reinterpret_cast<const uint4 *>(smem_raw);
 #pragma unroll
@@ -385,8 +402,7 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
                             if ((lane & 1) == 0 && b == 0 && row0 + r < row_end)
                                 a.dots[(size_t)(row0 + r) * bpr + (piece >> 1)] = full;
                         }
-                        const float wscale = DOTS ? 1.0f : half_bits_to_float(sc[st][r][u]);
-                        acc[r][b] = fmaf((float)isum, wscale * xscale, acc[r][b]);
+                        acc[r][b] = fmaf((float)isum, wsc[r] * xscale, acc[r][b]);
                     }
                 }
             } else {
@@ -415,9 +431,8 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
                 }
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    const float wscale = half_bits_to_float(sc[st][r][u]);
 #pragma unroll
-                    for (int b = 0; b < B; ++b) acc[r][b] = fmaf(wscale, p[r][b], acc[r][b]);
+                    for (int b = 0; b < B; ++b) acc[r][b] = fmaf(wsc[r], p[r][b], acc[r][b]);
                 }
             }
         }
@@ -436,25 +451,26 @@ __global__ void __launch_bounds__(kQ8SThreads) q8s_gemv_kernel(QGemvArgs a) {
         }
     };
 
+    // With SA a lane reads scales that other lanes copied: the warp synchronises after the wait and
+    // again before the stage is requested anew.
+    auto step = [&](auto stage_c) {
+        cp_async_wait<STAGES - 1>();
+        if (SA) __syncwarp();
+        consume(stage_c);
+        if (SA) __syncwarp();
+        issue(stage_c);
+    };
     while (cg < g_end) {
-        cp_async_wait<STAGES - 1>();
-        consume(std::integral_constant<int, 0>{});
-        issue(std::integral_constant<int, 0>{});
+        step(std::integral_constant<int, 0>{});
         if (cg >= g_end) break;
-        cp_async_wait<STAGES - 1>();
-        consume(std::integral_constant<int, 1>{});
-        issue(std::integral_constant<int, 1>{});
+        step(std::integral_constant<int, 1>{});
         if (STAGES > 2) {
             if (cg >= g_end) break;
-            cp_async_wait<STAGES - 1>();
-            consume(std::integral_constant<int, 2 % STAGES>{});
-            issue(std::integral_constant<int, 2 % STAGES>{});
+            step(std::integral_constant<int, 2 % STAGES>{});
         }
         if (STAGES > 3) {
             if (cg >= g_end) break;
-            cp_async_wait<STAGES - 1>();
-            consume(std::integral_constant<int, 3 % STAGES>{});
-            issue(std::integral_constant<int, 3 % STAGES>{});
+            step(std::integral_constant<int, 3 % STAGES>{});
         }
     }
     cp_async_wait<0>();
@@ -762,13 +778,13 @@ static size_t q8s_smem_bytes(int cols) {
     const int nseg = (cols + 511) / 512;
     size_t off = (size_t)B * nseg * (is_int ? 512 : 2048) + (is_int ? (size_t)B * (cols / 32) * 4 : 0);
     off = (off + 127) & ~(size_t)127;
-    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * Cfg::U * 512;
+    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * Cfg::U * (512 + 32);  // scales may ride in the ring
 }
 
-template <int B, int MODE, bool DOTS>
-static int launch_q8s(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+template <int B, int MODE, bool DOTS, bool SA>
+static int launch_q8s_sa(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     using Cfg = Q8SConfig<B, MODE>;
-    constexpr auto kernel = q8s_gemv_kernel<B, Cfg::R, Cfg::U, MODE, DOTS, Cfg::STAGES>;
+    constexpr auto kernel = q8s_gemv_kernel<B, Cfg::R, Cfg::U, MODE, DOTS, Cfg::STAGES, SA>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
     const size_t smem = q8s_smem_bytes<B, MODE>(a.cols);
@@ -779,6 +795,17 @@ static int launch_q8s(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) 
     const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;  // at least one group per warp
     if (grid > want) grid = want;
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a);
+}
+
+template <int B, int MODE, bool DOTS>
+static int launch_q8s(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+    if constexpr (DOTS) {
+        return launch_q8s_sa<B, MODE, DOTS, false>(a, di, s);  // the block-dot entry passes no scales
+    } else {
+        // worth it only where the kernel is bandwidth-bound: the float mode is FFMA-bound and keeps its scales in registers
+        const bool sa = MODE != MODE_FLOAT && a.cols % 256 == 0 && aligned_to(a.scales, 16);
+        return sa ? launch_q8s_sa<B, MODE, DOTS, true>(a, di, s) : launch_q8s_sa<B, MODE, DOTS, false>(a, di, s);
+    }
 }
 
 template <int FMT, int B, int MODE>

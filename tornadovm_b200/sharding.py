@@ -47,23 +47,27 @@ def gather_rows(y_local: torch.Tensor, rows: int, group=None, out: torch.Tensor 
 
 
 class ShardedQ8Gemv:
-    """Q8_0 (split layout) mat-vec whose weight rows are sharded over the ranks.
+    """Q8_0 mat-vec whose weight rows are sharded over the ranks.
 
-    ``run(x_host)`` is the end-to-end call: activation host->device, the local
-    shard's GEMV through the C ABI, all-gather of the output shards over NCCL,
-    gathered result device->host.
+    ``weights`` is this rank's row block: 34-byte blocks (``scales=None``) or the
+    split layout's int8 quants with ``scales`` its fp16 scales.  ``run(x_host)``
+    is the end-to-end call: activation host->device, the local shard's GEMV
+    through the C ABI (integer path by default), all-gather of the output shards
+    over NCCL, gathered result device->host.
     """
 
-    def __init__(self, rows: int, cols: int, batch: int, q_shard: torch.Tensor, scales_shard: torch.Tensor, group=None):
+    def __init__(self, rows: int, cols: int, batch: int, weights: torch.Tensor, scales: torch.Tensor | None = None,
+                 group=None, exact_int: bool = True):
         self.rows, self.cols, self.batch, self.group = rows, cols, batch, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.per = shard_rows(rows, self.world)
         r0, r1 = shard_range(rows, self.world, self.rank)
         self.local_rows = r1 - r0
-        assert q_shard.is_cuda and q_shard.numel() == self.local_rows * cols
-        self.q, self.scales = q_shard, scales_shard
-        dev = q_shard.device
+        per_row = cols if scales is not None else cols // 32 * 34
+        assert weights.is_cuda and weights.numel() == self.local_rows * per_row
+        self.w, self.scales, self.exact_int = weights, scales, exact_int
+        dev = weights.device
         self.lib = B200Native.load()
         self.stream = torch.cuda.Stream(device=dev)
         self.x_dev = torch.empty((batch, cols), dtype=torch.float32, device=dev)
@@ -71,6 +75,23 @@ class ShardedQ8Gemv:
         self.y_tmp = torch.empty((batch, max(self.local_rows, 1)), dtype=torch.float32, device=dev)
         self.gather_buf = torch.empty((self.world, batch, self.per), dtype=torch.float32, device=dev) if self.world > 1 else None
         self.y_host = torch.empty((batch, rows), dtype=torch.float32, pin_memory=True)
+        self.ws_bytes = self.lib.tb200_qx_workspace_bytes(cols, batch)
+        self.ws = torch.empty(max(self.ws_bytes, 16), dtype=torch.uint8, device=dev)
+
+    def _gemv(self, y: torch.Tensor) -> None:
+        P = lambda t: C.c_void_p(t.data_ptr())
+        S = C.c_void_p(self.stream.cuda_stream)
+        n, c, b = self.local_rows, self.cols, self.batch
+        if self.scales is None:
+            if self.exact_int:
+                fn, st = "tb200_q8b_gemv_i8", self.lib.tb200_q8b_gemv_i8(n, c, b, P(self.w), P(self.x_dev), P(y), P(self.ws), self.ws_bytes, S)
+            else:
+                fn, st = "tb200_q8b_gemv", self.lib.tb200_q8b_gemv(n, c, b, P(self.w), P(self.x_dev), P(y), S)
+        elif self.exact_int:
+            fn, st = "tb200_q8_gemv_i8", self.lib.tb200_q8_gemv_i8(n, c, b, P(self.w), P(self.scales), P(self.x_dev), P(y), P(self.ws), self.ws_bytes, S)
+        else:
+            fn, st = "tb200_q8_gemv", self.lib.tb200_q8_gemv(n, c, b, P(self.w), P(self.scales), P(self.x_dev), P(y), S)
+        B200Native.check_status(st, fn)
 
     def launch(self) -> torch.Tensor:
         """Enqueue GEMV + gather on this object's stream; returns the gathered device tensor."""
@@ -78,10 +99,7 @@ class ShardedQ8Gemv:
             if self.local_rows > 0:
                 # y of the shard is [batch][local_rows]; it lands in the padded [batch][per] block
                 tgt = self.y_local if self.local_rows == self.per else self.y_tmp
-                B200Native.check_status(
-                    self.lib.tb200_q8_gemv(self.local_rows, self.cols, self.batch, C.c_void_p(self.q.data_ptr()),
-                                           C.c_void_p(self.scales.data_ptr()), C.c_void_p(self.x_dev.data_ptr()),
-                                           C.c_void_p(tgt.data_ptr()), C.c_void_p(self.stream.cuda_stream)), "tb200_q8_gemv")
+                self._gemv(tgt)
                 if tgt is self.y_tmp:
                     self.y_local[:, :self.local_rows].copy_(self.y_tmp)
             return gather_rows(self.y_local, self.rows, self.group, self.gather_buf)
