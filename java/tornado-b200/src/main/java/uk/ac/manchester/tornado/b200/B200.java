@@ -1,0 +1,87 @@
+package uk.ac.manchester.tornado.b200;
+
+import java.util.Arrays;
+
+import uk.ac.manchester.tornado.api.common.Access;
+import uk.ac.manchester.tornado.api.common.LibraryTaskDescriptor;
+import uk.ac.manchester.tornado.api.exceptions.TornadoRuntimeException;
+import uk.ac.manchester.tornado.api.types.arrays.ByteArray;
+import uk.ac.manchester.tornado.api.types.arrays.FloatArray;
+import uk.ac.manchester.tornado.api.types.arrays.HalfFloatArray;
+import uk.ac.manchester.tornado.api.types.arrays.Int8Array;
+
+/**
+ * Factories of the {@code b200/linalg} library tasks: dense and quantised matrix-vector and
+ * matrix-matrix products on hand-written sm_100a kernels. Each factory validates shapes early and
+ * returns the descriptor whose parameters the provider later receives positionally.
+ */
+public final class B200 {
+
+    public static final String LIBRARY_NAME = "b200/linalg";
+    public static final int MAX_BATCH = 16;
+
+    private B200() {
+    }
+
+    private static void check(boolean ok, String message) {
+        if (!ok) {
+            throw new TornadoRuntimeException("[ERROR] " + message);
+        }
+    }
+
+    private static LibraryTaskDescriptor descriptor(String function, Object[] params, int out, boolean readWrite, Object tuning) {
+        Access[] access = new Access[params.length];
+        Arrays.fill(access, Access.READ_ONLY);
+        access[out] = readWrite ? Access.READ_WRITE : Access.WRITE_ONLY;
+        LibraryTaskDescriptor d = new LibraryTaskDescriptor().withLibrary(LIBRARY_NAME).withFunction(function).withParameters(params).withAccess(access);
+        return tuning == null ? d : d.withTuning(tuning);
+    }
+
+    /** {@code out[i] = sum_j m[i*cols+j] * v[j]}: the README mxv kernel as a library task. */
+    public static LibraryTaskDescriptor sgemv(int rows, int cols, FloatArray m, FloatArray v, FloatArray out) {
+        check(rows >= 0 && cols >= 0, "B200 sgemv requires non-negative sizes; got rows=" + rows + ", cols=" + cols);
+        check(m.getSize() >= (long) rows * cols && v.getSize() >= cols && out.getSize() >= rows, "B200 sgemv: array smaller than rows x cols");
+        return descriptor("sgemv", new Object[] { rows, cols, m, v, out }, 4, false, null);
+    }
+
+    private static void checkQuantised(String name, int rows, int cols, int batch, FloatArray x, FloatArray y) {
+        check(cols % 32 == 0, "B200 " + name + " requires cols to be a multiple of the 32-element block; got cols=" + cols);
+        check(batch >= 1 && batch <= MAX_BATCH, "B200 " + name + " requires 1 <= batch <= " + MAX_BATCH + "; got " + batch);
+        check(x.getSize() >= (long) batch * cols && y.getSize() >= (long) batch * rows, "B200 " + name + ": x or y too small");
+    }
+
+    /** Q8_0 mat-vec, split layout: int8 quants + fp16 scales; x is [batch][cols], y is [batch][rows]. */
+    public static LibraryTaskDescriptor q8Gemv(int rows, int cols, int batch, Int8Array q, HalfFloatArray scales, FloatArray x, FloatArray y, B200Options options) {
+        checkQuantised("q8Gemv", rows, cols, batch, x, y);
+        check(q.getSize() >= (long) rows * cols && scales.getSize() >= (long) rows * cols / 32, "B200 q8Gemv: weights too small");
+        return descriptor("q8Gemv", new Object[] { rows, cols, batch, q, scales, x, y }, 6, false, options);
+    }
+
+    /** Q8_0 mat-vec, unified 34-byte blocks (fp16 scale, 32 x int8). */
+    public static LibraryTaskDescriptor q8GemvBytes(int rows, int cols, int batch, ByteArray blocks, FloatArray x, FloatArray y, B200Options options) {
+        checkQuantised("q8GemvBytes", rows, cols, batch, x, y);
+        check(blocks.getSize() >= (long) rows * (cols / 32) * 34, "B200 q8GemvBytes: weights too small");
+        return descriptor("q8GemvBytes", new Object[] { rows, cols, batch, blocks, x, y }, 5, false, options);
+    }
+
+    /** Q4_0 mat-vec, 18-byte blocks (fp16 scale, 16 nibble bytes, value = nibble - 8). */
+    public static LibraryTaskDescriptor q4GemvBytes(int rows, int cols, int batch, ByteArray blocks, FloatArray x, FloatArray y, B200Options options) {
+        checkQuantised("q4GemvBytes", rows, cols, batch, x, y);
+        check(blocks.getSize() >= (long) rows * (cols / 32) * 18, "B200 q4GemvBytes: weights too small");
+        return descriptor("q4GemvBytes", new Object[] { rows, cols, batch, blocks, x, y }, 5, false, options);
+    }
+
+    /** {@code C = alpha*A*B + beta*C}, row-major FP32 on CUDA cores. */
+    public static LibraryTaskDescriptor sgemm(int m, int n, int k, float alpha, FloatArray a, FloatArray b, float beta, FloatArray c) {
+        check(m >= 0 && n >= 0 && k >= 0, "B200 sgemm requires non-negative sizes; got m=" + m + ", n=" + n + ", k=" + k);
+        check(a.getSize() >= (long) m * k && b.getSize() >= (long) k * n && c.getSize() >= (long) m * n, "B200 sgemm: array too small");
+        return descriptor("sgemm", new Object[] { m, n, k, alpha, a, b, beta, c }, 7, beta != 0.0f, null);
+    }
+
+    /** {@code C(fp32) = A(fp16) * B(fp16)}, row-major, tcgen05 tensor cores with fp32 accumulation. */
+    public static LibraryTaskDescriptor hgemmF32(int m, int n, int k, HalfFloatArray a, HalfFloatArray b, FloatArray c) {
+        check(m >= 0 && n >= 0 && k >= 0, "B200 hgemmF32 requires non-negative sizes; got m=" + m + ", n=" + n + ", k=" + k);
+        check(a.getSize() >= (long) m * k && b.getSize() >= (long) k * n && c.getSize() >= (long) m * n, "B200 hgemmF32: array too small");
+        return descriptor("hgemmF32", new Object[] { m, n, k, a, b, c }, 5, false, null);
+    }
+}
