@@ -173,7 +173,8 @@ def test_block_dots_unaligned_activations(lib):
     assert np.array_equal(dd.numpy(), o.q8_blockdots_i32(q, xq, cols, rows))
 
 
-@pytest.mark.parametrize("rows,cols,batch", [(512, 4096, 1), (96, 4096, 8), (64, 14336, 2), (20, 14336, 16), (33, 256, 1), (5, 96, 3)])
+@pytest.mark.parametrize("rows,cols,batch", [(512, 4096, 1), (96, 4096, 8), (64, 14336, 2), (20, 14336, 16), (33, 256, 1), (5, 96, 3),
+                                             (200, 4096, 3), (33, 512, 9), (130, 2048, 16), (2500, 1024, 5)])
 @pytest.mark.parametrize("fmt", ["q8", "q8b", "q4b"])
 @pytest.mark.parametrize("header", [16, 24])
 def test_gemv_int_mode(lib, rows, cols, batch, fmt, header):

@@ -1,0 +1,263 @@
+// Batched Q8_0 / Q4_0 mat-vec on the integer tensor-core path (batch 5..16).
+//
+// With several activation vectors the dp4a kernels run out of integer issue
+// slots long before HBM is busy, so each 32-element block dot of a 16-row x
+// 8-vector tile is one mma.sync.m16n8k32 (s8 x s8 -> s32): the int32 block dots
+// stay exact, and one fp32 FMA per output applies wscale * xscale, exactly as in
+// the dp4a kernels.  (mma.sync is the legacy tensor path; the arithmetic here is
+// tiny -- the kernel is HBM-bound -- so tcgen05 would add nothing.)
+//
+// One CTA per SM.  A CTA owns a contiguous range of 16-row units; in each round
+// its eight warps take one unit each and walk K together in chunks of 8 blocks
+// (256 columns): all threads cp.async the chunk's weights (8 units x 16 rows)
+// and the chunk of the quantised activations into a 4-stage shared-memory ring,
+// one __syncthreads per chunk.  Rows are padded to a 272- / 144-byte pitch in
+// shared memory so that the fragment loads are bank-conflict free.
+#include "common.cuh"
+
+namespace tb200 {
+
+constexpr int MM_THREADS = 256, MM_WARPS = 8, MM_KB = 8 /* blocks per chunk */, MM_STAGES = 4;
+
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+// 32-bit read at a byte offset that is 0 or 2 modulo 4
+template <int MISALIGNED>
+__device__ __forceinline__ uint32_t lds_u32_at(const unsigned char *base, int off) {
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(base + (off & ~3));
+    if (MISALIGNED) return __funnelshift_r(w[0], w[1], 16);
+    return w[0];
+}
+
+template <int FMT>
+struct MmaTraits {
+    static constexpr int BB = FMT == FMT_Q4B ? 18 : (FMT == FMT_Q8B ? 34 : 32);  // weight bytes per block in the row chunk
+    static constexpr int ROWB = MM_KB * BB;                                       // bytes per row chunk (272 / 144 / 256)
+    static constexpr int WS = FMT == FMT_Q4B ? 144 : 272;                         // shared-memory row pitch
+    static constexpr int PP = ROWB / 16 + (FMT == FMT_Q8S ? 1 : 0);              // 16-byte pieces per row (+ scales piece)
+    static constexpr int W_BYTES = MM_WARPS * 16 * WS;
+    static constexpr int SC_BYTES = FMT == FMT_Q8S ? MM_WARPS * 16 * 16 : 0;     // split layout: 8 fp16 scales per row
+};
+
+template <int FMT, int NT>
+struct MmaStage {
+    using T = MmaTraits<FMT>;
+    static constexpr int BP = NT * 8;
+    static constexpr int X_OFF = T::W_BYTES + T::SC_BYTES;
+    static constexpr int XS_OFF = X_OFF + BP * 272;
+    static constexpr int BYTES = (XS_OFF + BP * 32 + 127) & ~127;
+};
+
+template <int FMT, int NT>
+__global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
+    using T = MmaTraits<FMT>;
+    using S = MmaStage<FMT, NT>;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int cols = a.cols, rows = a.rows, batch = a.batch;
+    const int bpr = cols / 32;
+    const int nkc = bpr / MM_KB;  // cols % 256 == 0
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    const int nunits = (rows + 15) / 16;
+    const int ubeg = (int)((long long)nunits * blockIdx.x / gridDim.x);
+    const int uend = (int)((long long)nunits * (blockIdx.x + 1) / gridDim.x);
+    const int nrounds = (uend - ubeg + MM_WARPS - 1) / MM_WARPS;
+    const int total = nrounds * nkc;
+
+    // Copy plan of this thread: it always moves the same (row, piece) slots of a chunk, so the source
+    // pointers are set up once per round and only advance along K afterwards.
+    constexpr int NW = (MM_WARPS * 16 * T::PP + MM_THREADS - 1) / MM_THREADS;  // weight pieces per thread and chunk
+    constexpr int NX = (S::BP * 18 + MM_THREADS - 1) / MM_THREADS;            // activation pieces per thread and chunk
+    const unsigned char *wsrc[NW];
+    uint32_t wdst[NW];
+    int wstep[NW];
+    const unsigned char *xsrc[NX];
+    uint32_t xdst[NX];
+    int xstep[NX];
+#pragma unroll
+    for (int m = 0; m < NX; ++m) {
+        const int i = tid + m * MM_THREADS;
+        const int b = i / 18, p = i - b * 18;
+        xsrc[m] = nullptr, xdst[m] = 0, xstep[m] = 0;
+        if (i < S::BP * 18 && b < batch) {
+            if (p < 16) {
+                xsrc[m] = reinterpret_cast<const unsigned char *>(a.xq) + (size_t)b * cols + p * 16;
+                xdst[m] = S::X_OFF + b * 272 + p * 16, xstep[m] = 256;
+            } else {
+                xsrc[m] = reinterpret_cast<const unsigned char *>(a.xs + (size_t)b * bpr + (p - 16) * 4);
+                xdst[m] = S::XS_OFF + b * 32 + (p - 16) * 16, xstep[m] = MM_KB * 4;
+            }
+        }
+    }
+    auto plan_round = [&](int round) {
+        const int ufirst = ubeg + round * MM_WARPS;
+#pragma unroll
+        for (int m = 0; m < NW; ++m) {
+            const int i = tid + m * MM_THREADS;
+            const int rl = i / T::PP, p = i - rl * T::PP;
+            wsrc[m] = nullptr;
+            if (i < MM_WARPS * 16 * T::PP) {
+                const size_t grow = (size_t)min((ufirst + (rl >> 4)) * 16 + (rl & 15), rows - 1);
+                if (FMT == FMT_Q8S) {
+                    if (p < 16) {
+                        wsrc[m] = a.w + grow * cols + p * 16, wdst[m] = rl * T::WS + p * 16, wstep[m] = 256;
+                    } else {
+                        wsrc[m] = reinterpret_cast<const unsigned char *>(a.scales + grow * bpr);
+                        wdst[m] = T::W_BYTES + rl * 16, wstep[m] = MM_KB * 2;
+                    }
+                } else {
+                    wsrc[m] = a.w + grow * bpr * T::BB + p * 16, wdst[m] = rl * T::WS + p * 16, wstep[m] = T::ROWB;
+                }
+            }
+        }
+    };
+
+    // one chunk (8 units x 16 rows x 8 blocks of weights, 8 blocks of every activation vector) into a stage
+    int issue_kc = 0, issue_round = 0;
+    plan_round(0);
+    auto issue = [&](int it) {
+        if (it < total) {
+            const uint32_t base_s = smem_u32(smem_raw + (size_t)(it % MM_STAGES) * S::BYTES);
+#pragma unroll
+            for (int m = 0; m < NW; ++m)
+                if (wsrc[m]) cp_async_16(base_s + wdst[m], wsrc[m] + (size_t)issue_kc * wstep[m]);
+#pragma unroll
+            for (int m = 0; m < NX; ++m)
+                if (xsrc[m]) cp_async_16(base_s + xdst[m], xsrc[m] + (size_t)issue_kc * xstep[m]);
+            if (++issue_kc == nkc) {
+                issue_kc = 0;
+                if (++issue_round < nrounds) plan_round(issue_round);
+            }
+        }
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int s = 0; s < MM_STAGES - 1; ++s) issue(s);
+
+    float acc[NT][4];
+    for (int it = 0; it < total; ++it) {
+        cp_async_wait<MM_STAGES - 2>();
+        __syncthreads();             // chunk `it` has landed for everyone; chunk it-1 is no longer read
+        issue(it + MM_STAGES - 1);   // refills the stage of chunk it-1
+        const int round = it / nkc, kc = it - round * nkc;
+        const unsigned char *base = smem_raw + (size_t)(it % MM_STAGES) * S::BYTES;
+        const int unit = ubeg + round * MM_WARPS + warp;
+        if (unit >= uend) continue;  // warp-uniform; the warp still took part in the copies and the barrier
+        if (kc == 0) {
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+        }
+        const unsigned char *rp0 = base + (warp * 16 + g) * T::WS;
+        const unsigned char *rp1 = rp0 + 8 * T::WS;
+#pragma unroll
+        for (int kb = 0; kb < MM_KB; ++kb) {
+            uint32_t a0, a1, a2, a3;
+            float sw0, sw1;
+            if (FMT == FMT_Q8B) {
+                constexpr int dummy = 0;
+                (void)dummy;
+                const int off = kb * 34 + 2 + 4 * t;
+                if (kb % 2 == 0) {  // 34*kb + 2 is 2 modulo 4
+                    a0 = lds_u32_at<1>(rp0, off), a1 = lds_u32_at<1>(rp1, off);
+                    a2 = lds_u32_at<1>(rp0, off + 16), a3 = lds_u32_at<1>(rp1, off + 16);
+                } else {
+                    a0 = lds_u32_at<0>(rp0, off), a1 = lds_u32_at<0>(rp1, off);
+                    a2 = lds_u32_at<0>(rp0, off + 16), a3 = lds_u32_at<0>(rp1, off + 16);
+                }
+                sw0 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rp0 + kb * 34));
+                sw1 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rp1 + kb * 34));
+            } else if (FMT == FMT_Q4B) {
+                const int off = kb * 18 + 2 + 4 * t;
+                uint32_t w0, w1;
+                if (kb % 2 == 0) w0 = lds_u32_at<1>(rp0, off), w1 = lds_u32_at<1>(rp1, off);
+                else w0 = lds_u32_at<0>(rp0, off), w1 = lds_u32_at<0>(rp1, off);
+                // byte i holds element i (low nibble) and element i + 16 (high nibble)
+                a0 = w0 & 0x0F0F0F0Fu, a2 = (w0 >> 4) & 0x0F0F0F0Fu;
+                a1 = w1 & 0x0F0F0F0Fu, a3 = (w1 >> 4) & 0x0F0F0F0Fu;
+                sw0 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rp0 + kb * 18));
+                sw1 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(rp1 + kb * 18));
+            } else {
+                const int off = kb * 32 + 4 * t;
+                a0 = lds_u32_at<0>(rp0, off), a1 = lds_u32_at<0>(rp1, off);
+                a2 = lds_u32_at<0>(rp0, off + 16), a3 = lds_u32_at<0>(rp1, off + 16);
+                const unsigned char *sp = base + T::W_BYTES + (warp * 16 + g) * 16 + kb * 2;
+                sw0 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(sp));
+                sw1 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(sp + 8 * 16));
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const unsigned char *xrow = base + S::X_OFF + (j * 8 + g) * 272 + kb * 32 + 4 * t;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xrow);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xrow + 16);
+                int d[4];
+                mma_s8_16832(d, a0, a1, a2, a3, b0, b1);
+                if (FMT == FMT_Q4B) {
+                    // nibbles are 0..15: subtract 8 * sum(xq) of the block, itself one mma against all-ones rows
+                    int sx[4];
+                    mma_s8_16832(sx, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1);
+                    d[0] -= 8 * sx[0], d[1] -= 8 * sx[1], d[2] -= 8 * sx[0], d[3] -= 8 * sx[1];
+                }
+                const float *xsp = reinterpret_cast<const float *>(base + S::XS_OFF) + (j * 8 + 2 * t) * 8 + kb;
+                const float x0 = xsp[0], x1 = xsp[8];
+                acc[j][0] = fmaf((float)d[0], sw0 * x0, acc[j][0]);
+                acc[j][1] = fmaf((float)d[1], sw0 * x1, acc[j][1]);
+                acc[j][2] = fmaf((float)d[2], sw1 * x0, acc[j][2]);
+                acc[j][3] = fmaf((float)d[3], sw1 * x1, acc[j][3]);
+            }
+        }
+        if (kc == nkc - 1) {
+            const int r0 = unit * 16 + g, r1 = r0 + 8;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int n0 = j * 8 + 2 * t, n1 = n0 + 1;
+                if (n0 < batch) {
+                    if (r0 < rows) a.y[(size_t)n0 * rows + r0] = acc[j][0];
+                    if (r1 < rows) a.y[(size_t)n0 * rows + r1] = acc[j][2];
+                }
+                if (n1 < batch) {
+                    if (r0 < rows) a.y[(size_t)n1 * rows + r0] = acc[j][1];
+                    if (r1 < rows) a.y[(size_t)n1 * rows + r1] = acc[j][3];
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <int FMT, int NT>
+static int launch_qmma(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+    using S = MmaStage<FMT, NT>;
+    constexpr auto kernel = qmma_gemv_kernel<FMT, NT>;
+    int st = ensure_smem_optin<kernel>(di);
+    if (st) return st;
+    const size_t smem = (size_t)MM_STAGES * S::BYTES;
+    const int nunits = (a.rows + 15) / 16;
+    const int grid = nunits < di->sm_count ? nunits : di->sm_count;
+    return launch_kernel(kernel, dim3(grid), dim3(MM_THREADS), smem, s, false, a);
+}
+
+// Entry used by the dispatcher of gemv_quant.cu: already quantised activations (xq, xs), 5 <= batch <= 16.
+template <int FMT>
+static int qmma_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+    return a.batch <= 8 ? launch_qmma<FMT, 1>(a, di, s) : launch_qmma<FMT, 2>(a, di, s);
+}
+
+// Shapes and alignments the tensor-core kernel takes.
+template <int FMT>
+static bool qmma_eligible(const QGemvArgs &a) {
+    if (a.batch < 5 || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !aligned_to(a.xq, 16) || !a.xs || !aligned_to(a.xs, 16)) return false;
+    if (FMT == FMT_Q8S && (!a.scales || !aligned_to(a.scales, 16))) return false;
+    return a.y != nullptr;
+}
+
+}  // namespace tb200

@@ -852,6 +852,12 @@ static int launch_generic(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t
 
 enum Path { PATH_GENERIC, PATH_Q8S_DIRECT, PATH_RING };
 
+// tensor-core kernel for batches of 5..16 (gemv_mma.cu)
+template <int FMT>
+static bool qmma_eligible(const QGemvArgs &a);
+template <int FMT>
+static int qmma_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s);
+
 // Does one fast launch with `batch` activation vectors fit in shared memory?
 template <int FMT, int MODE>
 static bool fast_batch_fits(int cols, int batch, Path path, const DeviceInfo *di) {
@@ -965,7 +971,8 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     if (per < 1) path = PATH_GENERIC;
 
     if (MODE == MODE_INT_FUSED) {
-        const bool fuse = path != PATH_GENERIC && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per;
+        // batches of five and more go to the tensor-core kernel, which reads quantised activations from the workspace
+        const bool fuse = path != PATH_GENERIC && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per && a.batch <= 4;
         if (fuse) return launch_fast<FMT, MODE_INT_FUSED, false>(a, path, di, s);
         // separate quantiser into the workspace, then the MODE_INT kernels
         st = quantize_x(a.cols, a.batch, a.x, xq_ws, xs_ws, s);
@@ -975,6 +982,9 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
         return qgemv_dispatch<FMT, MODE_INT, false>(b, nullptr, nullptr, stream);
     } else {
         if (path == PATH_GENERIC) return launch_generic<FMT, INT>(a, di, s);
+        if constexpr (MODE == MODE_INT && !DOTS) {
+            if (qmma_eligible<FMT>(a)) return qmma_dispatch<FMT>(a, di, s);
+        }
         // more activation vectors than fit next to the ring: several passes over the weights
         for (int b0 = 0; b0 < a.batch; b0 += per) {
             QGemvArgs p = a;

@@ -4,6 +4,7 @@
 #include "api.cu"
 #include "gemv_f32.cu"
 #include "gemv_quant.cu"
+#include "gemv_mma.cu"
 #include "sgemm.cu"
 #include "hgemm.cu"
 #include "gemv_static.cu"
