@@ -308,13 +308,18 @@ def run_gpu_arm(args):
             if st:
                 B200Native.check_status(st, "tb200_q8b_gemv_i8")
 
-    # one step = LAYERS launches, captured once and replayed (how TornadoVM runs a plan withCUDAGraph)
+    # one step = LAYERS launches captured once and replayed (how TornadoVM runs a plan withCUDAGraph); with
+    # N > 1 the all-gather of the output shards follows the replay on the same stream.  (The collective is
+    # kept outside the graph: a graph that holds NCCL kernels has to be destroyed before the communicator,
+    # and capturing it did not shorten the step.)
     with torch.cuda.stream(stream):
-        enqueue_layers()
+        for _ in range(3):
+            enqueue_layers()  # warm-up outside capture: one-time kernel attribute calls
         stream.synchronize()
         layer_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(layer_graph, stream=stream):
             enqueue_layers()
+    kernel_graph = layer_graph  # kernels only, for the roofline
 
     def step():
         nonlocal launches
@@ -346,7 +351,7 @@ def run_gpu_arm(args):
         reps = max(args.steps, 10)
         k0.record(stream)
         for _ in range(reps):
-            layer_graph.replay()
+            kernel_graph.replay()
         k1.record(stream)
         stream.synchronize()
         kernel_s = k0.elapsed_time(k1) * 1e-3 / (reps * LAYERS)
@@ -413,7 +418,7 @@ def run_gpu_arm(args):
         "dtype": "s8", "data": "synthetic",
         "config": {"workload": f"Q8_0 GEMV W[{ROWS}x{COLS}] int8 blocks of 32 + fp16 scale (34-byte blocks), fp32 x, batch {BATCH}",
                    "layers_per_step": LAYERS, "l2_policy": f"{LAYERS} distinct weight matrices per step ({LAYERS * 62.4:.0f} MB > 126 MB L2)",
-                   "parallelism": f"rows sharded over {world} GPU(s), outputs all-gathered once per step" if world > 1 else "single GPU",
+                   "parallelism": f"rows sharded over {world} GPU(s), outputs all-gathered once per step (NCCL)" if world > 1 else "single GPU",
                    "mode": "int (fp32 activations quantised to int8 per 32-block inside the kernel, exact int32 block dots)",
                    "launch": "CUDA-graph replay, programmatic dependent launches"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -432,6 +437,8 @@ def run_gpu_arm(args):
                 line["secondary"] = secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak)
         print(json.dumps(line))
     if world > 1:
+        del layer_graph, kernel_graph
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
 
