@@ -96,7 +96,7 @@ class TornadoExecutionPlan:
         self.plan_id = next(self._ids)
         self.stream = self.device.torch_stream(self.plan_id)
         self.context = self.provider.createContext(self.device, self.plan_id)
-        self._buffers = {}  # id(array) -> (device uint8 tensor, pinned host tensor)
+        self._buffers = {}  # id(array) -> (device uint8 view, pinned host view, offset in the slabs)
         self._executions = 0
         self._use_graph = False
         self._cuda_graph = None
@@ -109,17 +109,62 @@ class TornadoExecutionPlan:
         return self
 
     # -- internals ------------------------------------------------------------
+    def _layout(self):
+        """One device slab and one pinned host slab for every array of the graph.
+
+        TornadoVM's off-heap arrays *are* the host side of a transfer (no staging copy), so each
+        array's segment is re-homed into the pinned slab: host<->device copies then move the
+        array's own memory.  Arrays copied back on every execution sit next to each other, so
+        that their device->host transfers merge into one copy.
+        """
+        g = self.graph
+        ordered, seen = [], set()
+
+        def add(arr):
+            if isinstance(arr, TornadoNativeArray) and id(arr) not in seen:
+                seen.add(id(arr))
+                ordered.append(arr)
+        for _, arr in g.to_host:          # outputs first and contiguous
+            add(arr)
+        for mode, arr in g.to_device:
+            if mode is DataTransferMode.EVERY_EXECUTION:
+                add(arr)
+        for _, arr in g.to_device:
+            add(arr)
+        for t in g.tasks:
+            for p in t.descriptor.getParameters():
+                add(p)
+        offsets, total = {}, 0
+        for arr in ordered:
+            offsets[id(arr)] = total
+            total += (arr.nbytes_with_header + 255) // 256 * 256  # cuMemAlloc-like 256-byte alignment per buffer
+        self._dev_slab = torch.empty(max(total, 256), dtype=torch.uint8, device=self.device.torch_device)
+        self._host_slab = torch.empty(max(total, 256), dtype=torch.uint8, pin_memory=True)
+        host_np = self._host_slab.numpy()
+        for arr in ordered:
+            off, n = offsets[id(arr)], arr.nbytes_with_header
+            host_np[off:off + n] = arr.segment
+            arr.segment = host_np[off:off + n]                      # the array now lives in pinned memory
+            arr.data = arr.segment[arr.header:].view(arr.dtype)
+            self._buffers[id(arr)] = (self._dev_slab[off:off + n], self._host_slab[off:off + n], off)
+        self._arrays = ordered
+
     def _buffer(self, arr: TornadoNativeArray):
-        key = id(arr)
-        if key not in self._buffers:
-            n = arr.nbytes_with_header
-            dev = torch.empty(n, dtype=torch.uint8, device=self.device.torch_device)
-            host = torch.empty(n, dtype=torch.uint8, pin_memory=True)
-            self._buffers[key] = (dev, host)
-        return self._buffers[key]
+        return self._buffers[id(arr)]
 
     def _device_pointer(self, arr: TornadoNativeArray) -> int:
         return self._buffer(arr)[0].data_ptr() + arr.header
+
+    @staticmethod
+    def _merge(spans):
+        """Merge (offset, nbytes) spans that touch (up to the 256-byte padding between buffers)."""
+        out = []
+        for off, n in sorted(spans):
+            if out and off <= out[-1][0] + out[-1][1] + 256:
+                out[-1][1] = off + n - out[-1][0]
+            else:
+                out.append([off, n])
+        return out
 
     def _launch_all(self):
         for t in self.graph.tasks:
@@ -134,19 +179,18 @@ class TornadoExecutionPlan:
         first = self._executions == 0
         with torch.cuda.device(self.device.index), torch.cuda.stream(self.stream):
             if first:
-                # allocate every buffer a task touches, then the pre-launch prepare pass
-                for t in g.tasks:
-                    for p in t.descriptor.getParameters():
-                        if isinstance(p, TornadoNativeArray):
-                            self._buffer(p)
+                self._layout()
+                for t in g.tasks:  # the pre-launch prepare pass
                     self.provider.prepare(t.descriptor, self.context)
-            h2d = 0
-            for mode, arr in g.to_device:
-                if first or mode is DataTransferMode.EVERY_EXECUTION:
-                    dev, host = self._buffer(arr)
-                    host.numpy()[:] = arr.segment
-                    dev.copy_(host, non_blocking=True)
-                    h2d += arr.nbytes_with_header
+            spans = [(self._buffer(arr)[2], arr.nbytes_with_header) for mode, arr in g.to_device
+                     if first or mode is DataTransferMode.EVERY_EXECUTION]
+            if first:
+                # allocation time: every buffer, outputs included, gets its header (element count) on the device
+                self._dev_slab.copy_(self._host_slab, non_blocking=True)
+            else:
+                for off, n in self._merge(spans):
+                    self._dev_slab[off:off + n].copy_(self._host_slab[off:off + n], non_blocking=True)
+            h2d = sum(n for _, n in spans)
             if self._use_graph:
                 if self._cuda_graph is None:
                     self._launch_all()  # warm run: module load and attribute calls happen outside capture
@@ -157,15 +201,11 @@ class TornadoExecutionPlan:
                 self._cuda_graph.replay()
             else:
                 self._launch_all()
-            d2h = 0
-            for mode, arr in g.to_host:
-                dev, host = self._buffer(arr)
-                host.copy_(dev, non_blocking=True)
-                d2h += arr.nbytes_with_header
+            spans = [(self._buffer(arr)[2], arr.nbytes_with_header) for _, arr in g.to_host]
+            for off, n in self._merge(spans):
+                self._host_slab[off:off + n].copy_(self._dev_slab[off:off + n], non_blocking=True)
+            d2h = sum(n for _, n in spans)
             self.stream.synchronize()
-            for mode, arr in g.to_host:
-                host = self._buffer(arr)[1]
-                arr.segment[arr.header:] = host.numpy()[arr.header:]
         self.h2d_bytes_last, self.d2h_bytes_last = h2d, d2h
         self._executions += 1
         return self
@@ -177,6 +217,7 @@ class TornadoExecutionPlan:
                 self.provider.destroyContext(self.context)
             self.context = None
         self._buffers.clear()
+        self._dev_slab = None
         self._cuda_graph = None
 
     def __enter__(self):
