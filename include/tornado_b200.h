@@ -81,7 +81,9 @@ int tb200_device_status(int *status_out);
  * reads activations or writes outputs.  Contract when on: a weight operand must
  * not be written by the kernel enqueued immediately before the mat-vec on the
  * same stream (copies and earlier kernels are fine). */
-enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1 };
+enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2 };
+/* TB200_OPT_HGEMM_SM_PAIRS: the FP16 GEMM runs 256 x 256 tiles on clusters of two CTAs
+ * (tcgen05 cta_group::2) instead of 128 x 256 tiles on single CTAs. */
 int tb200_set_option(int option, int value);
 int tb200_get_option(int option, int *value);
 

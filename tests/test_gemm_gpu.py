@@ -120,3 +120,34 @@ def test_gemm_argument_errors(lib):
     assert lib.tb200_sgemm(2, 2, 2, 1.0, None, d.ptr, 0.0, d.ptr, stream_ptr()) == -1
     assert lib.tb200_hgemm_f32(2, 2, 2, C.c_void_p(d.ptr.value + 1), d.ptr, d.ptr, stream_ptr()) == -2
     assert lib.tb200_hgemm_f32(0, 2, 2, d.ptr, d.ptr, d.ptr, stream_ptr()) == 0
+
+
+@pytest.mark.parametrize("pairs", [0, 1])
+@pytest.mark.parametrize("m,n,k", [(4096, 4096, 512), (3000, 4100 // 8 * 8, 264), (2304, 3328, 1024)])
+def test_hgemm_both_tensor_core_variants(lib, pairs, m, n, k):
+    """Single-CTA 128x256 tiles and SM-pair 256x256 tiles (tcgen05 cta_group::2) give the same product."""
+    import torch
+    old = C.c_int(0)
+    assert lib.tb200_get_option(2, C.byref(old)) == 0
+    try:
+        assert lib.tb200_set_option(2, pairs) == 0
+        g = torch.Generator(device="cuda").manual_seed(m + n + k)
+        a = (torch.randn((m, k), device="cuda", generator=g) / k**0.5).half()
+        b = (torch.randn((k, n), device="cuda", generator=g) / k**0.5).half()
+        c = torch.full((m, n), float("nan"), device="cuda")
+        P = lambda t: C.c_void_p(t.data_ptr())
+        _ok(lib.tb200_hgemm_f32(m, n, k, P(a), P(b), P(c), stream_ptr()), lib)
+        sync_and_check(lib)
+        rows = [0, 127, 128, 255, 256, m // 2, m - 1]
+        ah = a.cpu().numpy().view(np.uint16)
+        bh = b.cpu().numpy().view(np.uint16)
+        got = c.cpu().numpy()
+        assert not np.isnan(got).any()
+        for r in rows:
+            ref = o.hgemm_ref(np.ascontiguousarray(ah[r:r + 1]).ravel(), bh.ravel(), 1, n, k)
+            assert o.rel_l2(got[r:r + 1], ref) <= REL_L2_FP16
+        # every element against an fp32 matmul of the same halves (tolerance of the fp16 path)
+        ref_all = (a.float() @ b.float())
+        assert ((c - ref_all).norm() / ref_all.norm()).item() <= 1e-4
+    finally:
+        lib.tb200_set_option(2, old.value)

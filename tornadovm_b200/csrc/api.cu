@@ -6,6 +6,7 @@
 namespace tb200 {
 
 int g_overlap_launches = 0;
+extern int g_hgemm_pairs;
 
 static DeviceInfo g_info[kMaxDevices];
 static bool g_info_valid[kMaxDevices];
@@ -94,6 +95,9 @@ extern "C" int tb200_set_option(int option, int value) {
         case TB200_OPT_OVERLAP_LAUNCHES:
             tb200::g_overlap_launches = value != 0;
             return TB200_OK;
+        case TB200_OPT_HGEMM_SM_PAIRS:
+            tb200::g_hgemm_pairs = value != 0;
+            return TB200_OK;
         default:
             return TB200_ERR_INVALID_ARG;
     }
@@ -104,6 +108,9 @@ extern "C" int tb200_get_option(int option, int *value) {
     switch (option) {
         case TB200_OPT_OVERLAP_LAUNCHES:
             *value = tb200::g_overlap_launches;
+            return TB200_OK;
+        case TB200_OPT_HGEMM_SM_PAIRS:
+            *value = tb200::g_hgemm_pairs;
             return TB200_OK;
         default:
             return TB200_ERR_INVALID_ARG;

@@ -27,6 +27,8 @@
 
 namespace tb200 {
 
+int g_hgemm_pairs = 1;  // TB200_OPT_HGEMM_SM_PAIRS
+
 constexpr int HG_BM = 128, HG_BN = 256, HG_BK = 64, HG_STAGES = 4;
 constexpr int HG_THREADS = 192;
 constexpr int HG_A_BYTES = HG_BM * HG_BK * 2;      // 16 KB
@@ -99,6 +101,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
     return d;
 }
 
+// Tile order: bands of `gm` tile rows, inside a band the tile row changes fastest.  The CTAs that run
+// at the same time then share a few A row-panels (which stay in L2 for the whole band) and walk along
+// B together, instead of streaming all of A for every couple of B column-panels.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int gm, int &tm, int &tn) {
+    const int per_band = gm * tiles_n;
+    const int band = tile / per_band;
+    const int in_band = tile - band * per_band;
+    const int rows_here = min(gm, tiles_m - band * gm);  // the last band may be shorter
+    tn = in_band / rows_here;
+    tm = band * gm + (in_band - tn * rows_here);
+}
+
 // Instruction descriptor, kind::f16: D fp32, A/B fp16, A K-major, B MN-major (N contiguous), M128, N256.
 //   [4,6) D format 1 = F32   [7,10) A format 0 = F16   [10,13) B format 0 = F16
 //   bit 15 A major (0 = K)   bit 16 B major (1 = MN)   [17,23) N >> 3   [24,29) M >> 4
@@ -106,7 +120,7 @@ constexpr uint32_t HG_IDESC = (1u << 4) | (1u << 16) | ((uint32_t)(HG_BN >> 3) <
 
 __global__ void __launch_bounds__(HG_THREADS, 1)
 hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float *__restrict__ C,
-                int M, int N, int K, int c_vec_ok) {
+                int M, int N, int K, int c_vec_ok, int gm) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[HG_STAGES];
     __shared__ __align__(8) uint64_t empty_bar[HG_STAGES];
@@ -154,7 +168,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * HG_BM, n0 = (tile / tiles_m) * HG_BN;
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
+                const int m0 = tm * HG_BM, n0 = tn * HG_BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % HG_STAGES;
                     const uint32_t use = it / HG_STAGES;
@@ -214,7 +230,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const uint32_t acc = local_tile & 1, acc_use = local_tile >> 1;
-            const int m0 = (tile % tiles_m) * HG_BM, n0 = (tile / tiles_m) * HG_BN;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
+            const int m0 = tm * HG_BM, n0 = tn * HG_BN;
             ok = __all_sync(0xffffffffu, mbar_wait_abortable(&acc_full_bar[acc], acc_use & 1, abortp));
             if (!ok) break;
             tc_fence_after();
@@ -256,6 +274,216 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
 }
 
+// ---------------------------------------------------------------------------------
+// Two-CTA variant: a cluster of two CTAs (an SM pair) computes one 256 x 256 tile.
+// Each CTA stages its own 128 rows of A and its own 128 columns of B (plain TMA
+// loads, no multicast; both CTAs' loads signal the leader's mbarrier), the leader
+// issues tcgen05.mma.cta_group::2 (M256 N256 K16), which reads B halves from both
+// CTAs, and every CTA keeps the accumulator of its 128 rows in its own tensor
+// memory.  Per SM this halves the shared-memory traffic for B and leaves room for
+// a 6-stage ring.
+// ---------------------------------------------------------------------------------
+constexpr int H2_STAGES = 6;
+constexpr int H2_B_BYTES = HG_BK * 128 * 2;                 // 16 KB: two 64-column boxes
+constexpr int H2_STAGE_BYTES = HG_A_BYTES + H2_B_BYTES;     // 32 KB per CTA and stage
+constexpr int H2_SMEM_BYTES = H2_STAGES * H2_STAGE_BYTES + 1024;
+constexpr uint32_t H2_IDESC = (1u << 4) | (1u << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local` in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void *local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(local)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of one CTA of a pair; completion bytes go to the mbarrier at `bar_cluster_addr` (the leader's)
+__device__ __forceinline__ void tma_load_2d_pair(void *dst_smem, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void tc2_commit_both(uint64_t *bar) {  // arrives on `bar` in both CTAs of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(bar)),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void tc2_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HG_THREADS, 1)
+hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float *__restrict__ C,
+                 int M, int N, int K, int c_vec_ok, int gm) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[H2_STAGES];   // used in the leader only
+    __shared__ __align__(8) uint64_t empty_bar[H2_STAGES];  // one per CTA, signalled by the leader's commits
+    __shared__ __align__(8) uint64_t acc_full_bar[2];       // one per CTA
+    __shared__ __align__(8) uint64_t acc_empty_bar[2];      // leader only: 8 epilogue warps of the pair arrive
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    unsigned char *tiles = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + HG_BK - 1) / HG_BK;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < H2_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full_bar[i], 1);
+            mbar_init(&acc_empty_bar[i], 8);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(HG_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (one lane in each CTA) ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
+                const int m0 = tm * 256 + (int)rank * 128;
+                const int n0 = tn * 256 + (int)rank * 128;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % H2_STAGES;
+                    const uint32_t use = it / H2_STAGES;
+                    if (use > 0) {
+                        ok = mbar_wait_abortable(&empty_bar[s], (use - 1) & 1, abortp);
+                        if (!ok) break;
+                    }
+                    unsigned char *a_dst = tiles + (size_t)s * H2_STAGE_BYTES;
+                    unsigned char *b_dst = a_dst + HG_A_BYTES;
+                    if (leader) mbar_expect_tx(&full_bar[s], 2 * H2_STAGE_BYTES);  // bytes of both CTAs
+                    const uint32_t bar = map_to_cta(&full_bar[s], 0);
+                    tma_load_2d_pair(a_dst, &map_a, kb * HG_BK, m0, bar);
+                    tma_load_2d_pair(b_dst, &map_b, n0, kb * HG_BK, bar);
+                    tma_load_2d_pair(b_dst + HG_BK * 128, &map_b, n0 + 64, kb * HG_BK, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (leader && lane == 0) {
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++local_tile) {
+                const uint32_t acc = local_tile & 1, acc_use = local_tile >> 1;
+                if (acc_use > 0) {
+                    ok = mbar_wait_abortable(&acc_empty_bar[acc], (acc_use - 1) & 1, abortp);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                const uint32_t d_tmem = tmem_base + acc * 256;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % H2_STAGES;
+                    ok = mbar_wait_abortable(&full_bar[s], (it / H2_STAGES) & 1, abortp);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * H2_STAGE_BYTES);
+                    const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
+                    const uint64_t b_desc = make_smem_desc(a_addr + HG_A_BYTES, HG_BK * 128, 1024);
+#pragma unroll
+                    for (int k16 = 0; k16 < HG_BK / 16; ++k16)
+                        tc2_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), H2_IDESC,
+                                    (kb > 0 || k16 > 0) ? 1u : 0u);
+                    tc2_commit_both(&empty_bar[s]);  // frees this stage in both CTAs
+                }
+                if (ok) tc2_commit_both(&acc_full_bar[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 of each CTA, its own 128 rows ----------------
+        const int quarter = warp & 3;
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++local_tile) {
+            const uint32_t acc = local_tile & 1, acc_use = local_tile >> 1;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
+            const int m0 = tm * 256 + (int)rank * 128, n0 = tn * 256;
+            ok = __all_sync(0xffffffffu, mbar_wait_abortable(&acc_full_bar[acc], acc_use & 1, abortp));
+            if (!ok) break;
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
+#pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+                uint32_t v[32];
+                tc_ld_32cols(taddr + c * 32, v);
+                tc_wait_ld();
+                const int col0 = n0 + c * 32;
+                if (row < M && col0 < N) {
+                    float *dst = C + (size_t)row * N + col0;
+                    if (c_vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            *reinterpret_cast<float4 *>(dst + 4 * j) =
+                                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                            __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty_bar[acc], 0));
+        }
+    }
+
+    // ---------------- teardown: nobody leaves while the peer may still signal or read ----------------
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(HG_TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side -----------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -278,7 +506,7 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D fp16 tensor map: `inner` contiguous elements per row, `outer` rows, box of 64 x box_rows, 128-byte swizzle.
-static int make_map_f16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint32_t box_rows) {
+static int make_map_f16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint32_t box_rows) {  // box: 64 x box_rows
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return TB200_ERR_DRIVER;
     cuuint64_t dims[2] = {inner, outer};
@@ -318,11 +546,27 @@ extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uin
     if (st) return st;
     st = make_map_f16(&map_b, b, (uint64_t)n, (uint64_t)k, HG_BK);
     if (st) return st;
+    const int c_vec_ok = aligned_to(c, 16) && n % 4 == 0;
+    // tile rows per band: the band's A panels (rows x k halves) should take about 48 MB of the 126 MB L2
+    auto band_rows = [&](int tile_m) {
+        long long g = (48ll << 20) / ((long long)tile_m * k * 2);
+        return (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
+    };
+    // SM pairs pay off once there are at least two waves of 256 x 256 tiles; smaller products fill the
+    // machine better with 128 x 256 tiles on single CTAs
+    if (g_hgemm_pairs && ((m + 255) / 256) * ((n + 255) / 256) >= 2 * (di->sm_count / 2)) {
+        // SM pairs: 256 x 256 tiles, one cluster of two CTAs each
+        st = ensure_smem_optin<hgemm_tc2_kernel>(di);
+        if (st) return st;
+        const int tiles2 = ((m + 255) / 256) * ((n + 255) / 256);
+        const int pairs = tiles2 < di->sm_count / 2 ? tiles2 : di->sm_count / 2;
+        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, c, m, n, k, c_vec_ok, band_rows(256));
+        return check_launch();
+    }
     st = ensure_smem_optin<hgemm_tc_kernel>(di);
     if (st) return st;
     const int tiles = ((m + HG_BM - 1) / HG_BM) * ((n + HG_BN - 1) / HG_BN);
     const int grid = tiles < di->sm_count ? tiles : di->sm_count;
-    const int c_vec_ok = aligned_to(c, 16) && n % 4 == 0;
-    hgemm_tc_kernel<<<grid, HG_THREADS, HG_SMEM_BYTES, s>>>(map_a, map_b, c, m, n, k, c_vec_ok);
+    hgemm_tc_kernel<<<grid, HG_THREADS, HG_SMEM_BYTES, s>>>(map_a, map_b, c, m, n, k, c_vec_ok, band_rows(HG_BM));
     return check_launch();
 }
