@@ -3,8 +3,9 @@
 
 Headline workload (BASELINE.json configs[3]): Q8_0 quantised GEMV, decode style,
 W[14336 x 4096] as 32-element int8 blocks with one fp16 scale each, fp32
-activations, batch 1.  One "step" is one pass over LAYERS distinct weight
-matrices (LAYERS * 62.4 MB > the 126 MB L2, so every pass streams from HBM).
+activations, batch 1.  One "step" is one decode pass over LAYERS = 32 distinct
+weight matrices of that shape, one per decoder layer (2.0 GB > the 126 MB L2, so
+every mat-vec streams its weights from HBM).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -33,7 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 ROWS, COLS, BATCH = 14336, 4096, 1
-LAYERS = 8  # distinct weight matrices per step: 8 * 62.4 MB = 499 MB footprint
+LAYERS = 32  # one step = this projection in each of 32 decoder layers (Llama-3-8B depth): 32 distinct matrices, 2.0 GB
 # dram__bytes_read.sum + dram__bytes_write.sum of one 14336 x 4096 integer-mode launch, from the ncu capture
 # summarised in profiles/q8s_gemv_int_14336x4096.md (62.45 MB read + ~0.15 MB written)
 NCU_TRAFFIC_BYTES_PER_GEMV = 62_600_000
