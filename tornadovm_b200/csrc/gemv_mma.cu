@@ -11,13 +11,18 @@
 // its eight warps take one unit each and walk K together in chunks of 8 blocks
 // (256 columns): all threads cp.async the chunk's weights (8 units x 16 rows)
 // and the chunk of the quantised activations into a 4-stage shared-memory ring,
-// one __syncthreads per chunk.  Rows are padded to a 272- / 144-byte pitch in
-// shared memory so that the fragment loads are bank-conflict free.
+// one __syncthreads per chunk.  Two warps share a unit and take half of the
+// chunk's blocks each (more warps per scheduler hide the shared-memory and mma
+// latencies); their partial sums are added in a fixed order when the unit is
+// complete.  Rows are padded to a 272- / 144-byte pitch in shared memory so
+// that the fragment loads are bank-conflict free.
 #include "common.cuh"
 
 namespace tb200 {
 
-constexpr int MM_THREADS = 256, MM_WARPS = 8, MM_KB = 8 /* blocks per chunk */, MM_STAGES = 4;
+constexpr int MM_WARPS = 8 /* 16-row units per round */, MM_KSPLIT = 2 /* warps per unit */;
+constexpr int MM_THREADS = MM_WARPS * MM_KSPLIT * 32, MM_KB = 8 /* blocks per chunk */;
+constexpr int MM_STAGES = 4;
 
 __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                              uint32_t b1) {
@@ -52,9 +57,14 @@ struct MmaStage {
     static constexpr int X_OFF = T::W_BYTES + T::SC_BYTES;
     static constexpr int XS_OFF = X_OFF + BP * 272;
     static constexpr int BYTES = (XS_OFF + BP * 32 + 127) & ~127;
+    static constexpr int W_ONLY_BYTES = (X_OFF + 127) & ~127;  // a stage without the activation chunk
 };
 
-template <int FMT, int NT>
+// XFULL: all quantised activations (and their scales) are staged in shared memory once, in the prologue.
+// Otherwise every K chunk re-reads its slice of them from L2 -- which all CTAs then do at the same moment
+// for the same addresses; that hot spot costs about a microsecond per chunk, so XFULL is used whenever
+// the vectors fit beside the weight ring.
+template <int FMT, int NT, bool XFULL>
 __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
     using T = MmaTraits<FMT>;
     using S = MmaStage<FMT, NT>;
@@ -62,7 +72,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
     const int cols = a.cols, rows = a.rows, batch = a.batch;
     const int bpr = cols / 32;
     const int nkc = bpr / MM_KB;  // cols % 256 == 0
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = (tid >> 5) % MM_WARPS;   // unit slot of this warp
+    const int khalf = (tid >> 5) / MM_WARPS;  // which blocks of a chunk it takes
     const int g = lane >> 2, t = lane & 3;
 
     const int nunits = (rows + 15) / 16;
@@ -70,6 +82,12 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
     const int uend = (int)((long long)nunits * (blockIdx.x + 1) / gridDim.x);
     const int nrounds = (uend - ubeg + MM_WARPS - 1) / MM_WARPS;
     const int total = nrounds * nkc;
+    constexpr int STAGE_BYTES = XFULL ? S::W_ONLY_BYTES : S::BYTES;
+    float *red = reinterpret_cast<float *>(smem_raw + (size_t)MM_STAGES * STAGE_BYTES);  // [unit slot][lane][NT*4]
+    // resident activations: int8 rows with a pitch of cols + 16 bytes (bank spread), then fp32 scales [vector][block]
+    const int xpitch = cols + 16;
+    unsigned char *xfull = reinterpret_cast<unsigned char *>(red + MM_WARPS * 32 * NT * 4);
+    float *xsfull = reinterpret_cast<float *>(xfull + (size_t)S::BP * xpitch);
 
     // Copy plan of this thread: it always moves the same (row, piece) slots of a chunk, so the source
     // pointers are set up once per round and only advance along K afterwards.
@@ -103,7 +121,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
             const int i = tid + m * MM_THREADS;
             const int rl = i / T::PP, p = i - rl * T::PP;
             wsrc[m] = nullptr;
-            if (i < MM_WARPS * 16 * T::PP) {
+            // unit slots past the end of this CTA's range copy nothing (their warps idle through the round)
+            if (i < MM_WARPS * 16 * T::PP && ufirst + (rl >> 4) < uend) {
                 const size_t grow = (size_t)min((ufirst + (rl >> 4)) * 16 + (rl & 15), rows - 1);
                 if (FMT == FMT_Q8S) {
                     if (p < 16) {
@@ -124,13 +143,13 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
     plan_round(0);
     auto issue = [&](int it) {
         if (it < total) {
-            const uint32_t base_s = smem_u32(smem_raw + (size_t)(it % MM_STAGES) * S::BYTES);
+            const uint32_t base_s = smem_u32(smem_raw + (size_t)(it % MM_STAGES) * STAGE_BYTES);
 #pragma unroll
             for (int m = 0; m < NW; ++m)
                 if (wsrc[m]) cp_async_16(base_s + wdst[m], wsrc[m] + (size_t)issue_kc * wstep[m]);
 #pragma unroll
             for (int m = 0; m < NX; ++m)
-                if (xsrc[m]) cp_async_16(base_s + xdst[m], xsrc[m] + (size_t)issue_kc * xstep[m]);
+                if (!XFULL && xsrc[m]) cp_async_16(base_s + xdst[m], xsrc[m] + (size_t)issue_kc * xstep[m]);
             if (++issue_kc == nkc) {
                 issue_kc = 0;
                 if (++issue_round < nrounds) plan_round(issue_round);
@@ -141,6 +160,16 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
 
 #pragma unroll
     for (int s = 0; s < MM_STAGES - 1; ++s) issue(s);
+    if (XFULL) {
+        // visible to all warps after the first chunk's __syncthreads
+        const int n16 = cols / 16;
+        for (int i = tid; i < batch * n16; i += MM_THREADS) {
+            const int b = i / n16, p = i - b * n16;
+            *reinterpret_cast<uint4 *>(xfull + (size_t)b * xpitch + p * 16) =
+                __ldg(reinterpret_cast<const uint4 *>(a.xq + (size_t)b * cols) + p);
+        }
+        for (int i = tid; i < batch * bpr; i += MM_THREADS) xsfull[i] = __ldg(a.xs + i);
+    }
 
     float acc[NT][4];
     for (int it = 0; it < total; ++it) {
@@ -148,9 +177,9 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
         __syncthreads();             // chunk `it` has landed for everyone; chunk it-1 is no longer read
         issue(it + MM_STAGES - 1);   // refills the stage of chunk it-1
         const int round = it / nkc, kc = it - round * nkc;
-        const unsigned char *base = smem_raw + (size_t)(it % MM_STAGES) * S::BYTES;
+        const unsigned char *base = smem_raw + (size_t)(it % MM_STAGES) * STAGE_BYTES;
         const int unit = ubeg + round * MM_WARPS + warp;
-        if (unit >= uend) continue;  // warp-uniform; the warp still took part in the copies and the barrier
+        const bool active = unit < uend;  // warp-uniform; an idle warp still takes part in copies and barriers
         if (kc == 0) {
 #pragma unroll
             for (int j = 0; j < NT; ++j)
@@ -160,14 +189,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
         const unsigned char *rp0 = base + (warp * 16 + g) * T::WS;
         const unsigned char *rp1 = rp0 + 8 * T::WS;
 #pragma unroll
-        for (int kb = 0; kb < MM_KB; ++kb) {
+        for (int kbi = 0; kbi < (active ? MM_KB / MM_KSPLIT : 0); ++kbi) {
+            const int kb = khalf * (MM_KB / MM_KSPLIT) + kbi;  // kb % 2 == kbi % 2
             uint32_t a0, a1, a2, a3;
             float sw0, sw1;
             if (FMT == FMT_Q8B) {
                 constexpr int dummy = 0;
                 (void)dummy;
                 const int off = kb * 34 + 2 + 4 * t;
-                if (kb % 2 == 0) {  // 34*kb + 2 is 2 modulo 4
+                if (kbi % 2 == 0) {  // 34*kb + 2 is 2 modulo 4
                     a0 = lds_u32_at<1>(rp0, off), a1 = lds_u32_at<1>(rp1, off);
                     a2 = lds_u32_at<1>(rp0, off + 16), a3 = lds_u32_at<1>(rp1, off + 16);
                 } else {
@@ -179,7 +209,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
             } else if (FMT == FMT_Q4B) {
                 const int off = kb * 18 + 2 + 4 * t;
                 uint32_t w0, w1;
-                if (kb % 2 == 0) w0 = lds_u32_at<1>(rp0, off), w1 = lds_u32_at<1>(rp1, off);
+                if (kbi % 2 == 0) w0 = lds_u32_at<1>(rp0, off), w1 = lds_u32_at<1>(rp1, off);
                 else w0 = lds_u32_at<0>(rp0, off), w1 = lds_u32_at<0>(rp1, off);
                 // byte i holds element i (low nibble) and element i + 16 (high nibble)
                 a0 = w0 & 0x0F0F0F0Fu, a2 = (w0 >> 4) & 0x0F0F0F0Fu;
@@ -196,7 +226,8 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
             }
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const unsigned char *xrow = base + S::X_OFF + (j * 8 + g) * 272 + kb * 32 + 4 * t;
+                const unsigned char *xrow = XFULL ? xfull + (size_t)(j * 8 + g) * xpitch + (kc * MM_KB + kb) * 32 + 4 * t
+                                                  : base + S::X_OFF + (j * 8 + g) * 272 + kb * 32 + 4 * t;
                 const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xrow);
                 const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xrow + 16);
                 int d[4];
@@ -207,8 +238,15 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
                     mma_s8_16832(sx, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1);
                     d[0] -= 8 * sx[0], d[1] -= 8 * sx[1], d[2] -= 8 * sx[0], d[3] -= 8 * sx[1];
                 }
-                const float *xsp = reinterpret_cast<const float *>(base + S::XS_OFF) + (j * 8 + 2 * t) * 8 + kb;
-                const float x0 = xsp[0], x1 = xsp[8];
+                float x0, x1;
+                if (XFULL) {
+                    // vectors beyond the batch read shared memory that was never written: their outputs are dropped
+                    const float *xsp = xsfull + (size_t)(j * 8 + 2 * t) * bpr + kc * MM_KB + kb;
+                    x0 = xsp[0], x1 = xsp[bpr];
+                } else {
+                    const float *xsp = reinterpret_cast<const float *>(base + S::XS_OFF) + (j * 8 + 2 * t) * 8 + kb;
+                    x0 = xsp[0], x1 = xsp[8];
+                }
                 acc[j][0] = fmaf((float)d[0], sw0 * x0, acc[j][0]);
                 acc[j][1] = fmaf((float)d[1], sw0 * x1, acc[j][1]);
                 acc[j][2] = fmaf((float)d[2], sw1 * x0, acc[j][2]);
@@ -216,34 +254,56 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
             }
         }
         if (kc == nkc - 1) {
-            const int r0 = unit * 16 + g, r1 = r0 + 8;
+            // the round is complete: the second warp of each unit hands its partial tile to the first
+            float *tile = red + (size_t)warp * 32 * NT * 4 + lane * NT * 4;
+            if (khalf == 1) {
 #pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                const int n0 = j * 8 + 2 * t, n1 = n0 + 1;
-                if (n0 < batch) {
-                    if (r0 < rows) a.y[(size_t)n0 * rows + r0] = acc[j][0];
-                    if (r1 < rows) a.y[(size_t)n0 * rows + r1] = acc[j][2];
-                }
-                if (n1 < batch) {
-                    if (r0 < rows) a.y[(size_t)n1 * rows + r0] = acc[j][1];
-                    if (r1 < rows) a.y[(size_t)n1 * rows + r1] = acc[j][3];
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) tile[j * 4 + i] = acc[j][i];
+            }
+            __syncthreads();
+            if (khalf == 0 && active) {
+                const int r0 = unit * 16 + g, r1 = r0 + 8;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const float c0 = acc[j][0] + tile[j * 4 + 0], c1 = acc[j][1] + tile[j * 4 + 1];
+                    const float c2 = acc[j][2] + tile[j * 4 + 2], c3 = acc[j][3] + tile[j * 4 + 3];
+                    const int n0 = j * 8 + 2 * t, n1 = n0 + 1;
+                    if (n0 < batch) {
+                        if (r0 < rows) a.y[(size_t)n0 * rows + r0] = c0;
+                        if (r1 < rows) a.y[(size_t)n0 * rows + r1] = c2;
+                    }
+                    if (n1 < batch) {
+                        if (r0 < rows) a.y[(size_t)n1 * rows + r0] = c1;
+                        if (r1 < rows) a.y[(size_t)n1 * rows + r1] = c3;
+                    }
                 }
             }
+            // `red` is written again only at the end of the next round, behind that round's barriers
         }
     }
     cp_async_wait<0>();
 }
 
+template <int FMT, int NT, bool XFULL>
+static int launch_qmma_x(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, size_t smem) {
+    constexpr auto kernel = qmma_gemv_kernel<FMT, NT, XFULL>;
+    int st = ensure_smem_optin<kernel>(di);
+    if (st) return st;
+    const int nunits = (a.rows + 15) / 16;
+    const int grid = nunits < di->sm_count ? nunits : di->sm_count;
+    return launch_kernel(kernel, dim3(grid), dim3(MM_THREADS), smem, s, false, a);  // follows the quantiser kernel: plain stream order
+}
+
 template <int FMT, int NT>
 static int launch_qmma(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     using S = MmaStage<FMT, NT>;
-    constexpr auto kernel = qmma_gemv_kernel<FMT, NT>;
-    int st = ensure_smem_optin<kernel>(di);
-    if (st) return st;
-    const size_t smem = (size_t)MM_STAGES * S::BYTES;
-    const int nunits = (a.rows + 15) / 16;
-    const int grid = nunits < di->sm_count ? nunits : di->sm_count;
-    return launch_kernel(kernel, dim3(grid), dim3(MM_THREADS), smem, s, false, a);
+    const size_t red = (size_t)MM_WARPS * 32 * NT * 4 * sizeof(float);
+    const size_t xfull = (size_t)S::BP * (a.cols + 16) + (size_t)S::BP * (a.cols / 32) * 4;
+    const size_t resident = (size_t)MM_STAGES * S::W_ONLY_BYTES + red + xfull;
+    if (resident + 1024 <= (size_t)di->max_smem_optin) return launch_qmma_x<FMT, NT, true>(a, di, s, resident);
+    return launch_qmma_x<FMT, NT, false>(a, di, s, (size_t)MM_STAGES * S::BYTES + red);
 }
 
 // Entry used by the dispatcher of gemv_quant.cu: already quantised activations (xq, xs), 5 <= batch <= 16.

@@ -1022,6 +1022,14 @@ static int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs
     if (nblocks == 0) return TB200_OK;
     int grid = (nblocks + 7) / 8;
     if (grid > di->sm_count * 8) grid = di->sm_count * 8;
+    // The mat-vec kernels that follow run with the SM's largest shared-memory carve-out.  Without this hint the
+    // driver would switch the carve-out for this small kernel and back, draining the SMs twice (about 15 us).
+    static bool hinted[kMaxDevices];
+    if (!hinted[di->device]) {
+        cudaFuncSetAttribute(quantize_x_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaGetLastError();
+        hinted[di->device] = true;
+    }
     quantize_x_kernel<<<grid, 256, 0, s>>>(x, xq, xs, nblocks);
     return check_launch();
 }
