@@ -112,6 +112,45 @@ def test_q4_gemv_float_mode(lib, rows, cols, batch, header):
     assert dy.guard_intact() and dw.guard_intact()
 
 
+TB200_OPT_FLOAT_TENSOR_CORES = 3
+
+
+@pytest.mark.parametrize("rows,cols,batch", [(257, 4096, 1), (20000, 512, 2), (1024, 4096, 4), (100, 2048, 5), (48, 1024, 8), (31, 768, 16),
+                                              (2400, 256, 3)])
+@pytest.mark.parametrize("fmt", ["q8", "q8b", "q4b"])
+@pytest.mark.parametrize("setting", [0, 2])
+def test_float_mode_tensor_core_setting(lib, rows, cols, batch, fmt, setting):
+    """Float mode on the CUDA cores (0) and forced onto the tensor cores (2): both within the fp32 bound."""
+    if fmt == "q4b":
+        blocks, _, x = o.make_q4(rows, cols, batch)
+        y64 = np.stack([o.q4_gemv_f64(blocks, x[b * cols:(b + 1) * cols], cols, rows) for b in range(batch)])
+        yref = np.stack([o.q4_gemv_seq(blocks, x[b * cols:(b + 1) * cols], cols, rows) for b in range(batch)])
+    else:
+        q, s, x, blocks = _q8_case(rows, cols, batch)
+        y64, yref = _q8_oracle(q, s, x, rows, cols, batch)
+    dx, dy = DevBuf(x), out_buf(rows * batch)
+    _ok(lib.tb200_set_option(TB200_OPT_FLOAT_TENSOR_CORES, setting), lib)
+    try:
+        if fmt == "q8":
+            dq, ds = DevBuf(q), DevBuf(s)
+            st = lib.tb200_q8_gemv(rows, cols, batch, dq.ptr, ds.ptr, dx.ptr, dy.ptr, stream_ptr())
+        elif fmt == "q8b":
+            dq = DevBuf(blocks)
+            st = lib.tb200_q8b_gemv(rows, cols, batch, dq.ptr, dx.ptr, dy.ptr, stream_ptr())
+        else:
+            dq = DevBuf(blocks)
+            st = lib.tb200_q4b_gemv(rows, cols, batch, dq.ptr, dx.ptr, dy.ptr, stream_ptr())
+        _ok(st, lib)
+        sync_and_check(lib)
+    finally:
+        lib.tb200_set_option(TB200_OPT_FLOAT_TENSOR_CORES, 1)
+    got = dy.numpy().reshape(batch, rows)
+    err = o.rel_l2(got, y64)
+    assert err <= REL_L2_FP32
+    assert err <= max(o.rel_l2(yref, y64), 3e-7), (err, o.rel_l2(yref, y64))
+    assert dy.guard_intact() and dq.guard_intact()
+
+
 # --------------------------------------------------------------------------- integer path
 def _workspace(lib, cols, batch):
     n = lib.tb200_qx_workspace_bytes(cols, batch)

@@ -6,6 +6,8 @@
 namespace tb200 {
 
 int g_overlap_launches = 0;
+int g_float_tensor_cores = 1;
+int g_float_tc_min_batch = 0;  // 0: per-format default, 1: every eligible call
 extern int g_hgemm_pairs;
 
 static DeviceInfo g_info[kMaxDevices];
@@ -98,6 +100,10 @@ extern "C" int tb200_set_option(int option, int value) {
         case TB200_OPT_HGEMM_SM_PAIRS:
             tb200::g_hgemm_pairs = value != 0;
             return TB200_OK;
+        case TB200_OPT_FLOAT_TENSOR_CORES:
+            tb200::g_float_tensor_cores = value != 0;
+            tb200::g_float_tc_min_batch = value >= 2 ? 1 : 0;
+            return TB200_OK;
         default:
             return TB200_ERR_INVALID_ARG;
     }
@@ -111,6 +117,9 @@ extern "C" int tb200_get_option(int option, int *value) {
             return TB200_OK;
         case TB200_OPT_HGEMM_SM_PAIRS:
             *value = tb200::g_hgemm_pairs;
+            return TB200_OK;
+        case TB200_OPT_FLOAT_TENSOR_CORES:
+            *value = tb200::g_float_tensor_cores ? 1 + tb200::g_float_tc_min_batch : 0;
             return TB200_OK;
         default:
             return TB200_ERR_INVALID_ARG;

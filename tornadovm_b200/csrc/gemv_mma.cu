@@ -32,6 +32,25 @@ __device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Four bytes 0..255 -> two half2 registers holding (byte - bias): the byte is spliced into the mantissa of
+// fp16 1024.0 (exponent bits 0x64), which makes 1024 + byte exactly, and the bias is removed with one HSUB2.
+__device__ __forceinline__ void u8x4_to_h2x2(uint32_t u, uint32_t bias_h2, uint32_t &lo, uint32_t &hi) {
+    const uint32_t l = __byte_perm(u, 0x64646464u, 0x4140);  // bytes 0,1
+    const uint32_t h = __byte_perm(u, 0x64646464u, 0x4342);  // bytes 2,3
+    __half2 lv = __hsub2(*reinterpret_cast<const __half2 *>(&l), *reinterpret_cast<const __half2 *>(&bias_h2));
+    __half2 hv = __hsub2(*reinterpret_cast<const __half2 *>(&h), *reinterpret_cast<const __half2 *>(&bias_h2));
+    lo = *reinterpret_cast<uint32_t *>(&lv);
+    hi = *reinterpret_cast<uint32_t *>(&hv);
+}
+
 // 32-bit read at a byte offset that is 0 or 2 modulo 4
 template <int MISALIGNED>
 __device__ __forceinline__ uint32_t lds_u32_at(const unsigned char *base, int off) {
@@ -64,8 +83,18 @@ struct MmaStage {
 // Otherwise every K chunk re-reads its slice of them from L2 -- which all CTAs then do at the same moment
 // for the same addresses; that hot spot costs about a microsecond per chunk, so XFULL is used whenever
 // the vectors fit beside the weight ring.
-template <int FMT, int NT, bool XFULL>
+//
+// XM selects how the activations reach the tensor cores:
+//   0  int8, one slice per K chunk (the vectors do not fit in shared memory)
+//   1  int8, resident
+//   2  fp32 activations ("float mode"), resident as fp16 pairs: x = hi + lo with hi = fp16(x) and
+//      lo = fp16(x - hi), relative error 2^-22.  Weights are exact in fp16, every product is exact in
+//      fp32, so one m16n8k16 fp16 MMA with fp32 accumulation per 16 columns computes the reference's
+//      fp32 dot products to fp32 accuracy; column 2b of the MMA's B operand carries hi of vector b and
+//      column 2b+1 its lo part, and the two result columns are added.
+template <int FMT, int NT, int XM>
 __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
+    constexpr bool XFULL = XM != 0, FLT = XM == 2;
     using T = MmaTraits<FMT>;
     using S = MmaStage<FMT, NT>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -85,7 +114,7 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
     constexpr int STAGE_BYTES = XFULL ? S::W_ONLY_BYTES : S::BYTES;
     float *red = reinterpret_cast<float *>(smem_raw + (size_t)MM_STAGES * STAGE_BYTES);  // [unit slot][lane][NT*4]
     // resident activations: int8 rows with a pitch of cols + 16 bytes (bank spread), then fp32 scales [vector][block]
-    const int xpitch = cols + 16;
+    const int xpitch = FLT ? cols * 2 + 32 : cols + 16;  // float mode: 8-byte reads, rows 8 banks apart
     unsigned char *xfull = reinterpret_cast<unsigned char *>(red + MM_WARPS * 32 * NT * 4);
     float *xsfull = reinterpret_cast<float *>(xfull + (size_t)S::BP * xpitch);
 
@@ -160,7 +189,23 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
 
 #pragma unroll
     for (int s = 0; s < MM_STAGES - 1; ++s) issue(s);
-    if (XFULL) {
+    if (FLT) {
+        // weights are on their way; the activations may come from the kernel before this one
+        pdl_launch_dependents();
+        pdl_wait();
+        const int n4 = cols / 4;
+        for (int i = tid; i < batch * n4; i += MM_THREADS) {
+            const int b = i / n4, c4 = i - b * n4;
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)b * cols) + c4);
+            const __half h0 = __float2half_rn(v.x), h1 = __float2half_rn(v.y), h2 = __float2half_rn(v.z), h3 = __float2half_rn(v.w);
+            const __half l0 = __float2half_rn(v.x - __half2float(h0)), l1 = __float2half_rn(v.y - __half2float(h1));
+            const __half l2 = __float2half_rn(v.z - __half2float(h2)), l3 = __float2half_rn(v.w - __half2float(h3));
+            __half2 *hp = reinterpret_cast<__half2 *>(xfull + (size_t)(2 * b) * xpitch + c4 * 8);
+            __half2 *lp = reinterpret_cast<__half2 *>(xfull + (size_t)(2 * b + 1) * xpitch + c4 * 8);
+            hp[0] = __halves2half2(h0, h1), hp[1] = __halves2half2(h2, h3);
+            lp[0] = __halves2half2(l0, l1), lp[1] = __halves2half2(l2, l3);
+        }
+    } else if (XFULL) {
         // visible to all warps after the first chunk's __syncthreads
         const int n16 = cols / 16;
         for (int i = tid; i < batch * n16; i += MM_THREADS) {
@@ -224,6 +269,31 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
                 sw0 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(sp));
                 sw1 = half_bits_to_float(*reinterpret_cast<const uint16_t *>(sp + 8 * 16));
             }
+            if (FLT) {
+                // group 0 = elements 0..15 of the block, group 1 = elements 16..31; within a group this thread
+                // owns elements 4t..4t+3, which it feeds to the MMA as k = {2t, 2t+1} and {2t+8, 2t+9}
+                uint32_t p0, p1, p2, p3, q0, q1, q2, q3;
+                if (FMT == FMT_Q4B) {
+                    u8x4_to_h2x2(a0, 0x64086408u, p0, p2), u8x4_to_h2x2(a1, 0x64086408u, p1, p3);
+                    u8x4_to_h2x2(a2, 0x64086408u, q0, q2), u8x4_to_h2x2(a3, 0x64086408u, q1, q3);
+                } else {
+                    u8x4_to_h2x2(a0 ^ 0x80808080u, 0x64806480u, p0, p2), u8x4_to_h2x2(a1 ^ 0x80808080u, 0x64806480u, p1, p3);
+                    u8x4_to_h2x2(a2 ^ 0x80808080u, 0x64806480u, q0, q2), u8x4_to_h2x2(a3 ^ 0x80808080u, 0x64806480u, q1, q3);
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const unsigned char *xrow = xfull + (size_t)(j * 8 + g) * xpitch + ((kc * MM_KB + kb) * 32 + 4 * t) * 2;
+                    const uint2 bA = *reinterpret_cast<const uint2 *>(xrow);
+                    const uint2 bB = *reinterpret_cast<const uint2 *>(xrow + 32);
+                    float d[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_f16_16816(d, p0, p1, p2, p3, bA.x, bA.y);
+                    mma_f16_16816(d, q0, q1, q2, q3, bB.x, bB.y);
+                    // columns 2t (hi part) and 2t+1 (lo part) belong to vector j*4 + t
+                    acc[j][0] = fmaf(d[0] + d[1], sw0, acc[j][0]);
+                    acc[j][2] = fmaf(d[2] + d[3], sw1, acc[j][2]);
+                }
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 const unsigned char *xrow = XFULL ? xfull + (size_t)(j * 8 + g) * xpitch + (kc * MM_KB + kb) * 32 + 4 * t
@@ -269,6 +339,14 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
                 for (int j = 0; j < NT; ++j) {
                     const float c0 = acc[j][0] + tile[j * 4 + 0], c1 = acc[j][1] + tile[j * 4 + 1];
                     const float c2 = acc[j][2] + tile[j * 4 + 2], c3 = acc[j][3] + tile[j * 4 + 3];
+                    if (FLT) {
+                        const int n = j * 4 + t;
+                        if (n < batch) {
+                            if (r0 < rows) a.y[(size_t)n * rows + r0] = c0;
+                            if (r1 < rows) a.y[(size_t)n * rows + r1] = c2;
+                        }
+                        continue;
+                    }
                     const int n0 = j * 8 + 2 * t, n1 = n0 + 1;
                     if (n0 < batch) {
                         if (r0 < rows) a.y[(size_t)n0 * rows + r0] = c0;
@@ -286,14 +364,14 @@ __global__ void __launch_bounds__(MM_THREADS, 1) qmma_gemv_kernel(QGemvArgs a) {
     cp_async_wait<0>();
 }
 
-template <int FMT, int NT, bool XFULL>
-static int launch_qmma_x(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, size_t smem) {
-    constexpr auto kernel = qmma_gemv_kernel<FMT, NT, XFULL>;
+template <int FMT, int NT, int XM>
+static int launch_qmma_x(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, size_t smem, bool overlap = false) {
+    constexpr auto kernel = qmma_gemv_kernel<FMT, NT, XM>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
     const int nunits = (a.rows + 15) / 16;
     const int grid = nunits < di->sm_count ? nunits : di->sm_count;
-    return launch_kernel(kernel, dim3(grid), dim3(MM_THREADS), smem, s, false, a);  // follows the quantiser kernel: plain stream order
+    return launch_kernel(kernel, dim3(grid), dim3(MM_THREADS), smem, s, overlap, a);  // int modes follow the quantiser kernel: plain stream order
 }
 
 template <int FMT, int NT>
@@ -302,8 +380,8 @@ static int launch_qmma(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s)
     const size_t red = (size_t)MM_WARPS * 32 * NT * 4 * sizeof(float);
     const size_t xfull = (size_t)S::BP * (a.cols + 16) + (size_t)S::BP * (a.cols / 32) * 4;
     const size_t resident = (size_t)MM_STAGES * S::W_ONLY_BYTES + red + xfull;
-    if (resident + 1024 <= (size_t)di->max_smem_optin) return launch_qmma_x<FMT, NT, true>(a, di, s, resident);
-    return launch_qmma_x<FMT, NT, false>(a, di, s, (size_t)MM_STAGES * S::BYTES + red);
+    if (resident + 1024 <= (size_t)di->max_smem_optin) return launch_qmma_x<FMT, NT, 1>(a, di, s, resident);
+    return launch_qmma_x<FMT, NT, 0>(a, di, s, (size_t)MM_STAGES * S::BYTES + red);
 }
 
 // Entry used by the dispatcher of gemv_quant.cu: already quantised activations (xq, xs), 5 <= batch <= 16.
@@ -318,6 +396,30 @@ static bool qmma_eligible(const QGemvArgs &a) {
     if (a.batch < 5 || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !aligned_to(a.xq, 16) || !a.xs || !aligned_to(a.xs, 16)) return false;
     if (FMT == FMT_Q8S && (!a.scales || !aligned_to(a.scales, 16))) return false;
     return a.y != nullptr;
+}
+
+// Float mode (fp32 activations): batch <= 8 and vectors that stay resident in shared memory.
+template <int FMT>
+static bool qmma_float_eligible(const QGemvArgs &a, const DeviceInfo *di) {
+    if (a.batch < 1 || a.batch > 8 || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !a.x || !aligned_to(a.x, 16) || !a.y) return false;
+    if (FMT == FMT_Q8S && (!a.scales || !aligned_to(a.scales, 16))) return false;
+    const int nt = a.batch <= 4 ? 1 : 2;
+    const size_t need = (size_t)MM_STAGES * (nt == 1 ? MmaStage<FMT, 1>::W_ONLY_BYTES : MmaStage<FMT, 2>::W_ONLY_BYTES) +
+                        (size_t)MM_WARPS * 32 * nt * 4 * sizeof(float) + (size_t)nt * 8 * (a.cols * 2 + 32);
+    return need + 1024 <= (size_t)di->max_smem_optin;
+}
+
+template <int FMT, int NT>
+static int launch_qmma_float(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
+    using S = MmaStage<FMT, NT>;
+    const size_t smem = (size_t)MM_STAGES * S::W_ONLY_BYTES + (size_t)MM_WARPS * 32 * NT * 4 * sizeof(float) +
+                        (size_t)S::BP * (a.cols * 2 + 32);
+    return launch_qmma_x<FMT, NT, 2>(a, di, s, smem, overlap);
+}
+
+template <int FMT>
+static int qmma_float_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
+    return a.batch <= 4 ? launch_qmma_float<FMT, 1>(a, di, s, overlap) : launch_qmma_float<FMT, 2>(a, di, s, overlap);
 }
 
 }  // namespace tb200

@@ -857,6 +857,11 @@ template <int FMT>
 static bool qmma_eligible(const QGemvArgs &a);
 template <int FMT>
 static int qmma_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s);
+// the same kernel fed with fp32 activations split into fp16 pairs, batches of 1..8
+template <int FMT>
+static bool qmma_float_eligible(const QGemvArgs &a, const DeviceInfo *di);
+template <int FMT>
+static int qmma_float_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap);
 
 // Does one fast launch with `batch` activation vectors fit in shared memory?
 template <int FMT, int MODE>
@@ -984,6 +989,29 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
         if (path == PATH_GENERIC) return launch_generic<FMT, INT>(a, di, s);
         if constexpr (MODE == MODE_INT && !DOTS) {
             if (qmma_eligible<FMT>(a)) return qmma_dispatch<FMT>(a, di, s);
+        }
+        if constexpr (MODE == MODE_FLOAT && !DOTS) {
+            // measured on 14336 x 4096: the split layout gains from one vector on, the block layouts from two
+            const int min_batch = g_float_tc_min_batch > 0 ? g_float_tc_min_batch : (FMT == FMT_Q8S ? 1 : 2);
+            if (g_float_tensor_cores && a.batch >= min_batch) {
+                // most vectors per pass whose fp16 pairs fit in shared memory next to the weight ring
+                QGemvArgs p = a;
+                int cap = 0;
+                for (int c = 8; c >= 4 && !cap; c -= 4) {
+                    p.batch = a.batch < c ? a.batch : c;
+                    if (qmma_float_eligible<FMT>(p, di)) cap = c;
+                }
+                if (cap) {
+                    const int passes = (a.batch + cap - 1) / cap, each = (a.batch + passes - 1) / passes;
+                    for (int b0 = 0; b0 < a.batch; b0 += each) {
+                        p.batch = a.batch - b0 < each ? a.batch - b0 : each;
+                        p.x = a.x + (size_t)b0 * a.cols, p.y = a.y + (size_t)b0 * a.rows;
+                        st = qmma_float_dispatch<FMT>(p, di, s, g_overlap_launches != 0 && b0 == 0);
+                        if (st) return st;
+                    }
+                    return TB200_OK;
+                }
+            }
         }
         // more activation vectors than fit next to the ring: several passes over the weights
         for (int b0 = 0; b0 < a.batch; b0 += per) {
