@@ -205,7 +205,7 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             blocks = torch.empty((4, ROWS, COLS // 32, 34), dtype=torch.uint8, device=dev)
             blocks[..., :2] = sc.view(torch.uint8).view(4, ROWS, COLS // 32, 2)
             blocks[..., 2:] = q.view(torch.uint8).view(4, ROWS, COLS // 32, 32)
-            for batch in (1, 8):
+            for batch in (1, 4, 8):
                 x = torch.randn((batch, COLS), device=dev)
                 yb = torch.empty((batch, ROWS), device=dev)
                 ws_n = lib.tb200_qx_workspace_bytes(COLS, batch)
@@ -454,13 +454,17 @@ def main():
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q4,sgemm,hgemm) and print their timings; for profiling")
     ap.add_argument("--hgemm-sizes", default="2048,4096,8192,16384")
+    ap.add_argument("--hgemm-variant", default="pairs", choices=["pairs", "single"],
+                    help="with --sections: 256x256 tiles on SM pairs (the default of the library) or 128x256 tiles on single SMs")
     args = ap.parse_args()
     if args.sections:
         import torch
         from tornadovm_b200.native import B200Native
         torch.cuda.set_device(0)
         hbm_peak, tensor_peak, _ = measured_peaks()
-        res = secondary_metrics(torch, B200Native.load(), torch.cuda.Stream(), hbm_peak, tensor_peak,
+        lib = B200Native.load()
+        lib.tb200_set_option(2, 1 if args.hgemm_variant == "pairs" else 0)
+        res = secondary_metrics(torch, lib, torch.cuda.Stream(), hbm_peak, tensor_peak,
                                 tuple(args.sections.split(",")), tuple(int(v) for v in args.hgemm_sizes.split(",")))
         print(json.dumps({"sections": res}))
     elif args.impl == "reference":
