@@ -66,8 +66,8 @@ const char *tb200_status_string(int status);
 int tb200_version(void);
 
 /* Non-zero once any kernel of this library on the current device gave up a
- * bounded wait (value = TB200_ERR_TIMEOUT).  Synchronises the device; meant
- * for tests and diagnostics, not for the launch path. */
+ * bounded wait (value = TB200_ERR_TIMEOUT).  Reading it clears it.  Synchronises
+ * the device; meant for tests and diagnostics, not for the launch path. */
 int tb200_device_status(int *status_out);
 
 /* Process-wide options; the provider sets them from its tuning object
@@ -170,6 +170,50 @@ int tb200_q4b_gemv_i8(int rows, int cols, int batch, const uint8_t *blocks, cons
 #define TB200_STATIC_SCRATCH_BYTES 147456 /* enough for cols * batch <= 131072, e.g. 16384 x 8 */
 int tb200_q8_gemv_i8_static(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x,
                             float *y, tb200_stream_t stream);
+
+/* ---- Grouped integer-mode mat-vec and the multi-GPU output hand-off ------------
+ * `count` (<= 32) block matrices of one shape [rows][cols] that share the same
+ * activations are multiplied in ONE launch: the shape of a decoder layer's
+ * projections that read the same vector, and of a row shard of several matrices
+ * on one GPU of a group.  In the reference every mat-vec is its own task; the
+ * nearest interfaces are the batched GEMMs (CuBlas.cublasSgemmStridedBatched,
+ * tornado-cublas/.../CuBlas.java:206-228; Cutlass.cutlassHgemmBatched,
+ * Cutlass.java:177-191).  Multi-GPU execution has no counterpart in the reference.
+ *
+ * blocks[m] is matrix m (host array of device pointers).  Every result is stored
+ * to each of the `npeers` (<= 8) destination buffers dst[p] (host array of device
+ * pointers: this GPU's buffer and, mapped with tb200_ipc_open, its peers'), at
+ *     dst[p][half * half_stride + (m * batch + b) * rows_total + row_offset + r]
+ * where `half` is the low bit of *epoch (0 when epoch is NULL): two halves let a
+ * GPU fill the next step's outputs while a peer still reads this step's.  With
+ * npeers = 1, rows_total = rows, row_offset = 0, epoch = NULL this is a plain
+ * grouped mat-vec with y[count][batch][rows].
+ * One launch needs batch <= 4, cols % 256 == 0 and 16-byte aligned matrices;
+ * other cases are accepted only with a single local destination (one launch per
+ * matrix).  The workspace is used when batch * cols > 16384 (see above). */
+int tb200_q8b_gemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                              float *const *dst, int npeers, long long half_stride, const unsigned *epoch, int rows_total,
+                              int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+int tb200_q4b_gemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                              float *const *dst, int npeers, long long half_stride, const unsigned *epoch, int rows_total,
+                              int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+
+/* Completes a step whose outputs were stored to the peers' buffers: raises this
+ * GPU's flag (value *epoch + 1) in every GPU's flag array, waits until all flags
+ * of this GPU's own array have reached that value, then stores it to *epoch.
+ * flags[p] (host array of device pointers) is GPU p's array of 8 words, zero at
+ * start; flags[rank] is local, the others peer-mapped.  Enqueue it on every GPU
+ * of the group after the step's kernels.  The wait is bounded: after timeout_ms
+ * (0 = 2000) the kernel records TB200_ERR_TIMEOUT (tb200_device_status) and returns. */
+int tb200_peer_signal_wait(int rank, int npeers, unsigned *const *flags, unsigned *epoch, unsigned timeout_ms,
+                           tb200_stream_t stream);
+
+/* CUDA IPC plumbing for one process per GPU: export a tb200_device_malloc
+ * allocation as a 64-byte handle, map a peer's handle, unmap it.  Set-up and
+ * tear-down only. */
+int tb200_ipc_export(const void *device_allocation, void *handle64);
+int tb200_ipc_open(const void *handle64, void **peer_ptr);
+int tb200_ipc_close(void *peer_ptr);
 
 /* Test entry points: the raw int32 block dots, dots[r][blk], for one
  * already-quantised activation vector xq[cols].  Device form of the unit test

@@ -1,0 +1,147 @@
+"""Grouped integer-mode mat-vec (one launch for several matrices), multi-destination stores and the
+flag hand-shake, on one GPU: the peers of a multi-GPU group are stood in for by further buffers on
+the same device."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle as o
+from harness import DevBuf, out_buf, stream_ptr, sync_and_check
+
+pytestmark = pytest.mark.gpu
+
+TB200_ERR_TIMEOUT = -6
+
+
+def _ptr_array(bufs):
+    return (C.c_void_p * len(bufs))(*[b.ptr.value for b in bufs])
+
+
+def _case(fmt, rows, cols, batch, count):
+    mats, x = [], None
+    for m in range(count):
+        if fmt == "q8b":
+            q, s, xm = o.make_q8(rows, cols, batch, 100 + m)
+            mats.append(o.q8_pack_blocks(q, s))
+        else:
+            blocks, _, xm = o.make_q4(rows, cols, batch, 100 + m)
+            mats.append(blocks)
+        x = xm if x is None else x
+    return mats, x
+
+
+def _single(lib, fmt, rows, cols, batch, dw, dx):
+    dy = out_buf(rows * batch)
+    n = lib.tb200_qx_workspace_bytes(cols, batch)
+    ws = DevBuf(np.zeros(max(n, 16), np.uint8))
+    fn = lib.tb200_q8b_gemv_i8 if fmt == "q8b" else lib.tb200_q4b_gemv_i8
+    assert fn(rows, cols, batch, dw.ptr, dx.ptr, dy.ptr, ws.ptr, n, stream_ptr()) == 0
+    sync_and_check(lib)
+    return dy.numpy().reshape(batch, rows)
+
+
+@pytest.mark.parametrize("rows,cols,batch,count", [(257, 4096, 1, 3), (64, 1024, 2, 32), (1000, 256, 4, 2), (5, 2048, 3, 7),
+                                                   (40, 14336, 1, 2), (33, 96, 2, 3), (16, 4096, 8, 2)])
+@pytest.mark.parametrize("fmt", ["q8b", "q4b"])
+def test_grouped_equals_one_launch_per_matrix(lib, fmt, rows, cols, batch, count):
+    mats, x = _case(fmt, rows, cols, batch, count)
+    dws, dx = [DevBuf(m) for m in mats], DevBuf(x)
+    dy = out_buf(count * batch * rows)
+    n = lib.tb200_qx_workspace_bytes(cols, batch)
+    ws = DevBuf(np.zeros(max(n, 16), np.uint8))
+    fn = lib.tb200_q8b_gemv_i8_grouped if fmt == "q8b" else lib.tb200_q4b_gemv_i8_grouped
+    st = fn(count, rows, cols, batch, _ptr_array(dws), dx.ptr, _ptr_array([dy]), 1, 0, None, rows, 0, ws.ptr, n, stream_ptr())
+    assert st == 0, lib.tb200_status_string(st)
+    sync_and_check(lib)
+    got = dy.numpy().reshape(count, batch, rows)
+    for m in range(count):
+        want = _single(lib, fmt, rows, cols, batch, dws[m], dx)
+        assert np.array_equal(got[m], want), (m, np.abs(got[m] - want).max())
+    assert dy.guard_intact()
+
+
+def test_grouped_against_oracle(lib):
+    rows, cols, count = 96, 4096, 4
+    dws, want = [], []
+    q0, s0, x = o.make_q8(rows, cols, 1, 7)
+    xq, xs = o.quantize_x_block(x)
+    for m in range(count):
+        q, s, _ = o.make_q8(rows, cols, 1, 7 + m)
+        dws.append(DevBuf(o.q8_pack_blocks(q, s)))
+        dots = o.q8_blockdots_i32(q, xq, cols, rows)
+        want.append(o.blockdots_combine_f64(dots, s, xs, cols // 32, rows))
+    dx, dy = DevBuf(x), out_buf(count * rows)
+    st = lib.tb200_q8b_gemv_i8_grouped(count, rows, cols, 1, _ptr_array(dws), dx.ptr, _ptr_array([dy]), 1, 0, None, rows, 0, None, 0,
+                                       stream_ptr())
+    assert st == 0
+    sync_and_check(lib)
+    got = dy.numpy().reshape(count, rows)
+    assert o.rel_l2(got, np.stack(want)) <= 1e-5
+
+
+@pytest.mark.parametrize("half", [0, 1])
+def test_grouped_stores_to_every_destination_at_the_shard_offset(lib, half):
+    rows, cols, batch, count, npeers = 120, 2048, 2, 3, 4
+    rows_total, row_offset = 500, 260
+    mats, x = _case("q8b", rows, cols, batch, count)
+    dws, dx = [DevBuf(m) for m in mats], DevBuf(x)
+    half_floats = count * batch * rows_total
+    sentinel = np.float32(-777.0)
+    dsts = [DevBuf(np.full(2 * half_floats, sentinel, np.float32)) for _ in range(npeers)]
+    epoch = DevBuf(np.array([half + 4, 0, 0, 0], np.uint32))
+    st = lib.tb200_q8b_gemv_i8_grouped(count, rows, cols, batch, _ptr_array(dws), dx.ptr, _ptr_array(dsts), npeers, half_floats,
+                                       epoch.ptr, rows_total, row_offset, None, 0, stream_ptr())
+    assert st == 0, lib.tb200_status_string(st)
+    sync_and_check(lib)
+    want = np.full((2, count, batch, rows_total), sentinel, np.float32)
+    for m in range(count):
+        want[half, m, :, row_offset:row_offset + rows] = _single(lib, "q8b", rows, cols, batch, dws[m], dx)
+    for d in dsts:
+        assert np.array_equal(d.numpy().reshape(want.shape), want)
+        assert d.guard_intact()
+
+
+def test_grouped_argument_errors(lib):
+    rows, cols = 8, 256
+    mats, x = _case("q8b", rows, cols, 1, 2)
+    dws, dx, dy = [DevBuf(m) for m in mats], DevBuf(x), out_buf(2 * rows)
+    f = lib.tb200_q8b_gemv_i8_grouped
+    ok = lambda **k: f(k.get("count", 2), rows, cols, 1, _ptr_array(dws), dx.ptr, _ptr_array([dy]), k.get("npeers", 1), 0, None,
+                       k.get("rows_total", rows), k.get("row_offset", 0), None, 0, stream_ptr())
+    assert ok() == 0
+    assert ok(count=0) == -1 and ok(count=33) == -1
+    assert ok(npeers=0) == -1 and ok(npeers=9) == -1
+    assert ok(rows_total=rows - 1) == -1 and ok(row_offset=1) == -1
+    sync_and_check(lib)
+
+
+def test_signal_wait_raises_flags_everywhere_and_advances_the_epoch(lib):
+    npeers, rank = 4, 1
+    arrays = [DevBuf(np.zeros(8, np.uint32)) for _ in range(npeers)]
+    # the peers of this stand-in group have already signalled step 1 in this rank's array
+    mine = np.zeros(8, np.uint32)
+    mine[:npeers] = 1
+    mine[rank] = 0
+    arrays[rank] = DevBuf(mine)
+    epoch = DevBuf(np.zeros(4, np.uint32))
+    st = lib.tb200_peer_signal_wait(rank, npeers, _ptr_array(arrays), epoch.ptr, 200, stream_ptr())
+    assert st == 0
+    sync_and_check(lib)
+    for a in arrays:
+        assert a.numpy()[rank] == 1
+    assert epoch.numpy()[0] == 1
+
+
+def test_signal_wait_gives_up_after_its_time_limit(lib):
+    npeers, rank = 2, 0
+    arrays = [DevBuf(np.zeros(8, np.uint32)) for _ in range(npeers)]  # nothing ever raises peer 1's flag
+    epoch = DevBuf(np.zeros(4, np.uint32))
+    assert lib.tb200_peer_signal_wait(rank, npeers, _ptr_array(arrays), epoch.ptr, 20, stream_ptr()) == 0
+    import torch
+    torch.cuda.synchronize()
+    status = C.c_int(0)
+    assert lib.tb200_device_status(C.byref(status)) == 0
+    assert status.value == TB200_ERR_TIMEOUT
+    assert lib.tb200_device_status(C.byref(status)) == 0 and status.value == 0  # reading cleared it
+    assert epoch.numpy()[0] == 1 and arrays[1].numpy()[0] == 1

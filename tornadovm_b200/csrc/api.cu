@@ -76,6 +76,12 @@ extern "C" int tb200_device_status(int *status_out) {
     int v = 0;
     cudaError_t e = cudaMemcpyFromSymbol(&v, tb200::g_device_status, sizeof(int));
     if (e != cudaSuccess) return (int)e;
+    if (v != 0) {
+        // read and clear, like cudaGetLastError
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(tb200::g_device_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return (int)e;
+    }
     *status_out = v;
     return TB200_OK;
 }

@@ -50,6 +50,18 @@ struct QGemvArgs {
     int rows, cols, batch;
 };
 
+// Several matrices of one shape sharing the activation vectors, and several destinations for every
+// output value (this GPU's buffer and, peer-mapped, the other GPUs' buffers).
+constexpr int kMaxGroup = 32;
+constexpr int kMaxPeers = 8;
+struct QGroupArgs {
+    const uint8_t *w[kMaxGroup];   // block arrays, `rows_each` rows each
+    float *dst[kMaxPeers];         // output buffers: [2 halves][matrix][batch][rows_total]
+    const unsigned *epoch;         // device word whose low bit selects the half (null: half 0)
+    long long half_stride;         // floats between the halves
+    int count, rows_each, npeers, rows_total, row_offset;
+};
+
 __device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 
 // ---------------------------------------------------------------------------
@@ -520,8 +532,9 @@ __device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], 
     for (int i = 0; i < QW; ++i) qb[i] = wds[QW + 1 + i];
 }
 
-template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES>
-__global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, bool GROUPED>
+__device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupArgs *grp) {
+    // GROUPED: a.rows counts the rows of all matrices laid end to end; a.w and a.y are unused
     using T = RingTraits<FMT>;
     constexpr bool INT = MODE != MODE_FLOAT;
     static_assert(STAGES >= 2 && STAGES <= 4, "ring depth");
@@ -553,8 +566,14 @@ __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
             const int npieces = nblk * T::BB / 16;  // nblk is a multiple of 8: whole 16-byte pieces
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                const size_t row = (size_t)min(row_begin + ig * R + r, row_end - 1);
-                const unsigned char *src = a.w + row * row_bytes + (size_t)ich * T::CB + lane * 16;
+                const int vrow = min(row_begin + ig * R + r, row_end - 1);
+                const unsigned char *src;
+                if constexpr (GROUPED) {
+                    const int m = vrow / grp->rows_each;
+                    src = grp->w[m] + (size_t)(vrow - m * grp->rows_each) * row_bytes + (size_t)ich * T::CB + lane * 16;
+                } else {
+                    src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16;
+                }
                 const uint32_t dst = ring_s + (st * R + r) * T::CB + lane * 16;
 #pragma unroll
                 for (int i = 0; i < T::PIECES; ++i)
@@ -692,7 +711,21 @@ __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
         st = st + 1 == STAGES ? 0 : st + 1;
         if (++cch == nch) {
             cch = 0;
-            if (a.y) {
+            if constexpr (GROUPED) {
+                // every destination gets the value: plain stores, to this GPU's memory and to peer-mapped memory
+                const size_t half = grp->epoch ? (size_t)(*reinterpret_cast<const volatile unsigned *>(grp->epoch) & 1u) * grp->half_stride : 0;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int vrow = row0 + r;
+                    const int m = vrow / grp->rows_each;
+                    const size_t at = half + (size_t)m * B * grp->rows_total + grp->row_offset + (vrow - m * grp->rows_each);
+#pragma unroll
+                    for (int b = 0; b < B; ++b) {
+                        const float s = warp_sum(acc[r][b]);
+                        if (lane < grp->npeers && vrow < row_end) grp->dst[lane][at + (size_t)b * grp->rows_total] = s;
+                    }
+                }
+            } else if (a.y) {
 #pragma unroll
                 for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -705,6 +738,16 @@ __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
         }
     }
     cp_async_wait<0>();
+}
+
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES>
+__global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
+    qblk_gemv_body<FMT, B, R, MODE, DOTS, STAGES, false>(a, nullptr);
+}
+
+template <int FMT, int B, int R, int MODE, int STAGES>
+__global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_grouped_kernel(const QGemvArgs a, const __grid_constant__ QGroupArgs grp) {
+    qblk_gemv_body<FMT, B, R, MODE, false, STAGES, true>(a, &grp);
 }
 
 // ---------------------------------------------------------------------------
@@ -840,6 +883,31 @@ static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s)
     const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;
     if (grid > want) grid = want;
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a);
+}
+
+template <int FMT, int B, int MODE>
+static int launch_ring_grouped(const QGemvArgs &a, const QGroupArgs &grp, const DeviceInfo *di, cudaStream_t s) {
+    using Cfg = RingConfig<FMT, B, MODE>;
+    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols);
+    constexpr auto kernel = qblk_gemv_grouped_kernel<FMT, B, Cfg::R, MODE, Cfg::STAGES>;
+    int st = ensure_smem_optin<kernel>(di);
+    if (st) return st;
+    int grid = di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem);
+    const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
+    const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;
+    if (grid > want) grid = want;
+    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a, grp);
+}
+
+template <int FMT, int MODE>
+static int launch_ring_grouped_b(const QGemvArgs &a, const QGroupArgs &grp, const DeviceInfo *di, cudaStream_t s) {
+    switch (a.batch) {
+        case 1: return launch_ring_grouped<FMT, 1, MODE>(a, grp, di, s);
+        case 2: return launch_ring_grouped<FMT, 2, MODE>(a, grp, di, s);
+        case 3: return launch_ring_grouped<FMT, 3, MODE>(a, grp, di, s);
+        case 4: return launch_ring_grouped<FMT, 4, MODE>(a, grp, di, s);
+        default: return TB200_ERR_INVALID_ARG;
+    }
 }
 
 template <int FMT, bool INT>
@@ -1074,6 +1142,64 @@ static int qgemv_i8(int rows, int cols, int batch, const void *w, const uint16_t
     return qgemv_dispatch<FMT, MODE_INT_FUSED, false>(a, xq, xs, stream);
 }
 
+// Integer-mode mat-vec of `count` equally shaped block matrices on the same activations, one launch,
+// every output value stored to `npeers` destination buffers.
+template <int FMT>
+static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x, float *const *dst,
+                            int npeers, long long half_stride, const unsigned *epoch, int rows_total, int row_offset, void *workspace,
+                            size_t workspace_bytes, tb200_stream_t stream) {
+    if (count < 1 || count > kMaxGroup || npeers < 1 || npeers > kMaxPeers || !blocks || !dst || !x) return TB200_ERR_INVALID_ARG;
+    if (rows < 0 || cols < 0 || cols % 32 != 0 || batch < 1 || batch > kMaxBatch) return TB200_ERR_INVALID_ARG;
+    if (row_offset < 0 || rows_total < rows || row_offset > rows_total - rows || half_stride < 0) return TB200_ERR_INVALID_ARG;
+    if ((long long)count * rows > 0x7fffffffLL) return TB200_ERR_INVALID_ARG;
+    if (!aligned_to(x, 4) || (epoch && !aligned_to(epoch, 4))) return TB200_ERR_ALIGNMENT;
+    QGroupArgs grp{};
+    bool fast = cols % 256 == 0 && cols > 0;
+    for (int m = 0; m < count; ++m) {
+        if (!blocks[m]) return TB200_ERR_INVALID_ARG;
+        if (!aligned_to(blocks[m], 2)) return TB200_ERR_ALIGNMENT;
+        fast = fast && aligned_to(blocks[m], 16);
+        grp.w[m] = reinterpret_cast<const uint8_t *>(blocks[m]);
+    }
+    for (int p = 0; p < npeers; ++p) {
+        if (!dst[p]) return TB200_ERR_INVALID_ARG;
+        if (!aligned_to(dst[p], 4)) return TB200_ERR_ALIGNMENT;
+        grp.dst[p] = dst[p];
+    }
+    if (rows == 0) return TB200_OK;
+    grp.epoch = epoch, grp.half_stride = half_stride, grp.count = count, grp.rows_each = rows;
+    grp.npeers = npeers, grp.rows_total = rows_total, grp.row_offset = row_offset;
+    int st;
+    const DeviceInfo *di = device_info(&st);
+    if (!di) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, count * rows, cols, batch};
+    if (fast && batch <= 4 && fast_batch_fits<FMT, MODE_INT>(cols, batch, PATH_RING, di)) {
+        if ((long long)batch * cols <= kFusedQuantMaxElems) return launch_ring_grouped_b<FMT, MODE_INT_FUSED>(a, grp, di, s);
+        int8_t *xq;
+        float *xs;
+        st = split_workspace(cols, batch, workspace, workspace_bytes, &xq, &xs);
+        if (st) return st;
+        st = quantize_x(cols, batch, x, xq, xs, s);
+        if (st) return st;
+        a.x = nullptr, a.xq = xq, a.xs = xs;
+        return launch_ring_grouped_b<FMT, MODE_INT>(a, grp, di, s);
+    }
+    // other shapes and alignments: one launch per matrix, into the single local destination only
+    if (npeers != 1 || epoch) return TB200_ERR_INVALID_ARG;
+    int8_t *xq;
+    float *xs;
+    st = split_workspace(cols, batch, workspace, workspace_bytes, &xq, &xs);
+    if (st) return st;
+    for (int m = 0; m < count; ++m) {
+        if (batch > 1 && rows_total != rows) return TB200_ERR_INVALID_ARG;  // the single-matrix kernels write [batch][rows]
+        QGemvArgs one{grp.w[m], nullptr, x, nullptr, nullptr, dst[0] + (size_t)m * batch * rows_total + row_offset, nullptr, rows, cols, batch};
+        st = qgemv_dispatch<FMT, MODE_INT_FUSED, false>(one, xq, xs, stream);
+        if (st) return st;
+    }
+    return TB200_OK;
+}
+
 }  // namespace tb200
 
 using namespace tb200;
@@ -1128,6 +1254,20 @@ extern "C" int tb200_q4b_gemv_i8(int rows, int cols, int batch, const uint8_t *b
                                  void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
     if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
     return qgemv_i8<FMT_Q4B>(rows, cols, batch, blocks, nullptr, x, y, workspace, workspace_bytes, stream);
+}
+
+extern "C" int tb200_q8b_gemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                                         float *const *dst, int npeers, long long half_stride, const unsigned *epoch, int rows_total,
+                                         int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    return qgemv_i8_grouped<FMT_Q8B>(count, rows, cols, batch, blocks, x, dst, npeers, half_stride, epoch, rows_total, row_offset,
+                                     workspace, workspace_bytes, stream);
+}
+
+extern "C" int tb200_q4b_gemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                                         float *const *dst, int npeers, long long half_stride, const unsigned *epoch, int rows_total,
+                                         int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    return qgemv_i8_grouped<FMT_Q4B>(count, rows, cols, batch, blocks, x, dst, npeers, half_stride, epoch, rows_total, row_offset,
+                                     workspace, workspace_bytes, stream);
 }
 
 // The block-dot entries take an already quantised activation vector and write

@@ -8,3 +8,4 @@
 #include "sgemm.cu"
 #include "hgemm.cu"
 #include "gemv_static.cu"
+#include "peer.cu"

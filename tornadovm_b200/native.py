@@ -34,6 +34,12 @@ SIGNATURES = {
     "tb200_q8_gemv_i8_static": (_I, [_I, _I, _I, _P, _P, _P, _P, _P]),
     "tb200_q8b_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_q4b_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
+    "tb200_q8b_gemv_i8_grouped": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, C.c_longlong, _P, _I, _I, _P, _Z, _P]),
+    "tb200_q4b_gemv_i8_grouped": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, C.c_longlong, _P, _I, _I, _P, _Z, _P]),
+    "tb200_peer_signal_wait": (_I, [_I, _I, _P, _P, C.c_uint, _P]),
+    "tb200_ipc_export": (_I, [_P, _P]),
+    "tb200_ipc_open": (_I, [_P, C.POINTER(_P)]),
+    "tb200_ipc_close": (_I, [_P]),
     "tb200_q8_blockdots_i32": (_I, [_I, _I, _P, _P, _P, _P]),
     "tb200_q8b_blockdots_i32": (_I, [_I, _I, _P, _P, _P, _P]),
     "tb200_q4b_blockdots_i32": (_I, [_I, _I, _P, _P, _P, _P]),

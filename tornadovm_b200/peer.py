@@ -1,0 +1,168 @@
+"""Grouped, row-sharded integer-mode mat-vec whose outputs reach every GPU by peer stores.
+
+One process per GPU.  Each rank owns the same row block of ``count`` block-format matrices
+(Q8_0 34-byte or Q4_0 18-byte blocks) and runs ONE launch per step for all of them
+(``tb200_q8b_gemv_i8_grouped``); the kernel stores every output value into the gather buffer of
+every rank (its own and, over NVLink, the peers' CUDA-IPC mapped ones), and one small kernel per
+step (``tb200_peer_signal_wait``) is the hand-shake that replaces the all-gather.  The reference has
+no counterpart: its multi-device mode runs independent tasks with host round trips
+(docs/source/multi-device.rst:9-14).
+
+``torch.distributed`` is used at set-up only (exchange of the IPC handles) and for barriers at
+tear-down; no collective runs on the data path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .native import B200Native
+from .sharding import shard_range
+
+FLAG_WORDS = 8  # flag array of one rank: one word per peer
+
+
+class _RawDeviceMemory:
+    """A range of device memory that torch did not allocate, exposed through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def wrap_device_memory(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:
+    """uint8 tensor view of raw device memory (no copy, no ownership)."""
+    return torch.as_tensor(_RawDeviceMemory(ptr, nbytes), device=device)
+
+
+class PeerSlab:
+    """One device allocation per rank, mapped into every rank of the group.
+
+    Layout: ``[payload_bytes][flags: FLAG_WORDS x u32][epoch: u32]``, zero-filled.  ``ptrs[p]`` is rank p's
+    slab as addressable from this process.
+    """
+
+    def __init__(self, payload_bytes: int, device: torch.device, group=None):
+        self.lib = B200Native.load()
+        self.group, self.device = group, device
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.payload_bytes = (payload_bytes + 255) // 256 * 256
+        self.nbytes = self.payload_bytes + 256
+        own = C.c_void_p()
+        B200Native.check_status(self.lib.tb200_device_malloc(self.nbytes, C.byref(own)), "tb200_device_malloc")
+        self.own = own.value
+        self.bytes = wrap_device_memory(self.own, self.nbytes, device)
+        self.bytes.zero_()
+        torch.cuda.synchronize(device)
+        self.ptrs = [0] * self.world
+        self.ptrs[self.rank] = self.own
+        self._opened: list[int] = []
+        if self.world > 1:
+            handle = (C.c_ubyte * 64)()
+            B200Native.check_status(self.lib.tb200_ipc_export(C.c_void_p(self.own), handle), "tb200_ipc_export")
+            handles: list = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            for p, h in enumerate(handles):
+                if p == self.rank:
+                    continue
+                buf, out = (C.c_ubyte * 64).from_buffer_copy(h), C.c_void_p()
+                B200Native.check_status(self.lib.tb200_ipc_open(buf, C.byref(out)), "tb200_ipc_open")
+                self.ptrs[p] = out.value
+                self._opened.append(out.value)
+            dist.barrier(group=group)  # every slab is zeroed and mapped before anyone stores into it
+
+    @property
+    def flags_offset(self) -> int:
+        return self.payload_bytes
+
+    @property
+    def epoch_offset(self) -> int:
+        return self.payload_bytes + FLAG_WORDS * 4
+
+    def close(self) -> None:
+        """Unmap the peers and free the slab; collective (every rank must have stopped launching)."""
+        if self.own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for ptr in self._opened:
+            self.lib.tb200_ipc_close(C.c_void_p(ptr))
+        self._opened = []
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody frees memory a peer still has mapped
+        self.bytes = None
+        self.lib.tb200_device_free(C.c_void_p(self.own))
+        self.own = None
+
+
+class ShardedGroupedGemv:
+    """``count`` equally shaped block matrices, rows sharded over the ranks, one launch per step and rank.
+
+    ``weights[m]`` is this rank's row block of matrix m (uint8 CUDA tensor of 34- or 18-byte blocks, rows
+    ``shard_range(rows, world, rank)``).  ``launch()`` enqueues the step and returns the gathered
+    ``[count][batch][rows]`` device tensor of that step; ``run(x_host)`` adds the activation upload and
+    the download of the gathered result.
+    """
+
+    def __init__(self, rows: int, cols: int, batch: int, weights: list[torch.Tensor], fmt: str = "q8b", group=None,
+                 timeout_ms: int = 2000):
+        assert fmt in ("q8b", "q4b")
+        self.lib = B200Native.load()
+        self.fn_name = f"tb200_{fmt}_gemv_i8_grouped"
+        self.fn = getattr(self.lib, self.fn_name)
+        self.rows, self.cols, self.batch, self.count, self.group = rows, cols, batch, len(weights), group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.r0, r1 = shard_range(rows, self.world, self.rank)
+        self.local_rows = r1 - self.r0
+        block_bytes = 34 if fmt == "q8b" else 18
+        for w in weights:
+            assert w.is_cuda and w.dtype == torch.uint8 and w.numel() == self.local_rows * (cols // 32) * block_bytes
+        self.weights = weights
+        dev = weights[0].device
+        self.device, self.timeout_ms = dev, timeout_ms
+        self.stream = torch.cuda.Stream(device=dev)
+        self.half_floats = self.count * batch * rows
+        self.slab = PeerSlab(2 * self.half_floats * 4, dev, group)
+        self.halves = self.slab.bytes[:2 * self.half_floats * 4].view(torch.float32).view(2, self.count, batch, rows)
+        self.x_dev = torch.empty((batch, cols), dtype=torch.float32, device=dev)
+        self.y_host = torch.empty((self.count, batch, rows), dtype=torch.float32, pin_memory=True)
+        self.ws_bytes = self.lib.tb200_qx_workspace_bytes(cols, batch)
+        self.ws = torch.empty(max(self.ws_bytes, 16), dtype=torch.uint8, device=dev)
+        # host arrays of device pointers, kept alive with the object
+        self._w_ptrs = (C.c_void_p * self.count)(*[w.data_ptr() for w in weights])
+        self._dst_ptrs = (C.c_void_p * self.world)(*self.slab.ptrs)
+        self._flag_ptrs = (C.c_void_p * self.world)(*[p + self.slab.flags_offset for p in self.slab.ptrs])
+        self._epoch = C.c_void_p(self.slab.own + self.slab.epoch_offset) if self.world > 1 else None
+        self.steps = 0  # steps enqueued so far; step s writes half s & 1
+
+    def launch(self) -> torch.Tensor:
+        S = C.c_void_p(self.stream.cuda_stream)
+        with torch.cuda.stream(self.stream):
+            if self.local_rows > 0:
+                st = self.fn(self.count, self.local_rows, self.cols, self.batch, self._w_ptrs, C.c_void_p(self.x_dev.data_ptr()),
+                             self._dst_ptrs, self.world, self.half_floats, self._epoch, self.rows, self.r0,
+                             C.c_void_p(self.ws.data_ptr()), self.ws_bytes, S)
+                B200Native.check_status(st, self.fn_name)
+            if self.world > 1:
+                st = self.lib.tb200_peer_signal_wait(self.rank, self.world, self._flag_ptrs, self._epoch, self.timeout_ms, S)
+                B200Native.check_status(st, "tb200_peer_signal_wait")
+        half = self.steps & 1 if self.world > 1 else 0
+        self.steps += 1
+        return self.halves[half]
+
+    def run(self, x_host: torch.Tensor) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            self.x_dev.copy_(x_host, non_blocking=True)
+            y = self.launch()
+            self.y_host.copy_(y, non_blocking=True)
+        self.stream.synchronize()
+        return self.y_host
+
+    def close(self) -> None:
+        self.stream.synchronize()
+        self.halves = None
+        self.slab.close()
