@@ -162,7 +162,7 @@ def make_weights(torch, dev, rows, layers, seed):
     return q, sc
 
 
-def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgemv", "q8", "q4", "sgemm", "hgemm"), hgemm_sizes=(2048, 4096, 8192, 16384)):
+def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgemv", "q8", "q8layers", "q4", "sgemm", "hgemm"), hgemm_sizes=(2048, 4096, 8192, 16384)):
     """Short device-resident timings of the other kernels on the path (not the headline)."""
     out = {}
     P = lambda t: C.c_void_p(t.data_ptr())
@@ -221,6 +221,28 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                     t = timeit(fn, 10)
                     out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
             del q, sc, blocks
+        if "q8layers" in sections:
+            # the headline's 32 matrices, one launch per mat-vec (the granularity of the reference's tasks) and in
+            # groups of 2 (a layer's gate/up pair reads one vector) and 8
+            q, sc = make_weights(torch, dev, ROWS, LAYERS, 11)
+            blocks = torch.empty((LAYERS, ROWS, COLS // 32, 34), dtype=torch.uint8, device=dev)
+            blocks[..., :2] = sc.view(torch.uint8).view(LAYERS, ROWS, COLS // 32, 2)
+            blocks[..., 2:] = q.view(torch.uint8).view(LAYERS, ROWS, COLS // 32, 32)
+            del q, sc
+            x = torch.randn((1, COLS), device=dev)
+            yl = torch.empty((LAYERS, ROWS), device=dev)
+            by = algorithmic_bytes(ROWS, COLS, 1)
+            ws_n = lib.tb200_qx_workspace_bytes(COLS, 1)
+            ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
+            t = timeit(lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, 1, P(blocks[i]), P(x), P(yl[i]), P(ws), ws_n, S), 10, period=LAYERS)
+            out["q8_blocks_int_b1_one_launch_per_matvec"] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
+            for grp in (2, 8):
+                wp = [(C.c_void_p * grp)(*[blocks[c * grp + m].data_ptr() for m in range(grp)]) for c in range(LAYERS // grp)]
+                dp = [(C.c_void_p * 1)(yl[c * grp].data_ptr()) for c in range(LAYERS // grp)]
+                t = timeit(lambda i: lib.tb200_q8b_gemv_i8_grouped(grp, ROWS, COLS, 1, wp[i], P(x), dp[i], 1, 0, None, ROWS, 0, None, 0, S),
+                           10, period=LAYERS // grp)
+                out[f"q8_blocks_int_b1_{grp}_per_launch"] = {"GB/s": grp * by / t / 1e9, "frac_hbm": grp * by / t / 1e9 / hbm_peak, "us": t * 1e6}
+            del blocks
         if "q4" in sections:
             # Q4_0 Llama-3-8B-shaped layer sweep (configs[4]): 7 projections + the output projection
             shapes = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336), (128256, 4096)]
@@ -267,13 +289,17 @@ def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
     from tornadovm_b200.native import B200Native
-    from tornadovm_b200.sharding import ShardedQ8Gemv, gather_rows, shard_range, shard_rows
+    from tornadovm_b200.peer import ShardedGroupedGemv
+    from tornadovm_b200.sharding import shard_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the b200/linalg kernels have no CPU path")
+    group = args.group
+    if group < 1 or LAYERS % group:
+        raise SystemExit(f"--group must divide {LAYERS}")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -282,7 +308,6 @@ def run_gpu_arm(args):
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
 
     # ---- device-resident workload: rank r owns rows [r0, r1) of every layer -------------------------------
-    per = shard_rows(ROWS, world)
     r0, r1 = shard_range(ROWS, world, rank)
     lrows = r1 - r0
     q, sc = make_weights(torch, dev, lrows, LAYERS, 1234 + rank)
@@ -291,96 +316,73 @@ def run_gpu_arm(args):
     blocks[..., :2] = sc.view(torch.uint8).view(LAYERS, lrows, COLS // 32, 2)
     blocks[..., 2:] = q.view(torch.uint8).view(LAYERS, lrows, COLS // 32, 32)
     del q, sc
-    x = torch.randn((BATCH, COLS), device=dev, generator=torch.Generator(device=dev).manual_seed(99))
-    y_local = torch.zeros((LAYERS, BATCH, per), device=dev)  # [layer][batch][per]: one gather per step
-    gather_buf = torch.empty((world, LAYERS * BATCH, per), device=dev) if world > 1 else None
-    stream = torch.cuda.Stream(device=dev)
-    S = C.c_void_p(stream.cuda_stream)
-    P = lambda t: C.c_void_p(t.data_ptr())
-    launches = 0
-    ws_n = lib.tb200_qx_workspace_bytes(COLS, BATCH)
-    ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
-    # consecutive mat-vecs may overlap: each prefetches its weights while its predecessor drains
+    # consecutive mat-vec launches may overlap: each prefetches its weights while its predecessor drains
     B200Native.call("tb200_set_option", 1, 1)
-
-    def enqueue_layers():
-        for l in range(LAYERS):
-            st = lib.tb200_q8b_gemv_i8(lrows, COLS, BATCH, P(blocks[l]), P(x), P(y_local[l]), P(ws), ws_n, S)
-            if st:
-                B200Native.check_status(st, "tb200_q8b_gemv_i8")
-
-    # one step = LAYERS launches captured once and replayed (how TornadoVM runs a plan withCUDAGraph); with
-    # N > 1 the all-gather of the output shards follows the replay on the same stream.  (The collective is
-    # kept outside the graph: a graph that holds NCCL kernels has to be destroyed before the communicator,
-    # and capturing it did not shorten the step.)
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            enqueue_layers()  # warm-up outside capture: one-time kernel attribute calls
-        stream.synchronize()
-        layer_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(layer_graph, stream=stream):
-            enqueue_layers()
-    kernel_graph = layer_graph  # kernels only, for the roofline
-
-    def step():
-        nonlocal launches
-        layer_graph.replay()
-        launches += LAYERS
-        if world > 1:
-            gather_rows(y_local.view(LAYERS * BATCH, per), ROWS, None, gather_buf)
+    # The step: LAYERS mat-vecs, `group` matrices per launch.  Every output value is stored by the kernel into the
+    # gather buffer of every rank (peer stores over NVLink); with N > 1 one flag hand-shake per step completes it.
+    op = ShardedGroupedGemv(ROWS, COLS, BATCH, [blocks[l].view(-1) for l in range(LAYERS)], "q8b", per_launch=group)
+    stream = op.stream
+    op.x_dev.copy_(torch.randn((BATCH, COLS), device=dev, generator=torch.Generator(device=dev).manual_seed(99)))
+    launches_per_step = LAYERS // group + (1 if world > 1 else 0)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    barrier()
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
-            step()
+            op.launch()
         barrier()
-        launches = 0
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clocks:
             e0.record(stream)
             for _ in range(args.steps):
-                step()
+                op.launch()
             e1.record(stream)
             barrier()
         elapsed = e0.elapsed_time(e1) * 1e-3
-        # kernel-only duration for the roofline: the same launches without the gather, events on the launch stream
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(args.steps, 10)
-        k0.record(stream)
-        for _ in range(reps):
-            kernel_graph.replay()
-        k1.record(stream)
-        stream.synchronize()
-        kernel_s = k0.elapsed_time(k1) * 1e-3 / (reps * LAYERS)
-    gpu_launches = launches
+    gpu_launches = args.steps * launches_per_step
     if world > 1:
         t = torch.tensor([elapsed], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed = t.item()
+    # kernel-only duration for the roofline: the mat-vec launches of a step without the hand-shake, one rank at a
+    # time so that no peer is storing into this GPU meanwhile; events on the launch stream
+    kernel_s = None
+    if world == 1:
+        with torch.cuda.stream(stream):
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(args.steps, 10)
+            k0.record(stream)
+            for _ in range(reps):
+                op.launch()
+            k1.record(stream)
+            stream.synchronize()
+            kernel_s = k0.elapsed_time(k1) * 1e-3 / (reps * (LAYERS // group))
     total_bytes = LAYERS * algorithmic_bytes(ROWS, COLS, BATCH)  # whole job, all ranks
     value = total_bytes * args.steps / elapsed / 1e9
-    launch_bytes = algorithmic_bytes(lrows, COLS, BATCH)
+    launch_bytes = group * algorithmic_bytes(lrows, COLS, BATCH)
+    if kernel_s is None:  # N > 1: the step without its hand-shake share cannot be separated; use the step
+        kernel_s = elapsed / args.steps / (LAYERS // group)
     achieved = launch_bytes / kernel_s / 1e9
 
     # ---- end to end through the public API, host buffers ---------------------------------------------------
     e2e_steps = args.steps
     if world == 1:
         from tornadovm_b200.arrays import ByteArray, FloatArray
-        from tornadovm_b200.b200 import B200
+        from tornadovm_b200.b200 import B200, B200Options
         from tornadovm_b200.taskgraph import CudaDevice, DataTransferMode, TaskGraph, TornadoExecutionPlan
         wa = [ByteArray(blocks[l].cpu().numpy().ravel()) for l in range(LAYERS)]
-        xa = FloatArray(x.cpu().numpy())
-        ya = [FloatArray(ROWS * BATCH) for _ in range(LAYERS)]
-        from tornadovm_b200.b200 import B200Options
+        xa = FloatArray(op.x_dev.cpu().numpy())
+        ya = [FloatArray(group * ROWS * BATCH) for _ in range(LAYERS // group)]
         opts = B200Options(exact_int=True, overlap_launches=True)
         tg = TaskGraph("q8decode").transferToDevice(DataTransferMode.FIRST_EXECUTION, *wa) \
             .transferToDevice(DataTransferMode.EVERY_EXECUTION, xa)
-        for l in range(LAYERS):
-            tg.libraryTask(f"l{l}", B200.q8GemvBytes, ROWS, COLS, BATCH, wa[l], xa, ya[l], opts)
+        grouped = lambda *a: B200.q8GemvBytesGrouped(*a, options=opts)  # the factory with the plan's tuning object
+        for c in range(LAYERS // group):
+            tg.libraryTask(f"g{c}", grouped, ROWS, COLS, BATCH, xa, ya[c], *wa[c * group:(c + 1) * group])
         tg.transferToHost(DataTransferMode.EVERY_EXECUTION, *ya)
         with TornadoExecutionPlan(tg, CudaDevice(local)).withCUDAGraph() as plan:
             for _ in range(max(args.warmup, 3)):
@@ -392,53 +394,58 @@ def run_gpu_arm(args):
             torch.cuda.synchronize()
             e2e_s = time.perf_counter() - t0
             h2d, d2h = plan.h2d_bytes_last, plan.d2h_bytes_last
-        gpu_launches += e2e_steps * LAYERS
+        api = "TaskGraph.libraryTask(B200.q8GemvBytesGrouped) + TornadoExecutionPlan.withCUDAGraph().execute()"
     else:
-        ops = [ShardedQ8Gemv(ROWS, COLS, BATCH, blocks[l].view(-1)) for l in range(LAYERS)]
         xh = torch.randn((BATCH, COLS)).pin_memory()
         for _ in range(max(args.warmup, 3)):
-            for op in ops:
-                op.run(xh)
+            op.run(xh)
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            for op in ops:
-                op.run(xh)
+            op.run(xh)
         barrier()
         e2e_s = time.perf_counter() - t0
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = t.item()
-        h2d, d2h = LAYERS * BATCH * COLS * 4, LAYERS * BATCH * ROWS * 4
-        gpu_launches += e2e_steps * LAYERS
+        h2d, d2h = BATCH * COLS * 4, LAYERS * BATCH * ROWS * 4
+        api = "ShardedGroupedGemv.run"
+    gpu_launches += e2e_steps * launches_per_step
     e2e_value = total_bytes * e2e_steps / e2e_s / 1e9
+    status = C.c_int(0)
+    lib.tb200_device_status(C.byref(status))
+    if status.value:
+        raise SystemExit(f"a bounded device-side wait expired during the run (status {status.value})")
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "s8", "data": "synthetic",
         "config": {"workload": f"Q8_0 GEMV W[{ROWS}x{COLS}] int8 blocks of 32 + fp16 scale (34-byte blocks), fp32 x, batch {BATCH}",
-                   "layers_per_step": LAYERS, "l2_policy": f"{LAYERS} distinct weight matrices per step ({LAYERS * 62.4:.0f} MB > 126 MB L2)",
-                   "parallelism": f"rows sharded over {world} GPU(s), outputs all-gathered once per step (NCCL)" if world > 1 else "single GPU",
+                   "layers_per_step": LAYERS, "matrices_per_launch": group,
+                   "l2_policy": f"{LAYERS} distinct weight matrices per step ({LAYERS * 62.4:.0f} MB > 126 MB L2)",
+                   "parallelism": (f"rows sharded over {world} GPUs; the kernel stores each output into every GPU's gather buffer "
+                                   "(peer stores over NVLink), one flag hand-shake per step, no collective library on the data path")
+                   if world > 1 else "single GPU",
                    "mode": "int (fp32 activations quantised to int8 per 32-block inside the kernel, exact int32 block dots)",
-                   "launch": "CUDA-graph replay, programmatic dependent launches"},
+                   "launch": f"{LAYERS // group} grouped launch(es) per step, programmatic dependent launches"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s / e2e_steps * 1e3,
-                "api": "TaskGraph.libraryTask(B200.q8GemvBytes) + TornadoExecutionPlan.withCUDAGraph().execute()" if world == 1 else "ShardedQ8Gemv.run"},
+                "ms_per_step": e2e_s / e2e_steps * 1e3, "api": api},
         "gpu_launches": gpu_launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_GEMV * lrows // ROWS if world == 1 else None, "peak_source": f"{peak_kind} copy bandwidth", "kernel": "qblk_gemv_kernel",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_GEMV * group if world == 1 else None,
+                     "peak_source": f"{peak_kind} copy bandwidth", "kernel": "qblk_gemv_grouped_kernel",
                      "bytes_per_launch": launch_bytes, "us_per_launch": kernel_s * 1e6},
         "clocks": clocks.summary(),
     }
+    op.close()
     if rank == 0:
         if world == 1:
             line["cpu_baseline"] = cpu_reference(seconds_target=args.cpu_seconds)
             if not args.no_secondary:
-                line["secondary"] = secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak)
+                line["secondary"] = secondary_metrics(torch, lib, torch.cuda.Stream(device=dev), hbm_peak, tensor_peak)
         print(json.dumps(line))
     if world > 1:
-        del layer_graph, kernel_graph
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
@@ -452,7 +459,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=8.0)
     ap.add_argument("--no-secondary", action="store_true")
-    ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q4,sgemm,hgemm) and print their timings; for profiling")
+    ap.add_argument("--group", type=int, default=LAYERS, help="matrices per launch (a divisor of the 32 per step)")
+    ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q8layers,q4,sgemm,hgemm) and print their timings; for profiling")
     ap.add_argument("--hgemm-sizes", default="2048,4096,8192,16384")
     ap.add_argument("--hgemm-variant", default="pairs", choices=["pairs", "single"],
                     help="with --sections: 256x256 tiles on SM pairs (the default of the library) or 128x256 tiles on single SMs")

@@ -58,6 +58,33 @@ def test_q8_decode_graph_with_changing_activations(exact_int):
                 assert o.rel_l2(y.numpy(), yb.numpy()) <= 1e-6
 
 
+def test_grouped_q8_task_equals_separate_tasks():
+    """One grouped task for the matrices that read the same vector gives the results of one task per matrix."""
+    rows, cols, batch, count = 192, 2048, 2, 3
+    mats = []
+    for m in range(count):
+        q_h, s_h, x_h = o.make_q8(rows, cols, batch, 300 + m)
+        mats.append(ByteArray(o.q8_pack_blocks(q_h, s_h)))
+    x = FloatArray(o.JavaRandom(9).gaussian_f32(cols * batch))
+    ys = [FloatArray(rows * batch) for _ in range(count)]
+    yg = FloatArray(count * rows * batch)
+    opts = B200Options(exact_int=True)
+    tg = TaskGraph("layer").transferToDevice(DataTransferMode.FIRST_EXECUTION, *mats).transferToDevice(DataTransferMode.EVERY_EXECUTION, x)
+    for m in range(count):
+        tg.libraryTask(f"one{m}", B200.q8GemvBytes, rows, cols, batch, mats[m], x, ys[m], opts)
+    tg.libraryTask("all", B200.q8GemvBytesGrouped, rows, cols, batch, x, yg, *mats)
+    tg.transferToHost(DataTransferMode.EVERY_EXECUTION, yg, *ys)
+    with TornadoExecutionPlan(tg).withCUDAGraph() as plan:
+        for it in range(2):
+            x.numpy()[:] = o.JavaRandom(50 + it).gaussian_f32(cols * batch)
+            plan.execute()
+            got = yg.numpy().reshape(count, batch * rows)
+            for m in range(count):
+                assert np.array_equal(got[m], ys[m].numpy())
+    with pytest.raises(RuntimeError, match="1 to 32 matrices"):
+        B200.q8GemvBytesGrouped(rows, cols, batch, x, yg)
+
+
 def test_gemm_tasks_and_header_override():
     old = arrays.ARRAY_HEADER
     try:

@@ -15,6 +15,7 @@ from .descriptor import Access, LibraryTaskDescriptor
 
 LIBRARY_NAME = "b200/linalg"
 MAX_BATCH = 16
+MAX_GROUP = 32
 
 
 @dataclass
@@ -80,6 +81,28 @@ class B200:
         B200._check_q("q4GemvBytes", rows, cols, batch, x, y)
         _check(blocks.getSize() >= rows * (cols // 32) * 18, "B200 q4GemvBytes: weights too small")
         return _desc("q4GemvBytes", [rows, cols, batch, blocks, x, y], 5, tuning=options)
+
+    @staticmethod
+    def _grouped(name, block_bytes, rows, cols, batch, x, y, blocks, options):
+        B200._check_q(name, rows, cols, batch, x, y)
+        _check(1 <= len(blocks) <= MAX_GROUP, f"B200 {name} requires 1 to {MAX_GROUP} matrices; got {len(blocks)}")
+        _check(y.getSize() >= len(blocks) * batch * rows, f"B200 {name}: y smaller than count x batch x rows")
+        for b in blocks:
+            _check(b.getSize() >= rows * (cols // 32) * block_bytes, f"B200 {name}: weights too small")
+        _check(options is None or options.exact_int, f"B200 {name} computes in integer mode; exact_int must be set")
+        return _desc(name, [len(blocks), rows, cols, batch, x, y, *blocks], 5, tuning=options or B200Options(exact_int=True))
+
+    @staticmethod
+    def q8GemvBytesGrouped(rows, cols, batch, x: FloatArray, y: FloatArray, *blocks: ByteArray, options=None):  # noqa: N802
+        """Integer-mode Q8_0 mat-vec of several equally shaped matrices on the same activations in one launch:
+        y[m][b][r] for matrix m.  The reference launches one task per matrix; its batched interfaces are the
+        strided GEMMs (CuBlas.cublasSgemmStridedBatched, CuBlas.java:206-228)."""
+        return B200._grouped("q8GemvBytesGrouped", 34, rows, cols, batch, x, y, blocks, options)
+
+    @staticmethod
+    def q4GemvBytesGrouped(rows, cols, batch, x: FloatArray, y: FloatArray, *blocks: ByteArray, options=None):  # noqa: N802
+        """Q4_0 twin of q8GemvBytesGrouped."""
+        return B200._grouped("q4GemvBytesGrouped", 18, rows, cols, batch, x, y, blocks, options)
 
     @staticmethod
     def sgemm(m, n, k, alpha, a: FloatArray, b: FloatArray, beta, c: FloatArray):

@@ -99,7 +99,8 @@ class PeerSlab:
 
 
 class ShardedGroupedGemv:
-    """``count`` equally shaped block matrices, rows sharded over the ranks, one launch per step and rank.
+    """``count`` equally shaped block matrices, rows sharded over the ranks, ``per_launch`` matrices per launch
+    (one launch per step and rank by default) and one hand-shake per step.
 
     ``weights[m]`` is this rank's row block of matrix m (uint8 CUDA tensor of 34- or 18-byte blocks, rows
     ``shard_range(rows, world, rank)``).  ``launch()`` enqueues the step and returns the gathered
@@ -108,8 +109,9 @@ class ShardedGroupedGemv:
     """
 
     def __init__(self, rows: int, cols: int, batch: int, weights: list[torch.Tensor], fmt: str = "q8b", group=None,
-                 timeout_ms: int = 2000):
-        assert fmt in ("q8b", "q4b")
+                 timeout_ms: int = 2000, per_launch: int = 32):
+        assert fmt in ("q8b", "q4b") and 1 <= per_launch <= 32
+        self.per_launch = per_launch
         self.lib = B200Native.load()
         self.fn_name = f"tb200_{fmt}_gemv_i8_grouped"
         self.fn = getattr(self.lib, self.fn_name)
@@ -133,8 +135,12 @@ class ShardedGroupedGemv:
         self.ws_bytes = self.lib.tb200_qx_workspace_bytes(cols, batch)
         self.ws = torch.empty(max(self.ws_bytes, 16), dtype=torch.uint8, device=dev)
         # host arrays of device pointers, kept alive with the object
-        self._w_ptrs = (C.c_void_p * self.count)(*[w.data_ptr() for w in weights])
-        self._dst_ptrs = (C.c_void_p * self.world)(*self.slab.ptrs)
+        self._chunks = []  # (first matrix, matrices, weight pointers, destination pointers) of each launch
+        for m0 in range(0, self.count, per_launch):
+            n = min(per_launch, self.count - m0)
+            w_ptrs = (C.c_void_p * n)(*[w.data_ptr() for w in weights[m0:m0 + n]])
+            dst_ptrs = (C.c_void_p * self.world)(*[p + m0 * batch * rows * 4 for p in self.slab.ptrs])
+            self._chunks.append((m0, n, w_ptrs, dst_ptrs))
         self._flag_ptrs = (C.c_void_p * self.world)(*[p + self.slab.flags_offset for p in self.slab.ptrs])
         self._epoch = C.c_void_p(self.slab.own + self.slab.epoch_offset) if self.world > 1 else None
         self.steps = 0  # steps enqueued so far; step s writes half s & 1
@@ -143,10 +149,11 @@ class ShardedGroupedGemv:
         S = C.c_void_p(self.stream.cuda_stream)
         with torch.cuda.stream(self.stream):
             if self.local_rows > 0:
-                st = self.fn(self.count, self.local_rows, self.cols, self.batch, self._w_ptrs, C.c_void_p(self.x_dev.data_ptr()),
-                             self._dst_ptrs, self.world, self.half_floats, self._epoch, self.rows, self.r0,
-                             C.c_void_p(self.ws.data_ptr()), self.ws_bytes, S)
-                B200Native.check_status(st, self.fn_name)
+                for _, n, w_ptrs, dst_ptrs in self._chunks:
+                    st = self.fn(n, self.local_rows, self.cols, self.batch, w_ptrs, C.c_void_p(self.x_dev.data_ptr()),
+                                 dst_ptrs, self.world, self.half_floats, self._epoch, self.rows, self.r0,
+                                 C.c_void_p(self.ws.data_ptr()), self.ws_bytes, S)
+                    B200Native.check_status(st, self.fn_name)
             if self.world > 1:
                 st = self.lib.tb200_peer_signal_wait(self.rank, self.world, self._flag_ptrs, self._epoch, self.timeout_ms, S)
                 B200Native.check_status(st, "tb200_peer_signal_wait")

@@ -69,6 +69,7 @@ class B200Context:
 
 
 _QUANT_FUNCTIONS = {"q8Gemv", "q8GemvBytes", "q4GemvBytes"}
+_GROUPED_FUNCTIONS = {"q8GemvBytesGrouped": "tb200_q8b_gemv_i8_grouped", "q4GemvBytesGrouped": "tb200_q4b_gemv_i8_grouped"}
 
 
 class B200LibraryProvider:
@@ -92,6 +93,9 @@ class B200LibraryProvider:
             p = descriptor.getParameters()
             need = B200Native.load().tb200_qx_workspace_bytes(int(p[1]), int(p[2]))
             context.grow_workspace(int(need))
+        if fn in _GROUPED_FUNCTIONS:  # (count, rows, cols, batch, x, y, blocks...)
+            p = descriptor.getParameters()
+            context.grow_workspace(int(B200Native.load().tb200_qx_workspace_bytes(int(p[2]), int(p[3]))))
 
     def dispatch(self, functionName: str, inv: LibraryInvocation) -> None:  # noqa: N802
         ctx: B200Context = inv.getContext()
@@ -118,6 +122,12 @@ class B200LibraryProvider:
                 st = lib.tb200_q4b_gemv_i8(A(0), A(1), A(2), P(3), P(4), P(5), *ws, ctx.stream)
             else:
                 st = lib.tb200_q4b_gemv(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
+        elif functionName in _GROUPED_FUNCTIONS:  # (count, rows, cols, batch, x, y, blocks...)
+            count = A(0)
+            blocks = (C.c_void_p * count)(*[P(6 + m) for m in range(count)])
+            dst = (C.c_void_p * 1)(P(5))
+            st = getattr(lib, _GROUPED_FUNCTIONS[functionName])(count, A(1), A(2), A(3), blocks, P(4), dst, 1, 0, None, A(1), 0, *ws,
+                                                                ctx.stream)
         elif functionName == "sgemm":  # (m, n, k, alpha, a, b, beta, c)
             st = lib.tb200_sgemm(A(0), A(1), A(2), A(3), P(4), P(5), A(6), P(7), ctx.stream)
         elif functionName == "hgemmF32":  # (m, n, k, a, b, c)
