@@ -323,7 +323,7 @@ def run_gpu_arm(args):
     op = ShardedGroupedGemv(ROWS, COLS, BATCH, [blocks[l].view(-1) for l in range(LAYERS)], "q8b", per_launch=group)
     stream = op.stream
     op.x_dev.copy_(torch.randn((BATCH, COLS), device=dev, generator=torch.Generator(device=dev).manual_seed(99)))
-    launches_per_step = LAYERS // group + (1 if world > 1 else 0)
+    launches_per_step = LAYERS // group
 
     def barrier():
         if world > 1:
@@ -340,10 +340,11 @@ def run_gpu_arm(args):
             e0.record(stream)
             for _ in range(args.steps):
                 op.launch()
+            op.wait()  # the last step's outputs from every rank have arrived
             e1.record(stream)
             barrier()
         elapsed = e0.elapsed_time(e1) * 1e-3
-    gpu_launches = args.steps * launches_per_step
+    gpu_launches = args.steps * launches_per_step + (1 if world > 1 else 0)
     if world > 1:
         t = torch.tensor([elapsed], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -410,7 +411,7 @@ def run_gpu_arm(args):
         e2e_s = t.item()
         h2d, d2h = BATCH * COLS * 4, LAYERS * BATCH * ROWS * 4
         api = "ShardedGroupedGemv.run"
-    gpu_launches += e2e_steps * launches_per_step
+    gpu_launches += e2e_steps * (launches_per_step + (1 if world > 1 else 0))
     e2e_value = total_bytes * e2e_steps / e2e_s / 1e9
     status = C.c_int(0)
     lib.tb200_device_status(C.byref(status))
@@ -425,7 +426,7 @@ def run_gpu_arm(args):
                    "layers_per_step": LAYERS, "matrices_per_launch": group,
                    "l2_policy": f"{LAYERS} distinct weight matrices per step ({LAYERS * 62.4:.0f} MB > 126 MB L2)",
                    "parallelism": (f"rows sharded over {world} GPUs; the kernel stores each output into every GPU's gather buffer "
-                                   "(peer stores over NVLink), one flag hand-shake per step, no collective library on the data path")
+                                   "(peer stores over NVLink) and carries the flag hand-shake of the step, no collective library on the data path")
                    if world > 1 else "single GPU",
                    "mode": "int (fp32 activations quantised to int8 per 32-block inside the kernel, exact int32 block dots)",
                    "launch": f"{LAYERS // group} grouped launch(es) per step, programmatic dependent launches"},

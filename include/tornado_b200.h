@@ -198,6 +198,39 @@ int tb200_q4b_gemv_i8_grouped(int count, int rows, int cols, int batch, const vo
                               float *const *dst, int npeers, long long half_stride, const unsigned *epoch, int rows_total,
                               int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
 
+/* The same with the multi-GPU hand-shake inside the kernel (no separate launch
+ * between two steps).  The outputs rotate over nslots (2..4) slots of
+ * slot_stride floats: step s stores to slot s % nslots.  sync is two local
+ * words, zero at start: sync[0] counts this GPU's completed steps, sync[1] is
+ * scratch.  flags[p] is GPU p's flag array (8 words, zero at start; flags[rank]
+ * local, the others peer-mapped); flags[p][q] is the number of steps GPU q has
+ * announced as complete.  handshake bit 0: at its start (the launches before it
+ * have completed, so the stores of step s - 1 are performed) the kernel
+ * announces sync[0] = s to every GPU, and before its first store it waits until
+ * every GPU has announced s - nslots + 1, i.e. has started the step after the
+ * one whose outputs are about to be overwritten (two slots keep the GPUs within
+ * a step of one another, three give a step of slack); bit 1: the kernel advances
+ * sync[0] when its last CTA finishes.  A step made of several launches sets
+ * bit 0 on the first and bit 1 on the last.  Consumers of a step's outputs
+ * enqueue tb200_peer_wait first.  Needs the one-launch shapes (see above) and
+ * rows >= 1 on every GPU; waits are bounded by timeout_ms (0 = 2000), after
+ * which TB200_ERR_TIMEOUT is recorded (tb200_device_status) and the kernel
+ * carries on. */
+int tb200_q8b_gemv_i8_grouped_sync(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                                   float *const *dst, int npeers, int rank, int nslots, long long slot_stride, unsigned *sync,
+                                   unsigned *const *flags, int handshake, unsigned timeout_ms, int rows_total, int row_offset,
+                                   void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+int tb200_q4b_gemv_i8_grouped_sync(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                                   float *const *dst, int npeers, int rank, int nslots, long long slot_stride, unsigned *sync,
+                                   unsigned *const *flags, int handshake, unsigned timeout_ms, int rows_total, int row_offset,
+                                   void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+
+/* Announces sync[0] (this GPU's completed steps) to every GPU and waits
+ * (bounded) until every GPU has announced at least as many: all outputs of
+ * those steps have then arrived in this GPU's buffer.  Same flags / sync as above. */
+int tb200_peer_wait(int rank, int npeers, unsigned *const *flags, const unsigned *sync, unsigned timeout_ms,
+                    tb200_stream_t stream);
+
 /* Completes a step whose outputs were stored to the peers' buffers: raises this
  * GPU's flag (value *epoch + 1) in every GPU's flag array, waits until all flags
  * of this GPU's own array have reached that value, then stores it to *epoch.

@@ -145,3 +145,59 @@ def test_signal_wait_gives_up_after_its_time_limit(lib):
     assert status.value == TB200_ERR_TIMEOUT
     assert lib.tb200_device_status(C.byref(status)) == 0 and status.value == 0  # reading cleared it
     assert epoch.numpy()[0] == 1 and arrays[1].numpy()[0] == 1
+
+
+def test_grouped_sync_announces_waits_and_rotates_slots(lib):
+    """Three steps of the kernel that carries the hand-shake, as rank 0 of a stand-in group of two (two slots)."""
+    import torch
+    rows, cols, batch, count, npeers, rank, nslots = 300, 1024, 1, 2, 2, 0, 2
+    rows_total = 600
+    mats, x = _case("q8b", rows, cols, batch, count)
+    dws, dx = [DevBuf(m) for m in mats], DevBuf(x)
+    slot_floats = count * batch * rows_total
+    dsts = [DevBuf(np.full(nslots * slot_floats, np.float32(-5.0), np.float32)) for _ in range(npeers)]
+    flags = [DevBuf(np.zeros(8, np.uint32)) for _ in range(npeers)]
+    sync = DevBuf(np.zeros(4, np.uint32))
+    want = [_single(lib, "q8b", rows, cols, batch, dws[m], dx) for m in range(count)]
+
+    def set_peer_flag(v):  # what the other rank has announced, in this rank's flag array
+        flags[rank].t[flags[rank].header + 4:flags[rank].header + 8] = torch.tensor([v, 0, 0, 0], dtype=torch.uint8)
+
+    def step(timeout_ms=200):
+        st = lib.tb200_q8b_gemv_i8_grouped_sync(count, rows, cols, batch, _ptr_array(dws), dx.ptr, _ptr_array(dsts), npeers, rank,
+                                                nslots, slot_floats, sync.ptr, _ptr_array(flags), 3, timeout_ms, rows_total, 0, None, 0,
+                                                stream_ptr())
+        assert st == 0, lib.tb200_status_string(st)
+        torch.cuda.synchronize()
+
+    def slots(d):
+        return d.numpy().reshape(nslots, count, batch, rows_total)
+
+    step()  # step 0 needs nothing from the peer
+    sync_and_check(lib)
+    assert sync.numpy()[0] == 1 and sync.numpy()[1] == 0 and all(f.numpy()[rank] == 0 for f in flags)
+    for d in dsts:
+        assert all(np.array_equal(slots(d)[0, m, :, :rows], want[m]) for m in range(count))
+        assert (slots(d)[1] == -5.0).all() and (slots(d)[0, :, :, rows:] == -5.0).all()
+    step()  # step 1 announces one finished step and needs the peer to have started step 0: already true
+    sync_and_check(lib)
+    assert sync.numpy()[0] == 2 and all(f.numpy()[rank] == 1 for f in flags)
+    assert all(np.array_equal(slots(dsts[1])[1, m, :, :rows], want[m]) for m in range(count))
+    # step 2 overwrites slot 0 and needs the peer to have started its step 1; nothing has announced that,
+    # so the bounded wait gives up, records the fact and the kernel carries on
+    step(timeout_ms=20)
+    status = C.c_int(0)
+    assert lib.tb200_device_status(C.byref(status)) == 0 and status.value == TB200_ERR_TIMEOUT
+    assert sync.numpy()[0] == 3
+    set_peer_flag(2)
+    step()
+    sync_and_check(lib)
+    assert sync.numpy()[0] == 4 and all(f.numpy()[rank] == 3 for f in flags)
+    # completion for a consumer: announce 4 finished steps, wait for the peer to announce as many
+    assert lib.tb200_peer_wait(rank, npeers, _ptr_array(flags), sync.ptr, 20, stream_ptr()) == 0
+    torch.cuda.synchronize()
+    assert lib.tb200_device_status(C.byref(status)) == 0 and status.value == TB200_ERR_TIMEOUT  # peer is at 2 < 4
+    assert all(f.numpy()[rank] == 4 for f in flags)
+    set_peer_flag(4)
+    assert lib.tb200_peer_wait(rank, npeers, _ptr_array(flags), sync.ptr, 20, stream_ptr()) == 0
+    sync_and_check(lib)

@@ -60,7 +60,35 @@ struct QGroupArgs {
     const unsigned *epoch;         // device word whose low bit selects the half (null: half 0)
     long long half_stride;         // floats between the halves
     int count, rows_each, npeers, rows_total, row_offset;
+    // In-kernel hand-shake of a multi-GPU step (null flags[0]: none).  sync[0] is this GPU's step counter
+    // (the same word as `epoch`), sync[1] counts the CTAs of the running launch that have finished.
+    unsigned *flags[kMaxPeers];    // flags[p]: flag array of GPU p, one word per source GPU
+    unsigned *sync;
+    unsigned long long timeout_ns;
+    int rank;
+    int handshake;                 // bit 0: wait for the peers before the first store; bit 1: signal them at the end
+    int nslots;                    // output slots in rotation (the "halves" above when 2)
 };
+
+__device__ __forceinline__ unsigned long long qg_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait until the flag word has reached `target` (step numbers wrap, hence the signed difference).
+__device__ __forceinline__ void wait_flag_at_least(const unsigned *flag, unsigned target, unsigned long long timeout_ns) {
+    const unsigned long long t0 = qg_timer_ns();
+    for (unsigned spin = 0;; ++spin) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int)(v - target) >= 0) return;
+        if ((spin & 63) == 63 && qg_timer_ns() - t0 > timeout_ns) {
+            g_device_status = TB200_ERR_TIMEOUT;
+            return;
+        }
+    }
+}
 
 __device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 
@@ -589,6 +617,27 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     pdl_launch_dependents();
     pdl_wait();  // weights were requested above; activations and outputs wait for the predecessor
 
+    unsigned step = 0;
+    if constexpr (GROUPED) {
+        if (grp->flags[0]) {
+            // sync[0] = s steps of this GPU are complete (all their stores performed: the launches before this one
+            // have finished).  The first CTA tells every GPU so; then, before step s stores into the slot that
+            // held step s - nslots, every GPU must be done reading that slot, i.e. must have started its step
+            // s - nslots + 1, which is when it announced that count (bounded wait).  With two slots this holds
+            // GPUs within a step of one another; a third slot gives a further step of slack.
+            step = *reinterpret_cast<const volatile unsigned *>(grp->sync);
+            if ((grp->handshake & 1) && warp == 0 && lane < grp->npeers) {
+                if (blockIdx.x == 0) {
+                    __threadfence_system();
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(grp->flags[lane] + grp->rank), "r"(step) : "memory");
+                }
+                if (lane != grp->rank)
+                    wait_flag_at_least(grp->flags[grp->rank] + lane, step - (unsigned)(grp->nslots - 1), grp->timeout_ns);
+            }
+            // the other warps go on staging the activations; the barrier below joins them
+        }
+    }
+
     if (MODE == MODE_FLOAT) {
         stage_x_float<T::CPL>(reinterpret_cast<float4 *>(smem_raw), a.x, cols, B, slots);
     } else if (MODE == MODE_INT_FUSED) {
@@ -600,6 +649,17 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
 
     // ---- consume side ------------------------------------------------------------------
     float acc[R][B];
+    // GROUPED: results wait in registers (lane k holds the k-th pending row) until 32 consecutive rows of one
+    // matrix are complete, so that every destination -- peers over NVLink included -- gets 128-byte stores
+    float pend[B];
+    int pcnt = 0, pbase = 0;
+    size_t half = 0;
+    if constexpr (GROUPED) {
+        // the step counter was advanced by a kernel that completed before pdl_wait() returned
+        if (grp->flags[0]) half = (size_t)(step % (unsigned)grp->nslots) * grp->half_stride;
+        else if (grp->epoch) half = (size_t)(*reinterpret_cast<const volatile unsigned *>(grp->epoch) & 1u) * grp->half_stride;
+    }
+    const int warp_row_end = min(row_begin + g_end * R, row_end);
     int cg = g_begin, cch = 0, st = 0;
     while (cg < g_end) {
         cp_async_wait<STAGES - 1>();
@@ -712,17 +772,29 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
         if (++cch == nch) {
             cch = 0;
             if constexpr (GROUPED) {
-                // every destination gets the value: plain stores, to this GPU's memory and to peer-mapped memory
-                const size_t half = grp->epoch ? (size_t)(*reinterpret_cast<const volatile unsigned *>(grp->epoch) & 1u) * grp->half_stride : 0;
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     const int vrow = row0 + r;
-                    const int m = vrow / grp->rows_each;
-                    const size_t at = half + (size_t)m * B * grp->rows_total + grp->row_offset + (vrow - m * grp->rows_each);
+                    if (vrow < row_end) {  // warp-uniform
+                        if (pcnt == 0) pbase = vrow;
 #pragma unroll
-                    for (int b = 0; b < B; ++b) {
-                        const float s = warp_sum(acc[r][b]);
-                        if (lane < grp->npeers && vrow < row_end) grp->dst[lane][at + (size_t)b * grp->rows_total] = s;
+                        for (int b = 0; b < B; ++b) {
+                            const float s = warp_sum(acc[r][b]);
+                            if (lane == pcnt) pend[b] = s;
+                        }
+                        ++pcnt;
+                        const int m = pbase / grp->rows_each;
+                        if (pcnt == 32 || vrow + 1 == warp_row_end || vrow + 1 == (m + 1) * grp->rows_each) {
+                            const size_t at = half + (size_t)m * B * grp->rows_total + grp->row_offset + (pbase - m * grp->rows_each) + lane;
+                            if (lane < pcnt) {
+                                for (int p = 0; p < grp->npeers; ++p) {
+                                    float *d = grp->dst[p] + at;  // this GPU's buffer or a peer-mapped one: plain stores
+#pragma unroll
+                                    for (int b = 0; b < B; ++b) d[(size_t)b * grp->rows_total] = pend[b];
+                                }
+                            }
+                            pcnt = 0;
+                        }
                     }
                 }
             } else if (a.y) {
@@ -738,6 +810,20 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
         }
     }
     cp_async_wait<0>();
+    if constexpr (GROUPED) {
+        if (grp->flags[0] && (grp->handshake & 2)) {
+            // The CTA that finishes last advances the step counter (local memory only: the launch that follows,
+            // or tb200_peer_wait, announces it to the other GPUs once this launch has completed).
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned done = atomicAdd(grp->sync + 1, 1u);
+                if (done == gridDim.x - 1) {
+                    grp->sync[1] = 0;  // ready for the next launch
+                    grp->sync[0] = step + 1;
+                }
+            }
+        }
+    }
 }
 
 template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES>
@@ -1144,10 +1230,18 @@ static int qgemv_i8(int rows, int cols, int batch, const void *w, const uint16_t
 
 // Integer-mode mat-vec of `count` equally shaped block matrices on the same activations, one launch,
 // every output value stored to `npeers` destination buffers.
+struct GroupSync {  // in-kernel hand-shake of a multi-GPU step; flags == nullptr: none
+    unsigned *const *flags;
+    unsigned *sync;
+    int rank, handshake;
+    unsigned timeout_ms;
+    int nslots;
+};
+
 template <int FMT>
 static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x, float *const *dst,
                             int npeers, long long half_stride, const unsigned *epoch, int rows_total, int row_offset, void *workspace,
-                            size_t workspace_bytes, tb200_stream_t stream) {
+                            size_t workspace_bytes, tb200_stream_t stream, const GroupSync &gs = GroupSync{}) {
     if (count < 1 || count > kMaxGroup || npeers < 1 || npeers > kMaxPeers || !blocks || !dst || !x) return TB200_ERR_INVALID_ARG;
     if (rows < 0 || cols < 0 || cols % 32 != 0 || batch < 1 || batch > kMaxBatch) return TB200_ERR_INVALID_ARG;
     if (row_offset < 0 || rows_total < rows || row_offset > rows_total - rows || half_stride < 0) return TB200_ERR_INVALID_ARG;
@@ -1165,6 +1259,19 @@ static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void
         if (!dst[p]) return TB200_ERR_INVALID_ARG;
         if (!aligned_to(dst[p], 4)) return TB200_ERR_ALIGNMENT;
         grp.dst[p] = dst[p];
+    }
+    if (gs.flags) {
+        // every GPU of the group must take part in every step, and only the one-launch kernel holds the hand-shake
+        if (!gs.sync || gs.rank < 0 || gs.rank >= npeers || rows < 1 || !aligned_to(gs.sync, 4)) return TB200_ERR_INVALID_ARG;
+        if (gs.nslots < 2 || gs.nslots > 4) return TB200_ERR_INVALID_ARG;
+        grp.nslots = gs.nslots;
+        for (int p = 0; p < npeers; ++p) {
+            if (!gs.flags[p] || !aligned_to(gs.flags[p], 4)) return TB200_ERR_INVALID_ARG;
+            grp.flags[p] = gs.flags[p];
+        }
+        grp.sync = gs.sync, grp.rank = gs.rank, grp.handshake = gs.handshake;
+        grp.timeout_ns = (unsigned long long)(gs.timeout_ms ? gs.timeout_ms : 2000u) * 1000000ull;
+        epoch = gs.sync;
     }
     if (rows == 0) return TB200_OK;
     grp.epoch = epoch, grp.half_stride = half_stride, grp.count = count, grp.rows_each = rows;
@@ -1186,7 +1293,7 @@ static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void
         return launch_ring_grouped_b<FMT, MODE_INT>(a, grp, di, s);
     }
     // other shapes and alignments: one launch per matrix, into the single local destination only
-    if (npeers != 1 || epoch) return TB200_ERR_INVALID_ARG;
+    if (npeers != 1 || epoch || gs.flags) return TB200_ERR_INVALID_ARG;
     int8_t *xq;
     float *xs;
     st = split_workspace(cols, batch, workspace, workspace_bytes, &xq, &xs);
@@ -1268,6 +1375,24 @@ extern "C" int tb200_q4b_gemv_i8_grouped(int count, int rows, int cols, int batc
                                          int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
     return qgemv_i8_grouped<FMT_Q4B>(count, rows, cols, batch, blocks, x, dst, npeers, half_stride, epoch, rows_total, row_offset,
                                      workspace, workspace_bytes, stream);
+}
+
+extern "C" int tb200_q8b_gemv_i8_grouped_sync(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                                              float *const *dst, int npeers, int rank, int nslots, long long slot_stride, unsigned *sync,
+                                              unsigned *const *flags, int handshake, unsigned timeout_ms, int rows_total, int row_offset,
+                                              void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    if (!flags || !sync) return TB200_ERR_INVALID_ARG;
+    return qgemv_i8_grouped<FMT_Q8B>(count, rows, cols, batch, blocks, x, dst, npeers, slot_stride, nullptr, rows_total, row_offset,
+                                     workspace, workspace_bytes, stream, GroupSync{flags, sync, rank, handshake, timeout_ms, nslots});
+}
+
+extern "C" int tb200_q4b_gemv_i8_grouped_sync(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
+                                              float *const *dst, int npeers, int rank, int nslots, long long slot_stride, unsigned *sync,
+                                              unsigned *const *flags, int handshake, unsigned timeout_ms, int rows_total, int row_offset,
+                                              void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    if (!flags || !sync) return TB200_ERR_INVALID_ARG;
+    return qgemv_i8_grouped<FMT_Q4B>(count, rows, cols, batch, blocks, x, dst, npeers, slot_stride, nullptr, rows_total, row_offset,
+                                     workspace, workspace_bytes, stream, GroupSync{flags, sync, rank, handshake, timeout_ms, nslots});
 }
 
 // The block-dot entries take an already quantised activation vector and write

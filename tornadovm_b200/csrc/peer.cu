@@ -54,7 +54,36 @@ __global__ void __launch_bounds__(32) peer_signal_wait_kernel(const __grid_const
     if (p == 0) *a.epoch = e;
 }
 
+// Completion of the steps whose kernels carry the hand-shake themselves: announce this GPU's count of
+// finished steps to every GPU, then wait until every GPU has announced at least as many.
+__global__ void __launch_bounds__(32) peer_wait_kernel(const __grid_constant__ PeerFlagArgs a) {
+    const unsigned e = *reinterpret_cast<const volatile unsigned *>(a.epoch);
+    const int p = threadIdx.x;
+    if (p < a.npeers) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags[p] + a.rank), "r"(e) : "memory");
+        if (p != a.rank) wait_flag_at_least(a.flags[a.rank] + p, e, a.timeout_ns);
+    }
+}
+
 }  // namespace tb200
+
+extern "C" int tb200_peer_wait(int rank, int npeers, unsigned *const *flags, const unsigned *sync, unsigned timeout_ms,
+                               tb200_stream_t stream) {
+    using namespace tb200;
+    if (npeers < 1 || npeers > kPeerMax || rank < 0 || rank >= npeers || !flags || !sync) return TB200_ERR_INVALID_ARG;
+    PeerFlagArgs a{};
+    for (int p = 0; p < npeers; ++p) {
+        if (!flags[p]) return TB200_ERR_INVALID_ARG;
+        if (!aligned_to(flags[p], 4)) return TB200_ERR_ALIGNMENT;
+        a.flags[p] = flags[p];
+    }
+    if (!aligned_to(sync, 4)) return TB200_ERR_ALIGNMENT;
+    a.epoch = const_cast<unsigned *>(sync), a.rank = rank, a.npeers = npeers;
+    a.timeout_ns = (unsigned long long)(timeout_ms ? timeout_ms : 2000u) * 1000000ull;
+    // a plain launch: it starts only after everything enqueued before it has completed
+    return launch_kernel(peer_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, false, a);
+}
 
 extern "C" int tb200_peer_signal_wait(int rank, int npeers, unsigned *const *flags, unsigned *epoch, unsigned timeout_ms,
                                       tb200_stream_t stream) {

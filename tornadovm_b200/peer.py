@@ -2,9 +2,11 @@
 
 One process per GPU.  Each rank owns the same row block of ``count`` block-format matrices
 (Q8_0 34-byte or Q4_0 18-byte blocks) and runs ONE launch per step for all of them
-(``tb200_q8b_gemv_i8_grouped``); the kernel stores every output value into the gather buffer of
-every rank (its own and, over NVLink, the peers' CUDA-IPC mapped ones), and one small kernel per
-step (``tb200_peer_signal_wait``) is the hand-shake that replaces the all-gather.  The reference has
+(``tb200_q8b_gemv_i8_grouped_sync``); the kernel stores every output value into the gather buffer of
+every rank (its own and, over NVLink, the peers' CUDA-IPC mapped ones) and carries the hand-shake
+that replaces the all-gather: at its start it announces the steps this rank has completed to every
+rank and waits until no rank still reads the slot it is about to overwrite; ``wait()`` completes a step
+for a consumer.  The reference has
 no counterpart: its multi-device mode runs independent tasks with host round trips
 (docs/source/multi-device.rst:9-14).
 
@@ -39,7 +41,7 @@ def wrap_device_memory(ptr: int, nbytes: int, device: torch.device) -> torch.Ten
 class PeerSlab:
     """One device allocation per rank, mapped into every rank of the group.
 
-    Layout: ``[payload_bytes][flags: FLAG_WORDS x u32][epoch: u32]``, zero-filled.  ``ptrs[p]`` is rank p's
+    Layout: ``[payload_bytes][flags: FLAG_WORDS x u32][step counter: u32][scratch: u32]``, zero-filled.  ``ptrs[p]`` is rank p's
     slab as addressable from this process.
     """
 
@@ -109,8 +111,9 @@ class ShardedGroupedGemv:
     """
 
     def __init__(self, rows: int, cols: int, batch: int, weights: list[torch.Tensor], fmt: str = "q8b", group=None,
-                 timeout_ms: int = 2000, per_launch: int = 32):
-        assert fmt in ("q8b", "q4b") and 1 <= per_launch <= 32
+                 timeout_ms: int = 2000, per_launch: int = 32, nslots: int = 3):
+        assert fmt in ("q8b", "q4b") and 1 <= per_launch <= 32 and 2 <= nslots <= 4
+        self.nslots = nslots
         self.per_launch = per_launch
         self.lib = B200Native.load()
         self.fn_name = f"tb200_{fmt}_gemv_i8_grouped"
@@ -128,8 +131,8 @@ class ShardedGroupedGemv:
         self.device, self.timeout_ms = dev, timeout_ms
         self.stream = torch.cuda.Stream(device=dev)
         self.half_floats = self.count * batch * rows
-        self.slab = PeerSlab(2 * self.half_floats * 4, dev, group)
-        self.halves = self.slab.bytes[:2 * self.half_floats * 4].view(torch.float32).view(2, self.count, batch, rows)
+        self.slab = PeerSlab(nslots * self.half_floats * 4, dev, group)
+        self.halves = self.slab.bytes[:nslots * self.half_floats * 4].view(torch.float32).view(nslots, self.count, batch, rows)
         self.x_dev = torch.empty((batch, cols), dtype=torch.float32, device=dev)
         self.y_host = torch.empty((self.count, batch, rows), dtype=torch.float32, pin_memory=True)
         self.ws_bytes = self.lib.tb200_qx_workspace_bytes(cols, batch)
@@ -142,29 +145,46 @@ class ShardedGroupedGemv:
             dst_ptrs = (C.c_void_p * self.world)(*[p + m0 * batch * rows * 4 for p in self.slab.ptrs])
             self._chunks.append((m0, n, w_ptrs, dst_ptrs))
         self._flag_ptrs = (C.c_void_p * self.world)(*[p + self.slab.flags_offset for p in self.slab.ptrs])
-        self._epoch = C.c_void_p(self.slab.own + self.slab.epoch_offset) if self.world > 1 else None
-        self.steps = 0  # steps enqueued so far; step s writes half s & 1
+        self._flags_local = C.c_void_p(self.slab.own + self.slab.flags_offset)
+        self._sync = C.c_void_p(self.slab.own + self.slab.epoch_offset)  # [step counter][finished-CTA counter]
+        self.fn_sync = getattr(self.lib, self.fn_name + "_sync")
+        assert self.world == 1 or rows >= self.world * 1 and self.local_rows >= 1, "every rank needs at least one row"
+        self.steps = 0  # steps enqueued so far; step s writes slot s % nslots
 
     def launch(self) -> torch.Tensor:
+        """Enqueue one step.  With several ranks the kernels carry the hand-shake: the first launch of the step
+        announces the completed steps and waits until no rank reads the slot it is about to overwrite, the last
+        one advances the step counter.  The returned slot is complete on this rank once ``wait()`` (enqueued
+        after it) has passed."""
         S = C.c_void_p(self.stream.cuda_stream)
+        X, W = C.c_void_p(self.x_dev.data_ptr()), C.c_void_p(self.ws.data_ptr())
         with torch.cuda.stream(self.stream):
-            if self.local_rows > 0:
-                for _, n, w_ptrs, dst_ptrs in self._chunks:
-                    st = self.fn(n, self.local_rows, self.cols, self.batch, w_ptrs, C.c_void_p(self.x_dev.data_ptr()),
-                                 dst_ptrs, self.world, self.half_floats, self._epoch, self.rows, self.r0,
-                                 C.c_void_p(self.ws.data_ptr()), self.ws_bytes, S)
-                    B200Native.check_status(st, self.fn_name)
-            if self.world > 1:
-                st = self.lib.tb200_peer_signal_wait(self.rank, self.world, self._flag_ptrs, self._epoch, self.timeout_ms, S)
-                B200Native.check_status(st, "tb200_peer_signal_wait")
-        half = self.steps & 1 if self.world > 1 else 0
+            last = len(self._chunks) - 1
+            for i, (_, n, w_ptrs, dst_ptrs) in enumerate(self._chunks):
+                if self.world > 1:
+                    handshake = (1 if i == 0 else 0) | (2 if i == last else 0)
+                    st = self.fn_sync(n, self.local_rows, self.cols, self.batch, w_ptrs, X, dst_ptrs, self.world, self.rank,
+                                      self.nslots, self.half_floats, self._sync, self._flag_ptrs, handshake, self.timeout_ms, self.rows, self.r0,
+                                      W, self.ws_bytes, S)
+                else:
+                    st = self.fn(n, self.local_rows, self.cols, self.batch, w_ptrs, X, dst_ptrs, 1, 0, None, self.rows, 0,
+                                 W, self.ws_bytes, S)
+                B200Native.check_status(st, self.fn_name)
+        half = self.steps % self.nslots if self.world > 1 else 0
         self.steps += 1
         return self.halves[half]
+
+    def wait(self) -> None:
+        """Enqueue the completion of the steps launched so far: every rank's outputs have arrived in this rank's buffer."""
+        if self.world > 1:
+            st = self.lib.tb200_peer_wait(self.rank, self.world, self._flag_ptrs, self._sync, self.timeout_ms, C.c_void_p(self.stream.cuda_stream))
+            B200Native.check_status(st, "tb200_peer_wait")
 
     def run(self, x_host: torch.Tensor) -> torch.Tensor:
         with torch.cuda.stream(self.stream):
             self.x_dev.copy_(x_host, non_blocking=True)
             y = self.launch()
+            self.wait()
             self.y_host.copy_(y, non_blocking=True)
         self.stream.synchronize()
         return self.y_host
