@@ -71,6 +71,38 @@ public final class B200 {
         return descriptor("q4GemvBytes", new Object[] { rows, cols, batch, blocks, x, y }, 5, false, options);
     }
 
+    /**
+     * Integer-mode Q8_0 mat-vec of up to 32 equally shaped block matrices that read the same activations, in one launch:
+     * {@code y[matrix][batch][rows]}. Parameter list: (count, rows, cols, batch, x, y, blocks...).
+     */
+    public static LibraryTaskDescriptor q8GemvBytesGrouped(int rows, int cols, int batch, FloatArray x, FloatArray y, B200Options options, ByteArray... blocks) {
+        return grouped("q8GemvBytesGrouped", 34, rows, cols, batch, x, y, options, blocks);
+    }
+
+    /** Q4_0 twin of {@link #q8GemvBytesGrouped}. */
+    public static LibraryTaskDescriptor q4GemvBytesGrouped(int rows, int cols, int batch, FloatArray x, FloatArray y, B200Options options, ByteArray... blocks) {
+        return grouped("q4GemvBytesGrouped", 18, rows, cols, batch, x, y, options, blocks);
+    }
+
+    private static LibraryTaskDescriptor grouped(String name, int blockBytes, int rows, int cols, int batch, FloatArray x, FloatArray y, B200Options options, ByteArray[] blocks) {
+        checkQuantised(name, rows, cols, batch, x, y);
+        check(blocks.length >= 1 && blocks.length <= 32, "B200 " + name + " requires 1 to 32 matrices; got " + blocks.length);
+        check(y.getSize() >= (long) blocks.length * batch * rows, "B200 " + name + ": y smaller than count x batch x rows");
+        for (ByteArray b : blocks) {
+            check(b.getSize() >= (long) rows * (cols / 32) * blockBytes, "B200 " + name + ": weights too small");
+        }
+        check(options == null || options.exactInt, "B200 " + name + " computes in integer mode; exactInt must be set");
+        Object[] params = new Object[6 + blocks.length];
+        params[0] = blocks.length;
+        params[1] = rows;
+        params[2] = cols;
+        params[3] = batch;
+        params[4] = x;
+        params[5] = y;
+        System.arraycopy(blocks, 0, params, 6, blocks.length);
+        return descriptor(name, params, 5, false, options != null ? options : new B200Options().exactInt(true));
+    }
+
     /** {@code C = alpha*A*B + beta*C}, row-major FP32 on CUDA cores. */
     public static LibraryTaskDescriptor sgemm(int m, int n, int k, float alpha, FloatArray a, FloatArray b, float beta, FloatArray c) {
         check(m >= 0 && n >= 0 && k >= 0, "B200 sgemm requires non-negative sizes; got m=" + m + ", n=" + n + ", k=" + k);

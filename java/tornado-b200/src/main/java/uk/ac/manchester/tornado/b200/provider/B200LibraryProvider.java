@@ -70,6 +70,10 @@ public final class B200LibraryProvider implements TornadoLibraryProvider {
                 Object[] p = descriptor.getParameters();
                 ((B200Context) context).growWorkspace(B200Native.qxWorkspaceBytes((int) p[1], (int) p[2]));
             }
+            if (descriptor.getFunctionName().endsWith("Grouped")) { // (count, rows, cols, batch, ...)
+                Object[] p = descriptor.getParameters();
+                ((B200Context) context).growWorkspace(B200Native.qxWorkspaceBytes((int) p[2], (int) p[3]));
+            }
         }
     }
 
@@ -95,6 +99,16 @@ public final class B200LibraryProvider implements TornadoLibraryProvider {
                                 inv.getDevicePointer(4), inv.getDevicePointer(5), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream) //
                         : B200Native.blockGemv(kind, (int) inv.getArg(0), (int) inv.getArg(1), (int) inv.getArg(2), inv.getDevicePointer(3), //
                                 inv.getDevicePointer(4), inv.getDevicePointer(5), ctx.stream);
+            }
+            // (count, rows, cols, batch, x, y, blocks...)
+            case "q8GemvBytesGrouped", "q4GemvBytesGrouped" -> {
+                int count = (int) inv.getArg(0);
+                long[] blocks = new long[count];
+                for (int m = 0; m < count; m++) {
+                    blocks[m] = inv.getDevicePointer(6 + m);
+                }
+                yield B200Native.blockGemvI8Grouped(functionName.startsWith("q8") ? 0 : 1, count, (int) inv.getArg(1), (int) inv.getArg(2), (int) inv.getArg(3), //
+                        blocks, inv.getDevicePointer(4), inv.getDevicePointer(5), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream);
             }
             // (m, n, k, alpha, a, b, beta, c)
             case "sgemm" -> B200Native.sgemm((int) inv.getArg(0), (int) inv.getArg(1), (int) inv.getArg(2), (float) inv.getArg(3), //

@@ -32,6 +32,8 @@ public final class B200Native {
     private static MethodHandle q8bGemvI8;
     private static MethodHandle q4bGemv;
     private static MethodHandle q4bGemvI8;
+    private static MethodHandle q8bGemvI8Grouped;
+    private static MethodHandle q4bGemvI8Grouped;
     private static MethodHandle sgemm;
     private static MethodHandle hgemmF32;
     private static MethodHandle qxWorkspaceBytes;
@@ -65,6 +67,11 @@ public final class B200Native {
         q8bGemvI8 = handle("tb200_q8b_gemv_i8", gemvI);
         q4bGemv = handle("tb200_q4b_gemv", gemvF);
         q4bGemvI8 = handle("tb200_q4b_gemv_i8", gemvI);
+        // int tb200_q8b_gemv_i8_grouped(count, rows, cols, batch, blocks**, x, dst**, npeers, half_stride, epoch, rows_total, row_offset, ws, ws_bytes, stream)
+        FunctionDescriptor grouped = FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_INT,
+                JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG);
+        q8bGemvI8Grouped = handle("tb200_q8b_gemv_i8_grouped", grouped);
+        q4bGemvI8Grouped = handle("tb200_q4b_gemv_i8_grouped", grouped);
         sgemm = handle("tb200_sgemm", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_FLOAT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG, JAVA_LONG));
         hgemmF32 = handle("tb200_hgemm_f32", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG));
         qxWorkspaceBytes = handle("tb200_qx_workspace_bytes", FunctionDescriptor.of(JAVA_LONG, JAVA_INT, JAVA_INT));
@@ -114,6 +121,17 @@ public final class B200Native {
     public static int blockGemvI8(int kind, int rows, int cols, int batch, long blocks, long x, long y, long workspace, long workspaceBytes, long stream) {
         try {
             return (int) (kind == 0 ? q8bGemvI8 : q4bGemvI8).invokeExact(rows, cols, batch, blocks, x, y, workspace, workspaceBytes, stream);
+        } catch (Throwable t) {
+            throw wrap(t);
+        }
+    }
+
+    /** One launch for {@code blocks.length} matrices; the pointer arrays live in a confined arena for the duration of the call only. */
+    public static int blockGemvI8Grouped(int kind, int count, int rows, int cols, int batch, long[] blocks, long x, long y, long workspace, long workspaceBytes, long stream) {
+        try (Arena arena = Arena.ofConfined()) {
+            MemorySegment blockPtrs = arena.allocateFrom(JAVA_LONG, blocks);
+            MemorySegment dst = arena.allocateFrom(JAVA_LONG, y);
+            return (int) (kind == 0 ? q8bGemvI8Grouped : q4bGemvI8Grouped).invokeExact(count, rows, cols, batch, blockPtrs, x, dst, 1, 0L, 0L, rows, 0, workspace, workspaceBytes, stream);
         } catch (Throwable t) {
             throw wrap(t);
         }
