@@ -15,8 +15,10 @@ same metric through the public task-graph API with host buffers (activation
 host->device and result device->host inside every step); `roofline` compares
 the GEMV kernel with the measured HBM copy bandwidth; `cpu_baseline` times the
 CPU restatement of the reference's sequential / multi-core loop on the host.
-With N > 1 the weight rows are sharded over the ranks and the outputs are
-all-gathered over NCCL (strong scaling: the total work is fixed).
+The step is one grouped launch over the 32 matrices (--group G: G per launch).
+With N > 1 the weight rows are sharded over the ranks and the kernel stores every
+output into every rank's buffer over NVLink (strong scaling: the total work is
+fixed).
 """
 from __future__ import annotations
 
@@ -35,9 +37,10 @@ sys.path.insert(0, ROOT)
 
 ROWS, COLS, BATCH = 14336, 4096, 1
 LAYERS = 32  # one step = this projection in each of 32 decoder layers (Llama-3-8B depth): 32 distinct matrices, 2.0 GB
-# dram__bytes_read.sum + dram__bytes_write.sum of one 14336 x 4096 integer-mode launch, from the ncu capture
-# summarised in profiles/q8s_gemv_int_14336x4096.md (62.45 MB read + ~0.15 MB written)
-NCU_TRAFFIC_BYTES_PER_GEMV = 62_600_000
+# dram__bytes_read.sum + dram__bytes_write.sum per 14336 x 4096 matrix of a grouped integer-mode launch, from the ncu
+# capture summarised in profiles/qblk_gemv_grouped_32x14336x4096.md (8 matrices per launch: 499.3 MB read + 5.2 MB
+# written; the kernel reads every weight byte once, so traffic grows in proportion to the matrices of a launch)
+NCU_TRAFFIC_BYTES_PER_GEMV = 63_060_000
 METRIC = "q8_0_gemv_hbm_throughput"
 UNIT = "GB/s"
 
