@@ -346,6 +346,19 @@ def run_gpu_arm(args):
             op.wait()  # the last step's outputs from every rank have arrived
             e1.record(stream)
             barrier()
+            # nvidia-smi samples every 100 ms and a short timed region can fall between two samples: keep the
+            # same load running (untimed, every rank the same number of steps) until a few samples exist
+            t_load = time.perf_counter()
+            for _ in range(40):
+                enough = torch.tensor([1 if (len(clocks.rows) >= 3 or time.perf_counter() - t_load > 2.0) else 0], device=dev)
+                if world > 1:
+                    dist.all_reduce(enough, op=dist.ReduceOp.MIN)
+                if enough.item():
+                    break
+                for _ in range(200):
+                    op.launch()
+                op.wait()
+                barrier()
         elapsed = e0.elapsed_time(e1) * 1e-3
     gpu_launches = args.steps * launches_per_step + (1 if world > 1 else 0)
     if world > 1:
@@ -455,6 +468,60 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_hgemm_sharded(args):
+    """FP16 GEMM with B and C sharded by N-columns over the ranks (launch under torch.distributed.run):
+    the local tcgen05 GEMM alone and with the NCCL all-gather of the C column blocks."""
+    import torch
+    import torch.distributed as dist
+    from tornadovm_b200.sharding import ShardedHgemm, shard_cols
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _, tensor_peak, _ = measured_peaks()
+    out = {}
+    for n in (int(v) for v in args.hgemm_sizes.split(",")):
+        g = torch.Generator(device=dev).manual_seed(7)  # the same A on every rank
+        a = (torch.randn((n, n), device=dev, generator=g) / n**0.5).half()
+        b_local = (torch.randn((n, shard_cols(n, world)), device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank)) / n**0.5).half()
+        op = ShardedHgemm(n, n, n, a, b_local)
+
+        def timed(fn, reps=10):
+            for _ in range(3):
+                fn()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(op.stream)
+            for _ in range(reps):
+                fn()
+            e1.record(op.stream)
+            op.stream.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / reps * 1e-3], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+
+        def compute_only():
+            with torch.cuda.stream(op.stream):
+                op.compute()
+        tc, tg = timed(compute_only), timed(lambda: op.launch(assemble=False))
+        out[f"hgemm_{n}"] = {"gpus": world, "compute_TFLOP/s": 2 * n**3 / tc / 1e12, "compute_ms": tc * 1e3,
+                             "compute_plus_gather_TFLOP/s": 2 * n**3 / tg / 1e12, "compute_plus_gather_ms": tg * 1e3,
+                             "frac_tensor_compute": 2 * n**3 / tc / 1e12 / (tensor_peak * world)}
+        del op, a, b_local
+    if rank == 0:
+        print(json.dumps({"sections": out}))
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -464,12 +531,14 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=8.0)
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--group", type=int, default=LAYERS, help="matrices per launch (a divisor of the 32 per step)")
-    ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q8layers,q4,sgemm,hgemm) and print their timings; for profiling")
+    ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q8layers,q4,sgemm,hgemm; or hgemm_sharded under torch.distributed.run) and print their timings; for profiling")
     ap.add_argument("--hgemm-sizes", default="2048,4096,8192,16384")
     ap.add_argument("--hgemm-variant", default="pairs", choices=["pairs", "single"],
                     help="with --sections: 256x256 tiles on SM pairs (the default of the library) or 128x256 tiles on single SMs")
     args = ap.parse_args()
-    if args.sections:
+    if args.sections == "hgemm_sharded":
+        run_hgemm_sharded(args)
+    elif args.sections:
         import torch
         from tornadovm_b200.native import B200Native
         torch.cuda.set_device(0)

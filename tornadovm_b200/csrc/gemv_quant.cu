@@ -52,6 +52,9 @@ struct QGemvArgs {
 
 // Several matrices of one shape sharing the activation vectors, and several destinations for every
 // output value (this GPU's buffer and, peer-mapped, the other GPUs' buffers).
+// rows a warp of the grouped kernel collects before it stores them (32-byte sectors to every destination);
+// short runs keep the stores to peer memory spread over the launch instead of bunched at its end
+constexpr int kGroupFlushRows = 8;
 constexpr int kMaxGroup = 32;
 constexpr int kMaxPeers = 8;
 struct QGroupArgs {
@@ -649,8 +652,8 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
 
     // ---- consume side ------------------------------------------------------------------
     float acc[R][B];
-    // GROUPED: results wait in registers (lane k holds the k-th pending row) until 32 consecutive rows of one
-    // matrix are complete, so that every destination -- peers over NVLink included -- gets 128-byte stores
+    // GROUPED: results wait in registers (lane k holds the k-th pending row) until kGroupFlushRows consecutive rows
+    // of one matrix are complete, so that every destination -- peers over NVLink included -- gets whole sectors
     float pend[B];
     int pcnt = 0, pbase = 0;
     size_t half = 0;
@@ -784,7 +787,7 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                         }
                         ++pcnt;
                         const int m = pbase / grp->rows_each;
-                        if (pcnt == 32 || vrow + 1 == warp_row_end || vrow + 1 == (m + 1) * grp->rows_each) {
+                        if (pcnt == kGroupFlushRows || vrow + 1 == warp_row_end || vrow + 1 == (m + 1) * grp->rows_each) {
                             const size_t at = half + (size_t)m * B * grp->rows_total + grp->row_offset + (pbase - m * grp->rows_each) + lane;
                             if (lane < pcnt) {
                                 for (int p = 0; p < grp->npeers; ++p) {

@@ -111,3 +111,75 @@ class ShardedQ8Gemv:
             self.y_host.copy_(y, non_blocking=True)
         self.stream.synchronize()
         return self.y_host
+
+
+# ---------------------------------------------------------------------------------------------
+# FP16 GEMM: B and C sharded by N-columns, A replicated
+# ---------------------------------------------------------------------------------------------
+def shard_cols(n: int, world: int, multiple: int = 8) -> int:
+    """Columns per rank: equal blocks, rounded up to ``multiple`` (the tensor-core kernel needs n % 8 == 0)."""
+    per = (n + world - 1) // world
+    return (per + multiple - 1) // multiple * multiple
+
+
+def col_range(n: int, world: int, rank: int, multiple: int = 8) -> tuple[int, int]:
+    per = shard_cols(n, world, multiple)
+    c0 = min(rank * per, n)
+    return c0, min(c0 + per, n)
+
+
+def take_cols(b: torch.Tensor, n: int, world: int, rank: int) -> torch.Tensor:
+    """This rank's column block of a row-major ``[k][n]`` matrix as a contiguous ``[k][per]`` matrix
+    (zero-padded on the ranks whose block runs past n)."""
+    per = shard_cols(n, world)
+    c0, c1 = col_range(n, world, rank)
+    out = torch.zeros((b.shape[0], per), dtype=b.dtype, device=b.device)
+    out[:, :c1 - c0] = b[:, c0:c1]
+    return out
+
+
+def gather_cols(c_local: torch.Tensor, n: int, group=None, out: torch.Tensor | None = None, assemble: bool = True) -> torch.Tensor:
+    """All-gather per-rank ``[m][per]`` column blocks.  ``assemble=False`` returns the gathered
+    ``[world][m][per]`` buffer as it arrives (layout left to the consumer, no extra pass over C);
+    ``assemble=True`` returns the row-major ``[m][n]`` matrix (one strided copy)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    m, per = c_local.shape
+    if world == 1:
+        return c_local[:, :n] if assemble else c_local.view(1, m, per)
+    if out is None:
+        out = torch.empty((world, m, per), dtype=c_local.dtype, device=c_local.device)
+    dist.all_gather_into_tensor(out.view(-1), c_local.reshape(-1), group=group)
+    if not assemble:
+        return out
+    return out.permute(1, 0, 2).reshape(m, world * per)[:, :n].contiguous()
+
+
+class ShardedHgemm:
+    """``C(fp32)[m][n] = A(fp16)[m][k] * B(fp16)[k][n]`` with B and C sharded by columns over the ranks.
+
+    ``b_local`` is this rank's contiguous ``[k][shard_cols(n, world)]`` block (``take_cols``), ``a`` the
+    replicated A.  ``launch()`` enqueues the local tcgen05 GEMM and the NCCL all-gather of the C blocks.
+    """
+
+    def __init__(self, m: int, n: int, k: int, a: torch.Tensor, b_local: torch.Tensor, group=None):
+        self.m, self.n, self.k, self.group = m, n, k, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.per = shard_cols(n, self.world)
+        assert a.is_cuda and a.dtype == torch.float16 and a.shape == (m, k)
+        assert b_local.is_cuda and b_local.dtype == torch.float16 and b_local.shape == (k, self.per) and b_local.is_contiguous()
+        self.a, self.b = a, b_local
+        self.lib = B200Native.load()
+        self.stream = torch.cuda.Stream(device=a.device)
+        self.c_local = torch.empty((m, self.per), dtype=torch.float32, device=a.device)
+        self.gathered = torch.empty((self.world, m, self.per), dtype=torch.float32, device=a.device) if self.world > 1 else None
+
+    def compute(self) -> torch.Tensor:
+        P = lambda t: C.c_void_p(t.data_ptr())
+        st = self.lib.tb200_hgemm_f32(self.m, self.per, self.k, P(self.a), P(self.b), P(self.c_local), C.c_void_p(self.stream.cuda_stream))
+        B200Native.check_status(st, "tb200_hgemm_f32")
+        return self.c_local
+
+    def launch(self, assemble: bool = False) -> torch.Tensor:
+        with torch.cuda.stream(self.stream):
+            self.compute()
+            return gather_cols(self.c_local, self.n, self.group, self.gathered, assemble)
