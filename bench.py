@@ -266,7 +266,21 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 def sweep_i(i):
                     for (r, c), w in zip(shapes, wsets[i & 1]):
                         lib.tb200_q4b_gemv_i8(r, c, batch, P(w), P(xs[c]), P(ys[r]), P(ws), ws_n, S)
-                for name, fn in ((f"q4_layer_sweep_f32_b{batch}", sweep_f), (f"q4_layer_sweep_int_b{batch}", sweep_i)):
+                # the same sweep with every matrix that reads the 4096-element vector in one launch (7 of the 8)
+                idx = [[j for j, (r, c) in enumerate(shapes) if c == cc] for cc in (4096, 14336)]
+                ysep = [torch.empty((batch, r), device=dev) for r, c in shapes]  # one output array per matrix
+                garg = []
+                for k in range(2):
+                    garg.append([((C.c_int * len(ix))(*[shapes[j][0] for j in ix]), (C.c_void_p * len(ix))(*[wsets[k][j].data_ptr() for j in ix]),
+                                  (C.c_void_p * len(ix))(*[ysep[j].data_ptr() for j in ix]), len(ix), shapes[ix[0]][1]) for ix in idx])
+
+                def sweep_g(i):
+                    for rows_a, w_a, y_a, n, c in garg[i & 1]:
+                        lib.tb200_q4b_gemv_i8_grouped_rows(n, rows_a, c, batch, w_a, P(xs[c]), y_a, P(ws), ws_n, S)
+                runs = [(f"q4_layer_sweep_f32_b{batch}", sweep_f), (f"q4_layer_sweep_int_b{batch}", sweep_i)]
+                if batch <= 4:
+                    runs.append((f"q4_layer_sweep_int_grouped_b{batch}", sweep_g))
+                for name, fn in runs:
                     t = timeit(fn, 3, period=2)
                     out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
             del wsets

@@ -198,7 +198,16 @@ int tb200_q4b_gemv_i8_grouped(int count, int rows, int cols, int batch, const vo
                               float *const *dst, int npeers, long long half_stride, const unsigned *epoch, int rows_total,
                               int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
 
-/* The same with the multi-GPU hand-shake inside the kernel (no separate launch
+/* Matrices of different row counts (the Q, K and V projections of a layer, or
+ * every matrix of a decode step that reads the same vector): rows[m] rows for
+ * matrix m, and y[m] (host array of device pointers) its own [batch][rows[m]]
+ * output array on this GPU.  Same shape limits for the one-launch path. */
+int tb200_q8b_gemv_i8_grouped_rows(int count, const int *rows, int cols, int batch, const void *const *blocks, const float *x,
+                                   float *const *y, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+int tb200_q4b_gemv_i8_grouped_rows(int count, const int *rows, int cols, int batch, const void *const *blocks, const float *x,
+                                   float *const *y, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
+
+/* The equally shaped form with the multi-GPU hand-shake inside the kernel (no separate launch
  * between two steps).  The outputs rotate over nslots (2..4) slots of
  * slot_stride floats: step s stores to slot s % nslots.  sync is two local
  * words, zero at start: sync[0] counts this GPU's completed steps, sync[1] is

@@ -201,3 +201,31 @@ def test_grouped_sync_announces_waits_and_rotates_slots(lib):
     set_peer_flag(4)
     assert lib.tb200_peer_wait(rank, npeers, _ptr_array(flags), sync.ptr, 20, stream_ptr()) == 0
     sync_and_check(lib)
+
+
+@pytest.mark.parametrize("fmt", ["q8b", "q4b"])
+@pytest.mark.parametrize("cols,batch", [(1024, 1), (4096, 2), (96, 1), (14336, 4)])
+def test_grouped_rows_of_different_shapes_equal_one_launch_per_matrix(lib, fmt, cols, batch):
+    """The projections that read one vector (different row counts, one of them empty), each with its own output array."""
+    rows = [300, 64, 0, 64, 1000, 17] if cols < 8192 else [40, 9, 0, 33]
+    mats, x = [], None
+    for m, r in enumerate(rows):
+        ms, xm = _case(fmt, max(r, 1), cols, batch, 1)
+        mats.append(ms[0])
+        x = xm if x is None else x
+    dws, dx = [DevBuf(m) for m in mats], DevBuf(x)
+    dys = [out_buf(max(r, 1) * batch) for r in rows]
+    n = lib.tb200_qx_workspace_bytes(cols, batch)
+    ws = DevBuf(np.zeros(max(n, 16), np.uint8))
+    fn = lib.tb200_q8b_gemv_i8_grouped_rows if fmt == "q8b" else lib.tb200_q4b_gemv_i8_grouped_rows
+    st = fn(len(rows), (C.c_int * len(rows))(*rows), cols, batch, _ptr_array(dws), dx.ptr, _ptr_array(dys), ws.ptr, n, stream_ptr())
+    assert st == 0, lib.tb200_status_string(st)
+    sync_and_check(lib)
+    for m, r in enumerate(rows):
+        if r == 0:
+            assert np.isnan(dys[m].numpy()).all()  # untouched
+            continue
+        want = _single(lib, fmt, r, cols, batch, dws[m], dx)
+        got = dys[m].numpy()[:batch * r].reshape(batch, r)
+        assert np.array_equal(got, want), (m, r)
+        assert dys[m].guard_intact()

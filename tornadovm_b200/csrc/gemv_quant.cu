@@ -58,11 +58,15 @@ constexpr int kGroupFlushRows = 32;
 constexpr int kMaxGroup = 32;
 constexpr int kMaxPeers = 8;
 struct QGroupArgs {
-    const uint8_t *w[kMaxGroup];   // block arrays, `rows_each` rows each
-    float *dst[kMaxPeers];         // output buffers: [2 halves][matrix][batch][rows_total]
+    const uint8_t *w[kMaxGroup];   // block arrays; matrix m holds rows row_start[m] .. row_start[m+1] of the launch
+    int row_start[kMaxGroup + 1];
+    long long out_off[kMaxGroup];  // where matrix m's [batch][ld[m]] output block starts inside a slot (floats)
+    int ld[kMaxGroup];             // rows of the whole (unsharded) matrix m
+    int row_off[kMaxGroup];        // first row of this launch's share of matrix m
+    float *dst[kMaxPeers];         // output buffers, each [slots][...]
     const unsigned *epoch;         // device word whose low bit selects the half (null: half 0)
     long long half_stride;         // floats between the halves
-    int count, rows_each, npeers, rows_total, row_offset;
+    int count, npeers;
     // In-kernel hand-shake of a multi-GPU step (null flags[0]: none).  sync[0] is this GPU's step counter
     // (the same word as `epoch`), sync[1] counts the CTAs of the running launch that have finished.
     unsigned *flags[kMaxPeers];    // flags[p]: flag array of GPU p, one word per source GPU
@@ -591,6 +595,7 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
 
     // ---- issue side ------------------------------------------------------------------
     int ig = g_begin, ich = 0;
+    int im = 0;  // GROUPED: matrix of the row being requested; rows only move forward
     auto issue = [&](int st) {
         if (ig < g_end) {
             const int nblk = min(kChunkBlocks, bpr - ich * kChunkBlocks);
@@ -600,8 +605,8 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                 const int vrow = min(row_begin + ig * R + r, row_end - 1);
                 const unsigned char *src;
                 if constexpr (GROUPED) {
-                    const int m = vrow / grp->rows_each;
-                    src = grp->w[m] + (size_t)(vrow - m * grp->rows_each) * row_bytes + (size_t)ich * T::CB + lane * 16;
+                    while (vrow >= grp->row_start[im + 1]) ++im;  // vrow < row_start[count]
+                    src = grp->w[im] + (size_t)(vrow - grp->row_start[im]) * row_bytes + (size_t)ich * T::CB + lane * 16;
                 } else {
                     src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16;
                 }
@@ -655,7 +660,7 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     // GROUPED: results wait in registers (lane k holds the k-th pending row) until kGroupFlushRows consecutive rows
     // of one matrix are complete, so that every destination -- peers over NVLink included -- gets whole sectors
     float pend[B];
-    int pcnt = 0, pbase = 0;
+    int pcnt = 0, pbase = 0, cm = 0;
     size_t half = 0;
     if constexpr (GROUPED) {
         // the step counter was advanced by a kernel that completed before pdl_wait() returned
@@ -786,14 +791,15 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                             if (lane == pcnt) pend[b] = s;
                         }
                         ++pcnt;
-                        const int m = pbase / grp->rows_each;
-                        if (pcnt == kGroupFlushRows || vrow + 1 == warp_row_end || vrow + 1 == (m + 1) * grp->rows_each) {
-                            const size_t at = half + (size_t)m * B * grp->rows_total + grp->row_offset + (pbase - m * grp->rows_each) + lane;
+                        while (pbase >= grp->row_start[cm + 1]) ++cm;  // matrix of the pending run
+                        if (pcnt == kGroupFlushRows || vrow + 1 == warp_row_end || vrow + 1 == grp->row_start[cm + 1]) {
+                            const long long at = (long long)half + grp->out_off[cm] + grp->row_off[cm] + (pbase - grp->row_start[cm]) + lane;
+                            const size_t ld = (size_t)grp->ld[cm];
                             if (lane < pcnt) {
                                 for (int p = 0; p < grp->npeers; ++p) {
                                     float *d = grp->dst[p] + at;  // this GPU's buffer or a peer-mapped one: plain stores
 #pragma unroll
-                                    for (int b = 0; b < B; ++b) d[(size_t)b * grp->rows_total] = pend[b];
+                                    for (int b = 0; b < B; ++b) d[b * ld] = pend[b];
                                 }
                             }
                             pcnt = 0;
@@ -1241,23 +1247,35 @@ struct GroupSync {  // in-kernel hand-shake of a multi-GPU step; flags == nullpt
     int nslots;
 };
 
+struct GroupShape {  // per matrix: rows in this launch, output block offset inside a slot, whole-matrix rows, first row
+    int rows[kMaxGroup];
+    long long out_off[kMaxGroup];
+    int ld[kMaxGroup];
+    int row_off[kMaxGroup];
+};
+
 template <int FMT>
-static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x, float *const *dst,
-                            int npeers, long long half_stride, const unsigned *epoch, int rows_total, int row_offset, void *workspace,
-                            size_t workspace_bytes, tb200_stream_t stream, const GroupSync &gs = GroupSync{}) {
+static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, int batch, const void *const *blocks, const float *x,
+                                  float *const *dst, int npeers, long long half_stride, const unsigned *epoch, void *workspace,
+                                  size_t workspace_bytes, tb200_stream_t stream, const GroupSync &gs) {
     if (count < 1 || count > kMaxGroup || npeers < 1 || npeers > kMaxPeers || !blocks || !dst || !x) return TB200_ERR_INVALID_ARG;
-    if (rows < 0 || cols < 0 || cols % 32 != 0 || batch < 1 || batch > kMaxBatch) return TB200_ERR_INVALID_ARG;
-    if (row_offset < 0 || rows_total < rows || row_offset > rows_total - rows || half_stride < 0) return TB200_ERR_INVALID_ARG;
-    if ((long long)count * rows > 0x7fffffffLL) return TB200_ERR_INVALID_ARG;
+    if (cols < 0 || cols % 32 != 0 || batch < 1 || batch > kMaxBatch || half_stride < 0) return TB200_ERR_INVALID_ARG;
     if (!aligned_to(x, 4) || (epoch && !aligned_to(epoch, 4))) return TB200_ERR_ALIGNMENT;
     QGroupArgs grp{};
     bool fast = cols % 256 == 0 && cols > 0;
+    long long total = 0;
     for (int m = 0; m < count; ++m) {
-        if (!blocks[m]) return TB200_ERR_INVALID_ARG;
+        if (!blocks[m] || shape.rows[m] < 0) return TB200_ERR_INVALID_ARG;
+        if (shape.row_off[m] < 0 || shape.ld[m] < shape.rows[m] || shape.row_off[m] > shape.ld[m] - shape.rows[m]) return TB200_ERR_INVALID_ARG;
         if (!aligned_to(blocks[m], 2)) return TB200_ERR_ALIGNMENT;
         fast = fast && aligned_to(blocks[m], 16);
         grp.w[m] = reinterpret_cast<const uint8_t *>(blocks[m]);
+        grp.row_start[m] = (int)total;
+        grp.out_off[m] = shape.out_off[m], grp.ld[m] = shape.ld[m], grp.row_off[m] = shape.row_off[m];
+        total += shape.rows[m];
+        if (total > 0x7fffffffLL) return TB200_ERR_INVALID_ARG;
     }
+    grp.row_start[count] = (int)total;
     for (int p = 0; p < npeers; ++p) {
         if (!dst[p]) return TB200_ERR_INVALID_ARG;
         if (!aligned_to(dst[p], 4)) return TB200_ERR_ALIGNMENT;
@@ -1265,7 +1283,7 @@ static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void
     }
     if (gs.flags) {
         // every GPU of the group must take part in every step, and only the one-launch kernel holds the hand-shake
-        if (!gs.sync || gs.rank < 0 || gs.rank >= npeers || rows < 1 || !aligned_to(gs.sync, 4)) return TB200_ERR_INVALID_ARG;
+        if (!gs.sync || gs.rank < 0 || gs.rank >= npeers || total < 1 || !aligned_to(gs.sync, 4)) return TB200_ERR_INVALID_ARG;
         if (gs.nslots < 2 || gs.nslots > 4) return TB200_ERR_INVALID_ARG;
         grp.nslots = gs.nslots;
         for (int p = 0; p < npeers; ++p) {
@@ -1276,14 +1294,13 @@ static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void
         grp.timeout_ns = (unsigned long long)(gs.timeout_ms ? gs.timeout_ms : 2000u) * 1000000ull;
         epoch = gs.sync;
     }
-    if (rows == 0) return TB200_OK;
-    grp.epoch = epoch, grp.half_stride = half_stride, grp.count = count, grp.rows_each = rows;
-    grp.npeers = npeers, grp.rows_total = rows_total, grp.row_offset = row_offset;
+    if (total == 0) return TB200_OK;
+    grp.epoch = epoch, grp.half_stride = half_stride, grp.count = count, grp.npeers = npeers;
     int st;
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
     cudaStream_t s = (cudaStream_t)stream;
-    QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, count * rows, cols, batch};
+    QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, (int)total, cols, batch};
     if (fast && batch <= 4 && fast_batch_fits<FMT, MODE_INT>(cols, batch, PATH_RING, di)) {
         if ((long long)batch * cols <= kFusedQuantMaxElems) return launch_ring_grouped_b<FMT, MODE_INT_FUSED>(a, grp, di, s);
         int8_t *xq;
@@ -1302,12 +1319,45 @@ static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void
     st = split_workspace(cols, batch, workspace, workspace_bytes, &xq, &xs);
     if (st) return st;
     for (int m = 0; m < count; ++m) {
-        if (batch > 1 && rows_total != rows) return TB200_ERR_INVALID_ARG;  // the single-matrix kernels write [batch][rows]
-        QGemvArgs one{grp.w[m], nullptr, x, nullptr, nullptr, dst[0] + (size_t)m * batch * rows_total + row_offset, nullptr, rows, cols, batch};
+        if (batch > 1 && shape.ld[m] != shape.rows[m]) return TB200_ERR_INVALID_ARG;  // the single-matrix kernels write [batch][rows]
+        QGemvArgs one{grp.w[m], nullptr, x, nullptr, nullptr, dst[0] + shape.out_off[m] + shape.row_off[m], nullptr, shape.rows[m], cols, batch};
         st = qgemv_dispatch<FMT, MODE_INT_FUSED, false>(one, xq, xs, stream);
         if (st) return st;
     }
     return TB200_OK;
+}
+
+// equally shaped matrices, outputs [matrix][batch][rows_total] in every slot
+template <int FMT>
+static int qgemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x, float *const *dst,
+                            int npeers, long long half_stride, const unsigned *epoch, int rows_total, int row_offset, void *workspace,
+                            size_t workspace_bytes, tb200_stream_t stream, const GroupSync &gs = GroupSync{}) {
+    if (count < 1 || count > kMaxGroup || rows < 0 || batch < 1) return TB200_ERR_INVALID_ARG;
+    if (row_offset < 0 || rows_total < rows || row_offset > rows_total - rows) return TB200_ERR_INVALID_ARG;
+    if (gs.flags && rows < 1) return TB200_ERR_INVALID_ARG;
+    GroupShape shape;
+    for (int m = 0; m < count; ++m) {
+        shape.rows[m] = rows, shape.out_off[m] = (long long)m * batch * rows_total, shape.ld[m] = rows_total, shape.row_off[m] = row_offset;
+    }
+    return qgemv_i8_grouped_shape<FMT>(count, shape, cols, batch, blocks, x, dst, npeers, half_stride, epoch, workspace, workspace_bytes,
+                                       stream, gs);
+}
+
+// matrices of different row counts, each with its own [batch][rows[m]] output array on this GPU
+template <int FMT>
+static int qgemv_i8_grouped_rows(int count, const int *rows, int cols, int batch, const void *const *blocks, const float *x,
+                                 float *const *y, void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    if (count < 1 || count > kMaxGroup || !rows || !y) return TB200_ERR_INVALID_ARG;
+    GroupShape shape;
+    for (int m = 0; m < count; ++m) {
+        if (!y[m]) return TB200_ERR_INVALID_ARG;
+        if (!aligned_to(y[m], 4)) return TB200_ERR_ALIGNMENT;
+        shape.rows[m] = rows[m], shape.ld[m] = rows[m], shape.row_off[m] = 0;
+        shape.out_off[m] = y[m] - y[0];  // floats; may be negative
+    }
+    float *base[1] = {y[0]};
+    return qgemv_i8_grouped_shape<FMT>(count, shape, cols, batch, blocks, x, base, 1, 0, nullptr, workspace, workspace_bytes, stream,
+                                       GroupSync{});
 }
 
 }  // namespace tb200
@@ -1396,6 +1446,16 @@ extern "C" int tb200_q4b_gemv_i8_grouped_sync(int count, int rows, int cols, int
     if (!flags || !sync) return TB200_ERR_INVALID_ARG;
     return qgemv_i8_grouped<FMT_Q4B>(count, rows, cols, batch, blocks, x, dst, npeers, slot_stride, nullptr, rows_total, row_offset,
                                      workspace, workspace_bytes, stream, GroupSync{flags, sync, rank, handshake, timeout_ms, nslots});
+}
+
+extern "C" int tb200_q8b_gemv_i8_grouped_rows(int count, const int *rows, int cols, int batch, const void *const *blocks, const float *x,
+                                              float *const *y, void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    return qgemv_i8_grouped_rows<FMT_Q8B>(count, rows, cols, batch, blocks, x, y, workspace, workspace_bytes, stream);
+}
+
+extern "C" int tb200_q4b_gemv_i8_grouped_rows(int count, const int *rows, int cols, int batch, const void *const *blocks, const float *x,
+                                              float *const *y, void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    return qgemv_i8_grouped_rows<FMT_Q4B>(count, rows, cols, batch, blocks, x, y, workspace, workspace_bytes, stream);
 }
 
 // The block-dot entries take an already quantised activation vector and write

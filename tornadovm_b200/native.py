@@ -36,6 +36,8 @@ SIGNATURES = {
     "tb200_q4b_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_q8b_gemv_i8_grouped": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, C.c_longlong, _P, _I, _I, _P, _Z, _P]),
     "tb200_q4b_gemv_i8_grouped": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, C.c_longlong, _P, _I, _I, _P, _Z, _P]),
+    "tb200_q8b_gemv_i8_grouped_rows": (_I, [_I, _P, _I, _I, _P, _P, _P, _P, _Z, _P]),
+    "tb200_q4b_gemv_i8_grouped_rows": (_I, [_I, _P, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_q8b_gemv_i8_grouped_sync": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, _I, _I, C.c_longlong, _P, _P, _I, C.c_uint, _I, _I, _P, _Z, _P]),
     "tb200_q4b_gemv_i8_grouped_sync": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, _I, _I, C.c_longlong, _P, _P, _I, C.c_uint, _I, _I, _P, _Z, _P]),
     "tb200_peer_wait": (_I, [_I, _I, _P, _P, C.c_uint, _P]),
