@@ -7,6 +7,7 @@ namespace tb200 {
 
 int g_overlap_launches = 0;
 int g_float_tensor_cores = 1;
+int g_mma_warp_rings = 1;
 int g_float_tc_min_batch = 0;  // 0: per-format default, 1: every eligible call
 extern int g_hgemm_pairs;
 
@@ -106,6 +107,9 @@ extern "C" int tb200_set_option(int option, int value) {
         case TB200_OPT_HGEMM_SM_PAIRS:
             tb200::g_hgemm_pairs = value != 0;
             return TB200_OK;
+        case TB200_OPT_MMA_WARP_RINGS:
+            tb200::g_mma_warp_rings = value != 0;
+            return TB200_OK;
         case TB200_OPT_FLOAT_TENSOR_CORES:
             tb200::g_float_tensor_cores = value != 0;
             tb200::g_float_tc_min_batch = value >= 2 ? 1 : 0;
@@ -123,6 +127,9 @@ extern "C" int tb200_get_option(int option, int *value) {
             return TB200_OK;
         case TB200_OPT_HGEMM_SM_PAIRS:
             *value = tb200::g_hgemm_pairs;
+            return TB200_OK;
+        case TB200_OPT_MMA_WARP_RINGS:
+            *value = tb200::g_mma_warp_rings;
             return TB200_OK;
         case TB200_OPT_FLOAT_TENSOR_CORES:
             *value = tb200::g_float_tensor_cores ? 1 + tb200::g_float_tc_min_batch : 0;

@@ -595,7 +595,7 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
 
     // ---- issue side ------------------------------------------------------------------
     int ig = g_begin, ich = 0;
-    int im = 0;  // GROUPED: matrix of the row being requested; rows only move forward
+    int im = 0;  // GROUPED: matrix of the first row of the group being requested; groups only move forward
     auto issue = [&](int st) {
         if (ig < g_end) {
             const int nblk = min(kChunkBlocks, bpr - ich * kChunkBlocks);
@@ -605,8 +605,10 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                 const int vrow = min(row_begin + ig * R + r, row_end - 1);
                 const unsigned char *src;
                 if constexpr (GROUPED) {
-                    while (vrow >= grp->row_start[im + 1]) ++im;  // vrow < row_start[count]
-                    src = grp->w[im] + (size_t)(vrow - grp->row_start[im]) * row_bytes + (size_t)ich * T::CB + lane * 16;
+                    int m = im;
+                    while (vrow >= grp->row_start[m + 1]) ++m;  // vrow < row_start[count]
+                    if (r == 0) im = m;  // the later chunks of this group start from its first row again
+                    src = grp->w[m] + (size_t)(vrow - grp->row_start[m]) * row_bytes + (size_t)ich * T::CB + lane * 16;
                 } else {
                     src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16;
                 }
