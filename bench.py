@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the b200/linalg hot path.
 
-Headline workload (BASELINE.json configs[3]): Q8_0 quantised GEMV, decode style,
+Headline workload: Q8_0 quantised GEMV, decode style,
 W[14336 x 4096] as 32-element int8 blocks with one fp16 scale each, fp32
 activations, batch 1.  One "step" is one decode pass over LAYERS = 32 distinct
 weight matrices of that shape, one per decoder layer (2.0 GB > the 126 MB L2, so
@@ -194,7 +194,7 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
 
     with torch.cuda.stream(stream):
         if "sgemv" in sections:
-            # FP32 GEMV 8192 x 8192 (configs[0]); two matrices alternate (537 MB > L2)
+            # FP32 GEMV 8192 x 8192; two matrices alternate (537 MB > L2)
             m = torch.rand((2, 8192, 8192), device=dev) * 2 - 1
             v = torch.rand(8192, device=dev) * 2 - 1
             y = torch.empty(8192, device=dev)
@@ -247,7 +247,7 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 out[f"q8_blocks_int_b1_{grp}_per_launch"] = {"GB/s": grp * by / t / 1e9, "frac_hbm": grp * by / t / 1e9 / hbm_peak, "us": t * 1e6}
             del blocks
         if "q4" in sections:
-            # Q4_0 Llama-3-8B-shaped layer sweep (configs[4]): 7 projections + the output projection
+            # Q4_0 Llama-3-8B-shaped layer sweep: 7 projections + the output projection
             shapes = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336), (128256, 4096)]
             g = torch.Generator(device=dev).manual_seed(3)
             # two sets of weights alternate so that a pass never finds its matrices in L2 (2 x 418 MB)
@@ -285,14 +285,21 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                     out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
             del wsets
         if "sgemm" in sections:
-            # FP32 SGEMM 4096^3 (configs[1])
+            # FP32 SGEMM 4096^3
             a = torch.rand((4096, 4096), device=dev)
             bm = torch.rand((4096, 4096), device=dev)
             c = torch.empty((4096, 4096), device=dev)
-            t = timeit(lambda i: lib.tb200_sgemm(4096, 4096, 4096, C.c_float(1.0), P(a), P(bm), C.c_float(0.0), P(c), S), 3, period=2)
-            out["sgemm_4096"] = {"TFLOP/s": 2 * 4096**3 / t / 1e12, "ms": t * 1e3}
+            run = lambda i: lib.tb200_sgemm(4096, 4096, 4096, C.c_float(1.0), P(a), P(bm), C.c_float(0.0), P(c), S)
+            t = timeit(run, 3, period=2)
+            # the SM clock under sustained FFMA load decides what the CUDA cores can deliver: sample it over half a second
+            with ClockSampler(torch.cuda.current_device()) as ck:
+                t_long = timeit(run, 100, period=2)
+            mhz = ck.summary()["sm_mhz"]
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            out["sgemm_4096"] = {"TFLOP/s": 2 * 4096**3 / t / 1e12, "ms": t * 1e3, "sustained_TFLOP/s": 2 * 4096**3 / t_long / 1e12,
+                                 "sm_mhz_sustained": mhz, "frac_ffma_at_clock": (2 * 4096**3 / t_long / 1e12) / (sms * 128 * 2 * mhz * 1e-6) if mhz else None}
         if "hgemm" in sections:
-            # FP16 GEMM sweep (configs[2])
+            # FP16 GEMM sweep
             for n in hgemm_sizes:
                 ah = (torch.randn((n, n), device=dev) / n**0.5).half()
                 bh = (torch.randn((n, n), device=dev) / n**0.5).half()
