@@ -496,7 +496,7 @@ __global__ void __launch_bounds__(WM_THREADS, 1) qmmaw_gemv_kernel(QGemvArgs a) 
         }
         const unsigned char *rp0 = base + g * T::WS;
         const unsigned char *rp1 = rp0 + 8 * T::WS;
-#pragma unroll
+#pragma unroll 4
         for (int kb = 0; kb < MM_KB; ++kb) {
             uint32_t a0, a1, a2, a3;
             float sw0, sw1;
