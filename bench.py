@@ -508,7 +508,7 @@ def run_hgemm_sharded(args):
         g = torch.Generator(device=dev).manual_seed(7)  # the same A on every rank
         a = (torch.randn((n, n), device=dev, generator=g) / n**0.5).half()
         b_local = (torch.randn((n, shard_cols(n, world)), device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank)) / n**0.5).half()
-        op = ShardedHgemm(n, n, n, a, b_local)
+        op = ShardedHgemm(n, n, n, a, b_local, fused=n % (8 * world) == 0)
 
         def timed(fn, reps=10):
             for _ in range(3):
@@ -530,10 +530,24 @@ def run_hgemm_sharded(args):
         def compute_only():
             with torch.cuda.stream(op.stream):
                 op.compute()
+
+        def fused():
+            with torch.cuda.stream(op.stream):
+                op.launch_fused()
         tc, tg = timed(compute_only), timed(lambda: op.launch(assemble=False))
         out[f"hgemm_{n}"] = {"gpus": world, "compute_TFLOP/s": 2 * n**3 / tc / 1e12, "compute_ms": tc * 1e3,
-                             "compute_plus_gather_TFLOP/s": 2 * n**3 / tg / 1e12, "compute_plus_gather_ms": tg * 1e3,
+                             "compute_plus_nccl_gather_TFLOP/s": 2 * n**3 / tg / 1e12, "compute_plus_nccl_gather_ms": tg * 1e3,
                              "frac_tensor_compute": 2 * n**3 / tc / 1e12 / (tensor_peak * world)}
+        if op.slab is not None:
+            tf = timed(fused)
+            # the fused result against the gathered one (same kernel arithmetic: equal bit for bit)
+            with torch.cuda.stream(op.stream):
+                cf = op.launch_fused()
+                cg = op.launch(assemble=True)
+            op.stream.synchronize()
+            out[f"hgemm_{n}"].update({"fused_epilogue_gather_TFLOP/s": 2 * n**3 / tf / 1e12, "fused_epilogue_gather_ms": tf * 1e3,
+                                      "fused_equals_gathered": bool(torch.equal(cf, cg))})
+        op.close()
         del op, a, b_local
     if rank == 0:
         print(json.dumps({"sections": out}))

@@ -288,6 +288,16 @@ int tb200_sgemm(int m, int n, int k, float alpha, const float *a, const float *b
  * 16-byte aligned; any other case takes a CUDA-core kernel. */
 int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c, tb200_stream_t stream);
 
+/* The same product with every finished tile stored to ndst (<= 8) destination
+ * buffers at dst[p][row * ld + col_offset + col]: this GPU's buffer and, mapped
+ * with tb200_ipc_open, its peers'.  With B and C sharded by N-columns over the
+ * GPUs (b is this GPU's contiguous [k][n] column block, ld the unsharded N,
+ * col_offset the block's first column) the all-gather of C is part of the
+ * epilogue; follow it with tb200_peer_signal_wait.  Tensor-core shapes only
+ * (see above).  No counterpart in the reference. */
+int tb200_hgemm_f32_scatter(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *const *dst, int ndst,
+                            long long ld, long long col_offset, tb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

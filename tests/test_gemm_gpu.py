@@ -151,3 +151,27 @@ def test_hgemm_both_tensor_core_variants(lib, pairs, m, n, k):
         assert ((c - ref_all).norm() / ref_all.norm()).item() <= 1e-4
     finally:
         lib.tb200_set_option(2, old.value)
+
+
+def test_hgemm_scatter_stores_every_tile_to_every_destination(lib):
+    """The column-sharded form on one GPU: two destination buffers (stand-ins for two GPUs' results), the
+    shard's columns land at their offset of the wide row-major matrix, nothing else is touched."""
+    m, n_local, k, n_total, col_off = 384, 512, 256, 1536, 512
+    a16, b16 = o.make_hgemm(m, n_local, k)
+    da, db = DevBuf(a16), DevBuf(b16)
+    plain = out_buf(m * n_local)
+    assert lib.tb200_hgemm_f32(m, n_local, k, da.ptr, db.ptr, plain.ptr, stream_ptr()) == 0
+    sentinel = np.float32(-3.0)
+    dsts = [DevBuf(np.full(m * n_total, sentinel, np.float32)) for _ in range(2)]
+    ptrs = (C.c_void_p * 2)(*[d.ptr.value for d in dsts])
+    st = lib.tb200_hgemm_f32_scatter(m, n_local, k, da.ptr, db.ptr, ptrs, 2, n_total, col_off, stream_ptr())
+    assert st == 0, lib.tb200_status_string(st)
+    sync_and_check(lib)
+    want = np.full((m, n_total), sentinel, np.float32)
+    want[:, col_off:col_off + n_local] = plain.numpy().reshape(m, n_local)
+    for d in dsts:
+        assert np.array_equal(d.numpy().reshape(m, n_total), want)
+        assert d.guard_intact()
+    # argument checks: the block must fit inside the wide matrix
+    assert lib.tb200_hgemm_f32_scatter(m, n_local, k, da.ptr, db.ptr, ptrs, 2, n_total, n_total - n_local + 8, stream_ptr()) == -1
+    assert lib.tb200_hgemm_f32_scatter(m, n_local, k, da.ptr, db.ptr, ptrs, 9, n_total, 0, stream_ptr()) == -1

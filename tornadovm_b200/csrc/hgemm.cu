@@ -34,7 +34,11 @@ constexpr int HG_THREADS = 192;
 constexpr int HG_A_BYTES = HG_BM * HG_BK * 2;      // 16 KB
 constexpr int HG_B_BYTES = HG_BK * HG_BN * 2;      // 32 KB, four 8 KB boxes of 64 columns
 constexpr int HG_STAGE_BYTES = HG_A_BYTES + HG_B_BYTES;
-constexpr int HG_SMEM_BYTES = HG_STAGES * HG_STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
+// Each epilogue warp owns a 32 x 32 fp32 transposition buffer (row pitch 36 floats: conflict-free float4 access both ways),
+// used when tiles go to several destinations: stores to peer memory should be whole 128-byte lines, not 16-byte pieces
+// of 32 different rows.
+constexpr int HG_XPOSE_PITCH = 36, HG_XPOSE_BYTES = 4 * 32 * HG_XPOSE_PITCH * 4;
+constexpr int HG_SMEM_BYTES = HG_STAGES * HG_STAGE_BYTES + 1024 + HG_XPOSE_BYTES;  // + slack for 1024-byte alignment
 constexpr uint32_t HG_TMEM_COLS = 512;
 
 // ---- PTX wrappers ------------------------------------------------------------
@@ -118,8 +122,19 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 //   bit 15 A major (0 = K)   bit 16 B major (1 = MN)   [17,23) N >> 3   [24,29) M >> 4
 constexpr uint32_t HG_IDESC = (1u << 4) | (1u << 16) | ((uint32_t)(HG_BN >> 3) << 17) | ((uint32_t)(HG_BM >> 4) << 24);
 
+// Where the epilogue stores a tile: every destination gets C[row][col] at dst[p][row * ld + col_off + col].
+// One local destination with ld = N is the plain GEMM; several destinations (this GPU's buffer and
+// peer-mapped buffers of other GPUs) with ld = the unsharded N and col_off = the first column of this GPU's
+// column block make the all-gather of a column-sharded GEMM part of the epilogue.
+constexpr int HG_MAX_DST = 8;
+struct HgOut {
+    float *dst[HG_MAX_DST];
+    long long ld, col_off;
+    int ndst;
+};
+
 __global__ void __launch_bounds__(HG_THREADS, 1)
-hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float *__restrict__ C,
+hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ HgOut out,
                 int M, int N, int K, int c_vec_ok, int gm) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[HG_STAGES];
@@ -244,18 +259,40 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 tc_ld_32cols(taddr + c * 32, v);
                 tc_wait_ld();
                 const int col0 = n0 + c * 32;
-                if (row < M && col0 < N) {
-                    float *dst = C + (size_t)row * N + col0;
-                    if (c_vec_ok && col0 + 32 <= N) {
+                if (out.ndst > 1 && c_vec_ok && col0 + 32 <= N) {
+                    // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
+                    float *stg = reinterpret_cast<float *>(tiles + (size_t)HG_STAGES * HG_STAGE_BYTES) + (warp - 2) * 32 * HG_XPOSE_PITCH;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            *reinterpret_cast<float4 *>(dst + 4 * j) =
-                                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                            __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                    } else {
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4 *>(stg + lane * HG_XPOSE_PITCH + 4 * j) =
+                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                        __uint_as_float(v[4 * j + 3]));
+                    __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
+                    for (int i = 0; i < 8; ++i) {
+                        const int rl = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+                        const float4 val = *reinterpret_cast<const float4 *>(stg + rl * HG_XPOSE_PITCH + c4);
+                        const int grow = row - lane + rl;
+                        if (grow < M) {
+                            for (int p = 0; p < out.ndst; ++p)  // plain stores, to local or peer-mapped memory
+                                *reinterpret_cast<float4 *>(out.dst[p] + (size_t)grow * out.ld + out.col_off + col0 + c4) = val;
+                        }
+                    }
+                    __syncwarp();
+                } else if (row < M && col0 < N) {
+                    for (int p = 0; p < out.ndst; ++p) {  // plain stores, to local or peer-mapped memory
+                        float *dst = out.dst[p] + (size_t)row * out.ld + out.col_off + col0;
+                        if (c_vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4 *>(dst + 4 * j) =
+                                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -286,7 +323,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 constexpr int H2_STAGES = 6;
 constexpr int H2_B_BYTES = HG_BK * 128 * 2;                 // 16 KB: two 64-column boxes
 constexpr int H2_STAGE_BYTES = HG_A_BYTES + H2_B_BYTES;     // 32 KB per CTA and stage
-constexpr int H2_SMEM_BYTES = H2_STAGES * H2_STAGE_BYTES + 1024;
+constexpr int H2_SMEM_BYTES = H2_STAGES * H2_STAGE_BYTES + 1024 + HG_XPOSE_BYTES;
 constexpr uint32_t H2_IDESC = (1u << 4) | (1u << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -331,7 +368,7 @@ __device__ __forceinline__ void tc2_mma_f16(uint32_t d_tmem, uint64_t a_desc, ui
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HG_THREADS, 1)
-hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, float *__restrict__ C,
+hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ HgOut out,
                  int M, int N, int K, int c_vec_ok, int gm) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[H2_STAGES];   // used in the leader only
@@ -453,18 +490,40 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc_ld_32cols(taddr + c * 32, v);
                 tc_wait_ld();
                 const int col0 = n0 + c * 32;
-                if (row < M && col0 < N) {
-                    float *dst = C + (size_t)row * N + col0;
-                    if (c_vec_ok && col0 + 32 <= N) {
+                if (out.ndst > 1 && c_vec_ok && col0 + 32 <= N) {
+                    // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
+                    float *stg = reinterpret_cast<float *>(tiles + (size_t)H2_STAGES * H2_STAGE_BYTES) + (warp - 2) * 32 * HG_XPOSE_PITCH;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            *reinterpret_cast<float4 *>(dst + 4 * j) =
-                                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                            __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                    } else {
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4 *>(stg + lane * HG_XPOSE_PITCH + 4 * j) =
+                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
+                                        __uint_as_float(v[4 * j + 3]));
+                    __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
+                    for (int i = 0; i < 8; ++i) {
+                        const int rl = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+                        const float4 val = *reinterpret_cast<const float4 *>(stg + rl * HG_XPOSE_PITCH + c4);
+                        const int grow = row - lane + rl;
+                        if (grow < M) {
+                            for (int p = 0; p < out.ndst; ++p)  // plain stores, to local or peer-mapped memory
+                                *reinterpret_cast<float4 *>(out.dst[p] + (size_t)grow * out.ld + out.col_off + col0 + c4) = val;
+                        }
+                    }
+                    __syncwarp();
+                } else if (row < M && col0 < N) {
+                    for (int p = 0; p < out.ndst; ++p) {  // plain stores, to local or peer-mapped memory
+                        float *dst = out.dst[p] + (size_t)row * out.ld + out.col_off + col0;
+                        if (c_vec_ok && col0 + 32 <= N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4 *>(dst + 4 * j) =
+                                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -523,12 +582,19 @@ static int make_map_f16(CUtensorMap *map, const void *base, uint64_t inner, uint
 
 using namespace tb200;
 
-extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c,
-                               tb200_stream_t stream) {
+// C(fp32) = A(fp16) * B(fp16) with the tile stores described by `out`.
+static int hgemm_launch(int m, int n, int k, const uint16_t *a, const uint16_t *b, const HgOut &out, tb200_stream_t stream) {
     if (m < 0 || n < 0 || k < 0) return TB200_ERR_INVALID_ARG;
     if (m == 0 || n == 0) return TB200_OK;
-    if (!c || (k > 0 && (!a || !b))) return TB200_ERR_INVALID_ARG;
-    if (!aligned_to(a, 2) || !aligned_to(b, 2) || !aligned_to(c, 4)) return TB200_ERR_ALIGNMENT;
+    if (k > 0 && (!a || !b)) return TB200_ERR_INVALID_ARG;
+    if (out.ndst < 1 || out.ndst > HG_MAX_DST || out.ld < n || out.col_off < 0 || out.col_off > out.ld - n) return TB200_ERR_INVALID_ARG;
+    if (!aligned_to(a, 2) || !aligned_to(b, 2)) return TB200_ERR_ALIGNMENT;
+    bool vec = n % 4 == 0 && out.ld % 4 == 0 && out.col_off % 4 == 0;
+    for (int p = 0; p < out.ndst; ++p) {
+        if (!out.dst[p]) return TB200_ERR_INVALID_ARG;
+        if (!aligned_to(out.dst[p], 4)) return TB200_ERR_ALIGNMENT;
+        vec = vec && aligned_to(out.dst[p], 16);
+    }
     int st;
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
@@ -537,8 +603,10 @@ extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uin
     const bool tensor = k >= 32 && k % 8 == 0 && n % 8 == 0 && aligned_to(a, 16) && aligned_to(b, 16) &&
                         (long long)m * n >= 64 * 64;
     if (!tensor) {
+        // the CUDA-core kernel writes one dense [m][n] matrix
+        if (out.ndst != 1 || out.ld != n) return TB200_ERR_INVALID_ARG;
         dim3 grid((n + 31) / 32, (m + 31) / 32);
-        gemm_generic_kernel<uint16_t><<<grid, 1024, 0, s>>>(m, n, k, 1.0f, a, b, 0.0f, c);
+        gemm_generic_kernel<uint16_t><<<grid, 1024, 0, s>>>(m, n, k, 1.0f, a, b, 0.0f, out.dst[0]);
         return check_launch();
     }
     CUtensorMap map_a, map_b;
@@ -546,7 +614,7 @@ extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uin
     if (st) return st;
     st = make_map_f16(&map_b, b, (uint64_t)n, (uint64_t)k, HG_BK);
     if (st) return st;
-    const int c_vec_ok = aligned_to(c, 16) && n % 4 == 0;
+    const int c_vec_ok = vec;
     // tile rows per band: the band's A panels (rows x k halves) should take about 48 MB of the 126 MB L2
     auto band_rows = [&](int tile_m) {
         long long g = (48ll << 20) / ((long long)tile_m * k * 2);
@@ -560,13 +628,30 @@ extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uin
         if (st) return st;
         const int tiles2 = ((m + 255) / 256) * ((n + 255) / 256);
         const int pairs = tiles2 < di->sm_count / 2 ? tiles2 : di->sm_count / 2;
-        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, c, m, n, k, c_vec_ok, band_rows(256));
+        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, out, m, n, k, c_vec_ok, band_rows(256));
         return check_launch();
     }
     st = ensure_smem_optin<hgemm_tc_kernel>(di);
     if (st) return st;
     const int tiles = ((m + HG_BM - 1) / HG_BM) * ((n + HG_BN - 1) / HG_BN);
     const int grid = tiles < di->sm_count ? tiles : di->sm_count;
-    hgemm_tc_kernel<<<grid, HG_THREADS, HG_SMEM_BYTES, s>>>(map_a, map_b, c, m, n, k, c_vec_ok, band_rows(HG_BM));
+    hgemm_tc_kernel<<<grid, HG_THREADS, HG_SMEM_BYTES, s>>>(map_a, map_b, out, m, n, k, c_vec_ok, band_rows(HG_BM));
     return check_launch();
+}
+
+extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c, tb200_stream_t stream) {
+    if (m > 0 && n > 0 && !c) return TB200_ERR_INVALID_ARG;
+    HgOut out{};
+    out.dst[0] = c, out.ld = n, out.col_off = 0, out.ndst = 1;
+    if (m == 0 || n == 0) return m < 0 || n < 0 || k < 0 ? TB200_ERR_INVALID_ARG : TB200_OK;
+    return hgemm_launch(m, n, k, a, b, out, stream);
+}
+
+extern "C" int tb200_hgemm_f32_scatter(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *const *dst, int ndst,
+                                       long long ld, long long col_offset, tb200_stream_t stream) {
+    if (!dst || ndst < 1 || ndst > HG_MAX_DST) return TB200_ERR_INVALID_ARG;
+    HgOut out{};
+    for (int p = 0; p < ndst; ++p) out.dst[p] = dst[p];
+    out.ld = ld, out.col_off = col_offset, out.ndst = ndst;
+    return hgemm_launch(m, n, k, a, b, out, stream);
 }

@@ -50,6 +50,7 @@ SIGNATURES = {
     "tb200_q4b_blockdots_i32": (_I, [_I, _I, _P, _P, _P, _P]),
     "tb200_sgemm": (_I, [_I, _I, _I, _F, _P, _P, _F, _P, _P]),
     "tb200_hgemm_f32": (_I, [_I, _I, _I, _P, _P, _P, _P]),
+    "tb200_hgemm_f32_scatter": (_I, [_I, _I, _I, _P, _P, _P, _I, C.c_longlong, C.c_longlong, _P]),
 }
 
 

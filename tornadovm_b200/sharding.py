@@ -158,12 +158,20 @@ class ShardedHgemm:
     """``C(fp32)[m][n] = A(fp16)[m][k] * B(fp16)[k][n]`` with B and C sharded by columns over the ranks.
 
     ``b_local`` is this rank's contiguous ``[k][shard_cols(n, world)]`` block (``take_cols``), ``a`` the
-    replicated A.  ``launch()`` enqueues the local tcgen05 GEMM and the NCCL all-gather of the C blocks.
+    replicated A.  Two ways to end with all of C on every rank:
+
+    * ``launch()``: the local tcgen05 GEMM, then an NCCL all-gather of the C blocks (the unfused baseline);
+    * ``launch_fused()`` (``fused=True``): the GEMM's epilogue stores every finished tile straight into the
+      row-major ``[m][n]`` result of every rank (its own and, over NVLink, the peers' CUDA-IPC mapped ones),
+      so the transfer overlaps the remaining tiles; one flag hand-shake kernel ends the step.  Needs
+      ``n % world == 0`` and a column block that is a multiple of 8.
     """
 
-    def __init__(self, m: int, n: int, k: int, a: torch.Tensor, b_local: torch.Tensor, group=None):
+    def __init__(self, m: int, n: int, k: int, a: torch.Tensor, b_local: torch.Tensor, group=None, fused: bool = False,
+                 timeout_ms: int = 2000):
         self.m, self.n, self.k, self.group = m, n, k, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.per = shard_cols(n, self.world)
         assert a.is_cuda and a.dtype == torch.float16 and a.shape == (m, k)
         assert b_local.is_cuda and b_local.dtype == torch.float16 and b_local.shape == (k, self.per) and b_local.is_contiguous()
@@ -172,6 +180,15 @@ class ShardedHgemm:
         self.stream = torch.cuda.Stream(device=a.device)
         self.c_local = torch.empty((m, self.per), dtype=torch.float32, device=a.device)
         self.gathered = torch.empty((self.world, m, self.per), dtype=torch.float32, device=a.device) if self.world > 1 else None
+        self.slab, self.timeout_ms, self.steps = None, timeout_ms, 0
+        if fused:
+            from .peer import PeerSlab  # local import: peer.py imports this module
+            assert self.per * self.world == n, "the fused gather needs equal column blocks"
+            self.slab = PeerSlab(2 * m * n * 4, a.device, group)  # two halves: a rank may still read the step before
+            self.halves = self.slab.bytes[:2 * m * n * 4].view(torch.float32).view(2, m, n)
+            self._dst = [(C.c_void_p * self.world)(*[p + h * m * n * 4 for p in self.slab.ptrs]) for h in range(2)]
+            self._flags = (C.c_void_p * self.world)(*[p + self.slab.flags_offset for p in self.slab.ptrs])
+            self._epoch = C.c_void_p(self.slab.own + self.slab.epoch_offset)
 
     def compute(self) -> torch.Tensor:
         P = lambda t: C.c_void_p(t.data_ptr())
@@ -183,3 +200,25 @@ class ShardedHgemm:
         with torch.cuda.stream(self.stream):
             self.compute()
             return gather_cols(self.c_local, self.n, self.group, self.gathered, assemble)
+
+    def launch_fused(self) -> torch.Tensor:
+        """Enqueue GEMM-with-scatter and the hand-shake; returns this rank's complete ``[m][n]`` result of the step."""
+        assert self.slab is not None, "construct with fused=True"
+        P = lambda t: C.c_void_p(t.data_ptr())
+        S = C.c_void_p(self.stream.cuda_stream)
+        half = self.steps & 1
+        st = self.lib.tb200_hgemm_f32_scatter(self.m, self.per, self.k, P(self.a), P(self.b), self._dst[half], self.world, self.n,
+                                              self.rank * self.per, S)
+        B200Native.check_status(st, "tb200_hgemm_f32_scatter")
+        if self.world > 1:
+            st = self.lib.tb200_peer_signal_wait(self.rank, self.world, self._flags, self._epoch, self.timeout_ms, S)
+            B200Native.check_status(st, "tb200_peer_signal_wait")
+        self.steps += 1
+        return self.halves[half]
+
+    def close(self) -> None:
+        self.stream.synchronize()
+        if self.slab is not None:
+            self.halves = None
+            self.slab.close()
+            self.slab = None
