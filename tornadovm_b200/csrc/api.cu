@@ -10,6 +10,7 @@ int g_float_tensor_cores = 1;
 int g_mma_warp_rings = 1;
 int g_float_tc_min_batch = 0;  // 0: per-format default, 1: every eligible call
 extern int g_hgemm_pairs;
+extern int g_hgemm_xpose_min_dst;
 
 static DeviceInfo g_info[kMaxDevices];
 static bool g_info_valid[kMaxDevices];
@@ -110,6 +111,10 @@ extern "C" int tb200_set_option(int option, int value) {
         case TB200_OPT_MMA_WARP_RINGS:
             tb200::g_mma_warp_rings = value != 0;
             return TB200_OK;
+        case TB200_OPT_HGEMM_LINE_STORES:
+            if (value < 1) return TB200_ERR_INVALID_ARG;
+            tb200::g_hgemm_xpose_min_dst = value;
+            return TB200_OK;
         case TB200_OPT_FLOAT_TENSOR_CORES:
             tb200::g_float_tensor_cores = value != 0;
             tb200::g_float_tc_min_batch = value >= 2 ? 1 : 0;
@@ -130,6 +135,9 @@ extern "C" int tb200_get_option(int option, int *value) {
             return TB200_OK;
         case TB200_OPT_MMA_WARP_RINGS:
             *value = tb200::g_mma_warp_rings;
+            return TB200_OK;
+        case TB200_OPT_HGEMM_LINE_STORES:
+            *value = tb200::g_hgemm_xpose_min_dst;
             return TB200_OK;
         case TB200_OPT_FLOAT_TENSOR_CORES:
             *value = tb200::g_float_tensor_cores ? 1 + tb200::g_float_tc_min_batch : 0;

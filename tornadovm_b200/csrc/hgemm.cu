@@ -28,6 +28,7 @@
 namespace tb200 {
 
 int g_hgemm_pairs = 1;  // TB200_OPT_HGEMM_SM_PAIRS
+int g_hgemm_xpose_min_dst = 2;  // TB200_OPT_HGEMM_LINE_STORES: destinations from which the epilogue stores whole lines
 
 constexpr int HG_BM = 128, HG_BN = 256, HG_BK = 64, HG_STAGES = 4;
 constexpr int HG_THREADS = 192;
@@ -131,6 +132,7 @@ struct HgOut {
     float *dst[HG_MAX_DST];
     long long ld, col_off;
     int ndst;
+    int xpose;  // store through the transposition buffer (whole 128-byte lines per row)
 };
 
 __global__ void __launch_bounds__(HG_THREADS, 1)
@@ -259,7 +261,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 tc_ld_32cols(taddr + c * 32, v);
                 tc_wait_ld();
                 const int col0 = n0 + c * 32;
-                if (out.ndst > 1 && c_vec_ok && col0 + 32 <= N) {
+                if (out.xpose && c_vec_ok && col0 + 32 <= N) {
                     // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
                     float *stg = reinterpret_cast<float *>(tiles + (size_t)HG_STAGES * HG_STAGE_BYTES) + (warp - 2) * 32 * HG_XPOSE_PITCH;
 #pragma unroll
@@ -490,7 +492,7 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tc_ld_32cols(taddr + c * 32, v);
                 tc_wait_ld();
                 const int col0 = n0 + c * 32;
-                if (out.ndst > 1 && c_vec_ok && col0 + 32 <= N) {
+                if (out.xpose && c_vec_ok && col0 + 32 <= N) {
                     // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
                     float *stg = reinterpret_cast<float *>(tiles + (size_t)H2_STAGES * H2_STAGE_BYTES) + (warp - 2) * 32 * HG_XPOSE_PITCH;
 #pragma unroll
@@ -583,7 +585,8 @@ static int make_map_f16(CUtensorMap *map, const void *base, uint64_t inner, uint
 using namespace tb200;
 
 // C(fp32) = A(fp16) * B(fp16) with the tile stores described by `out`.
-static int hgemm_launch(int m, int n, int k, const uint16_t *a, const uint16_t *b, const HgOut &out, tb200_stream_t stream) {
+static int hgemm_launch(int m, int n, int k, const uint16_t *a, const uint16_t *b, HgOut out, tb200_stream_t stream) {
+    out.xpose = out.ndst >= g_hgemm_xpose_min_dst;
     if (m < 0 || n < 0 || k < 0) return TB200_ERR_INVALID_ARG;
     if (m == 0 || n == 0) return TB200_OK;
     if (k > 0 && (!a || !b)) return TB200_ERR_INVALID_ARG;
