@@ -548,6 +548,16 @@ def run_hgemm_sharded(args):
             out[f"hgemm_{n}"].update({"fused_epilogue_gather_TFLOP/s": 2 * n**3 / tf / 1e12, "fused_epilogue_gather_ms": tf * 1e3,
                                       "fused_equals_gathered": bool(torch.equal(cf, cg))})
         op.close()
+        if n % (8 * world) == 0 and world > 1:
+            op = ShardedHgemm(n, n, n, a, b_local, fused=True, layout="blocks")
+            tf = timed(fused)
+            with torch.cuda.stream(op.stream):
+                cf = op.launch_fused()
+                cg = op.launch(assemble=False)
+            op.stream.synchronize()
+            out[f"hgemm_{n}"].update({"fused_block_layout_TFLOP/s": 2 * n**3 / tf / 1e12, "fused_block_layout_ms": tf * 1e3,
+                                      "fused_blocks_equal_gathered": bool(torch.equal(cf, cg))})
+            op.close()
         del op, a, b_local
     if rank == 0:
         print(json.dumps({"sections": out}))
