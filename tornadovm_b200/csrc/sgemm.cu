@@ -34,7 +34,10 @@ sgemm_tiled_kernel(int m, int n, int k, float alpha, const float *__restrict__ A
     const int b_col = (tid & 31) * 4;  // 0..124
 
     // thread tile: rows ty*4 + {0..3} and 64 + ty*4 + {0..3}; same for columns
-    const int ty = tid >> 4, tx = tid & 15;
+    // a warp covers 4 x 8 threads of the 16 x 16 grid: its B reads are 128 contiguous bytes (one shared-memory
+    // wavefront), its A reads four broadcast addresses
+    const int warp = tid >> 5, lane = tid & 31;
+    const int ty = (warp >> 1) * 4 + (lane >> 3), tx = (warp & 1) * 8 + (lane & 7);
 
     float acc[8][8];
 #pragma unroll
