@@ -182,15 +182,23 @@ class TornadoExecutionPlan:
                 self._layout()
                 for t in g.tasks:  # the pre-launch prepare pass
                     self.provider.prepare(t.descriptor, self.context)
-            spans = [(self._buffer(arr)[2], arr.nbytes_with_header) for mode, arr in g.to_device
-                     if first or mode is DataTransferMode.EVERY_EXECUTION]
             if first:
+                spans = [(self._buffer(arr)[2], arr.nbytes_with_header) for _, arr in g.to_device]
                 # allocation time: every buffer, outputs included, gets its header (element count) on the device
                 self._dev_slab.copy_(self._host_slab, non_blocking=True)
+                h2d = sum(n for _, n in spans)
+                # the transfers of every later execution never change: merged spans as (device view, host view) pairs
+                every = [(self._buffer(arr)[2], arr.nbytes_with_header) for mode, arr in g.to_device
+                         if mode is DataTransferMode.EVERY_EXECUTION]
+                self._h2d_pairs = [(self._dev_slab[off:off + n], self._host_slab[off:off + n]) for off, n in self._merge(every)]
+                self._h2d_bytes = sum(n for _, n in every)
+                out = [(self._buffer(arr)[2], arr.nbytes_with_header) for _, arr in g.to_host]
+                self._d2h_pairs = [(self._host_slab[off:off + n], self._dev_slab[off:off + n]) for off, n in self._merge(out)]
+                self._d2h_bytes = sum(n for _, n in out)
             else:
-                for off, n in self._merge(spans):
-                    self._dev_slab[off:off + n].copy_(self._host_slab[off:off + n], non_blocking=True)
-            h2d = sum(n for _, n in spans)
+                for dst, src in self._h2d_pairs:
+                    dst.copy_(src, non_blocking=True)
+                h2d = self._h2d_bytes
             if self._use_graph:
                 if self._cuda_graph is None:
                     self._launch_all()  # warm run: module load and attribute calls happen outside capture
@@ -201,10 +209,9 @@ class TornadoExecutionPlan:
                 self._cuda_graph.replay()
             else:
                 self._launch_all()
-            spans = [(self._buffer(arr)[2], arr.nbytes_with_header) for _, arr in g.to_host]
-            for off, n in self._merge(spans):
-                self._host_slab[off:off + n].copy_(self._dev_slab[off:off + n], non_blocking=True)
-            d2h = sum(n for _, n in spans)
+            for dst, src in self._d2h_pairs:
+                dst.copy_(src, non_blocking=True)
+            d2h = self._d2h_bytes
             self.stream.synchronize()
         self.h2d_bytes_last, self.d2h_bytes_last = h2d, d2h
         self._executions += 1
