@@ -508,7 +508,7 @@ def run_hgemm_sharded(args):
         g = torch.Generator(device=dev).manual_seed(7)  # the same A on every rank
         a = (torch.randn((n, n), device=dev, generator=g) / n**0.5).half()
         b_local = (torch.randn((n, shard_cols(n, world)), device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank)) / n**0.5).half()
-        op = ShardedHgemm(n, n, n, a, b_local, fused=n % (8 * world) == 0)
+        op = ShardedHgemm(n, n, n, a, b_local, fused=n % (8 * world) == 0, layout="assembled")
 
         def timed(fn, reps=10):
             for _ in range(3):

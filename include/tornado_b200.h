@@ -82,7 +82,7 @@ int tb200_device_status(int *status_out);
  * not be written by the kernel enqueued immediately before the mat-vec on the
  * same stream (copies and earlier kernels are fine). */
 enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2, TB200_OPT_FLOAT_TENSOR_CORES = 3, TB200_OPT_MMA_WARP_RINGS = 4,
-                    TB200_OPT_HGEMM_LINE_STORES = 5 };
+                    TB200_OPT_HGEMM_LINE_STORES = 5, TB200_OPT_INT_TENSOR_CORE_MIN_BATCH = 6 };
 /* TB200_OPT_HGEMM_SM_PAIRS (default 1): the FP16 GEMM runs 256 x 256 tiles on clusters of two CTAs
  * (tcgen05 cta_group::2) instead of 128 x 256 tiles on single CTAs.
  * TB200_OPT_FLOAT_TENSOR_CORES (default 1): the float-mode quantised mat-vecs (tb200_q8_gemv,
@@ -94,7 +94,9 @@ enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2
  * ring per warp (no CTA-wide barrier) when the activations fit in shared memory; 0 keeps the CTA-wide
  * ring (diagnostics).
  * TB200_OPT_HGEMM_LINE_STORES (default 2): the FP16 GEMM's epilogue transposes its tiles through shared memory
- * and stores whole 128-byte lines when a tile goes to at least `value` destinations (1 = always). */
+ * and stores whole 128-byte lines when a tile goes to at least `value` destinations (1 = always).
+ * TB200_OPT_INT_TENSOR_CORE_MIN_BATCH (default 4, 2..17): the integer-mode mat-vecs take the tensor-core kernel from
+ * this many activation vectors on (17 = never); smaller batches stay on the dp4a kernels. */
 int tb200_set_option(int option, int value);
 int tb200_get_option(int option, int *value);
 

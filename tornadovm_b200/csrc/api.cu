@@ -8,6 +8,7 @@ namespace tb200 {
 int g_overlap_launches = 0;
 int g_float_tensor_cores = 1;
 int g_mma_warp_rings = 1;
+int g_int_tc_min_batch = 4;
 int g_float_tc_min_batch = 0;  // 0: per-format default, 1: every eligible call
 extern int g_hgemm_pairs;
 extern int g_hgemm_xpose_min_dst;
@@ -111,6 +112,10 @@ extern "C" int tb200_set_option(int option, int value) {
         case TB200_OPT_MMA_WARP_RINGS:
             tb200::g_mma_warp_rings = value != 0;
             return TB200_OK;
+        case TB200_OPT_INT_TENSOR_CORE_MIN_BATCH:
+            if (value < 2 || value > 17) return TB200_ERR_INVALID_ARG;
+            tb200::g_int_tc_min_batch = value;
+            return TB200_OK;
         case TB200_OPT_HGEMM_LINE_STORES:
             if (value < 1) return TB200_ERR_INVALID_ARG;
             tb200::g_hgemm_xpose_min_dst = value;
@@ -135,6 +140,9 @@ extern "C" int tb200_get_option(int option, int *value) {
             return TB200_OK;
         case TB200_OPT_MMA_WARP_RINGS:
             *value = tb200::g_mma_warp_rings;
+            return TB200_OK;
+        case TB200_OPT_INT_TENSOR_CORE_MIN_BATCH:
+            *value = tb200::g_int_tc_min_batch;
             return TB200_OK;
         case TB200_OPT_HGEMM_LINE_STORES:
             *value = tb200::g_hgemm_xpose_min_dst;

@@ -62,6 +62,7 @@ static int ensure_smem_optin(const DeviceInfo *di) {
 extern int g_overlap_launches;
 extern int g_float_tensor_cores;   // float-mode quantised mat-vec on the tensor cores (fp16 hi/lo split of x)
 extern int g_float_tc_min_batch;
+extern int g_int_tc_min_batch;     // smallest batch of the integer mode that runs on the tensor cores
 extern int g_mma_warp_rings;      // tensor-core mat-vec: per-warp rings (1) or the CTA-wide ring (0)   // smallest batch that takes that path
 
 // Launch through cudaLaunchKernelEx so that a kernel can carry the programmatic

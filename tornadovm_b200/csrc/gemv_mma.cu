@@ -648,7 +648,7 @@ static int qmma_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t 
 // Shapes and alignments the tensor-core kernel takes.
 template <int FMT>
 static bool qmma_eligible(const QGemvArgs &a) {
-    if (a.batch < 5 || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !aligned_to(a.xq, 16) || !a.xs || !aligned_to(a.xs, 16)) return false;
+    if (a.batch < g_int_tc_min_batch || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !aligned_to(a.xq, 16) || !a.xs || !aligned_to(a.xs, 16)) return false;
     if (FMT == FMT_Q8S && (!a.scales || !aligned_to(a.scales, 16))) return false;
     return a.y != nullptr;
 }

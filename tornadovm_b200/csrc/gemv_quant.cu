@@ -1142,7 +1142,7 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
 
     if (MODE == MODE_INT_FUSED) {
         // batches of five and more go to the tensor-core kernel, which reads quantised activations from the workspace
-        const bool fuse = path != PATH_GENERIC && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per && a.batch <= 4;
+        const bool fuse = path != PATH_GENERIC && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per && a.batch <= 4 && a.batch < g_int_tc_min_batch;
         if (fuse) return launch_fast<FMT, MODE_INT_FUSED, false>(a, path, di, s);
         // separate quantiser into the workspace, then the MODE_INT kernels
         st = quantize_x(a.cols, a.batch, a.x, xq_ws, xs_ws, s);

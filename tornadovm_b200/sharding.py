@@ -168,9 +168,13 @@ class ShardedHgemm:
     """
 
     def __init__(self, m: int, n: int, k: int, a: torch.Tensor, b_local: torch.Tensor, group=None, fused: bool = False,
-                 timeout_ms: int = 2000, layout: str = "assembled"):
-        assert layout in ("assembled", "blocks")  # fused result: row-major [m][n], or [world][m][per] like the all-gather
-        self.layout = layout
+                 timeout_ms: int = 2000, layout: str = "auto"):
+        # fused result: row-major [m][n] ("assembled"), or [world][m][per] like the all-gather ("blocks"); "auto" takes
+        # the assembled matrix on one or two GPUs and blocks beyond, where rows 4*n bytes apart in seven peer
+        # mappings made the stores far slower than rows 4*per bytes apart (8192^3 on 8 GPUs: 2.63 ms against 0.45 ms)
+        assert layout in ("auto", "assembled", "blocks")
+        world_now = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.layout = layout if layout != "auto" else ("assembled" if world_now <= 2 else "blocks")
         self.m, self.n, self.k, self.group = m, n, k, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -187,7 +191,7 @@ class ShardedHgemm:
             from .peer import PeerSlab  # local import: peer.py imports this module
             assert self.per * self.world == n, "the fused gather needs equal column blocks"
             self.slab = PeerSlab(2 * m * n * 4, a.device, group)  # two halves: a rank may still read the step before
-            if layout == "assembled":
+            if self.layout == "assembled":
                 self.halves = self.slab.bytes[:2 * m * n * 4].view(torch.float32).view(2, m, n)
                 self._dst = [(C.c_void_p * self.world)(*[p + h * m * n * 4 for p in self.slab.ptrs]) for h in range(2)]
                 self._ld, self._col = n, self.rank * self.per
@@ -226,13 +230,12 @@ class ShardedHgemm:
         return self.halves[half]
 
     def launch_best(self) -> torch.Tensor:
-        """The faster of the two on this pool: the fused epilogue on two GPUs (0.48 ms against 0.73 ms at 8192^3),
-        the NCCL gather of C blocks from four GPUs on, where the epilogue's stores to seven peers were measured
-        far slower than the collective (2.9 ms against 0.54 ms at 8192^3 on eight GPUs).  Returns the row-major
-        ``[m][n]`` result."""
-        if self.slab is not None and self.world <= 2 and self.layout == "assembled":
+        """The fused epilogue when the object was built for it (faster than the NCCL gather at 2 and at 8 GPUs:
+        8192^3 0.48 against 0.73 ms, and 0.45 against 0.54 ms), else the NCCL gather.  Returns the result in the
+        object's layout: ``[m][n]`` ("assembled") or ``[world][m][per]`` ("blocks")."""
+        if self.slab is not None:
             return self.launch_fused()
-        return self.launch(assemble=True)
+        return self.launch(assemble=self.layout != "blocks")
 
     def close(self) -> None:
         self.stream.synchronize()
