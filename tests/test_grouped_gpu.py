@@ -12,6 +12,7 @@ from harness import DevBuf, out_buf, stream_ptr, sync_and_check
 pytestmark = pytest.mark.gpu
 
 TB200_ERR_TIMEOUT = -6
+TB200_OPT_INT_TENSOR_CORE_MIN_BATCH = 6
 
 
 def _ptr_array(bufs):
@@ -36,8 +37,15 @@ def _single(lib, fmt, rows, cols, batch, dw, dx):
     n = lib.tb200_qx_workspace_bytes(cols, batch)
     ws = DevBuf(np.zeros(max(n, 16), np.uint8))
     fn = lib.tb200_q8b_gemv_i8 if fmt == "q8b" else lib.tb200_q4b_gemv_i8
-    assert fn(rows, cols, batch, dw.ptr, dx.ptr, dy.ptr, ws.ptr, n, stream_ptr()) == 0
-    sync_and_check(lib)
+    # the grouped launch runs the dp4a kernel; keep the single launch on it too (batches of four and more would
+    # otherwise take the tensor-core kernel, whose fp32 summation order differs)
+    # (above four vectors the grouped entry itself falls back to one ordinary launch per matrix)
+    assert lib.tb200_set_option(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH, 17 if batch <= 4 else 4) == 0
+    try:
+        assert fn(rows, cols, batch, dw.ptr, dx.ptr, dy.ptr, ws.ptr, n, stream_ptr()) == 0
+        sync_and_check(lib)
+    finally:
+        lib.tb200_set_option(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH, 4)
     return dy.numpy().reshape(batch, rows)
 
 
