@@ -133,6 +133,8 @@ def run_reference_arm(args):
     if rank != 0:
         return
     # K steps of LAYERS mat-vecs each would take minutes on a CPU: each step is a bounded sample (one mat-vec)
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks; the CPU arm uses every core it may run on
+    os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     import numpy as np
     import oracle as o
     rng = np.random.default_rng(42)
