@@ -798,7 +798,11 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                             const long long at = (long long)half + grp->out_off[cm] + grp->row_off[cm] + (pbase - grp->row_start[cm]) + lane;
                             const size_t ld = (size_t)grp->ld[cm];
                             if (lane < pcnt) {
-                                for (int p = 0; p < grp->npeers; ++p) {
+                                for (int i = 0; i < grp->npeers; ++i) {
+                                    // start with this GPU's own buffer and go round: at any moment the GPUs of a
+                                    // group then store to different destinations instead of all to the same one
+                                    int p = grp->rank + i;
+                                    p = p >= grp->npeers ? p - grp->npeers : p;
                                     float *d = grp->dst[p] + at;  // this GPU's buffer or a peer-mapped one: plain stores
 #pragma unroll
                                     for (int b = 0; b < B; ++b) d[b * ld] = pend[b];
