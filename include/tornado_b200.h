@@ -70,9 +70,31 @@ int tb200_version(void);
  * the device; meant for tests and diagnostics, not for the launch path. */
 int tb200_device_status(int *status_out);
 
-/* Process-wide options; the provider sets them from its tuning object
- * (LibraryTaskDescriptor.withTuning, tornado-api/.../common/LibraryTaskDescriptor.java:79-86;
- * applied like CuBlasOptions in CuBlasLibraryProvider.java:124-151).
+/* One-time work of the CUDA context that is current on the calling thread: loads every kernel of the
+ * selected operation classes into the context, sets their attributes (dynamic shared memory opt-in,
+ * carve-out) and resolves the driver entry points the library needs.  A provider calls it from
+ * createContext / prepare, i.e. in the reference's pre-compile pass
+ * (tornado-runtime/.../interpreter/TornadoVMInterpreter.java:1036-1055,
+ * spi/TornadoLibraryProvider.java:63-72), because with withCUDAGraph() the FIRST dispatch of a plan
+ * already runs inside a stream capture in global mode (TornadoVMInterpreter.java:462-476), where module
+ * loads and attribute calls are not allowed.  Idempotent and cheap when repeated; op_classes = 0 means
+ * all.  Without it the same work happens on the first launch of each kernel. */
+enum tb200_prepare_class {
+    TB200_PREPARE_GEMV_F32 = 1,
+    TB200_PREPARE_GEMV_QUANT = 2,
+    TB200_PREPARE_GEMM_F32 = 4,
+    TB200_PREPARE_GEMM_F16 = 8,
+    TB200_PREPARE_PEER = 16,
+    TB200_PREPARE_ALL = 31
+};
+int tb200_prepare(int op_classes);
+
+/* Options.  tb200_set_option changes the process-wide default; tb200_set_thread_option overrides it for
+ * the calls the calling thread makes until tb200_clear_thread_options.  A provider applies a task's
+ * tuning object (LibraryTaskDescriptor.withTuning, tornado-api/.../common/LibraryTaskDescriptor.java:79-86)
+ * by setting thread options before the native call of a dispatch and clearing them after it, the way
+ * CuBlasLibraryProvider applies and resets CuBlasOptions around a call (CuBlasLibraryProvider.java:124-151),
+ * so one plan's tuning never leaks into another plan or thread.
  *
  * TB200_OPT_OVERLAP_LAUNCHES (default 0): the mat-vec kernels are launched with
  * programmatic stream serialization.  A kernel may then start while the kernel
@@ -87,18 +109,19 @@ enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2
  * (tcgen05 cta_group::2) instead of 128 x 256 tiles on single CTAs.
  * TB200_OPT_FLOAT_TENSOR_CORES (default 1): the float-mode quantised mat-vecs (tb200_q8_gemv,
  * tb200_q8b_gemv, tb200_q4b_gemv) feed the tensor cores with the fp32 vector split into two fp16
- * halves (relative representation error 2^-22) when shape and alignment allow.  0 keeps them on the
- * CUDA-core kernels; 1 takes the tensor-core kernel from the batch size where it was measured faster;
- * 2 takes it for every eligible call.
- * TB200_OPT_MMA_WARP_RINGS (default 1): the tensor-core mat-vec kernels stream the weights through one
- * ring per warp (no CTA-wide barrier) when the activations fit in shared memory; 0 keeps the CTA-wide
- * ring (diagnostics).
+ * halves (relative representation error 2^-22 of the vector's largest element) when shape and alignment
+ * allow.  0 keeps them on the CUDA-core kernels; 1 takes the tensor-core kernel from the batch size
+ * where it was measured faster; 2 takes it for every eligible call.
+ * TB200_OPT_MMA_WARP_RINGS (default 1): diagnostics; 0 selects the older CTA-wide ring of the
+ * tensor-core mat-vec kernels.
  * TB200_OPT_HGEMM_LINE_STORES (default 2): the FP16 GEMM's epilogue transposes its tiles through shared memory
  * and stores whole 128-byte lines when a tile goes to at least `value` destinations (1 = always).
  * TB200_OPT_INT_TENSOR_CORE_MIN_BATCH (default 4, 2..17): the integer-mode mat-vecs take the tensor-core kernel from
  * this many activation vectors on (17 = never); smaller batches stay on the dp4a kernels. */
 int tb200_set_option(int option, int value);
 int tb200_get_option(int option, int *value);
+int tb200_set_thread_option(int option, int value);
+int tb200_clear_thread_options(void);
 
 /* Device scratch owned by the provider's context (grow-only workspace of the
  * integer path).  Replaces CutlassNativeLib.allocateDeviceMemory /
@@ -162,22 +185,25 @@ int tb200_q4b_gemv_i8(int rows, int cols, int batch, const uint8_t *blocks, cons
  *
  * Same arithmetic and results as tb200_q8_gemv_i8, but the quantised
  * activations are kept in a fixed TB200_STATIC_SCRATCH_BYTES array inside the
- * library image (present on every GPU that loads the library, until the process
- * exits) instead of a workspace argument.  Meant for code that may not allocate
+ * library image (present in every CUDA context that loads the library, until the
+ * process exits) instead of a workspace argument.  Meant for code that may not allocate
  * device memory where it calls from: a provider whose only hook is the launch
  * itself (TornadoVM owns the plan's device memory and forbids allocation in
  * dispatch), or a caller already inside a stream capture.
  *   - Shapes whose tb200_qx_workspace_bytes(cols, batch) exceeds
  *     TB200_STATIC_SCRATCH_BYTES are rejected with TB200_ERR_WORKSPACE.
- *   - The first call on a device looks up the array's device address; make that
+ *   - The first call in a CUDA context looks up the array's device address there; make that
  *     first call before any stream capture begins.  No call allocates or frees.
- *   - All calls on a device share the one array and each call overwrites every
+ *   - All calls in a context share the one array and each call overwrites every
  *     byte it later reads, so nothing needs clearing between calls; two calls
  *     whose kernels can run at the same time on one GPU (different streams)
  *     race on it and must be ordered by the caller. */
 #define TB200_STATIC_SCRATCH_BYTES 147456 /* enough for cols * batch <= 131072, e.g. 16384 x 8 */
 int tb200_q8_gemv_i8_static(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x,
                             float *y, tb200_stream_t stream);
+/* Test hook: the device address of that array in the CUDA context that is current (each context that
+ * loads the library has its own copy of it). */
+int tb200_static_scratch_address(void **out);
 
 /* ---- Grouped integer-mode mat-vec and the multi-GPU output hand-off ------------
  * `count` (<= 32) block matrices of one shape [rows][cols] that share the same

@@ -1,61 +1,219 @@
-// Status strings, version and per-device bookkeeping of libtornado_b200.
+// Status strings, version, options, and the per-context bookkeeping of libtornado_b200.
+#include <cuda.h>
+
 #include <mutex>
 
 #include "common.cuh"
 
+TB200_TU_STATUS(api)
+
 namespace tb200 {
 
-int g_overlap_launches = 0;
-int g_float_tensor_cores = 1;
-int g_mma_warp_rings = 1;
-int g_int_tc_min_batch = 4;
-int g_float_tc_min_batch = 0;  // 0: per-format default, 1: every eligible call
-extern int g_hgemm_pairs;
-extern int g_hgemm_xpose_min_dst;
+// status readers of the other translation units (TB200_TU_STATUS in each)
+int tu_status_gemv_f32(int *);
+int tu_status_gemv_quant(int *);
+int tu_status_gemv_mma(int *);
+int tu_status_gemv_tc(int *);
+int tu_status_sgemm(int *);
+int tu_status_hgemm(int *);
+int tu_status_peer(int *);
 
-static DeviceInfo g_info[kMaxDevices];
-static bool g_info_valid[kMaxDevices];
+// ---- options ---------------------------------------------------------------------------------
+constexpr int kNumOptions = 8;  // option ids are 1 .. kNumOptions - 1
+static std::atomic<int> g_option[kNumOptions] = {{0}, {0}, {1}, {1}, {1}, {2}, {4}, {0}};
+struct ThreadOptions {
+    unsigned set_mask = 0;
+    int value[kNumOptions] = {};
+};
+static thread_local ThreadOptions t_options;
+
+static int validate_option(int option, int &value) {
+    switch (option) {
+        case TB200_OPT_OVERLAP_LAUNCHES:
+        case TB200_OPT_HGEMM_SM_PAIRS:
+        case TB200_OPT_MMA_WARP_RINGS:
+            value = value != 0;
+            return TB200_OK;
+        case TB200_OPT_INT_TENSOR_CORE_MIN_BATCH:
+            return value < 2 || value > 17 ? TB200_ERR_INVALID_ARG : TB200_OK;
+        case TB200_OPT_HGEMM_LINE_STORES:
+            return value < 1 ? TB200_ERR_INVALID_ARG : TB200_OK;
+        case TB200_OPT_FLOAT_TENSOR_CORES:
+            value = value < 0 ? 0 : (value > 2 ? 2 : value);
+            return TB200_OK;
+        default:
+            return TB200_ERR_INVALID_ARG;
+    }
+}
+
+int option_value(int option) {
+    if (option < 1 || option >= kNumOptions) return 0;
+    if (t_options.set_mask & (1u << option)) return t_options.value[option];
+    return g_option[option].load(std::memory_order_relaxed);
+}
+
+// ---- per-context facts -------------------------------------------------------------------------
+typedef CUresult (*CtxGetCurrentFn)(CUcontext *);
+typedef CUresult (*CtxGetIdFn)(CUcontext, unsigned long long *);
+typedef CUresult (*CtxGetDeviceFn)(CUdevice *);
+
+struct DriverFns {
+    CtxGetCurrentFn get_current = nullptr;
+    CtxGetIdFn get_id = nullptr;
+    CtxGetDeviceFn get_device = nullptr;
+    bool ok = false;
+};
+
+static const DriverFns &driver_fns() {
+    static DriverFns fns = [] {
+        DriverFns f;
+        cudaDriverEntryPointQueryResult q;
+        void *p = nullptr;
+        bool ok = true;
+        auto get = [&](const char *name) -> void * {
+            p = nullptr;
+            if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+                cudaGetLastError();
+                ok = false;
+                return nullptr;
+            }
+            return p;
+        };
+        f.get_current = reinterpret_cast<CtxGetCurrentFn>(get("cuCtxGetCurrent"));
+        f.get_id = reinterpret_cast<CtxGetIdFn>(get("cuCtxGetId"));
+        f.get_device = reinterpret_cast<CtxGetDeviceFn>(get("cuCtxGetDevice"));
+        f.ok = ok;
+        return f;
+    }();
+    return fns;
+}
+
+static DeviceInfo g_info[kMaxContexts];
+static std::atomic<unsigned long long> g_info_id[kMaxContexts];  // context id + 1 of a filled slot, 0 = free
+static std::atomic<int> g_info_count{0};
 static std::mutex g_info_mutex;
 
 const DeviceInfo *device_info(int *status) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) {
-        *status = (int)e;
+    const DriverFns &drv = driver_fns();
+    if (!drv.ok) {
+        *status = TB200_ERR_DRIVER;
         return nullptr;
     }
-    if (dev < 0 || dev >= kMaxDevices) {
-        *status = TB200_ERR_INVALID_ARG;
+    CUcontext ctx = nullptr;
+    if (drv.get_current(&ctx) != CUDA_SUCCESS || !ctx) {
+        // no context bound to this thread yet: the runtime binds the device's primary context on demand
+        cudaError_t e = cudaFree(nullptr);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            *status = (int)e;
+            return nullptr;
+        }
+        if (drv.get_current(&ctx) != CUDA_SUCCESS || !ctx) {
+            *status = TB200_ERR_DRIVER;
+            return nullptr;
+        }
+    }
+    unsigned long long id = 0;
+    if (drv.get_id(ctx, &id) != CUDA_SUCCESS) {
+        *status = TB200_ERR_DRIVER;
         return nullptr;
     }
-    if (!g_info_valid[dev]) {
+    const unsigned long long key = id + 1;
+    int n = g_info_count.load(std::memory_order_acquire);
+    int slot = -1;
+    for (int i = 0; i < n; ++i)
+        if (g_info_id[i].load(std::memory_order_acquire) == key) {
+            slot = i;
+            break;
+        }
+    if (slot < 0) {
         std::lock_guard<std::mutex> lock(g_info_mutex);
-        if (!g_info_valid[dev]) {
+        n = g_info_count.load(std::memory_order_acquire);
+        for (int i = 0; i < n && slot < 0; ++i)
+            if (g_info_id[i].load(std::memory_order_acquire) == key) slot = i;
+        if (slot < 0) {
+            if (n >= kMaxContexts) {  // more live-and-dead contexts than the caches hold
+                *status = TB200_ERR_UNSUPPORTED;
+                return nullptr;
+            }
             DeviceInfo di{};
+            CUdevice dev = 0;
+            if (drv.get_device(&dev) != CUDA_SUCCESS) {
+                *status = TB200_ERR_DRIVER;
+                return nullptr;
+            }
             int v = 0;
-            if ((e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) {
+            cudaError_t e = cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, (int)dev);
+            if (e != cudaSuccess) {
+                cudaGetLastError();
                 *status = (int)e;
                 return nullptr;
             }
-            di.device = dev;
-            di.sm_count = v;
-            cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, dev);
+            di.device = (int)dev, di.sm_count = v;
+            cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, (int)dev);
             di.cc_major = v;
-            cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+            cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, (int)dev);
             di.max_smem_optin = v;
-            g_info[dev] = di;
-            g_info_valid[dev] = true;
+            di.slot = n, di.context_id = id;
+            g_info[n] = di;
+            g_info_id[n].store(key, std::memory_order_release);
+            g_info_count.store(n + 1, std::memory_order_release);
+            slot = n;
         }
     }
-    if (g_info[dev].cc_major != 10) {
+    if (g_info[slot].cc_major != 10) {
         *status = TB200_ERR_UNSUPPORTED;
         return nullptr;
     }
     *status = TB200_OK;
-    return &g_info[dev];
+    return &g_info[slot];
 }
 
+// ---- kernel registry -----------------------------------------------------------------------------
+static std::atomic<KernelEntry *> &kernel_list() {
+    static std::atomic<KernelEntry *> head{nullptr};
+    return head;
+}
+
+bool register_kernel(KernelEntry *e, const void *func, int flags, int op_class) {
+    e->func = func, e->flags = flags, e->op_class = op_class;
+    std::atomic<KernelEntry *> &head = kernel_list();
+    KernelEntry *old = head.load(std::memory_order_relaxed);
+    do {
+        e->next = old;
+    } while (!head.compare_exchange_weak(old, e, std::memory_order_release, std::memory_order_relaxed));
+    return true;
+}
+
+int prepare_kernel(KernelEntry *e, const DeviceInfo *di) {
+    // the attribute query loads the kernel into the current context
+    cudaFuncAttributes attr;
+    cudaError_t err = cudaFuncGetAttributes(&attr, e->func);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return (int)err;
+    }
+    if (e->flags & KERNEL_OPTIN_SMEM) {
+        // the opt-in limit covers static + dynamic shared memory of the kernel
+        err = cudaFuncSetAttribute(e->func, cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin - (int)attr.sharedSizeBytes);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return (int)err;
+        }
+    }
+    if (e->flags & KERNEL_MAX_CARVEOUT) {
+        cudaFuncSetAttribute(e->func, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaGetLastError();
+    }
+    e->ready[di->slot].store(1, std::memory_order_release);
+    return TB200_OK;
+}
+
+int hgemm_prepare_driver();  // hgemm.cu: resolves the tensor-map encoder
+
 }  // namespace tb200
+
+using namespace tb200;
 
 extern "C" const char *tb200_status_string(int status) {
     switch (status) {
@@ -76,16 +234,33 @@ extern "C" int tb200_version(void) { return TB200_VERSION; }
 
 extern "C" int tb200_device_status(int *status_out) {
     if (!status_out) return TB200_ERR_INVALID_ARG;
-    int v = 0;
-    cudaError_t e = cudaMemcpyFromSymbol(&v, tb200::g_device_status, sizeof(int));
-    if (e != cudaSuccess) return (int)e;
-    if (v != 0) {
-        // read and clear, like cudaGetLastError
-        const int zero = 0;
-        e = cudaMemcpyToSymbol(tb200::g_device_status, &zero, sizeof(int));
-        if (e != cudaSuccess) return (int)e;
+    int (*const readers[])(int *) = {tu_status_api,   tu_status_gemv_f32, tu_status_gemv_quant, tu_status_gemv_mma,
+                                     tu_status_gemv_tc, tu_status_sgemm,    tu_status_hgemm,      tu_status_peer};
+    int combined = 0;
+    for (auto reader : readers) {
+        int v = 0;
+        const int st = reader(&v);  // read and clear, like cudaGetLastError
+        if (st) return st;
+        if (v != 0 && combined == 0) combined = v;
     }
-    *status_out = v;
+    *status_out = combined;
+    return TB200_OK;
+}
+
+extern "C" int tb200_prepare(int op_classes) {
+    int st;
+    const DeviceInfo *di = device_info(&st);
+    if (!di) return st;
+    if (op_classes == 0) op_classes = TB200_PREPARE_ALL;
+    for (KernelEntry *e = kernel_list().load(std::memory_order_acquire); e; e = e->next) {
+        if (!(e->op_class & op_classes) || e->ready[di->slot].load(std::memory_order_acquire)) continue;
+        st = prepare_kernel(e, di);
+        if (st) return st;
+    }
+    if (op_classes & TB200_PREPARE_GEMM_F16) {
+        st = hgemm_prepare_driver();
+        if (st) return st;
+    }
     return TB200_OK;
 }
 
@@ -102,55 +277,27 @@ extern "C" int tb200_device_free(void *ptr) {
 }
 
 extern "C" int tb200_set_option(int option, int value) {
-    switch (option) {
-        case TB200_OPT_OVERLAP_LAUNCHES:
-            tb200::g_overlap_launches = value != 0;
-            return TB200_OK;
-        case TB200_OPT_HGEMM_SM_PAIRS:
-            tb200::g_hgemm_pairs = value != 0;
-            return TB200_OK;
-        case TB200_OPT_MMA_WARP_RINGS:
-            tb200::g_mma_warp_rings = value != 0;
-            return TB200_OK;
-        case TB200_OPT_INT_TENSOR_CORE_MIN_BATCH:
-            if (value < 2 || value > 17) return TB200_ERR_INVALID_ARG;
-            tb200::g_int_tc_min_batch = value;
-            return TB200_OK;
-        case TB200_OPT_HGEMM_LINE_STORES:
-            if (value < 1) return TB200_ERR_INVALID_ARG;
-            tb200::g_hgemm_xpose_min_dst = value;
-            return TB200_OK;
-        case TB200_OPT_FLOAT_TENSOR_CORES:
-            tb200::g_float_tensor_cores = value != 0;
-            tb200::g_float_tc_min_batch = value >= 2 ? 1 : 0;
-            return TB200_OK;
-        default:
-            return TB200_ERR_INVALID_ARG;
-    }
+    const int st = validate_option(option, value);
+    if (st) return st;
+    g_option[option].store(value, std::memory_order_relaxed);
+    return TB200_OK;
 }
 
 extern "C" int tb200_get_option(int option, int *value) {
-    if (!value) return TB200_ERR_INVALID_ARG;
-    switch (option) {
-        case TB200_OPT_OVERLAP_LAUNCHES:
-            *value = tb200::g_overlap_launches;
-            return TB200_OK;
-        case TB200_OPT_HGEMM_SM_PAIRS:
-            *value = tb200::g_hgemm_pairs;
-            return TB200_OK;
-        case TB200_OPT_MMA_WARP_RINGS:
-            *value = tb200::g_mma_warp_rings;
-            return TB200_OK;
-        case TB200_OPT_INT_TENSOR_CORE_MIN_BATCH:
-            *value = tb200::g_int_tc_min_batch;
-            return TB200_OK;
-        case TB200_OPT_HGEMM_LINE_STORES:
-            *value = tb200::g_hgemm_xpose_min_dst;
-            return TB200_OK;
-        case TB200_OPT_FLOAT_TENSOR_CORES:
-            *value = tb200::g_float_tensor_cores ? 1 + tb200::g_float_tc_min_batch : 0;
-            return TB200_OK;
-        default:
-            return TB200_ERR_INVALID_ARG;
-    }
+    if (!value || option < 1 || option >= kNumOptions) return TB200_ERR_INVALID_ARG;
+    *value = option_value(option);
+    return TB200_OK;
+}
+
+extern "C" int tb200_set_thread_option(int option, int value) {
+    const int st = validate_option(option, value);
+    if (st) return st;
+    t_options.set_mask |= 1u << option;
+    t_options.value[option] = value;
+    return TB200_OK;
+}
+
+extern "C" int tb200_clear_thread_options(void) {
+    t_options.set_mask = 0;
+    return TB200_OK;
 }

@@ -6,14 +6,18 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "tornado_b200.h"
 
 namespace tb200 {
 
-// Device-wide sticky status word: a kernel that gives up a bounded wait stores
+// Sticky status word: a kernel that gives up a bounded wait stores
 // TB200_ERR_TIMEOUT here instead of trapping, so the context stays usable.
-// (The library is built as one translation unit, see libtornado_b200.cu.)
-__device__ int g_device_status = 0;
+// The library is several translation units without relocatable device code, so
+// each unit owns one copy; TB200_TU_STATUS(name) below exports a reader for it
+// and tb200_device_status (api.cu) combines them.
+static __device__ int g_device_status = 0;
 
 constexpr int kWarp = 32;
 
@@ -28,42 +32,105 @@ static inline int check_launch() {
 
 static inline bool aligned_to(const void *p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
 
-// Cached per-device facts (queried once per device, no allocation).
+// Facts about the CUDA context that is current on the calling thread, cached per
+// context (queried once, no allocation).  TornadoVM's NVIDIA backends each create
+// their own context per device (cuCtxCreate; cuda-jni/.../CUDAPlatform.cpp:118-146,
+// ptx-jni/.../PTXContext.cpp:37-51) next to the primary one, and kernel attributes,
+// loaded modules and __device__ symbol addresses all belong to a context, not to a
+// device ordinal: every cache of the library is therefore indexed by `slot`.
+constexpr int kMaxContexts = 64;
 struct DeviceInfo {
     int device;
     int sm_count;
     int cc_major;
     int max_smem_optin;
+    int slot;                      // index of the current context in the per-context caches
+    unsigned long long context_id; // cuCtxGetId of that context
 };
 const DeviceInfo *device_info(int *status);
 
-constexpr int kMaxDevices = 64;
+// One entry per __global__ function the library launches.  Entries register themselves when the
+// library is loaded, so that tb200_prepare can make every kernel resident and configured in the
+// current context before a stream capture begins (the first launch of a kernel otherwise loads its
+// module and sets its attributes lazily, which a capture in global mode does not allow).
+constexpr int KERNEL_OPTIN_SMEM = 1;     // opt in to the device's full dynamic shared memory
+constexpr int KERNEL_MAX_CARVEOUT = 2;   // prefer the largest shared-memory carve-out
+struct KernelEntry {
+    const void *func;
+    int flags;
+    int op_class;                              // TB200_PREPARE_* bit of the unit that launches it
+    std::atomic<unsigned char> ready[kMaxContexts];
+    std::atomic<long long> occupancy[kMaxContexts];  // (dynamic smem bytes << 8 | resident CTAs) of the last query, 0 = none
+    KernelEntry *next;
+};
+bool register_kernel(KernelEntry *e, const void *func, int flags, int op_class);
+int prepare_kernel(KernelEntry *e, const DeviceInfo *di);
 
-// Opt a kernel in to the device's full dynamic shared memory, once per device
-// and kernel.  The first call for a kernel should come from a warm-up launch or
-// a prepare step, outside any stream capture.
+#ifndef TB200_OP_CLASS
+#define TB200_OP_CLASS 0
+#endif
+
+template <auto kernel, int FLAGS>
+struct KernelReg {
+    static KernelEntry entry;
+    static const bool registered;
+};
+template <auto kernel, int FLAGS>
+KernelEntry KernelReg<kernel, FLAGS>::entry;
+template <auto kernel, int FLAGS>
+const bool KernelReg<kernel, FLAGS>::registered =
+    register_kernel(&KernelReg<kernel, FLAGS>::entry, reinterpret_cast<const void *>(kernel), FLAGS, TB200_OP_CLASS);
+
+// Makes `kernel` ready in the current context: loaded, and opted in to the full dynamic shared
+// memory when FLAGS asks for it.  After tb200_prepare this is one relaxed load.
+template <auto kernel, int FLAGS = KERNEL_OPTIN_SMEM>
+static inline int ensure_kernel(const DeviceInfo *di) {
+    (void)&KernelReg<kernel, FLAGS>::registered;  // instantiates the registration
+    KernelEntry *e = &KernelReg<kernel, FLAGS>::entry;
+    if (e->ready[di->slot].load(std::memory_order_acquire)) return TB200_OK;
+    return prepare_kernel(e, di);
+}
 template <auto kernel>
-static int ensure_smem_optin(const DeviceInfo *di) {
-    static bool done[kMaxDevices];
-    if (!done[di->device]) {
-        // the opt-in limit covers static + dynamic shared memory of the kernel
-        cudaFuncAttributes attr;
-        cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 di->max_smem_optin - (int)attr.sharedSizeBytes);
-        if (e != cudaSuccess) return (int)e;
-        done[di->device] = true;
+static inline int ensure_smem_optin(const DeviceInfo *di) { return ensure_kernel<kernel, KERNEL_OPTIN_SMEM>(di); }
+
+// Resident CTAs per SM of a kernel at a given block size and dynamic shared memory, cached per
+// context for the size last asked about (a mat-vec task asks for the same size on every launch).
+template <auto kernel, int FLAGS = KERNEL_OPTIN_SMEM>
+static inline int resident_ctas(const DeviceInfo *di, int threads, size_t smem) {
+    KernelEntry *e = &KernelReg<kernel, FLAGS>::entry;
+    const long long cached = e->occupancy[di->slot].load(std::memory_order_relaxed);
+    if (cached && (size_t)(cached >> 8) == smem) return (int)(cached & 0xFF);
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess) {
+        cudaGetLastError();
+        n = 1;
     }
-    return TB200_OK;
+    n = n < 1 ? 1 : (n > 255 ? 255 : n);
+    e->occupancy[di->slot].store(((long long)smem << 8) | n, std::memory_order_relaxed);
+    return n;
 }
 
-// Process-wide options (tb200_set_option).
-extern int g_overlap_launches;
-extern int g_float_tensor_cores;   // float-mode quantised mat-vec on the tensor cores (fp16 hi/lo split of x)
-extern int g_float_tc_min_batch;
-extern int g_int_tc_min_batch;     // smallest batch of the integer mode that runs on the tensor cores
-extern int g_mma_warp_rings;      // tensor-core mat-vec: per-warp rings (1) or the CTA-wide ring (0)   // smallest batch that takes that path
+// Exports this translation unit's status word (read, and clear when set).
+#define TB200_TU_STATUS(name)                                                                   \
+    namespace tb200 {                                                                           \
+    int tu_status_##name(int *value) {                                                          \
+        int v = 0;                                                                              \
+        cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));                 \
+        if (e != cudaSuccess) return (int)e;                                                    \
+        if (v != 0) {                                                                           \
+            const int zero = 0;                                                                 \
+            e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));                        \
+            if (e != cudaSuccess) return (int)e;                                                \
+        }                                                                                       \
+        *value = v;                                                                             \
+        return TB200_OK;                                                                        \
+    }                                                                                           \
+    }
+
+// Options: process-wide defaults (tb200_set_option) that a thread may override for the calls it
+// makes (tb200_set_thread_option / tb200_clear_thread_options), which is how a provider applies a
+// task's tuning object around one dispatch without touching other plans.
+int option_value(int option);
 
 // Launch through cudaLaunchKernelEx so that a kernel can carry the programmatic
 // stream serialization attribute: it may then begin while its predecessor in
@@ -173,6 +240,27 @@ __device__ __forceinline__ uint2 ldg_stream_v2(const void *p) {
     uint2 r;
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
     return r;
+}
+
+// ---- bounded waits on flags that another GPU writes ----
+__device__ __forceinline__ unsigned long long qg_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait until the flag word has reached `target` (step numbers wrap, hence the signed difference).
+__device__ __forceinline__ void wait_flag_at_least(const unsigned *flag, unsigned target, unsigned long long timeout_ns) {
+    const unsigned long long t0 = qg_timer_ns();
+    for (unsigned spin = 0;; ++spin) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int)(v - target) >= 0) return;
+        if ((spin & 63) == 63 && qg_timer_ns() - t0 > timeout_ns) {
+            g_device_status = TB200_ERR_TIMEOUT;
+            return;
+        }
+    }
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

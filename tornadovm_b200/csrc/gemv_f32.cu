@@ -7,7 +7,10 @@
 // async copy), partial sums are combined with warp shuffles.
 //
 // Algorithmic bytes per launch: 4 * (rows*cols + cols + rows).
+#define TB200_OP_CLASS TB200_PREPARE_GEMV_F32
 #include "common.cuh"
+
+TB200_TU_STATUS(gemv_f32)
 
 namespace tb200 {
 
@@ -137,6 +140,8 @@ extern "C" int tb200_sgemv(int rows, int cols, const float *m, const float *v, f
         int grid = di->sm_count * 8;
         int need = (rows + warps - 1) / warps;
         if (grid > need) grid = need;
+        st = ensure_kernel<sgemv_generic_kernel, 0>(di);
+        if (st) return st;
         sgemv_generic_kernel<<<grid, kSgemvThreads, 0, s>>>(m, v, out, rows, cols);
     }
     return check_launch();

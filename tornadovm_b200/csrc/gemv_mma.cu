@@ -16,7 +16,10 @@
 // latencies); their partial sums are added in a fixed order when the unit is
 // complete.  Rows are padded to a 272- / 144-byte pitch in shared memory so
 // that the fragment loads are bank-conflict free.
-#include "common.cuh"
+#define TB200_OP_CLASS TB200_PREPARE_GEMV_QUANT
+#include "gemv_common.cuh"
+
+TB200_TU_STATUS(gemv_mma)
 
 namespace tb200 {
 
@@ -615,7 +618,7 @@ static int launch_qmmaw(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s
 
 template <int FMT, int NT, bool FLT>
 static bool qmmaw_fits(const QGemvArgs &a, const DeviceInfo *di) {
-    return g_mma_warp_rings && wm_smem_bytes<FMT, NT, FLT>(a.cols) + 1024 <= (size_t)di->max_smem_optin;
+    return option_value(TB200_OPT_MMA_WARP_RINGS) && wm_smem_bytes<FMT, NT, FLT>(a.cols) + 1024 <= (size_t)di->max_smem_optin;
 }
 
 template <int FMT, int NT, int XM>
@@ -641,21 +644,21 @@ static int launch_qmma(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s)
 
 // Entry used by the dispatcher of gemv_quant.cu: already quantised activations (xq, xs), 5 <= batch <= 16.
 template <int FMT>
-static int qmma_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+static int qmma_dispatch_t(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     return a.batch <= 8 ? launch_qmma<FMT, 1>(a, di, s) : launch_qmma<FMT, 2>(a, di, s);
 }
 
 // Shapes and alignments the tensor-core kernel takes.
 template <int FMT>
-static bool qmma_eligible(const QGemvArgs &a) {
-    if (a.batch < g_int_tc_min_batch || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !aligned_to(a.xq, 16) || !a.xs || !aligned_to(a.xs, 16)) return false;
+static bool qmma_eligible_t(const QGemvArgs &a) {
+    if (a.batch < option_value(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH) || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !aligned_to(a.xq, 16) || !a.xs || !aligned_to(a.xs, 16)) return false;
     if (FMT == FMT_Q8S && (!a.scales || !aligned_to(a.scales, 16))) return false;
     return a.y != nullptr;
 }
 
 // Float mode (fp32 activations): batch <= 8 and vectors that stay resident in shared memory.
 template <int FMT>
-static bool qmma_float_eligible(const QGemvArgs &a, const DeviceInfo *di) {
+static bool qmma_float_eligible_t(const QGemvArgs &a, const DeviceInfo *di) {
     if (a.batch < 1 || a.batch > 8 || a.cols % 256 != 0 || !aligned_to(a.w, 16) || !a.x || !aligned_to(a.x, 16) || !a.y) return false;
     if (FMT == FMT_Q8S && (!a.scales || !aligned_to(a.scales, 16))) return false;
     const int nt = a.batch <= 4 ? 1 : 2;
@@ -674,8 +677,23 @@ static int launch_qmma_float(const QGemvArgs &a, const DeviceInfo *di, cudaStrea
 }
 
 template <int FMT>
-static int qmma_float_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
+static int qmma_float_dispatch_t(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
     return a.batch <= 4 ? launch_qmma_float<FMT, 1>(a, di, s, overlap) : launch_qmma_float<FMT, 2>(a, di, s, overlap);
+}
+
+bool qmma_eligible(int fmt, const QGemvArgs &a) {
+    return fmt == FMT_Q8S ? qmma_eligible_t<FMT_Q8S>(a) : fmt == FMT_Q8B ? qmma_eligible_t<FMT_Q8B>(a) : qmma_eligible_t<FMT_Q4B>(a);
+}
+int qmma_dispatch(int fmt, const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+    return fmt == FMT_Q8S ? qmma_dispatch_t<FMT_Q8S>(a, di, s) : fmt == FMT_Q8B ? qmma_dispatch_t<FMT_Q8B>(a, di, s) : qmma_dispatch_t<FMT_Q4B>(a, di, s);
+}
+bool qmma_float_eligible(int fmt, const QGemvArgs &a, const DeviceInfo *di) {
+    return fmt == FMT_Q8S ? qmma_float_eligible_t<FMT_Q8S>(a, di)
+                          : fmt == FMT_Q8B ? qmma_float_eligible_t<FMT_Q8B>(a, di) : qmma_float_eligible_t<FMT_Q4B>(a, di);
+}
+int qmma_float_dispatch(int fmt, const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
+    return fmt == FMT_Q8S ? qmma_float_dispatch_t<FMT_Q8S>(a, di, s, overlap)
+                          : fmt == FMT_Q8B ? qmma_float_dispatch_t<FMT_Q8B>(a, di, s, overlap) : qmma_float_dispatch_t<FMT_Q4B>(a, di, s, overlap);
 }
 
 }  // namespace tb200

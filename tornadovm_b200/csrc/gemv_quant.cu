@@ -29,75 +29,14 @@
 // Algorithmic bytes per launch:
 //   Q8: 34 * rows*cols/32 + 4*batch*(cols + rows)
 //   Q4: 18 * rows*cols/32 + 4*batch*(cols + rows)
-#include <mutex>
 #include <type_traits>
 
-#include "common.cuh"
+#define TB200_OP_CLASS TB200_PREPARE_GEMV_QUANT
+#include "gemv_common.cuh"
+
+TB200_TU_STATUS(gemv_quant)
 
 namespace tb200 {
-
-constexpr int FMT_Q8S = 0, FMT_Q8B = 1, FMT_Q4B = 2;
-constexpr int kMaxBatch = 16;
-
-struct QGemvArgs {
-    const uint8_t *w;        // quants (split) or blocks
-    const uint16_t *scales;  // split layout only
-    const float *x;          // float mode: [batch][cols]
-    const int8_t *xq;        // int mode:   [batch][cols]
-    const float *xs;         // int mode:   [batch][cols/32]
-    float *y;                // [batch][rows]; may be null when dots is set
-    int32_t *dots;           // optional [rows][cols/32] (batch 1, int mode)
-    int rows, cols, batch;
-};
-
-// Several matrices of one shape sharing the activation vectors, and several destinations for every
-// output value (this GPU's buffer and, peer-mapped, the other GPUs' buffers).
-// rows a warp of the grouped kernel collects before it stores them (128-byte stores to every destination;
-// runs of 8 rows were measured no faster on two GPUs and slightly slower on one)
-constexpr int kGroupFlushRows = 32;
-constexpr int kMaxGroup = 32;
-constexpr int kMaxPeers = 8;
-struct QGroupArgs {
-    const uint8_t *w[kMaxGroup];   // block arrays; matrix m holds rows row_start[m] .. row_start[m+1] of the launch
-    int row_start[kMaxGroup + 1];
-    long long out_off[kMaxGroup];  // where matrix m's [batch][ld[m]] output block starts inside a slot (floats)
-    int ld[kMaxGroup];             // rows of the whole (unsharded) matrix m
-    int row_off[kMaxGroup];        // first row of this launch's share of matrix m
-    float *dst[kMaxPeers];         // output buffers, each [slots][...]
-    const unsigned *epoch;         // device word whose low bit selects the half (null: half 0)
-    long long half_stride;         // floats between the halves
-    int count, npeers;
-    // In-kernel hand-shake of a multi-GPU step (null flags[0]: none).  sync[0] is this GPU's step counter
-    // (the same word as `epoch`), sync[1] counts the CTAs of the running launch that have finished.
-    unsigned *flags[kMaxPeers];    // flags[p]: flag array of GPU p, one word per source GPU
-    unsigned *sync;
-    unsigned long long timeout_ns;
-    int rank;
-    int handshake;                 // bit 0: wait for the peers before the first store; bit 1: signal them at the end
-    int nslots;                    // output slots in rotation (the "halves" above when 2)
-};
-
-__device__ __forceinline__ unsigned long long qg_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait until the flag word has reached `target` (step numbers wrap, hence the signed difference).
-__device__ __forceinline__ void wait_flag_at_least(const unsigned *flag, unsigned target, unsigned long long timeout_ns) {
-    const unsigned long long t0 = qg_timer_ns();
-    for (unsigned spin = 0;; ++spin) {
-        unsigned v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if ((int)(v - target) >= 0) return;
-        if ((spin & 63) == 63 && qg_timer_ns() - t0 > timeout_ns) {
-            g_device_status = TB200_ERR_TIMEOUT;
-            return;
-        }
-    }
-}
-
-__device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 
 // ---------------------------------------------------------------------------
 // Generic kernels: one warp per row, one lane per block, byte loads.
@@ -190,7 +129,6 @@ __device__ __forceinline__ int permuted_slot(int col) {
     return seg * (SEG / PIECE) + k * 32 + l;
 }
 
-__host__ __device__ __forceinline__ int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // float mode: xs4[b * slots_per_vec + slot]
 template <int CPL>
@@ -213,10 +151,6 @@ __device__ __forceinline__ void stage_x_float(float4 *xs4, const float *x, int c
         }
     }
 }
-
-constexpr int MODE_FLOAT = 0;     // fp32 activations
-constexpr int MODE_INT = 1;       // int8 activations read from the workspace
-constexpr int MODE_INT_FUSED = 2; // int8 activations quantised in the prologue of this kernel
 
 // Integer activations into shared memory.  Eight consecutive threads share a
 // 32-element block, four elements each: quantise on the fly (QUANTIZE) or copy
@@ -313,15 +247,6 @@ __device__ __forceinline__ void stage_x_blocks(unsigned char *xq_smem, float *xs
 // ---------------------------------------------------------------------------
 constexpr int kQ8SThreads = 256;
 constexpr int kQ8SWarps = kQ8SThreads / 32;
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src_gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src_gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 // SA: the scales of a trip are 16-byte aligned runs and travel through the ring as well (cols % 256 == 0,
 // 16-byte aligned scale array); otherwise they are loaded into registers when the trip is requested.
@@ -875,18 +800,6 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float *__restrict
 // Host side
 // ---------------------------------------------------------------------------
 
-// Resident CTAs per SM of a kernel at a given dynamic shared memory size,
-// cached per (kernel, device, size class).  Host-side query, no device work.
-template <auto kernel>
-static int resident_ctas(const DeviceInfo *di, int threads, size_t smem) {
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess) {
-        cudaGetLastError();
-        n = 1;
-    }
-    return n < 1 ? 1 : n;
-}
-
 // Pick a CTA count <= max_ctas that wastes the fewest warp slots in the last
 // round of a grid-stride loop over `units` (row groups).
 static int balanced_grid(int units, int warps_per_cta, int max_ctas) {
@@ -938,7 +851,7 @@ static int launch_q8s_sa(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t 
     const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
     const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;  // at least one group per warp
     if (grid > want) grid = want;
-    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a);
+    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a);
 }
 
 template <int B, int MODE, bool DOTS>
@@ -983,7 +896,7 @@ static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s)
     const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
     const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;
     if (grid > want) grid = want;
-    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a);
+    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a);
 }
 
 template <int FMT, int B, int MODE>
@@ -997,7 +910,7 @@ static int launch_ring_grouped(const QGemvArgs &a, const QGroupArgs &grp, const 
     const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
     const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;
     if (grid > want) grid = want;
-    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, g_overlap_launches != 0, a, grp);
+    return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a, grp);
 }
 
 template <int FMT, int MODE>
@@ -1015,22 +928,13 @@ template <int FMT, bool INT>
 static int launch_generic(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     int need = (a.rows + 7) / 8;
     int grid = di->sm_count * 8 < need ? di->sm_count * 8 : need;
+    const int st = ensure_kernel<qgemv_generic_kernel<FMT, INT>, 0>(di);
+    if (st) return st;
     qgemv_generic_kernel<FMT, INT><<<grid, 256, 0, s>>>(a);
     return check_launch();
 }
 
 enum Path { PATH_GENERIC, PATH_Q8S_DIRECT, PATH_RING };
-
-// tensor-core kernel for batches of 5..16 (gemv_mma.cu)
-template <int FMT>
-static bool qmma_eligible(const QGemvArgs &a);
-template <int FMT>
-static int qmma_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s);
-// the same kernel fed with fp32 activations split into fp16 pairs, batches of 1..8
-template <int FMT>
-static bool qmma_float_eligible(const QGemvArgs &a, const DeviceInfo *di);
-template <int FMT>
-static int qmma_float_dispatch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap);
 
 // Does one fast launch with `batch` activation vectors fit in shared memory?
 template <int FMT, int MODE>
@@ -1111,8 +1015,6 @@ constexpr int kFusedQuantMaxElems = 16384;
 template <int FMT, int MODE, bool DOTS>
 static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream_t stream);
 
-static int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s);
-
 template <int FMT, int MODE, bool DOTS>
 static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream_t stream) {
     constexpr bool INT = MODE != MODE_FLOAT;
@@ -1146,7 +1048,7 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
 
     if (MODE == MODE_INT_FUSED) {
         // batches of five and more go to the tensor-core kernel, which reads quantised activations from the workspace
-        const bool fuse = path != PATH_GENERIC && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per && a.batch <= 4 && a.batch < g_int_tc_min_batch;
+        const bool fuse = path != PATH_GENERIC && (long long)a.batch * a.cols <= kFusedQuantMaxElems && a.batch == per && a.batch <= 4 && a.batch < option_value(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH);
         if (fuse) return launch_fast<FMT, MODE_INT_FUSED, false>(a, path, di, s);
         // separate quantiser into the workspace, then the MODE_INT kernels
         st = quantize_x(a.cols, a.batch, a.x, xq_ws, xs_ws, s);
@@ -1157,25 +1059,26 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     } else {
         if (path == PATH_GENERIC) return launch_generic<FMT, INT>(a, di, s);
         if constexpr (MODE == MODE_INT && !DOTS) {
-            if (qmma_eligible<FMT>(a)) return qmma_dispatch<FMT>(a, di, s);
+            if (qmma_eligible(FMT, a)) return qmma_dispatch(FMT, a, di, s);
         }
         if constexpr (MODE == MODE_FLOAT && !DOTS) {
             // measured on 14336 x 4096: the split layout gains from one vector on, the block layouts from two
-            const int min_batch = g_float_tc_min_batch > 0 ? g_float_tc_min_batch : (FMT == FMT_Q8S ? 1 : 2);
-            if (g_float_tensor_cores && a.batch >= min_batch) {
+            const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 from the measured batch on, 2 always
+            const int min_batch = float_tc >= 2 ? 1 : (FMT == FMT_Q8S ? 1 : 2);
+            if (float_tc && a.batch >= min_batch) {
                 // most vectors per pass whose fp16 pairs fit in shared memory next to the weight ring
                 QGemvArgs p = a;
                 int cap = 0;
                 for (int c = 8; c >= 4 && !cap; c -= 4) {
                     p.batch = a.batch < c ? a.batch : c;
-                    if (qmma_float_eligible<FMT>(p, di)) cap = c;
+                    if (qmma_float_eligible(FMT, p, di)) cap = c;
                 }
                 if (cap) {
                     const int passes = (a.batch + cap - 1) / cap, each = (a.batch + passes - 1) / passes;
                     for (int b0 = 0; b0 < a.batch; b0 += each) {
                         p.batch = a.batch - b0 < each ? a.batch - b0 : each;
                         p.x = a.x + (size_t)b0 * a.cols, p.y = a.y + (size_t)b0 * a.rows;
-                        st = qmma_float_dispatch<FMT>(p, di, s, g_overlap_launches != 0 && b0 == 0);
+                        st = qmma_float_dispatch(FMT, p, di, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0 && b0 == 0);
                         if (st) return st;
                     }
                     return TB200_OK;
@@ -1200,33 +1103,31 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     }
 }
 
-static int split_workspace(int cols, int batch, void *workspace, size_t workspace_bytes, int8_t **xq, float **xs) {
+int split_workspace(int cols, int batch, void *workspace, size_t workspace_bytes, int8_t **xq, float **xs) {
     if (cols < 0 || cols % 32 != 0 || batch < 1 || batch > kMaxBatch) return TB200_ERR_INVALID_ARG;
     if (!workspace || workspace_bytes < tb200_qx_workspace_bytes(cols, batch)) return TB200_ERR_WORKSPACE;
     if (!aligned_to(workspace, 16)) return TB200_ERR_ALIGNMENT;
     *xq = reinterpret_cast<int8_t *>(workspace);
-    *xs = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + round_up(cols * batch, 16));
+    *xs = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + (((size_t)cols * batch + 15) & ~(size_t)15));
     return TB200_OK;
 }
 
-static int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s) {
+int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s) {
     if (!x) return TB200_ERR_INVALID_ARG;
     if (!aligned_to(x, 4)) return TB200_ERR_ALIGNMENT;
     int st;
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
-    int nblocks = cols / 32 * batch;
+    const long long nblocks_ll = (long long)(cols / 32) * batch;
+    if (nblocks_ll > 0x7fffffffLL) return TB200_ERR_INVALID_ARG;
+    int nblocks = (int)nblocks_ll;
     if (nblocks == 0) return TB200_OK;
     int grid = (nblocks + 7) / 8;
     if (grid > di->sm_count * 8) grid = di->sm_count * 8;
     // The mat-vec kernels that follow run with the SM's largest shared-memory carve-out.  Without this hint the
     // driver would switch the carve-out for this small kernel and back, draining the SMs twice (about 15 us).
-    static bool hinted[kMaxDevices];
-    if (!hinted[di->device]) {
-        cudaFuncSetAttribute(quantize_x_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-        cudaGetLastError();
-        hinted[di->device] = true;
-    }
+    st = ensure_kernel<quantize_x_kernel, KERNEL_MAX_CARVEOUT>(di);
+    if (st) return st;
     quantize_x_kernel<<<grid, 256, 0, s>>>(x, xq, xs, nblocks);
     return check_launch();
 }
@@ -1366,6 +1267,11 @@ static int qgemv_i8_grouped_rows(int count, const int *rows, int cols, int batch
                                        GroupSync{});
 }
 
+// split-layout integer mat-vec on activations that are already quantised (a.xq, a.xs)
+int q8s_gemv_quantised(const QGemvArgs &a, tb200_stream_t stream) {
+    return qgemv_dispatch<FMT_Q8S, MODE_INT, false>(a, nullptr, nullptr, stream);
+}
+
 }  // namespace tb200
 
 using namespace tb200;
@@ -1392,7 +1298,7 @@ extern "C" int tb200_q4b_gemv(int rows, int cols, int batch, const uint8_t *bloc
 
 extern "C" size_t tb200_qx_workspace_bytes(int cols, int batch) {
     if (cols < 0 || batch < 0) return 0;
-    return (size_t)round_up(cols * batch, 16) + (size_t)(cols / 32) * batch * sizeof(float);
+    return (((size_t)cols * batch + 15) & ~(size_t)15) + (size_t)(cols / 32) * batch * sizeof(float);
 }
 
 extern "C" int tb200_quantize_x(int cols, int batch, const float *x, void *workspace, size_t workspace_bytes,

@@ -1,40 +1,50 @@
 // Allocation-free entry point of the integer-path Q8_0 mat-vec (split layout).
 //
-// Part of the single translation unit of the library (see libtornado_b200.cu):
-// it reuses the quantiser and the mat-vec dispatch of gemv_quant.cu and adds
+// It reuses the quantiser and the mat-vec dispatch of gemv_quant.cu and adds
 // only the built-in scratch array and the entry point that uses it.
-#include <mutex>
-
-#include "common.cuh"
+#define TB200_OP_CLASS TB200_PREPARE_GEMV_QUANT
+#include "gemv_common.cuh"
 
 // The quantised activations go to a fixed scratch array that is part of the
-// loaded library image on every device, instead of caller-provided workspace.
+// loaded library image in every CUDA context, instead of caller-provided workspace.
 namespace tb200 {
 
 static __device__ __align__(256) unsigned char g_static_qx_scratch[TB200_STATIC_SCRATCH_BYTES];
 
-// Device address of the scratch array, resolved once per device.  The array's
-// name is only a host-side handle here; kernels need the address the runtime
-// reports for the device that is current.
-static void *g_static_scratch_ptr[kMaxDevices];
-static std::mutex g_static_scratch_mutex;
+// Device address of the scratch array, resolved once per CUDA context.  The
+// array's name is only a host-side handle here; kernels need the address the
+// runtime reports for the context that is current.  A __device__ variable is
+// instantiated once per context that loads the library (a process may hold
+// several contexts on one GPU), so the cache is indexed by the context's slot,
+// never by the device ordinal.
+static std::atomic<void *> g_static_scratch_ptr[kMaxContexts];
 
 static int static_scratch(const DeviceInfo *di, void **out) {
-    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
-    if (!g_static_scratch_ptr[di->device]) {
-        void *p = nullptr;
+    void *p = g_static_scratch_ptr[di->slot].load(std::memory_order_acquire);
+    if (!p) {
         cudaError_t e = cudaGetSymbolAddress(&p, g_static_qx_scratch);
         if (e != cudaSuccess) {
             cudaGetLastError();
             return (int)e;
         }
-        g_static_scratch_ptr[di->device] = p;
+        g_static_scratch_ptr[di->slot].store(p, std::memory_order_release);
     }
-    *out = g_static_scratch_ptr[di->device];
+    *out = p;
     return TB200_OK;
 }
 
 }  // namespace tb200
+
+using namespace tb200;
+
+// Test hook: the address the entry point below will hand to its kernels in the current context.
+extern "C" int tb200_static_scratch_address(void **out) {
+    if (!out) return TB200_ERR_INVALID_ARG;
+    int st;
+    const DeviceInfo *di = device_info(&st);
+    if (!di) return st;
+    return static_scratch(di, out);
+}
 
 extern "C" int tb200_q8_gemv_i8_static(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales,
                                        const float *x, float *y, tb200_stream_t stream) {
@@ -56,5 +66,5 @@ extern "C" int tb200_q8_gemv_i8_static(int rows, int cols, int batch, const int8
     st = quantize_x(cols, batch, x, xq, xs, (cudaStream_t)stream);
     if (st) return st;
     QGemvArgs a{reinterpret_cast<const uint8_t *>(q), scales, nullptr, xq, xs, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT_Q8S, MODE_INT, false>(a, nullptr, nullptr, stream);
+    return q8s_gemv_quantised(a, stream);
 }

@@ -23,12 +23,13 @@
 // flops per launch: 2*m*n*k; roofline: dense fp16 tensor throughput.
 #include <cuda.h>
 
+#define TB200_OP_CLASS TB200_PREPARE_GEMM_F16
 #include "common.cuh"
+#include "gemm_generic.cuh"
+
+TB200_TU_STATUS(hgemm)
 
 namespace tb200 {
-
-int g_hgemm_pairs = 1;  // TB200_OPT_HGEMM_SM_PAIRS
-int g_hgemm_xpose_min_dst = 2;  // TB200_OPT_HGEMM_LINE_STORES: destinations from which the epilogue stores whole lines
 
 constexpr int HG_BM = 128, HG_BN = 256, HG_BK = 64, HG_STAGES = 4;
 constexpr int HG_THREADS = 192;
@@ -551,20 +552,21 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
+    // resolved once per process (thread-safe initialisation of a local static); tb200_prepare calls this
+    // before any stream capture
+    static const EncodeTiledFn fn = [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-        else
-            cudaGetLastError();
-        tried = true;
-    }
+            return reinterpret_cast<EncodeTiledFn>(p);
+        cudaGetLastError();
+        return (EncodeTiledFn) nullptr;
+    }();
     return fn;
 }
+
+int hgemm_prepare_driver() { return encode_tiled_fn() ? TB200_OK : TB200_ERR_DRIVER; }
 
 // 2-D fp16 tensor map: `inner` contiguous elements per row, `outer` rows, box of 64 x box_rows, 128-byte swizzle.
 static int make_map_f16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint32_t box_rows) {  // box: 64 x box_rows
@@ -586,7 +588,7 @@ using namespace tb200;
 
 // C(fp32) = A(fp16) * B(fp16) with the tile stores described by `out`.
 static int hgemm_launch(int m, int n, int k, const uint16_t *a, const uint16_t *b, HgOut out, tb200_stream_t stream) {
-    out.xpose = out.ndst >= g_hgemm_xpose_min_dst;
+    out.xpose = out.ndst >= option_value(TB200_OPT_HGEMM_LINE_STORES);
     if (m < 0 || n < 0 || k < 0) return TB200_ERR_INVALID_ARG;
     if (m == 0 || n == 0) return TB200_OK;
     if (k > 0 && (!a || !b)) return TB200_ERR_INVALID_ARG;
@@ -609,6 +611,8 @@ static int hgemm_launch(int m, int n, int k, const uint16_t *a, const uint16_t *
         // the CUDA-core kernel writes one dense [m][n] matrix
         if (out.ndst != 1 || out.ld != n) return TB200_ERR_INVALID_ARG;
         dim3 grid((n + 31) / 32, (m + 31) / 32);
+        st = ensure_kernel<gemm_generic_kernel<uint16_t>, 0>(di);
+        if (st) return st;
         gemm_generic_kernel<uint16_t><<<grid, 1024, 0, s>>>(m, n, k, 1.0f, a, b, 0.0f, out.dst[0]);
         return check_launch();
     }
@@ -625,7 +629,7 @@ static int hgemm_launch(int m, int n, int k, const uint16_t *a, const uint16_t *
     };
     // SM pairs pay off once there are at least two waves of 256 x 256 tiles; smaller products fill the
     // machine better with 128 x 256 tiles on single CTAs
-    if (g_hgemm_pairs && ((m + 255) / 256) * ((n + 255) / 256) >= 2 * (di->sm_count / 2)) {
+    if (option_value(TB200_OPT_HGEMM_SM_PAIRS) && ((m + 255) / 256) * ((n + 255) / 256) >= 2 * (di->sm_count / 2)) {
         // SM pairs: 256 x 256 tiles, one cluster of two CTAs each
         st = ensure_smem_optin<hgemm_tc2_kernel>(di);
         if (st) return st;

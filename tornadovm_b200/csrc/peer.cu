@@ -9,7 +9,10 @@
 // Buffers are exchanged between the processes as CUDA IPC handles (tb200_ipc_export / _open).
 #include <cstring>
 
+#define TB200_OP_CLASS TB200_PREPARE_PEER
 #include "common.cuh"
+
+TB200_TU_STATUS(peer)
 
 namespace tb200 {
 
@@ -81,6 +84,11 @@ extern "C" int tb200_peer_wait(int rank, int npeers, unsigned *const *flags, con
     if (!aligned_to(sync, 4)) return TB200_ERR_ALIGNMENT;
     a.epoch = const_cast<unsigned *>(sync), a.rank = rank, a.npeers = npeers;
     a.timeout_ns = (unsigned long long)(timeout_ms ? timeout_ms : 2000u) * 1000000ull;
+    int st;
+    const DeviceInfo *di = device_info(&st);
+    if (!di) return st;
+    st = ensure_kernel<peer_wait_kernel, 0>(di);
+    if (st) return st;
     // a plain launch: it starts only after everything enqueued before it has completed
     return launch_kernel(peer_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, false, a);
 }
@@ -98,6 +106,11 @@ extern "C" int tb200_peer_signal_wait(int rank, int npeers, unsigned *const *fla
     if (!aligned_to(epoch, 4)) return TB200_ERR_ALIGNMENT;
     a.epoch = epoch, a.rank = rank, a.npeers = npeers;
     a.timeout_ns = (unsigned long long)(timeout_ms ? timeout_ms : 2000u) * 1000000ull;
+    int st;
+    const DeviceInfo *di = device_info(&st);
+    if (!di) return st;
+    st = ensure_kernel<peer_signal_wait_kernel, 0>(di);
+    if (st) return st;
     // a plain launch: it starts only after everything enqueued before it has completed
     return launch_kernel(peer_signal_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, false, a);
 }

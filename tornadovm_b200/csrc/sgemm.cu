@@ -10,7 +10,11 @@
 // shared memory so that both operands are read as float4 along the output
 // dimension.  Roofline: FP32 FFMA peak = SMs * 128 lanes * 2 * clock.
 // flops per launch: 2*m*n*k.
+#define TB200_OP_CLASS TB200_PREPARE_GEMM_F32
 #include "common.cuh"
+#include "gemm_generic.cuh"
+
+TB200_TU_STATUS(sgemm)
 
 namespace tb200 {
 
@@ -127,39 +131,6 @@ sgemm_tiled_kernel(int m, int n, int k, float alpha, const float *__restrict__ A
     }
 }
 
-// Any shape and 4-byte alignment: 32x32 tiles, one output per thread.
-// TA / TB are float or __half-bit patterns (uint16_t): the FP16 GEMM reuses this
-// kernel for shapes its tensor-core path does not take.
-template <typename TA>
-__device__ __forceinline__ float to_f32(TA v);
-template <>
-__device__ __forceinline__ float to_f32<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ float to_f32<uint16_t>(uint16_t v) { return half_bits_to_float(v); }
-
-template <typename TIN>
-__global__ void __launch_bounds__(1024)
-gemm_generic_kernel(int m, int n, int k, float alpha, const TIN *__restrict__ A, const TIN *__restrict__ B, float beta,
-                    float *__restrict__ C) {
-    __shared__ float As[32][33];
-    __shared__ float Bs[32][33];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int row = blockIdx.y * 32 + ty, col = blockIdx.x * 32 + tx;
-    float acc = 0.f;
-    for (int k0 = 0; k0 < k; k0 += 32) {
-        As[ty][tx] = (row < m && k0 + tx < k) ? to_f32<TIN>(A[(size_t)row * k + k0 + tx]) : 0.f;
-        Bs[ty][tx] = (k0 + ty < k && col < n) ? to_f32<TIN>(B[(size_t)(k0 + ty) * n + col]) : 0.f;
-        __syncthreads();
-#pragma unroll
-        for (int kk = 0; kk < 32; ++kk) acc = fmaf(As[ty][kk], Bs[kk][tx], acc);
-        __syncthreads();
-    }
-    if (row < m && col < n) {
-        float *cp = C + (size_t)row * n + col;
-        *cp = beta != 0.f ? fmaf(beta, *cp, alpha * acc) : alpha * acc;
-    }
-}
-
 }  // namespace tb200
 
 using namespace tb200;
@@ -177,9 +148,13 @@ extern "C" int tb200_sgemm(int m, int n, int k, float alpha, const float *a, con
     const bool fast = k > 0 && k % 4 == 0 && n % 4 == 0 && aligned_to(a, 16) && aligned_to(b, 16) && m >= 64 && n >= 64;
     if (fast) {
         dim3 grid((n + SG_BN - 1) / SG_BN, (m + SG_BM - 1) / SG_BM);
+        st = ensure_kernel<sgemm_tiled_kernel, 0>(di);
+        if (st) return st;
         sgemm_tiled_kernel<<<grid, SG_THREADS, 0, s>>>(m, n, k, alpha, a, b, beta, c);
     } else {
         dim3 grid((n + 31) / 32, (m + 31) / 32);
+        st = ensure_kernel<gemm_generic_kernel<float>, 0>(di);
+        if (st) return st;
         gemm_generic_kernel<float><<<grid, 1024, 0, s>>>(m, n, k, alpha, a, b, beta, c);
     }
     return check_launch();

@@ -20,8 +20,11 @@ SIGNATURES = {
     "tb200_status_string": (C.c_char_p, [_I]),
     "tb200_version": (_I, []),
     "tb200_device_status": (_I, [C.POINTER(_I)]),
+    "tb200_prepare": (_I, [_I]),
     "tb200_set_option": (_I, [_I, _I]),
     "tb200_get_option": (_I, [_I, C.POINTER(_I)]),
+    "tb200_set_thread_option": (_I, [_I, _I]),
+    "tb200_clear_thread_options": (_I, []),
     "tb200_device_malloc": (_I, [_Z, C.POINTER(_P)]),
     "tb200_device_free": (_I, [_P]),
     "tb200_sgemv": (_I, [_I, _I, _P, _P, _P, _P]),
@@ -32,6 +35,7 @@ SIGNATURES = {
     "tb200_quantize_x": (_I, [_I, _I, _P, _P, _Z, _P]),
     "tb200_q8_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "tb200_q8_gemv_i8_static": (_I, [_I, _I, _I, _P, _P, _P, _P, _P]),
+    "tb200_static_scratch_address": (_I, [C.POINTER(_P)]),
     "tb200_q8b_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_q4b_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_q8b_gemv_i8_grouped": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, C.c_longlong, _P, _I, _I, _P, _Z, _P]),
