@@ -37,10 +37,11 @@ sys.path.insert(0, ROOT)
 
 ROWS, COLS, BATCH = 14336, 4096, 1
 LAYERS = 32  # one step = this projection in each of 32 decoder layers (Llama-3-8B depth): 32 distinct matrices, 2.0 GB
-# dram__bytes_read.sum + dram__bytes_write.sum per 14336 x 4096 matrix of a grouped integer-mode launch, from the ncu
-# capture summarised in profiles/qblk_gemv_grouped_32x14336x4096.md (8 matrices per launch: 499.3 MB read + 5.2 MB
-# written; the kernel reads every weight byte once, so traffic grows in proportion to the matrices of a launch)
+# dram__bytes_read.sum + dram__bytes_write.sum per 14336 x 4096 matrix of a grouped integer-mode launch, from an ncu
+# capture of 8 matrices per launch (499.3 MB read + 5.2 MB written; the kernel reads every weight byte once, so
+# traffic grows in proportion to the matrices of a launch)
 NCU_TRAFFIC_BYTES_PER_GEMV = 63_060_000
+REF_MATVECS = 8  # mat-vecs per step of the CPU reference arm
 METRIC = "q8_0_gemv_hbm_throughput"
 UNIT = "GB/s"
 
@@ -141,15 +142,20 @@ def run_reference_arm(args):
     q = rng.integers(-127, 128, ROWS * COLS, dtype=np.int8)
     s = (np.abs(rng.standard_normal(ROWS * COLS // 32)) * 0.02).astype(np.float16).view(np.uint16)
     x = rng.standard_normal(COLS).astype(np.float32)
-    for _ in range(args.warmup):
-        o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=True)
+    # one step = REF_MATVECS mat-vecs of the GPU step's 32, so that a run of 20 steps spans more than half a second
+    # (a single 3 ms mat-vec per step is dominated by thread wake-up noise)
+    for _ in range(max(args.warmup, 1)):
+        for _ in range(REF_MATVECS):
+            o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=True)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=True)
+        for _ in range(REF_MATVECS):
+            o.q8_gemv_seq(q, s, x, COLS, ROWS, threads=True)
     dt = time.perf_counter() - t0
     per = dt / args.steps
-    val = algorithmic_bytes(ROWS, COLS, 1) / per / 1e9
-    sample = f"each step = one full {ROWS}x{COLS} batch-1 mat-vec (of the {LAYERS} per GPU step) on {o.num_threads()} host threads"
+    val = REF_MATVECS * algorithmic_bytes(ROWS, COLS, 1) / per / 1e9
+    sample = (f"each step = {REF_MATVECS} full {ROWS}x{COLS} batch-1 mat-vecs (of the {LAYERS} per GPU step) on "
+              f"{o.num_threads()} host threads")
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -311,6 +317,41 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
     return out
 
 
+def verify_sharded_step(torch, dist, lib, op, blocks, lrows, r0, dev):
+    """Untimed check of the multi-GPU data path: over several consecutive steps with changing activations (so that
+    the output slots rotate and are reused), every rank recomputes its own row shard of every matrix with the
+    single-launch kernel, the shards are all-gathered with torch.distributed, and the slot the fused kernel
+    filled through peer stores must equal the assembled result bit for bit on every rank."""
+    P = lambda t: C.c_void_p(t.data_ptr())
+    world = dist.get_world_size()
+    S = C.c_void_p(op.stream.cuda_stream)
+    n_ws = lib.tb200_qx_workspace_bytes(COLS, BATCH)
+    ws = torch.empty(max(n_ws, 16), dtype=torch.uint8, device=dev)
+    local = torch.empty((LAYERS, BATCH, lrows), device=dev)
+    ok = True
+    for step in range(5):
+        g = torch.Generator(device=dev).manual_seed(1000 + step)  # the same activations on every rank
+        op.x_dev.copy_(torch.randn((BATCH, COLS), device=dev, generator=g))
+        torch.cuda.synchronize()
+        with torch.cuda.stream(op.stream):
+            fused = op.launch()
+            op.wait()
+            for l in range(LAYERS):
+                st = lib.tb200_q8b_gemv_i8(lrows, COLS, BATCH, P(blocks[l]), P(op.x_dev), P(local[l]), P(ws), n_ws, S)
+                if st:
+                    raise SystemExit(f"tb200_q8b_gemv_i8 failed with status {st}")
+        op.stream.synchronize()
+        op.check()
+        shards = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(shards, local)  # equal shards: ROWS is a multiple of the rank count
+        want = torch.cat(shards, dim=2)
+        ok = ok and bool(torch.equal(fused, want))
+        dist.barrier()  # nobody starts the next step (and overwrites a slot) before everyone has compared
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(flag.item())
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -357,6 +398,17 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
 
     barrier()
+    verified = None
+    if world > 1:
+        verified = verify_sharded_step(torch, dist, lib, op, blocks, lrows, r0, dev)
+        if not verified:
+            raise SystemExit("the gathered outputs of the sharded step differ from the single-launch results")
+        # every peer mapping, flag page and output slot has been touched before anything is timed
+        with torch.cuda.stream(stream):
+            for _ in range(60):
+                op.launch()
+            op.wait()
+        barrier()
     with torch.cuda.stream(stream):
         for _ in range(max(args.warmup, 3)):
             op.launch()
@@ -414,15 +466,16 @@ def run_gpu_arm(args):
         from tornadovm_b200.arrays import ByteArray, FloatArray
         from tornadovm_b200.b200 import B200, B200Options
         from tornadovm_b200.taskgraph import CudaDevice, DataTransferMode, TaskGraph, TornadoExecutionPlan
-        wa = [ByteArray(blocks[l].cpu().numpy().ravel()) for l in range(LAYERS)]
+        # one ByteArray per task holds the task's `group` matrices back to back (7 task arguments whatever the count:
+        # a library task carries at most 20, TaskGraph.java:886)
+        wa = [ByteArray(blocks[c * group:(c + 1) * group].cpu().numpy().ravel()) for c in range(LAYERS // group)]
         xa = FloatArray(op.x_dev.cpu().numpy())
         ya = [FloatArray(group * ROWS * BATCH) for _ in range(LAYERS // group)]
         opts = B200Options(exact_int=True, overlap_launches=True)
         tg = TaskGraph("q8decode").transferToDevice(DataTransferMode.FIRST_EXECUTION, *wa) \
             .transferToDevice(DataTransferMode.EVERY_EXECUTION, xa)
-        grouped = lambda *a: B200.q8GemvBytesGrouped(*a, options=opts)  # the factory with the plan's tuning object
         for c in range(LAYERS // group):
-            tg.libraryTask(f"g{c}", grouped, ROWS, COLS, BATCH, xa, ya[c], *wa[c * group:(c + 1) * group])
+            tg.libraryTask(f"g{c}", B200.q8GemvBytesPacked, group, ROWS, COLS, BATCH, wa[c], xa, ya[c], opts)
         tg.transferToHost(DataTransferMode.EVERY_EXECUTION, *ya)
         with TornadoExecutionPlan(tg, CudaDevice(local)).withCUDAGraph() as plan:
             for _ in range(max(args.warmup, 3)):
@@ -434,15 +487,17 @@ def run_gpu_arm(args):
             torch.cuda.synchronize()
             e2e_s = time.perf_counter() - t0
             h2d, d2h = plan.h2d_bytes_last, plan.d2h_bytes_last
-        api = "TaskGraph.libraryTask(B200.q8GemvBytesGrouped) + TornadoExecutionPlan.withCUDAGraph().execute()"
+        api = "TaskGraph.libraryTask(B200.q8GemvBytesPacked) + TornadoExecutionPlan.withCUDAGraph().execute()"
     else:
         xh = torch.randn((BATCH, COLS)).pin_memory()
+        # the job's result reaches the host once: rank 0 downloads the gathered outputs, the other ranks (whose
+        # consumers would read them on the device) only complete the step
         for _ in range(max(args.warmup, 3)):
-            op.run(xh)
+            op.run(xh, download=rank == 0)
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            op.run(xh)
+            op.run(xh, download=rank == 0)
         barrier()
         e2e_s = time.perf_counter() - t0
         t = torch.tensor([e2e_s], device=dev)
@@ -478,6 +533,8 @@ def run_gpu_arm(args):
                      "bytes_per_launch": launch_bytes, "us_per_launch": kernel_s * 1e6},
         "clocks": clocks.summary(),
     }
+    if verified is not None:
+        line["verified"] = verified  # N > 1: fused peer-store gather == all-gathered single launches, bit for bit, on every rank
     op.close()
     if rank == 0:
         if world == 1:

@@ -69,6 +69,9 @@ int tb200_version(void);
  * bounded wait (value = TB200_ERR_TIMEOUT).  Reading it clears it.  Synchronises
  * the device; meant for tests and diagnostics, not for the launch path. */
 int tb200_device_status(int *status_out);
+/* The same for the kernels of the given operation classes only (tb200_prepare_class bits, 0 = all): fewer
+ * device reads for a caller that knows which kernels it ran. */
+int tb200_device_status_of(int op_classes, int *status_out);
 
 /* One-time work of the CUDA context that is current on the calling thread: loads every kernel of the
  * selected operation classes into the context, sets their attributes (dynamic shared memory opt-in,
@@ -104,7 +107,7 @@ int tb200_prepare(int op_classes);
  * not be written by the kernel enqueued immediately before the mat-vec on the
  * same stream (copies and earlier kernels are fine). */
 enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2, TB200_OPT_FLOAT_TENSOR_CORES = 3, TB200_OPT_MMA_WARP_RINGS = 4,
-                    TB200_OPT_HGEMM_LINE_STORES = 5, TB200_OPT_INT_TENSOR_CORE_MIN_BATCH = 6 };
+                    TB200_OPT_HGEMM_LINE_STORES = 5, TB200_OPT_INT_TENSOR_CORE_MIN_BATCH = 6, TB200_OPT_TC_REGISTER_KERNEL = 7 };
 /* TB200_OPT_HGEMM_SM_PAIRS (default 1): the FP16 GEMM runs 256 x 256 tiles on clusters of two CTAs
  * (tcgen05 cta_group::2) instead of 128 x 256 tiles on single CTAs.
  * TB200_OPT_FLOAT_TENSOR_CORES (default 1): the float-mode quantised mat-vecs (tb200_q8_gemv,
@@ -116,8 +119,11 @@ enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2
  * tensor-core mat-vec kernels.
  * TB200_OPT_HGEMM_LINE_STORES (default 2): the FP16 GEMM's epilogue transposes its tiles through shared memory
  * and stores whole 128-byte lines when a tile goes to at least `value` destinations (1 = always).
- * TB200_OPT_INT_TENSOR_CORE_MIN_BATCH (default 4, 2..17): the integer-mode mat-vecs take the tensor-core kernel from
- * this many activation vectors on (17 = never); smaller batches stay on the dp4a kernels. */
+ * TB200_OPT_INT_TENSOR_CORE_MIN_BATCH (default 4, 1..17): the integer-mode mat-vecs take the tensor-core kernel from
+ * this many activation vectors on (17 = never); smaller batches stay on the dp4a kernels.  With 1 the block-dot
+ * test entries (tb200_*_blockdots_i32) run on the tensor-core kernel as well.
+ * TB200_OPT_TC_REGISTER_KERNEL (default 1): the tensor-core mat-vecs use the kernel that keeps the activations
+ * in registers (one 256-column slice of K per warp); 0 selects the older shared-memory kernels (diagnostics). */
 int tb200_set_option(int option, int value);
 int tb200_get_option(int option, int *value);
 int tb200_set_thread_option(int option, int value);
@@ -201,9 +207,10 @@ int tb200_q4b_gemv_i8(int rows, int cols, int batch, const uint8_t *blocks, cons
 #define TB200_STATIC_SCRATCH_BYTES 147456 /* enough for cols * batch <= 131072, e.g. 16384 x 8 */
 int tb200_q8_gemv_i8_static(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x,
                             float *y, tb200_stream_t stream);
-/* Test hook: the device address of that array in the CUDA context that is current (each context that
- * loads the library has its own copy of it). */
-int tb200_static_scratch_address(void **out);
+/* Test hook: the device address of that array the entry point will use in the CUDA context that is current
+ * (`in_use`) and the address the runtime reports for it there (`fresh`); each context that loads the library
+ * has its own copy of the array, so the two must agree in every context. */
+int tb200_static_scratch_address(void **in_use, void **fresh);
 
 /* ---- Grouped integer-mode mat-vec and the multi-GPU output hand-off ------------
  * `count` (<= 32) block matrices of one shape [rows][cols] that share the same
@@ -301,6 +308,15 @@ int tb200_q8b_blockdots_i32(int rows, int cols, const uint8_t *blocks, const int
                             tb200_stream_t stream);
 int tb200_q4b_blockdots_i32(int rows, int cols, const uint8_t *blocks, const int8_t *xq, int32_t *dots,
                             tb200_stream_t stream);
+
+/* The same check for the tensor-core mat-vec kernel (mma.sync.m16n8k32.s8), which serves the batches:
+ * dots[b][r][blk] for `batch` (<= 16) already-quantised vectors xq[batch][cols], every column of the MMA
+ * tiles included.  format: 0 = Q8_0 split quants (Int8Array), 1 = Q8_0 34-byte blocks, 2 = Q4_0 18-byte
+ * blocks.  Needs cols % 256 == 0 and 8-byte aligned weights.  Pin: TestMatrixMultiplicationMMAInt8
+ * (tornado-unittests/.../TestMatrixMultiplicationMMAInt8.java:314-322) demands exact equality of the
+ * int8 tile products in the same way. */
+int tb200_blockdots_i32_batched(int format, int rows, int cols, int batch, const void *weights, const int8_t *xq,
+                                int32_t *dots, tb200_stream_t stream);
 
 /* ---- FP32 SGEMM -------------------------------------------------------------
  * C = alpha * A * B + beta * C, A[m][k], B[k][n], C[m][n] row-major.

@@ -60,3 +60,28 @@ def test_sharded_hgemm_one_rank_fused_equals_plain():
         assert B200Native.device_status() == 0
     finally:
         op.close()
+
+
+def test_expired_device_wait_becomes_an_exception():
+    """A bounded wait that ran out (here: a flag that nothing sets, 20 ms limit) must surface in the host
+    classes: check() -- called by run() after every step -- raises instead of returning stale outputs."""
+    from tornadovm_b200.native import TornadoB200Error
+    from tornadovm_b200.peer import ShardedGroupedGemv
+    rows, cols = 64, 1024
+    lib = B200Native.load()
+    q, s, x = o.make_q8(rows, cols, 1, 9)
+    op = ShardedGroupedGemv(rows, cols, 1, [torch.from_numpy(o.q8_pack_blocks(q, s)).cuda()], "q8b")
+    try:
+        flags = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+        epoch = torch.zeros(4, dtype=torch.int32, device="cuda")
+        fp = (C.c_void_p * 2)(*[f.data_ptr() for f in flags])
+        S = C.c_void_p(op.stream.cuda_stream)
+        assert lib.tb200_peer_signal_wait(0, 2, fp, C.c_void_p(epoch.data_ptr()), 20, S) == 0
+        op.stream.synchronize()
+        with pytest.raises(TornadoB200Error, match="TB200_ERR_TIMEOUT"):
+            op.check()
+        op.check()  # reading cleared it
+        y = op.run(torch.from_numpy(x).reshape(1, cols).pin_memory())
+        assert torch.isfinite(y).all()
+    finally:
+        op.close()

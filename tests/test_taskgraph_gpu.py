@@ -81,7 +81,7 @@ def test_grouped_q8_task_equals_separate_tasks():
             got = yg.numpy().reshape(count, batch * rows)
             for m in range(count):
                 assert np.array_equal(got[m], ys[m].numpy())
-    with pytest.raises(RuntimeError, match="1 to 32 matrices"):
+    with pytest.raises(RuntimeError, match="1 to 15 matrices"):
         B200.q8GemvBytesGrouped(rows, cols, batch, x, yg)
 
 
@@ -116,3 +116,84 @@ def test_native_status_becomes_exception():
     with TornadoExecutionPlan(tg) as plan:
         with pytest.raises(TornadoB200Error, match=r"\[ERROR\] q8Gemv failed with status: TB200_ERR_INVALID_ARG"):
             plan.execute()
+
+
+def test_in_out_task_under_cuda_graph_runs_once_per_execute():
+    """C = A*B + C with withCUDAGraph(): every execute() applies the task exactly once, the first one
+    included (its launch is captured, not run twice)."""
+    n = 128
+    a_h, b_h = o.JavaRandom(1).uniform_f32(n * n, 0, 1), o.JavaRandom(2).uniform_f32(n * n, 0, 1)
+    a, b, c = FloatArray(a_h), FloatArray(b_h), FloatArray(np.zeros(n * n, np.float32))
+    tg = (TaskGraph("acc")
+          .transferToDevice(DataTransferMode.FIRST_EXECUTION, a, b, c)
+          .libraryTask("sgemm", B200.sgemm, n, n, n, 1.0, a, b, 1.0, c)
+          .transferToHost(DataTransferMode.EVERY_EXECUTION, c))
+    ab = o.sgemm_f64(a_h, b_h, n, n, n).ravel()
+    with TornadoExecutionPlan(tg).withCUDAGraph() as plan:
+        for k in (1, 2, 3):
+            plan.execute()
+            assert o.rel_l2(c.numpy(), k * ab) <= 1e-5, k
+
+
+def test_first_dispatch_of_every_factory_is_captured():
+    """The reference captures the FIRST execution of a plan (TornadoVMInterpreter.java:462-476): prepare() must
+    have made every kernel resident, so a fresh plan with one task of each factory captures and replays."""
+    rows, cols, batch, n = 128, 4096, 8, 256
+    q_h, s_h, x_h = o.make_q8(rows, cols, batch, 77)
+    blk_h = o.q8_pack_blocks(q_h, s_h)
+    q4_h, _, _ = o.make_q4(rows, cols, batch, 78)
+    m_h, v_h = o.make_sgemv(rows, cols, 79)
+    ha_h, hb_h = o.make_hgemm(n, n, n, 80)
+    fa_h, fb_h = o.JavaRandom(81).uniform_f32(n * n, 0, 1), o.JavaRandom(82).uniform_f32(n * n, 0, 1)
+    q, s, x = Int8Array(q_h), HalfFloatArray(s_h), FloatArray(x_h)
+    blk, q4 = ByteArray(blk_h), ByteArray(q4_h)
+    packed = ByteArray(np.concatenate([blk_h, blk_h]))
+    m, v, out = FloatArray(m_h), FloatArray(v_h), FloatArray(rows)
+    ha, hb, hc = HalfFloatArray(ha_h), HalfFloatArray(hb_h), FloatArray(n * n)
+    fa, fb, fc = FloatArray(fa_h), FloatArray(fb_h), FloatArray(n * n)
+    ys = [FloatArray(rows * batch) for _ in range(6)]
+    yp = FloatArray(2 * rows * batch)
+    exact, flt = B200Options(exact_int=True, overlap_launches=True), B200Options()
+    tg = (TaskGraph("all")
+          .transferToDevice(DataTransferMode.FIRST_EXECUTION, q, s, blk, q4, packed, m, v, ha, hb, fa, fb)
+          .transferToDevice(DataTransferMode.EVERY_EXECUTION, x)
+          .libraryTask("t0", B200.sgemv, rows, cols, m, v, out)
+          .libraryTask("t1", B200.q8Gemv, rows, cols, batch, q, s, x, ys[0], flt)
+          .libraryTask("t2", B200.q8Gemv, rows, cols, batch, q, s, x, ys[1], exact)
+          .libraryTask("t3", B200.q8GemvBytes, rows, cols, batch, blk, x, ys[2], flt)
+          .libraryTask("t4", B200.q8GemvBytes, rows, cols, batch, blk, x, ys[3], exact)
+          .libraryTask("t5", B200.q4GemvBytes, rows, cols, batch, q4, x, ys[4], flt)
+          .libraryTask("t6", B200.q4GemvBytes, rows, cols, batch, q4, x, ys[5], exact)
+          .libraryTask("t7", B200.q8GemvBytesPacked, 2, rows, cols, 2, packed, x, yp)
+          .libraryTask("t8", B200.sgemm, n, n, n, 1.0, fa, fb, 0.0, fc)
+          .libraryTask("t9", B200.hgemmF32, n, n, n, ha, hb, hc)
+          .transferToHost(DataTransferMode.EVERY_EXECUTION, out, fc, hc, yp, *ys))
+    with TornadoExecutionPlan(tg).withCUDAGraph() as plan:
+        for _ in range(2):
+            plan.execute()
+            xs = np.ascontiguousarray(x.numpy())
+            f64 = np.stack([o.q8_gemv_f64(q_h, s_h, xs[b * cols:(b + 1) * cols], cols, rows) for b in range(batch)])
+            assert o.rel_l2(out.numpy(), o.sgemv_f64(m_h, v_h, cols, rows)) <= 1e-5
+            assert o.rel_l2(ys[0].numpy().reshape(batch, rows), f64) <= 1e-5
+            assert o.rel_l2(ys[2].numpy().reshape(batch, rows), f64) <= 1e-5
+            assert o.rel_l2(ys[1].numpy().reshape(batch, rows), f64) <= 2e-2
+            # same exact block dots, different fp32 summation order (tensor-core kernel vs dp4a kernel)
+            assert o.rel_l2(yp.numpy()[:2 * 2 * rows].reshape(2, 2, rows)[0], ys[3].numpy().reshape(batch, rows)[:2]) <= 1e-6
+            q4f = np.stack([o.q4_gemv_f64(q4_h, xs[b * cols:(b + 1) * cols], cols, rows) for b in range(batch)])
+            assert o.rel_l2(ys[4].numpy().reshape(batch, rows), q4f) <= 1e-5
+            assert o.rel_l2(ys[5].numpy().reshape(batch, rows), q4f) <= 2e-2
+            assert o.rel_l2(fc.numpy(), o.sgemm_f64(fa_h, fb_h, n, n, n)) <= 1e-5
+            assert o.rel_l2(hc.numpy(), o.hgemm_ref(ha_h, hb_h, n, n, n)) <= 2e-3
+
+
+def test_library_task_argument_limit():
+    """A library task carries at most 20 arguments (TaskGraph.java:886); the grouped factory therefore
+    stops at 15 matrices and the packed form carries up to 32 in one ByteArray."""
+    rows, cols = 4, 256
+    x, y = FloatArray(cols), FloatArray(32 * rows)
+    mats = [ByteArray(rows * (cols // 32) * 34) for _ in range(16)]
+    with pytest.raises(RuntimeError, match="1 to 15 matrices"):
+        B200.q8GemvBytesGrouped(rows, cols, 1, x, y, *mats)
+    with pytest.raises(TypeError, match="1 to 20 task arguments"):
+        TaskGraph("big").libraryTask("t", B200.q8GemvBytesGrouped, rows, cols, 1, x, y, *mats)
+    B200.q8GemvBytesPacked(32, rows, cols, 1, ByteArray(32 * rows * (cols // 32) * 34), x, y)

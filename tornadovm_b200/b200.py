@@ -16,6 +16,8 @@ from .descriptor import Access, LibraryTaskDescriptor
 LIBRARY_NAME = "b200/linalg"
 MAX_BATCH = 16
 MAX_GROUP = 32
+#: TaskGraph.libraryTask takes at most 20 arguments (TaskGraph.java:886): rows, cols, batch, x, y + 15 matrices
+MAX_GROUP_TASK_ARGS = 15
 
 
 @dataclass
@@ -85,7 +87,9 @@ class B200:
     @staticmethod
     def _grouped(name, block_bytes, rows, cols, batch, x, y, blocks, options):
         B200._check_q(name, rows, cols, batch, x, y)
-        _check(1 <= len(blocks) <= MAX_GROUP, f"B200 {name} requires 1 to {MAX_GROUP} matrices; got {len(blocks)}")
+        _check(1 <= len(blocks) <= MAX_GROUP_TASK_ARGS,
+               f"B200 {name} requires 1 to {MAX_GROUP_TASK_ARGS} matrices (a library task carries 20 arguments); got {len(blocks)}; "
+               f"use {name.replace('Grouped', 'Packed')} for up to {MAX_GROUP}")
         _check(y.getSize() >= len(blocks) * batch * rows, f"B200 {name}: y smaller than count x batch x rows")
         for b in blocks:
             _check(b.getSize() >= rows * (cols // 32) * block_bytes, f"B200 {name}: weights too small")
@@ -103,6 +107,29 @@ class B200:
     def q4GemvBytesGrouped(rows, cols, batch, x: FloatArray, y: FloatArray, *blocks: ByteArray, options=None):  # noqa: N802
         """Q4_0 twin of q8GemvBytesGrouped."""
         return B200._grouped("q4GemvBytesGrouped", 18, rows, cols, batch, x, y, blocks, options)
+
+    @staticmethod
+    def _packed(name, block_bytes, count, rows, cols, batch, blocks, x, y, options):
+        B200._check_q(name, rows, cols, batch, x, y)
+        _check(1 <= count <= MAX_GROUP, f"B200 {name} requires 1 to {MAX_GROUP} matrices; got {count}")
+        per = rows * (cols // 32) * block_bytes
+        _check(count == 1 or per % 16 == 0, f"B200 {name} requires matrices of a multiple of 16 bytes; got {per}")
+        _check(blocks.getSize() >= count * per, f"B200 {name}: weights smaller than count x rows x cols/32 x {block_bytes}")
+        _check(y.getSize() >= count * batch * rows, f"B200 {name}: y smaller than count x batch x rows")
+        _check(options is None or options.exact_int, f"B200 {name} computes in integer mode; exact_int must be set")
+        return _desc(name, [count, rows, cols, batch, blocks, x, y], 6, tuning=options or B200Options(exact_int=True))
+
+    @staticmethod
+    def q8GemvBytesPacked(count, rows, cols, batch, blocks: ByteArray, x: FloatArray, y: FloatArray, options=None):  # noqa: N802
+        """The grouped integer-mode mat-vec with its ``count`` (<= 32) equally shaped matrices back to back in ONE
+        ByteArray, matrix m at byte m * rows * cols/32 * 34: seven arguments whatever the count, so that a whole
+        decode step fits the 20-argument library-task interface (TaskGraph.java:886).  y is [count][batch][rows]."""
+        return B200._packed("q8GemvBytesPacked", 34, count, rows, cols, batch, blocks, x, y, options)
+
+    @staticmethod
+    def q4GemvBytesPacked(count, rows, cols, batch, blocks: ByteArray, x: FloatArray, y: FloatArray, options=None):  # noqa: N802
+        """Q4_0 twin of q8GemvBytesPacked (18-byte blocks)."""
+        return B200._packed("q4GemvBytesPacked", 18, count, rows, cols, batch, blocks, x, y, options)
 
     @staticmethod
     def sgemm(m, n, k, alpha, a: FloatArray, b: FloatArray, beta, c: FloatArray):

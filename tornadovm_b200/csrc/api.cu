@@ -20,7 +20,7 @@ int tu_status_peer(int *);
 
 // ---- options ---------------------------------------------------------------------------------
 constexpr int kNumOptions = 8;  // option ids are 1 .. kNumOptions - 1
-static std::atomic<int> g_option[kNumOptions] = {{0}, {0}, {1}, {1}, {1}, {2}, {4}, {0}};
+static std::atomic<int> g_option[kNumOptions] = {{0}, {0}, {1}, {1}, {1}, {2}, {4}, {1}};
 struct ThreadOptions {
     unsigned set_mask = 0;
     int value[kNumOptions] = {};
@@ -32,10 +32,11 @@ static int validate_option(int option, int &value) {
         case TB200_OPT_OVERLAP_LAUNCHES:
         case TB200_OPT_HGEMM_SM_PAIRS:
         case TB200_OPT_MMA_WARP_RINGS:
+        case TB200_OPT_TC_REGISTER_KERNEL:
             value = value != 0;
             return TB200_OK;
         case TB200_OPT_INT_TENSOR_CORE_MIN_BATCH:
-            return value < 2 || value > 17 ? TB200_ERR_INVALID_ARG : TB200_OK;
+            return value < 1 || value > 17 ? TB200_ERR_INVALID_ARG : TB200_OK;
         case TB200_OPT_HGEMM_LINE_STORES:
             return value < 1 ? TB200_ERR_INVALID_ARG : TB200_OK;
         case TB200_OPT_FLOAT_TENSOR_CORES:
@@ -232,20 +233,34 @@ extern "C" const char *tb200_status_string(int status) {
 
 extern "C" int tb200_version(void) { return TB200_VERSION; }
 
-extern "C" int tb200_device_status(int *status_out) {
+extern "C" int tb200_device_status_of(int op_classes, int *status_out) {
     if (!status_out) return TB200_ERR_INVALID_ARG;
-    int (*const readers[])(int *) = {tu_status_api,   tu_status_gemv_f32, tu_status_gemv_quant, tu_status_gemv_mma,
-                                     tu_status_gemv_tc, tu_status_sgemm,    tu_status_hgemm,      tu_status_peer};
+    struct Reader {
+        int (*fn)(int *);
+        int op_class;
+    };
+    const Reader readers[] = {{tu_status_api, TB200_PREPARE_ALL},
+                              {tu_status_gemv_f32, TB200_PREPARE_GEMV_F32},
+                              {tu_status_gemv_quant, TB200_PREPARE_GEMV_QUANT},
+                              {tu_status_gemv_mma, TB200_PREPARE_GEMV_QUANT},
+                              {tu_status_gemv_tc, TB200_PREPARE_GEMV_QUANT},
+                              {tu_status_sgemm, TB200_PREPARE_GEMM_F32},
+                              {tu_status_hgemm, TB200_PREPARE_GEMM_F16},
+                              {tu_status_peer, TB200_PREPARE_PEER}};
+    if (op_classes == 0) op_classes = TB200_PREPARE_ALL;
     int combined = 0;
-    for (auto reader : readers) {
+    for (const Reader &r : readers) {
+        if (r.op_class != TB200_PREPARE_ALL ? !(r.op_class & op_classes) : op_classes != TB200_PREPARE_ALL) continue;
         int v = 0;
-        const int st = reader(&v);  // read and clear, like cudaGetLastError
+        const int st = r.fn(&v);  // read and clear, like cudaGetLastError
         if (st) return st;
         if (v != 0 && combined == 0) combined = v;
     }
     *status_out = combined;
     return TB200_OK;
 }
+
+extern "C" int tb200_device_status(int *status_out) { return tb200_device_status_of(TB200_PREPARE_ALL, status_out); }
 
 extern "C" int tb200_prepare(int op_classes) {
     int st;

@@ -27,41 +27,6 @@ constexpr int MM_WARPS = 8 /* 16-row units per round */, MM_KSPLIT = 2 /* warps 
 constexpr int MM_THREADS = MM_WARPS * MM_KSPLIT * 32, MM_KB = 8 /* blocks per chunk */;
 constexpr int MM_STAGES = 4;
 
-__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                             uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
-}
-
-__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                              uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// Four bytes 0..255 -> two half2 registers holding (byte - bias): the byte is spliced into the mantissa of
-// fp16 1024.0 (exponent bits 0x64), which makes 1024 + byte exactly, and the bias is removed with one HSUB2.
-__device__ __forceinline__ void u8x4_to_h2x2(uint32_t u, uint32_t bias_h2, uint32_t &lo, uint32_t &hi) {
-    const uint32_t l = __byte_perm(u, 0x64646464u, 0x4140);  // bytes 0,1
-    const uint32_t h = __byte_perm(u, 0x64646464u, 0x4342);  // bytes 2,3
-    __half2 lv = __hsub2(*reinterpret_cast<const __half2 *>(&l), *reinterpret_cast<const __half2 *>(&bias_h2));
-    __half2 hv = __hsub2(*reinterpret_cast<const __half2 *>(&h), *reinterpret_cast<const __half2 *>(&bias_h2));
-    lo = *reinterpret_cast<uint32_t *>(&lv);
-    hi = *reinterpret_cast<uint32_t *>(&hv);
-}
-
-// 32-bit read at a byte offset that is 0 or 2 modulo 4
-template <int MISALIGNED>
-__device__ __forceinline__ uint32_t lds_u32_at(const unsigned char *base, int off) {
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(base + (off & ~3));
-    if (MISALIGNED) return __funnelshift_r(w[0], w[1], 16);
-    return w[0];
-}
-
 template <int FMT>
 struct MmaTraits {
     static constexpr int BB = FMT == FMT_Q4B ? 18 : (FMT == FMT_Q8B ? 34 : 32);  // weight bytes per block in the row chunk

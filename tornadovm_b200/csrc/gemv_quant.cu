@@ -212,12 +212,8 @@ __device__ __forceinline__ void stage_x_blocks(unsigned char *xq_smem, float *xs
                 m = fmaxf(m, __shfl_xor_sync(mask, m, 4));
                 scale = (m == 0.0f) ? 1.0f : __fdiv_rn(m, 127.0f);
                 const float inv = __fdiv_rn(1.0f, scale);
-                const int q0 = (int)floorf(__fadd_rn(__fmul_rn(v[t].x, inv), 0.5f));
-                const int q1 = (int)floorf(__fadd_rn(__fmul_rn(v[t].y, inv), 0.5f));
-                const int q2 = (int)floorf(__fadd_rn(__fmul_rn(v[t].z, inv), 0.5f));
-                const int q3 = (int)floorf(__fadd_rn(__fmul_rn(v[t].w, inv), 0.5f));
-                packed = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
-                         ((uint32_t)(q3 & 0xFF) << 24);
+                packed = quantize_byte(v[t].x, inv) | (quantize_byte(v[t].y, inv) << 8) | (quantize_byte(v[t].z, inv) << 16) |
+                         (quantize_byte(v[t].w, inv) << 24);
             }
             *reinterpret_cast<uint32_t *>(xq_smem + ((size_t)b * slots_per_vec + permuted_slot<CPL, 16>(col)) * 16 + (col & 15)) = packed;
             if (WANT_SUM) {
@@ -790,8 +786,7 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float *__restrict
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         const float scale = (m == 0.0f) ? 1.0f : __fdiv_rn(m, 127.0f);
         const float inv = __fdiv_rn(1.0f, scale);
-        const float r = floorf(__fadd_rn(__fmul_rn(v, inv), 0.5f));
-        xq[(size_t)blk * 32 + lane] = (int8_t)(int)r;
+        xq[(size_t)blk * 32 + lane] = (int8_t)quantize_byte(v, inv);
         if (lane == 0) xs[blk] = scale;
     }
 }
@@ -1040,6 +1035,35 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     if (aligned_to(a.w, 16)) {
         if (FMT == FMT_Q8S) path = PATH_Q8S_DIRECT;
         else if (a.cols % 256 == 0) path = PATH_RING;
+    }
+    // Tensor-core kernel with the activations in registers (gemv_tc.cu): integer mode from
+    // TB200_OPT_INT_TENSOR_CORE_MIN_BATCH vectors on, float mode from the measured batch on, and every batch
+    // when the weights are only 8-byte aligned (an array behind a 24-byte header), where the alternative is
+    // the byte-load kernel.
+    const bool overlap = option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0;
+    if (option_value(TB200_OPT_TC_REGISTER_KERNEL)) {
+        const bool only8 = !aligned_to(a.w, 16) || (FMT == FMT_Q8S && a.scales && !aligned_to(a.scales, 16));
+        if (MODE == MODE_FLOAT) {
+            const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 from the measured batch on, 2 always
+            const int min_batch = float_tc >= 2 || only8 ? 1 : (FMT == FMT_Q8S ? 1 : 2);
+            QGemvArgs p = a;
+            p.batch = a.batch < 8 ? a.batch : 8;
+            if ((float_tc || only8) && a.batch >= min_batch && qtc_eligible(FMT, MODE_FLOAT, p, di)) {
+                // at most eight vectors (sixteen fp16 columns) per pass over the weights
+                const int passes = (a.batch + 7) / 8, each = (a.batch + passes - 1) / passes;
+                for (int b0 = 0; b0 < a.batch; b0 += each) {
+                    p.batch = a.batch - b0 < each ? a.batch - b0 : each;
+                    p.x = a.x + (size_t)b0 * a.cols, p.y = a.y + (size_t)b0 * a.rows;
+                    st = qtc_dispatch(FMT, MODE_FLOAT, p, di, s, overlap && b0 == 0);
+                    if (st) return st;
+                }
+                return TB200_OK;
+            }
+        } else if (a.batch >= (only8 ? 1 : option_value(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH)) && (!DOTS || a.batch == 1) &&
+                   qtc_eligible(FMT, MODE, a, di)) {
+            // MODE_INT follows the quantiser kernel in plain stream order; the fused form may overlap its predecessor
+            return qtc_dispatch(FMT, MODE, a, di, s, MODE == MODE_INT_FUSED && overlap);
+        }
     }
     const int per = path == PATH_GENERIC
                         ? 0

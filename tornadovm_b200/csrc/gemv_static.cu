@@ -37,13 +37,21 @@ static int static_scratch(const DeviceInfo *di, void **out) {
 
 using namespace tb200;
 
-// Test hook: the address the entry point below will hand to its kernels in the current context.
-extern "C" int tb200_static_scratch_address(void **out) {
-    if (!out) return TB200_ERR_INVALID_ARG;
+// Test hook: the address the entry point below will hand to its kernels in the current context
+// (`in_use`) and what the runtime reports for the array in this context right now (`fresh`).
+extern "C" int tb200_static_scratch_address(void **in_use, void **fresh) {
+    if (!in_use || !fresh) return TB200_ERR_INVALID_ARG;
     int st;
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
-    return static_scratch(di, out);
+    st = static_scratch(di, in_use);
+    if (st) return st;
+    cudaError_t e = cudaGetSymbolAddress(fresh, g_static_qx_scratch);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return (int)e;
+    }
+    return TB200_OK;
 }
 
 extern "C" int tb200_q8_gemv_i8_static(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales,

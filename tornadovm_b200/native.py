@@ -20,6 +20,7 @@ SIGNATURES = {
     "tb200_status_string": (C.c_char_p, [_I]),
     "tb200_version": (_I, []),
     "tb200_device_status": (_I, [C.POINTER(_I)]),
+    "tb200_device_status_of": (_I, [_I, C.POINTER(_I)]),
     "tb200_prepare": (_I, [_I]),
     "tb200_set_option": (_I, [_I, _I]),
     "tb200_get_option": (_I, [_I, C.POINTER(_I)]),
@@ -35,7 +36,7 @@ SIGNATURES = {
     "tb200_quantize_x": (_I, [_I, _I, _P, _P, _Z, _P]),
     "tb200_q8_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "tb200_q8_gemv_i8_static": (_I, [_I, _I, _I, _P, _P, _P, _P, _P]),
-    "tb200_static_scratch_address": (_I, [C.POINTER(_P)]),
+    "tb200_static_scratch_address": (_I, [C.POINTER(_P), C.POINTER(_P)]),
     "tb200_q8b_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_q4b_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_q8b_gemv_i8_grouped": (_I, [_I, _I, _I, _I, _P, _P, _P, _I, C.c_longlong, _P, _I, _I, _P, _Z, _P]),
@@ -52,6 +53,7 @@ SIGNATURES = {
     "tb200_q8_blockdots_i32": (_I, [_I, _I, _P, _P, _P, _P]),
     "tb200_q8b_blockdots_i32": (_I, [_I, _I, _P, _P, _P, _P]),
     "tb200_q4b_blockdots_i32": (_I, [_I, _I, _P, _P, _P, _P]),
+    "tb200_blockdots_i32_batched": (_I, [_I, _I, _I, _I, _P, _P, _P, _P]),
     "tb200_sgemm": (_I, [_I, _I, _I, _F, _P, _P, _F, _P, _P]),
     "tb200_hgemm_f32": (_I, [_I, _I, _I, _P, _P, _P, _P]),
     "tb200_hgemm_f32_scatter": (_I, [_I, _I, _I, _P, _P, _P, _I, C.c_longlong, C.c_longlong, _P]),
@@ -99,7 +101,8 @@ class B200Native:
         cls.check_status(getattr(cls.load(), function)(*args), function)
 
     @classmethod
-    def device_status(cls) -> int:
+    def device_status(cls, op_classes: int = 0) -> int:
+        """Read-and-clear the device status of the kernels of ``op_classes`` (tb200_prepare_class bits; 0 = all)."""
         v = C.c_int(0)
-        cls.check_status(cls.load().tb200_device_status(C.byref(v)), "tb200_device_status")
+        cls.check_status(cls.load().tb200_device_status_of(op_classes, C.byref(v)), "tb200_device_status_of")
         return v.value

@@ -20,7 +20,7 @@ import ctypes as C
 import torch
 import torch.distributed as dist
 
-from .native import B200Native
+from .native import B200Native, TornadoB200Error
 from .sharding import shard_range
 
 FLAG_WORDS = 8  # flag array of one rank: one word per peer
@@ -180,14 +180,26 @@ class ShardedGroupedGemv:
             st = self.lib.tb200_peer_wait(self.rank, self.world, self._flag_ptrs, self._sync, self.timeout_ms, C.c_void_p(self.stream.cuda_stream))
             B200Native.check_status(st, "tb200_peer_wait")
 
-    def run(self, x_host: torch.Tensor) -> torch.Tensor:
+    def check(self) -> None:
+        """Raise if a bounded device-side wait of this GPU has expired since the last check: a rank that did not
+        arrive in time leaves stale or missing outputs, which must not pass for results.  Synchronises the
+        device; ``run()`` calls it after every step, ``launch()`` / ``wait()`` users call it where they consume."""
+        status = B200Native.device_status(2 | 16)  # the mat-vec kernels and the hand-shake kernels
+        if status != 0:
+            raise TornadoB200Error(f"{self.fn_name} (step {self.steps})", status, B200Native.status_string(status))
+
+    def run(self, x_host: torch.Tensor, download: bool = True) -> torch.Tensor:
+        """One step end to end.  ``download=False`` leaves the gathered result on the device (returned as the
+        device tensor): a rank whose consumer reads it there need not copy it to the host."""
         with torch.cuda.stream(self.stream):
             self.x_dev.copy_(x_host, non_blocking=True)
             y = self.launch()
             self.wait()
-            self.y_host.copy_(y, non_blocking=True)
+            if download:
+                self.y_host.copy_(y, non_blocking=True)
         self.stream.synchronize()
-        return self.y_host
+        self.check()
+        return self.y_host if download else y
 
     def close(self) -> None:
         self.stream.synchronize()

@@ -70,6 +70,7 @@ class B200Context:
 
 _QUANT_FUNCTIONS = {"q8Gemv", "q8GemvBytes", "q4GemvBytes"}
 _GROUPED_FUNCTIONS = {"q8GemvBytesGrouped": "tb200_q8b_gemv_i8_grouped", "q4GemvBytesGrouped": "tb200_q4b_gemv_i8_grouped"}
+_PACKED_FUNCTIONS = {"q8GemvBytesPacked": ("tb200_q8b_gemv_i8_grouped", 34), "q4GemvBytesPacked": ("tb200_q4b_gemv_i8_grouped", 18)}
 
 
 class B200LibraryProvider:
@@ -84,16 +85,26 @@ class B200LibraryProvider:
         B200Native.load()
         return B200Context(device.getNativeStream(executionPlanId))
 
+    # operation classes of tb200_prepare (include/tornado_b200.h)
+    _PREPARE_CLASS = {"sgemv": 1, "q8Gemv": 2, "q8GemvBytes": 2, "q4GemvBytes": 2, "q8GemvBytesGrouped": 2,
+                      "q4GemvBytesGrouped": 2, "q8GemvBytesPacked": 2, "q4GemvBytesPacked": 2, "sgemm": 4, "hgemmF32": 8}
+
     def prepare(self, descriptor, context: B200Context) -> None:
+        """Runs in the pre-launch pass, before any capture (TornadoVMInterpreter.java:1036-1055) and possibly
+        several times: loads and configures every kernel the task may launch in the plan's CUDA context, so that
+        dispatch issues nothing but kernel launches, and sizes the workspace.  Tuning is NOT applied here: it is
+        set around each dispatch and reset after it (cf. CuBlasLibraryProvider.java:124-151)."""
         fn = descriptor.getFunctionName()
         tuning = descriptor.getTuning()
-        if isinstance(tuning, B200Options) and tuning.overlap_launches:
-            B200Native.call("tb200_set_option", 1, 1)  # TB200_OPT_OVERLAP_LAUNCHES
+        B200Native.call("tb200_prepare", self._PREPARE_CLASS.get(fn, 0))
         if fn in _QUANT_FUNCTIONS and isinstance(tuning, B200Options) and tuning.exact_int:
             p = descriptor.getParameters()
             need = B200Native.load().tb200_qx_workspace_bytes(int(p[1]), int(p[2]))
             context.grow_workspace(int(need))
-        if fn in _GROUPED_FUNCTIONS:  # (count, rows, cols, batch, x, y, blocks...)
+        if fn in _PACKED_FUNCTIONS:  # (count, rows, cols, batch, blocks, x, y)
+            p = descriptor.getParameters()
+            context.grow_workspace(int(B200Native.load().tb200_qx_workspace_bytes(int(p[2]), int(p[3]))))
+        if fn in _GROUPED_FUNCTIONS:  # (count, rows, cols, batch, x, y, blocks...); integer mode whatever the tuning says
             p = descriptor.getParameters()
             context.grow_workspace(int(B200Native.load().tb200_qx_workspace_bytes(int(p[2]), int(p[3]))))
 
@@ -102,6 +113,19 @@ class B200LibraryProvider:
         lib = B200Native.load()
         tuning = inv.getTuning()
         exact = isinstance(tuning, B200Options) and tuning.exact_int
+        # the task's tuning holds for this call on this thread only
+        scoped = isinstance(tuning, B200Options) and tuning.overlap_launches
+        if scoped:
+            B200Native.call("tb200_set_thread_option", 1, 1)  # TB200_OPT_OVERLAP_LAUNCHES
+        try:
+            st = self._dispatch(lib, functionName, inv, ctx, exact)
+        finally:
+            if scoped:
+                lib.tb200_clear_thread_options()
+        B200Native.check_status(st, functionName)
+
+    @staticmethod
+    def _dispatch(lib, functionName, inv, ctx, exact) -> int:  # noqa: N803
         P = inv.getDevicePointer
         A = inv.getArg
         ws = (ctx.workspace_ptr, ctx.workspace_bytes)
@@ -128,13 +152,19 @@ class B200LibraryProvider:
             dst = (C.c_void_p * 1)(P(5))
             st = getattr(lib, _GROUPED_FUNCTIONS[functionName])(count, A(1), A(2), A(3), blocks, P(4), dst, 1, 0, None, A(1), 0, *ws,
                                                                 ctx.stream)
+        elif functionName in _PACKED_FUNCTIONS:  # (count, rows, cols, batch, blocks, x, y)
+            native, block_bytes = _PACKED_FUNCTIONS[functionName]
+            count, per = A(0), A(1) * (A(2) // 32) * block_bytes
+            blocks = (C.c_void_p * count)(*[P(4) + m * per for m in range(count)])
+            dst = (C.c_void_p * 1)(P(6))
+            st = getattr(lib, native)(count, A(1), A(2), A(3), blocks, P(5), dst, 1, 0, None, A(1), 0, *ws, ctx.stream)
         elif functionName == "sgemm":  # (m, n, k, alpha, a, b, beta, c)
             st = lib.tb200_sgemm(A(0), A(1), A(2), A(3), P(4), P(5), A(6), P(7), ctx.stream)
         elif functionName == "hgemmF32":  # (m, n, k, a, b, c)
             st = lib.tb200_hgemm_f32(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
         else:
             raise RuntimeError(f"[ERROR] B200 function not supported: {functionName}")
-        B200Native.check_status(st, functionName)
+        return st
 
     def destroyContext(self, context: B200Context) -> None:  # noqa: N802
         if context.workspace_ptr:

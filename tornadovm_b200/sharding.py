@@ -170,8 +170,8 @@ class ShardedHgemm:
     def __init__(self, m: int, n: int, k: int, a: torch.Tensor, b_local: torch.Tensor, group=None, fused: bool = False,
                  timeout_ms: int = 2000, layout: str = "auto"):
         # fused result: row-major [m][n] ("assembled"), or [world][m][per] like the all-gather ("blocks"); "auto" takes
-        # the assembled matrix on one or two GPUs and blocks beyond, where rows 4*n bytes apart in seven peer
-        # mappings made the stores far slower than rows 4*per bytes apart (8192^3 on 8 GPUs: 2.63 ms against 0.45 ms)
+        # the assembled matrix on one or two GPUs and blocks beyond: with rows 4*n bytes apart in many peer mappings
+        # the stores are far slower than with rows 4*per bytes apart
         assert layout in ("auto", "assembled", "blocks")
         world_now = dist.get_world_size(group) if dist.is_initialized() else 1
         self.layout = layout if layout != "auto" else ("assembled" if world_now <= 2 else "blocks")
@@ -229,9 +229,15 @@ class ShardedHgemm:
         self.steps += 1
         return self.halves[half]
 
+    def check(self) -> None:
+        """Raise if a bounded device-side wait has expired since the last check (synchronises the device)."""
+        status = B200Native.device_status(8 | 16)  # the FP16 GEMM and the hand-shake kernels
+        if status != 0:
+            from .native import TornadoB200Error
+            raise TornadoB200Error(f"tb200_hgemm_f32_scatter (step {self.steps})", status, B200Native.status_string(status))
+
     def launch_best(self) -> torch.Tensor:
-        """The fused epilogue when the object was built for it (faster than the NCCL gather at 2 and at 8 GPUs:
-        8192^3 0.48 against 0.73 ms, and 0.45 against 0.54 ms), else the NCCL gather.  Returns the result in the
+        """The fused epilogue when the object was built for it, else the NCCL gather.  Returns the result in the
         object's layout: ``[m][n]`` ("assembled") or ``[world][m][per]`` ("blocks")."""
         if self.slab is not None:
             return self.launch_fused()

@@ -72,7 +72,10 @@ class TaskGraph:
         return self
 
     def libraryTask(self, task_id: str, factory, *args):  # noqa: N802
-        # the factory runs immediately and its descriptor is what the runtime keeps (TaskGraph.java:737-739)
+        # the factory runs immediately and its descriptor is what the runtime keeps (TaskGraph.java:737-739);
+        # the reference has overloads for 1 to 20 arguments and no varargs form (TaskGraph.java:737-893)
+        if not 1 <= len(args) <= 20:
+            raise TypeError(f"libraryTask takes 1 to 20 task arguments, got {len(args)}")
         self.tasks.append(_LibraryTask(task_id, factory(*args)))
         return self
 
@@ -201,7 +204,8 @@ class TornadoExecutionPlan:
                 h2d = self._h2d_bytes
             if self._use_graph:
                 if self._cuda_graph is None:
-                    self._launch_all()  # warm run: module load and attribute calls happen outside capture
+                    # as in the reference (TornadoVMInterpreter.java:462-476), the FIRST dispatch of every task
+                    # already happens inside the capture: everything capture-unsafe was done by prepare()
                     self.stream.synchronize()
                     self._cuda_graph = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(self._cuda_graph, stream=self.stream):
