@@ -119,7 +119,7 @@ enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2
  * tensor-core mat-vec kernels.
  * TB200_OPT_HGEMM_LINE_STORES (default 2): the FP16 GEMM's epilogue transposes its tiles through shared memory
  * and stores whole 128-byte lines when a tile goes to at least `value` destinations (1 = always).
- * TB200_OPT_INT_TENSOR_CORE_MIN_BATCH (default 4, 1..17): the integer-mode mat-vecs take the tensor-core kernel from
+ * TB200_OPT_INT_TENSOR_CORE_MIN_BATCH (default 2, 1..17): the integer-mode mat-vecs take the tensor-core kernel from
  * this many activation vectors on (17 = never); smaller batches stay on the dp4a kernels.  With 1 the block-dot
  * test entries (tb200_*_blockdots_i32) run on the tensor-core kernel as well.
  * TB200_OPT_TC_REGISTER_KERNEL (default 1): the tensor-core mat-vecs use the kernel that keeps the activations
@@ -344,6 +344,32 @@ int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, f
  * (see above).  No counterpart in the reference. */
 int tb200_hgemm_f32_scatter(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *const *dst, int ndst,
                             long long ld, long long col_offset, tb200_stream_t stream);
+
+/* ---- FP16 / BF16 GEMM with fused epilogue, output type and batches -----------
+ *   D[b] = act(alpha * A[b] * B[b] + beta * C[b] + bias),  b = 0 .. batch_count - 1
+ * A[m][k], B[k][n] row-major fp16 or bf16 bit patterns (in_type), fp32 accumulation on tcgen05 tensor cores;
+ * D, C [m][n] and bias [n] (added to every row) have the element type out_type; the matrices of a batch lie
+ * back to back (strides m*k, k*n, m*n).  c == NULL with beta != 0 means C = D (in place); bias may be NULL;
+ * bias needs batch_count == 1.  Replaces, with row-major operands of any 8-element-aligned shape:
+ *   Cutlass.cutlassHgemm / cutlassBgemm (alpha, beta, fp16 / bf16 out; tornado-cutlass.cu:201-259),
+ *   cutlassGemmBias{Relu,Gelu,Silu,Sigmoid,Tanh,HardSwish} (act(A*B + bias); tornado-cutlass.cu:101-140, :279-396),
+ *   cutlassHgemmBatched (tornado-cutlass.cu:411-433), CuBlas.cublasGemmExFP16 / BF16 / FP16FP32
+ *   (tornado-cublas/.../CuBlas.java:237-305).
+ * Tensor-core shapes: k % 8 == 0, n % 8 == 0, 16-byte aligned A and B; other cases return
+ * TB200_ERR_UNSUPPORTED unless the call is a plain fp16 -> fp32 product. */
+enum tb200_gemm_in { TB200_IN_F16 = 0, TB200_IN_BF16 = 1 };
+enum tb200_gemm_out { TB200_OUT_F32 = 0, TB200_OUT_F16 = 1, TB200_OUT_BF16 = 2 };
+enum tb200_activation {
+    TB200_ACT_NONE = 0,
+    TB200_ACT_RELU = 1,
+    TB200_ACT_GELU = 2,      /* 0.5 x (1 + erf(x / sqrt 2)) */
+    TB200_ACT_SILU = 3,      /* x / (1 + exp(-x)) */
+    TB200_ACT_SIGMOID = 4,
+    TB200_ACT_TANH = 5,
+    TB200_ACT_HARDSWISH = 6  /* x * min(max(x + 3, 0), 6) / 6 */
+};
+int tb200_gemm_ex(int m, int n, int k, int in_type, const void *a, const void *b, int out_type, void *d, float alpha, float beta,
+                  const void *c, const void *bias, int activation, int batch_count, tb200_stream_t stream);
 
 #ifdef __cplusplus
 }

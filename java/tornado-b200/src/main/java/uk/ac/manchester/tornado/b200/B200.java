@@ -5,6 +5,7 @@ import java.util.Arrays;
 import uk.ac.manchester.tornado.api.common.Access;
 import uk.ac.manchester.tornado.api.common.LibraryTaskDescriptor;
 import uk.ac.manchester.tornado.api.exceptions.TornadoRuntimeException;
+import uk.ac.manchester.tornado.api.types.arrays.BFloat16Array;
 import uk.ac.manchester.tornado.api.types.arrays.ByteArray;
 import uk.ac.manchester.tornado.api.types.arrays.FloatArray;
 import uk.ac.manchester.tornado.api.types.arrays.HalfFloatArray;
@@ -72,8 +73,10 @@ public final class B200 {
     }
 
     /**
-     * Integer-mode Q8_0 mat-vec of up to 32 equally shaped block matrices that read the same activations, in one launch:
-     * {@code y[matrix][batch][rows]}. Parameter list: (count, rows, cols, batch, x, y, blocks...).
+     * Integer-mode Q8_0 mat-vec of up to 14 equally shaped block matrices that read the same activations, in one launch:
+     * {@code y[matrix][batch][rows]}. Parameter list: (count, rows, cols, batch, x, y, blocks...). A library task carries at
+     * most 20 arguments (TaskGraph.java:886): rows, cols, batch, x, y, options and 14 matrices; {@link #q8GemvBytesPacked}
+     * carries up to 32 in one array.
      */
     public static LibraryTaskDescriptor q8GemvBytesGrouped(int rows, int cols, int batch, FloatArray x, FloatArray y, B200Options options, ByteArray... blocks) {
         return grouped("q8GemvBytesGrouped", 34, rows, cols, batch, x, y, options, blocks);
@@ -86,7 +89,7 @@ public final class B200 {
 
     private static LibraryTaskDescriptor grouped(String name, int blockBytes, int rows, int cols, int batch, FloatArray x, FloatArray y, B200Options options, ByteArray[] blocks) {
         checkQuantised(name, rows, cols, batch, x, y);
-        check(blocks.length >= 1 && blocks.length <= 32, "B200 " + name + " requires 1 to 32 matrices; got " + blocks.length);
+        check(blocks.length >= 1 && blocks.length <= 14, "B200 " + name + " requires 1 to 14 matrices (a library task carries 20 arguments); got " + blocks.length);
         check(y.getSize() >= (long) blocks.length * batch * rows, "B200 " + name + ": y smaller than count x batch x rows");
         for (ByteArray b : blocks) {
             check(b.getSize() >= (long) rows * (cols / 32) * blockBytes, "B200 " + name + ": weights too small");
@@ -101,6 +104,88 @@ public final class B200 {
         params[5] = y;
         System.arraycopy(blocks, 0, params, 6, blocks.length);
         return descriptor(name, params, 5, false, options != null ? options : new B200Options().exactInt(true));
+    }
+
+    /**
+     * The grouped integer-mode mat-vec with its {@code count} (at most 32) equally shaped matrices back to back in one
+     * ByteArray, matrix m at byte {@code m * rows * cols/32 * 34}: seven arguments whatever the count.
+     */
+    public static LibraryTaskDescriptor q8GemvBytesPacked(int count, int rows, int cols, int batch, ByteArray blocks, FloatArray x, FloatArray y, B200Options options) {
+        return packed("q8GemvBytesPacked", 34, count, rows, cols, batch, blocks, x, y, options);
+    }
+
+    /** Q4_0 twin of {@link #q8GemvBytesPacked} (18-byte blocks). */
+    public static LibraryTaskDescriptor q4GemvBytesPacked(int count, int rows, int cols, int batch, ByteArray blocks, FloatArray x, FloatArray y, B200Options options) {
+        return packed("q4GemvBytesPacked", 18, count, rows, cols, batch, blocks, x, y, options);
+    }
+
+    private static LibraryTaskDescriptor packed(String name, int blockBytes, int count, int rows, int cols, int batch, ByteArray blocks, FloatArray x, FloatArray y,
+            B200Options options) {
+        checkQuantised(name, rows, cols, batch, x, y);
+        check(count >= 1 && count <= 32, "B200 " + name + " requires 1 to 32 matrices; got " + count);
+        long per = (long) rows * (cols / 32) * blockBytes;
+        check(count == 1 || per % 16 == 0, "B200 " + name + " requires matrices of a multiple of 16 bytes; got " + per);
+        check(blocks.getSize() >= count * per && y.getSize() >= (long) count * batch * rows, "B200 " + name + ": weights or y too small");
+        check(options == null || options.exactInt, "B200 " + name + " computes in integer mode; exactInt must be set");
+        return descriptor(name, new Object[] { count, rows, cols, batch, blocks, x, y }, 6, false, options != null ? options : new B200Options().exactInt(true));
+    }
+
+    private static void checkTensorCore(String name, int m, int n, int k) {
+        check(m >= 0 && n >= 0 && k >= 0, "B200 " + name + " requires non-negative sizes; got m=" + m + ", n=" + n + ", k=" + k);
+        check(k % 8 == 0 && n % 8 == 0, "B200 " + name + " requires k and n to be multiples of 8; got k=" + k + ", n=" + n);
+    }
+
+    /** {@code D(fp16) = alpha*A*B + beta*D}, fp32 accumulation; signature of {@code Cutlass.cutlassHgemm}. */
+    public static LibraryTaskDescriptor hgemm(int m, int n, int k, float alpha, HalfFloatArray a, HalfFloatArray b, float beta, HalfFloatArray d) {
+        checkTensorCore("hgemm", m, n, k);
+        check(a.getSize() >= (long) m * k && b.getSize() >= (long) k * n && d.getSize() >= (long) m * n, "B200 hgemm: array too small");
+        return descriptor("hgemm", new Object[] { m, n, k, alpha, a, b, beta, d }, 7, beta != 0.0f, null);
+    }
+
+    /** bfloat16 twin of {@link #hgemm}; signature of {@code Cutlass.cutlassBgemm}. */
+    public static LibraryTaskDescriptor bgemm(int m, int n, int k, float alpha, BFloat16Array a, BFloat16Array b, float beta, BFloat16Array d) {
+        checkTensorCore("bgemm", m, n, k);
+        check(a.getSize() >= (long) m * k && b.getSize() >= (long) k * n && d.getSize() >= (long) m * n, "B200 bgemm: array too small");
+        return descriptor("bgemm", new Object[] { m, n, k, alpha, a, b, beta, d }, 7, beta != 0.0f, null);
+    }
+
+    /** {@code D = act(A*B + bias)}, bias broadcast over the rows; act is Relu, Gelu, Silu, Sigmoid, Tanh or HardSwish. */
+    public static LibraryTaskDescriptor gemmBias(String act, int m, int n, int k, HalfFloatArray a, HalfFloatArray b, HalfFloatArray bias, HalfFloatArray d) {
+        checkTensorCore("gemmBias" + act, m, n, k);
+        check(a.getSize() >= (long) m * k && b.getSize() >= (long) k * n && bias.getSize() >= n && d.getSize() >= (long) m * n, "B200 gemmBias" + act + ": array too small");
+        return descriptor("gemmBias" + act, new Object[] { m, n, k, a, b, bias, d }, 6, false, null);
+    }
+
+    public static LibraryTaskDescriptor gemmBiasRelu(int m, int n, int k, HalfFloatArray a, HalfFloatArray b, HalfFloatArray bias, HalfFloatArray d) {
+        return gemmBias("Relu", m, n, k, a, b, bias, d);
+    }
+
+    public static LibraryTaskDescriptor gemmBiasGelu(int m, int n, int k, HalfFloatArray a, HalfFloatArray b, HalfFloatArray bias, HalfFloatArray d) {
+        return gemmBias("Gelu", m, n, k, a, b, bias, d);
+    }
+
+    public static LibraryTaskDescriptor gemmBiasSilu(int m, int n, int k, HalfFloatArray a, HalfFloatArray b, HalfFloatArray bias, HalfFloatArray d) {
+        return gemmBias("Silu", m, n, k, a, b, bias, d);
+    }
+
+    public static LibraryTaskDescriptor gemmBiasSigmoid(int m, int n, int k, HalfFloatArray a, HalfFloatArray b, HalfFloatArray bias, HalfFloatArray d) {
+        return gemmBias("Sigmoid", m, n, k, a, b, bias, d);
+    }
+
+    public static LibraryTaskDescriptor gemmBiasTanh(int m, int n, int k, HalfFloatArray a, HalfFloatArray b, HalfFloatArray bias, HalfFloatArray d) {
+        return gemmBias("Tanh", m, n, k, a, b, bias, d);
+    }
+
+    public static LibraryTaskDescriptor gemmBiasHardSwish(int m, int n, int k, HalfFloatArray a, HalfFloatArray b, HalfFloatArray bias, HalfFloatArray d) {
+        return gemmBias("HardSwish", m, n, k, a, b, bias, d);
+    }
+
+    /** {@code batchCount} independent fp16 GEMMs packed back to back; signature of {@code Cutlass.cutlassHgemmBatched}. */
+    public static LibraryTaskDescriptor hgemmBatched(int m, int n, int k, float alpha, HalfFloatArray a, HalfFloatArray b, float beta, HalfFloatArray d, int batchCount) {
+        checkTensorCore("hgemmBatched", m, n, k);
+        check(batchCount >= 1, "B200 hgemmBatched requires batchCount >= 1; got " + batchCount);
+        check(a.getSize() >= (long) batchCount * m * k && b.getSize() >= (long) batchCount * k * n && d.getSize() >= (long) batchCount * m * n, "B200 hgemmBatched: array too small");
+        return descriptor("hgemmBatched", new Object[] { m, n, k, alpha, a, b, beta, d, batchCount }, 7, beta != 0.0f, null);
     }
 
     /** {@code C = alpha*A*B + beta*C}, row-major FP32 on CUDA cores. */

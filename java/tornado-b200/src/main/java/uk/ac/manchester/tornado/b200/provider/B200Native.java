@@ -22,6 +22,11 @@ import uk.ac.manchester.tornado.api.exceptions.TornadoRuntimeException;
 public final class B200Native {
 
     public static final int OPT_OVERLAP_LAUNCHES = 1;
+    /** Operation classes of tb200_prepare. */
+    public static final int PREPARE_GEMV_F32 = 1;
+    public static final int PREPARE_GEMV_QUANT = 2;
+    public static final int PREPARE_GEMM_F32 = 4;
+    public static final int PREPARE_GEMM_F16 = 8;
 
     private static final Linker LINKER = Linker.nativeLinker();
     private static SymbolLookup lib;
@@ -41,6 +46,10 @@ public final class B200Native {
     private static MethodHandle deviceFree;
     private static MethodHandle statusString;
     private static MethodHandle setOption;
+    private static MethodHandle setThreadOption;
+    private static MethodHandle clearThreadOptions;
+    private static MethodHandle prepare;
+    private static MethodHandle gemmEx;
 
     private B200Native() {
     }
@@ -79,6 +88,12 @@ public final class B200Native {
         deviceFree = handle("tb200_device_free", FunctionDescriptor.of(JAVA_INT, JAVA_LONG));
         statusString = handle("tb200_status_string", FunctionDescriptor.of(ADDRESS, JAVA_INT));
         setOption = handle("tb200_set_option", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT));
+        setThreadOption = handle("tb200_set_thread_option", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT));
+        clearThreadOptions = handle("tb200_clear_thread_options", FunctionDescriptor.of(JAVA_INT));
+        prepare = handle("tb200_prepare", FunctionDescriptor.of(JAVA_INT, JAVA_INT));
+        // int tb200_gemm_ex(m, n, k, in_type, a, b, out_type, d, alpha, beta, c, bias, activation, batch_count, stream)
+        gemmEx = handle("tb200_gemm_ex", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_INT, JAVA_LONG, JAVA_FLOAT,
+                JAVA_FLOAT, JAVA_LONG, JAVA_LONG, JAVA_INT, JAVA_INT, JAVA_LONG));
     }
 
     private static RuntimeException wrap(Throwable t) {
@@ -189,6 +204,42 @@ public final class B200Native {
             checkStatus((int) setOption.invokeExact(option, value), "tb200_set_option");
         } catch (TornadoRuntimeException e) {
             throw e;
+        } catch (Throwable t) {
+            throw wrap(t);
+        }
+    }
+
+    /** Overrides an option for the calls this thread makes until {@link #clearThreadOptions()}. */
+    public static int setThreadOption(int option, int value) {
+        try {
+            return (int) setThreadOption.invokeExact(option, value);
+        } catch (Throwable t) {
+            throw wrap(t);
+        }
+    }
+
+    public static void clearThreadOptions() {
+        try {
+            int ignored = (int) clearThreadOptions.invokeExact();
+        } catch (Throwable t) {
+            throw wrap(t);
+        }
+    }
+
+    /** Makes the kernels of the given operation classes resident in the CUDA context that is current. */
+    public static int prepare(int opClasses) {
+        try {
+            return (int) prepare.invokeExact(opClasses);
+        } catch (Throwable t) {
+            throw wrap(t);
+        }
+    }
+
+    /** D = act(alpha*A*B + beta*C + bias); inType 0 fp16, 1 bf16; outType 0 fp32, 1 fp16, 2 bf16; c, bias may be 0. */
+    public static int gemmEx(int m, int n, int k, int inType, long a, long b, int outType, long d, float alpha, float beta, long c, long bias, int activation,
+            int batchCount, long stream) {
+        try {
+            return (int) gemmEx.invokeExact(m, n, k, inType, a, b, outType, d, alpha, beta, c, bias, activation, batchCount, stream);
         } catch (Throwable t) {
             throw wrap(t);
         }

@@ -321,3 +321,51 @@ def make_q4(rows, cols, batch=1, seed=42):
     scales = f32_to_f16(g)
     x = r.gaussian_f32(batch * cols)
     return q4_pack_blocks(nib, scales), scales, x
+
+
+# -- fused GEMM epilogues (restated from the reference's own test oracles) ------------
+def bf16_to_f32(h: np.ndarray) -> np.ndarray:
+    """bfloat16 bit patterns -> float32 (BFloat16Array keeps the upper 16 bits of a float)."""
+    return (np.asarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns, round to nearest even."""
+    u = np.asarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    r = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return r.astype(np.uint16)
+
+
+def activation_ref(x: np.ndarray, act: str) -> np.ndarray:
+    """The activations as TestCutlass.java checks them (tornado-unittests/.../cutlass/TestCutlass.java:302-545):
+    relu = max(0, x); gelu = 0.5 x (1 + erf(x / sqrt 2)); silu = x / (1 + exp(-x)); sigmoid; tanh;
+    hardswish = x * min(max(x + 3, 0), 6) / 6.  Evaluated in double."""
+    from math import erf
+    x = np.asarray(x, np.float64)
+    if act == "none":
+        return x
+    if act == "relu":
+        return np.maximum(x, 0.0)
+    if act == "gelu":
+        return 0.5 * x * (1.0 + np.vectorize(erf)(x / np.sqrt(2.0)))
+    if act == "silu":
+        return x / (1.0 + np.exp(-x))
+    if act == "sigmoid":
+        return 1.0 / (1.0 + np.exp(-x))
+    if act == "tanh":
+        return np.tanh(x)
+    if act == "hardswish":
+        return x * np.minimum(np.maximum(x + 3.0, 0.0), 6.0) / 6.0
+    raise ValueError(act)
+
+
+def gemm_epilogue_ref(prod, act="none", alpha=1.0, beta=0.0, c=None, bias=None):
+    """act(alpha * prod + beta * C + bias) in double on an fp32-accumulated product [m][n]
+    (hgemmJava + the per-test expression of TestCutlass.java:302-545; alpha / beta as
+    Cutlass.cutlassHgemm, Cutlass.java:83-100)."""
+    x = alpha * np.asarray(prod, np.float64)
+    if beta != 0.0:
+        x = x + beta * np.asarray(c, np.float64)
+    if bias is not None:
+        x = x + np.asarray(bias, np.float64)[None, :]
+    return activation_ref(x, act)

@@ -41,7 +41,8 @@ def out_buf(n, dtype=np.float32, header=16):
     """Output buffer pre-filled with NaN (or a sentinel) so unwritten elements show."""
     if np.dtype(dtype).kind == "f":
         return DevBuf(np.full(n, np.nan, dtype), header)
-    return DevBuf(np.full(n, -2, dtype), header)
+    sentinel = np.iinfo(dtype).max - 1 if np.dtype(dtype).kind == "u" else -2
+    return DevBuf(np.full(n, sentinel, dtype), header)
 
 
 def stream_ptr():

@@ -37,15 +37,17 @@ def _single(lib, fmt, rows, cols, batch, dw, dx):
     n = lib.tb200_qx_workspace_bytes(cols, batch)
     ws = DevBuf(np.zeros(max(n, 16), np.uint8))
     fn = lib.tb200_q8b_gemv_i8 if fmt == "q8b" else lib.tb200_q4b_gemv_i8
-    # the grouped launch runs the dp4a kernel; keep the single launch on it too (batches of four and more would
-    # otherwise take the tensor-core kernel, whose fp32 summation order differs)
-    # (above four vectors the grouped entry itself falls back to one ordinary launch per matrix)
-    assert lib.tb200_set_option(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH, 17 if batch <= 4 else 4) == 0
+    # Bit-for-bit comparisons need the same fp32 summation order, i.e. the same kernel family: the grouped launch
+    # runs the dp4a kernel, so the single launch is kept on it for this call (from two vectors on it would otherwise
+    # take the tensor-core kernel; that kernel's exact block dots and its results have their own tests).  Above four
+    # vectors the grouped entry itself falls back to one ordinary launch per matrix, with the default choice.
+    if batch <= 4:
+        assert lib.tb200_set_thread_option(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH, 17) == 0
     try:
         assert fn(rows, cols, batch, dw.ptr, dx.ptr, dy.ptr, ws.ptr, n, stream_ptr()) == 0
         sync_and_check(lib)
     finally:
-        lib.tb200_set_option(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH, 4)
+        lib.tb200_clear_thread_options()
     return dy.numpy().reshape(batch, rows)
 
 

@@ -67,6 +67,19 @@ class HalfFloatArray(TornadoNativeArray):
         return self.data.view(np.float16).astype(np.float32)
 
 
+class BFloat16Array(TornadoNativeArray):
+    """bfloat16 bit patterns in 16-bit words (tornado-api/.../types/arrays/BFloat16Array.java)."""
+    dtype = np.uint16
+
+    @classmethod
+    def from_float32(cls, values, header=None):
+        u = np.asarray(values, np.float32).view(np.uint32).astype(np.uint64)
+        return cls(((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16), header)
+
+    def to_float32(self) -> np.ndarray:
+        return (self.data.astype(np.uint32) << 16).view(np.float32)
+
+
 class Int8Array(TornadoNativeArray):
     dtype = np.int8
 

@@ -10,14 +10,14 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from .arrays import ByteArray, FloatArray, HalfFloatArray, Int8Array
+from .arrays import BFloat16Array, ByteArray, FloatArray, HalfFloatArray, Int8Array
 from .descriptor import Access, LibraryTaskDescriptor
 
 LIBRARY_NAME = "b200/linalg"
 MAX_BATCH = 16
 MAX_GROUP = 32
-#: TaskGraph.libraryTask takes at most 20 arguments (TaskGraph.java:886): rows, cols, batch, x, y + 15 matrices
-MAX_GROUP_TASK_ARGS = 15
+#: TaskGraph.libraryTask takes at most 20 arguments (TaskGraph.java:886): rows, cols, batch, x, y, options + 14 matrices
+MAX_GROUP_TASK_ARGS = 14
 
 
 @dataclass
@@ -144,3 +144,67 @@ class B200:
         _check(m >= 0 and n >= 0 and k >= 0, f"B200 hgemmF32 requires non-negative sizes; got m={m}, n={n}, k={k}")
         _check(a.getSize() >= m * k and b.getSize() >= k * n and c.getSize() >= m * n, "B200 hgemmF32: array too small")
         return _desc("hgemmF32", [m, n, k, a, b, c], 5)
+
+    # ---- fused epilogues, typed outputs, batches (tb200_gemm_ex) ---------------------------------------
+    @staticmethod
+    def _check_tc(name, m, n, k):
+        _check(m >= 0 and n >= 0 and k >= 0, f"B200 {name} requires non-negative sizes; got m={m}, n={n}, k={k}")
+        # the tensor-core tiles are fetched by TMA: rows of A and B must be multiples of 16 bytes (cf. Cutlass.java:68-77)
+        _check(k % 8 == 0 and n % 8 == 0, f"B200 {name} requires k and n to be multiples of 8; got k={k}, n={n}")
+
+    @staticmethod
+    def hgemm(m, n, k, alpha, a: HalfFloatArray, b: HalfFloatArray, beta, d: HalfFloatArray):
+        """D(fp16) = alpha*A*B + beta*D, fp32 accumulation; signature of Cutlass.cutlassHgemm (Cutlass.java:83-100)."""
+        B200._check_tc("hgemm", m, n, k)
+        _check(a.getSize() >= m * k and b.getSize() >= k * n and d.getSize() >= m * n, "B200 hgemm: array too small")
+        return _desc("hgemm", [m, n, k, float(alpha), a, b, float(beta), d], 7, read_write=(beta != 0.0))
+
+    @staticmethod
+    def bgemm(m, n, k, alpha, a: BFloat16Array, b: BFloat16Array, beta, d: BFloat16Array):
+        """bfloat16 twin of hgemm; signature of Cutlass.cutlassBgemm (Cutlass.java:102-117)."""
+        B200._check_tc("bgemm", m, n, k)
+        _check(a.getSize() >= m * k and b.getSize() >= k * n and d.getSize() >= m * n, "B200 bgemm: array too small")
+        return _desc("bgemm", [m, n, k, float(alpha), a, b, float(beta), d], 7, read_write=(beta != 0.0))
+
+    @staticmethod
+    def _gemm_bias(act, m, n, k, a, b, bias, d):
+        name = "gemmBias" + act
+        B200._check_tc(name, m, n, k)
+        _check(a.getSize() >= m * k and b.getSize() >= k * n and bias.getSize() >= n and d.getSize() >= m * n,
+               f"B200 {name}: array too small")
+        return _desc(name, [m, n, k, a, b, bias, d], 6)
+
+    @staticmethod
+    def gemmBiasRelu(m, n, k, a: HalfFloatArray, b: HalfFloatArray, bias: HalfFloatArray, d: HalfFloatArray):  # noqa: N802
+        """D = relu(A*B + bias), bias broadcast over the rows; Cutlass.cutlassGemmBiasRelu (Cutlass.java:119-125)."""
+        return B200._gemm_bias("Relu", m, n, k, a, b, bias, d)
+
+    @staticmethod
+    def gemmBiasGelu(m, n, k, a, b, bias, d):  # noqa: N802
+        """Cutlass.cutlassGemmBiasGelu (Cutlass.java:127-135), erf form."""
+        return B200._gemm_bias("Gelu", m, n, k, a, b, bias, d)
+
+    @staticmethod
+    def gemmBiasSilu(m, n, k, a, b, bias, d):  # noqa: N802
+        return B200._gemm_bias("Silu", m, n, k, a, b, bias, d)
+
+    @staticmethod
+    def gemmBiasSigmoid(m, n, k, a, b, bias, d):  # noqa: N802
+        return B200._gemm_bias("Sigmoid", m, n, k, a, b, bias, d)
+
+    @staticmethod
+    def gemmBiasTanh(m, n, k, a, b, bias, d):  # noqa: N802
+        return B200._gemm_bias("Tanh", m, n, k, a, b, bias, d)
+
+    @staticmethod
+    def gemmBiasHardSwish(m, n, k, a, b, bias, d):  # noqa: N802
+        return B200._gemm_bias("HardSwish", m, n, k, a, b, bias, d)
+
+    @staticmethod
+    def hgemmBatched(m, n, k, alpha, a: HalfFloatArray, b: HalfFloatArray, beta, d: HalfFloatArray, batchCount):  # noqa: N802,N803
+        """batchCount independent fp16 GEMMs packed back to back; Cutlass.cutlassHgemmBatched (Cutlass.java:177-191)."""
+        B200._check_tc("hgemmBatched", m, n, k)
+        _check(batchCount >= 1, f"B200 hgemmBatched requires batchCount >= 1; got {batchCount}")
+        _check(a.getSize() >= batchCount * m * k and b.getSize() >= batchCount * k * n and d.getSize() >= batchCount * m * n,
+               "B200 hgemmBatched: array too small")
+        return _desc("hgemmBatched", [m, n, k, float(alpha), a, b, float(beta), d, batchCount], 7, read_write=(beta != 0.0))

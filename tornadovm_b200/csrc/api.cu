@@ -20,7 +20,7 @@ int tu_status_peer(int *);
 
 // ---- options ---------------------------------------------------------------------------------
 constexpr int kNumOptions = 8;  // option ids are 1 .. kNumOptions - 1
-static std::atomic<int> g_option[kNumOptions] = {{0}, {0}, {1}, {1}, {1}, {2}, {4}, {1}};
+static std::atomic<int> g_option[kNumOptions] = {{0}, {0}, {1}, {1}, {1}, {2}, {2}, {1}};
 struct ThreadOptions {
     unsigned set_mask = 0;
     int value[kNumOptions] = {};

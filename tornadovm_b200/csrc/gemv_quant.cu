@@ -795,21 +795,24 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float *__restrict
 // Host side
 // ---------------------------------------------------------------------------
 
-// Pick a CTA count <= max_ctas that wastes the fewest warp slots in the last
-// round of a grid-stride loop over `units` (row groups).
-static int balanced_grid(int units, int warps_per_cta, int max_ctas) {
-    int need = (units + warps_per_cta - 1) / warps_per_cta;
-    if (need <= max_ctas) return need > 0 ? need : 1;
+// CTA count <= max_ctas (one resident wave) for kernels whose CTAs own contiguous row ranges and whose
+// warps own contiguous runs of row groups (R rows each).  The launch is HBM-bound and every warp streams at
+// the same rate, so it ends when the warp with the most groups ends: with 14336 rows on 296 x 8 warps, 128
+// warps would stream a seventh row while the rest of the machine idles (a seventh of the run time at 5 % of
+// the bandwidth).  Picks the count in the upper half of the wave that maximises
+// rows / (warps x rows of the busiest warp); ties go to the larger count.
+static int balanced_ctas(int rows, int R, int max_ctas) {
+    const int groups = (rows + R - 1) / R;
+    const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;  // at least one group per warp
+    if (want <= max_ctas) return want > 0 ? want : 1;
     int best = max_ctas;
     double best_eff = 0.0;
-    for (int g = max_ctas; g >= (max_ctas * 3) / 4; --g) {
-        long long w = (long long)g * warps_per_cta;
-        long long rounds = (units + w - 1) / w;
-        double eff = (double)units / (double)(rounds * w);
-        if (eff > best_eff + 1e-9) {
-            best_eff = eff;
-            best = g;
-        }
+    for (int g = max_ctas; g >= max_ctas / 2; --g) {
+        const int cta_rows = (rows + g - 1) / g;                       // the largest CTA share
+        const int cta_groups = (cta_rows + R - 1) / R;
+        const int warp_groups = (cta_groups + kQ8SWarps - 1) / kQ8SWarps;  // the busiest warp
+        const double eff = (double)rows / ((double)g * kQ8SWarps * warp_groups * R);
+        if (eff > best_eff + 1e-9) best_eff = eff, best = g;
     }
     return best;
 }
@@ -841,11 +844,8 @@ static int launch_q8s_sa(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t 
     if (st) return st;
     const size_t smem = q8s_smem_bytes<B, MODE>(a.cols);
     if (smem + 1024 > (size_t)di->max_smem_optin) return TB200_ERR_INVALID_ARG;
-    // one resident wave: a multiple of the SM count, so that every SM streams the same number of rows
-    int grid = di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem);
-    const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
-    const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;  // at least one group per warp
-    if (grid > want) grid = want;
+    // at most one resident wave, sized so that all warps own (nearly) the same number of rows
+    const int grid = balanced_ctas(a.rows, Cfg::R, di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem));
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a);
 }
 
@@ -886,11 +886,8 @@ static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s)
     constexpr auto kernel = qblk_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
-    // one resident wave, a multiple of the SM count; small matrices use fewer CTAs (one group per warp at least)
-    int grid = di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem);
-    const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
-    const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;
-    if (grid > want) grid = want;
+    // at most one resident wave, sized so that all warps own (nearly) the same number of rows
+    const int grid = balanced_ctas(a.rows, Cfg::R, di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem));
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a);
 }
 
@@ -901,10 +898,7 @@ static int launch_ring_grouped(const QGemvArgs &a, const QGroupArgs &grp, const 
     constexpr auto kernel = qblk_gemv_grouped_kernel<FMT, B, Cfg::R, MODE, Cfg::STAGES>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
-    int grid = di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem);
-    const int groups = (a.rows + Cfg::R - 1) / Cfg::R;
-    const int want = (groups + kQ8SWarps - 1) / kQ8SWarps;
-    if (grid > want) grid = want;
+    const int grid = balanced_ctas(a.rows, Cfg::R, di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem));
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a, grp);
 }
 
@@ -1089,7 +1083,9 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
             // measured on 14336 x 4096: the split layout gains from one vector on, the block layouts from two
             const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 from the measured batch on, 2 always
             const int min_batch = float_tc >= 2 ? 1 : (FMT == FMT_Q8S ? 1 : 2);
-            if (float_tc && a.batch >= min_batch) {
+            // diagnostics only (TB200_OPT_TC_REGISTER_KERNEL = 0): this older kernel splits x into fp16 pairs without a
+            // prescale, so it is accurate only for activations inside the normal fp16 range
+            if (float_tc && a.batch >= min_batch && !option_value(TB200_OPT_TC_REGISTER_KERNEL)) {
                 // most vectors per pass whose fp16 pairs fit in shared memory next to the weight ring
                 QGemvArgs p = a;
                 int cap = 0;

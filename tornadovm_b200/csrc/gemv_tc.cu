@@ -307,10 +307,14 @@ __device__ __forceinline__ void consume_chunk(const QGemvArgs &a, const unsigned
                         if (n < a.batch && r < row_end) a.dots[((size_t)n * a.rows + r) * bpr + blk0 + kb] = d[i] >> sh;
                     }
                 } else {
-                    acc[j][0] = fmaf(small_int_to_float(d[0]), sw0 * xsr[kb][j][0], acc[j][0]);
-                    acc[j][1] = fmaf(small_int_to_float(d[1]), sw0 * xsr[kb][j][1], acc[j][1]);
-                    acc[j][2] = fmaf(small_int_to_float(d[2]), sw1 * xsr[kb][j][0], acc[j][2]);
-                    acc[j][3] = fmaf(small_int_to_float(d[3]), sw1 * xsr[kb][j][1], acc[j][3]);
+                    // One column tile: the conversion unit has room for four conversions per block (one issue slot
+                    // each).  Two tiles would saturate it: there the conversion is an integer add and an exact
+                    // float subtract on the ordinary pipes.
+                    auto cvt = [](int v) { return NT == 1 ? __int2float_rn(v) : small_int_to_float(v); };
+                    acc[j][0] = fmaf(cvt(d[0]), sw0 * xsr[kb][j][0], acc[j][0]);
+                    acc[j][1] = fmaf(cvt(d[1]), sw0 * xsr[kb][j][1], acc[j][1]);
+                    acc[j][2] = fmaf(cvt(d[2]), sw1 * xsr[kb][j][0], acc[j][2]);
+                    acc[j][3] = fmaf(cvt(d[3]), sw1 * xsr[kb][j][1], acc[j][3]);
                 }
             }
         }

@@ -22,6 +22,7 @@
 //
 // flops per launch: 2*m*n*k; roofline: dense fp16 tensor throughput.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #define TB200_OP_CLASS TB200_PREPARE_GEMM_F16
 #include "common.cuh"
@@ -31,16 +32,17 @@ TB200_TU_STATUS(hgemm)
 
 namespace tb200 {
 
-constexpr int HG_BM = 128, HG_BN = 256, HG_BK = 64, HG_STAGES = 4;
+constexpr int HG_BM = 128, HG_BK = 64;
 constexpr int HG_THREADS = 192;
 constexpr int HG_A_BYTES = HG_BM * HG_BK * 2;      // 16 KB
-constexpr int HG_B_BYTES = HG_BK * HG_BN * 2;      // 32 KB, four 8 KB boxes of 64 columns
-constexpr int HG_STAGE_BYTES = HG_A_BYTES + HG_B_BYTES;
 // Each epilogue warp owns a 32 x 32 fp32 transposition buffer (row pitch 36 floats: conflict-free float4 access both ways),
 // used when tiles go to several destinations: stores to peer memory should be whole 128-byte lines, not 16-byte pieces
 // of 32 different rows.
 constexpr int HG_XPOSE_PITCH = 36, HG_XPOSE_BYTES = 4 * 32 * HG_XPOSE_PITCH * 4;
-constexpr int HG_SMEM_BYTES = HG_STAGES * HG_STAGE_BYTES + 1024 + HG_XPOSE_BYTES;  // + slack for 1024-byte alignment
+// Staging area of the epilogue: the transposition buffers above, or -- single destination -- two 32 x 32 fp32 tiles
+// (128-byte rows, 128-byte swizzle) per epilogue warp from which finished pieces leave as TMA tensor stores.
+constexpr int HG_TMA_TILE_BYTES = 32 * 128, HG_STAGING_BYTES = 4 * 2 * HG_TMA_TILE_BYTES;
+static_assert(HG_STAGING_BYTES >= HG_XPOSE_BYTES, "staging area holds either form");
 constexpr uint32_t HG_TMEM_COLS = 512;
 
 // ---- PTX wrappers ------------------------------------------------------------
@@ -50,6 +52,31 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
                  "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
                  : "memory");
 }
+
+__device__ __forceinline__ void tma_load_3d(void *dst_smem, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+                 : "memory");
+}
+// shared -> global tensor store (x must be a multiple of 16 bytes; out-of-range parts of the box are clipped)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void *src_smem, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(smem_u32(src_smem)),
+                 "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 8-byte asynchronous copy with zero fill: src_bytes = 0 writes zeros (out-of-range pieces of a tile)
+__device__ __forceinline__ void cp_async_8_zfill(uint32_t dst_smem, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -119,29 +146,273 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tm = band * gm + (in_band - tn * rows_here);
 }
 
-// Instruction descriptor, kind::f16: D fp32, A/B fp16, A K-major, B MN-major (N contiguous), M128, N256.
-//   [4,6) D format 1 = F32   [7,10) A format 0 = F16   [10,13) B format 0 = F16
+// Instruction descriptor, kind::f16: D fp32, A/B fp16 or bf16, A K-major, B MN-major (N contiguous).
+//   [4,6) D format 1 = F32   [7,10) A format 0 = F16, 1 = BF16   [10,13) B format likewise
 //   bit 15 A major (0 = K)   bit 16 B major (1 = MN)   [17,23) N >> 3   [24,29) M >> 4
-constexpr uint32_t HG_IDESC = (1u << 4) | (1u << 16) | ((uint32_t)(HG_BN >> 3) << 17) | ((uint32_t)(HG_BM >> 4) << 24);
+static uint32_t hg_idesc(int m, int n, bool bf16) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
 
-// Where the epilogue stores a tile: every destination gets C[row][col] at dst[p][row * ld + col_off + col].
-// One local destination with ld = N is the plain GEMM; several destinations (this GPU's buffer and
-// peer-mapped buffers of other GPUs) with ld = the unsharded N and col_off = the first column of this GPU's
-// column block make the all-gather of a column-sharded GEMM part of the epilogue.
+// What the epilogue does with a finished accumulator tile:
+//     D[row][col] = act(alpha * acc + beta * C[row][col] + bias[col])        (fp32 arithmetic)
+// converted to the output type and stored to every destination at dst[p][batch * batch_stride + row * ld + col_off + col].
+// One local destination with ld = N is the plain GEMM; several destinations (this GPU's buffer and peer-mapped
+// buffers of other GPUs) with ld = the unsharded N and col_off = the first column of this GPU's column block make
+// the all-gather of a column-sharded GEMM part of the epilogue.  The fused forms follow the reference's CUTLASS
+// epilogues (tornado-cutlass.cu:101-140: act(alpha * A * B + bias) with the bias row broadcast) and its alpha / beta
+// GEMMs with fp16 / bf16 outputs (Cutlass.cutlassHgemm, cutlassBgemm).
 constexpr int HG_MAX_DST = 8;
 struct HgOut {
-    float *dst[HG_MAX_DST];
-    long long ld, col_off;
+    void *dst[HG_MAX_DST];
+    long long ld, col_off, batch_stride;  // in elements of the output type
+    const void *c;                        // source of beta * C: output type, laid out like dst[0] (may be dst[0]); null: none
+    const void *bias;                     // [N] of the output type; null: none
+    float alpha, beta;
     int ndst;
-    int xpose;  // store through the transposition buffer (whole 128-byte lines per row)
+    int xpose;      // store through the transposition buffer (whole 128-byte lines per row)
+    int out_type;   // tb200_gemm_out
+    int act;        // tb200_activation
+    int tma_store;  // fp32, one dense destination: pieces leave shared memory as TMA tensor stores
+    int plain;      // alpha == 1, beta == 0, no bias, no activation, fp32: the accumulator is stored as it is
 };
 
-__global__ void __launch_bounds__(HG_THREADS, 1)
-hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ HgOut out,
-                int M, int N, int K, int c_vec_ok, int gm) {
+// erf to about 2e-7 absolute (Abramowitz & Stegun 7.1.26) in a dozen instructions: the library erff costs
+// three times as much, and the epilogue of a tile must finish within the main loop of the next one
+__device__ __forceinline__ float hg_erf(float x) {
+    const float ax = fabsf(x);
+    const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
+    const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
+    const float r = 1.0f - poly * __expf(-ax * ax);
+    return copysignf(r, x);
+}
+
+template <int ACT>
+__device__ __forceinline__ float hg_activate(float x) {
+    if (ACT == TB200_ACT_RELU) return fmaxf(x, 0.f);
+    if (ACT == TB200_ACT_GELU) return 0.5f * x * (1.0f + hg_erf(x * 0.70710678118654752f));
+    if (ACT == TB200_ACT_SILU) return x * __frcp_rn(1.0f + __expf(-x));
+    if (ACT == TB200_ACT_SIGMOID) return __frcp_rn(1.0f + __expf(-x));
+    if (ACT == TB200_ACT_TANH) {
+        const float e = __expf(-2.0f * fabsf(x));  // tanh |x| = (1 - e) / (1 + e), no overflow
+        return copysignf((1.0f - e) * __frcp_rn(1.0f + e), x);
+    }
+    if (ACT == TB200_ACT_HARDSWISH) return x * fminf(fmaxf(x + 3.0f, 0.f), 6.0f) * (1.0f / 6.0f);
+    return x;
+}
+
+// 32 consecutive elements of the output type starting at element index i of p, as floats (all lanes may read the
+// same elements: one broadcast transaction per load)
+template <int OUT>
+__device__ __forceinline__ void hg_load32(const void *p, size_t i, int valid, bool vec, float (&f)[32]) {
+    if (OUT == TB200_OUT_F32) {
+        const float *q = reinterpret_cast<const float *>(p) + i;
+        if (vec && valid == 32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(q) + j);
+                f[4 * j] = v.x, f[4 * j + 1] = v.y, f[4 * j + 2] = v.z, f[4 * j + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = j < valid ? __ldg(q + j) : 0.f;
+        }
+    } else {
+        const uint16_t *q = reinterpret_cast<const uint16_t *>(p) + i;
+        auto cvt = [](uint16_t h) { return OUT == TB200_OUT_F16 ? half_bits_to_float(h) : __uint_as_float((uint32_t)h << 16); };
+        if (vec && valid == 32) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(q) + j);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) f[8 * j + 2 * k] = cvt((uint16_t)(w[k] & 0xFFFF)), f[8 * j + 2 * k + 1] = cvt((uint16_t)(w[k] >> 16));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = j < valid ? cvt(__ldg(q + j)) : 0.f;
+        }
+    }
+}
+
+// v = act(alpha * v + beta * C + bias) on the lane's 32 accumulator values (bit patterns of floats)
+template <int OUT, int ACT>
+__device__ __forceinline__ void hg_fuse32(uint32_t (&v)[32], const HgOut &out, size_t at, int col0, int valid, bool row_ok, bool vec) {
+    float x[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = out.alpha * __uint_as_float(v[j]);
+    if (out.beta != 0.f && out.c && row_ok) {
+        float c[32];
+        hg_load32<OUT>(out.c, at, valid, vec, c);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] = fmaf(out.beta, c[j], x[j]);
+    }
+    if (out.bias) {
+        float b[32];
+        hg_load32<OUT>(out.bias, (size_t)col0, valid, vec, b);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) x[j] += b[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(hg_activate<ACT>(x[j]));
+}
+
+template <int OUT>
+__device__ __forceinline__ void hg_fuse32_act(uint32_t (&v)[32], const HgOut &out, size_t at, int col0, int valid, bool row_ok, bool vec) {
+    switch (out.act) {
+        case TB200_ACT_RELU: return hg_fuse32<OUT, TB200_ACT_RELU>(v, out, at, col0, valid, row_ok, vec);
+        case TB200_ACT_GELU: return hg_fuse32<OUT, TB200_ACT_GELU>(v, out, at, col0, valid, row_ok, vec);
+        case TB200_ACT_SILU: return hg_fuse32<OUT, TB200_ACT_SILU>(v, out, at, col0, valid, row_ok, vec);
+        case TB200_ACT_SIGMOID: return hg_fuse32<OUT, TB200_ACT_SIGMOID>(v, out, at, col0, valid, row_ok, vec);
+        case TB200_ACT_TANH: return hg_fuse32<OUT, TB200_ACT_TANH>(v, out, at, col0, valid, row_ok, vec);
+        case TB200_ACT_HARDSWISH: return hg_fuse32<OUT, TB200_ACT_HARDSWISH>(v, out, at, col0, valid, row_ok, vec);
+        default: return hg_fuse32<OUT, TB200_ACT_NONE>(v, out, at, col0, valid, row_ok, vec);
+    }
+}
+
+__device__ __forceinline__ uint16_t hg_to_out16(float x, int out_type) {
+    if (out_type == TB200_OUT_F16) return __half_as_ushort(__float2half_rn(x));
+    return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+
+// Epilogue of one warp for one accumulator tile: NCHUNK pieces of 32 rows (one per lane) x 32 columns.
+//   taddr     tensor-memory address of the warp's lane quarter, first column of the tile's accumulator
+//   row0      first row of the warp's 32 rows, n0 first column of the tile, batch index of the matrix
+//   staging   this warp's part of the staging area (HG_STAGING_BYTES / 4 bytes, 1024-byte aligned)
+//   nstores   running count of this warp's TMA stores (selects the staging tile)
+template <int NCHUNK>
+__device__ __forceinline__ void hg_epilogue_tile(const HgOut &out, const CUtensorMap *map_d, uint32_t taddr, int row0, int n0, int batch,
+                                                 int M, int N, int vec_ok, unsigned char *staging, int lane, uint32_t &nstores) {
+    const int row = row0 + lane;
+    const size_t boff = (size_t)batch * out.batch_stride;
+#pragma unroll 1
+    for (int c = 0; c < NCHUNK; ++c) {
+        uint32_t v[32];
+        tc_ld_32cols(taddr + c * 32, v);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (col0 >= N) continue;  // warp-uniform
+        const bool full = col0 + 32 <= N;
+        if (!out.plain) {
+            const size_t at = boff + (size_t)row * out.ld + out.col_off + col0;
+            const int valid = full ? 32 : N - col0;
+            if (out.out_type == TB200_OUT_F32) hg_fuse32_act<TB200_OUT_F32>(v, out, at, col0, valid, row < M, vec_ok != 0);
+            else if (out.out_type == TB200_OUT_F16) hg_fuse32_act<TB200_OUT_F16>(v, out, at, col0, valid, row < M, vec_ok != 0);
+            else hg_fuse32_act<TB200_OUT_BF16>(v, out, at, col0, valid, row < M, vec_ok != 0);
+        }
+        if (out.out_type != TB200_OUT_F32) {
+            // 16-bit outputs: the lane's 32 values are 64 contiguous bytes of its row
+            if (row < M) {
+                for (int p = 0; p < out.ndst; ++p) {
+                    uint16_t *dst = reinterpret_cast<uint16_t *>(out.dst[p]) + boff + (size_t)row * out.ld + out.col_off + col0;
+                    if (vec_ok && full) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                w[i] = (uint32_t)hg_to_out16(__uint_as_float(v[8 * j + 2 * i]), out.out_type) |
+                                       ((uint32_t)hg_to_out16(__uint_as_float(v[8 * j + 2 * i + 1]), out.out_type) << 16);
+                            *reinterpret_cast<uint4 *>(dst + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) dst[j] = hg_to_out16(__uint_as_float(v[j]), out.out_type);
+                    }
+                }
+            }
+            continue;
+        }
+        if (out.tma_store) {
+            // lane r writes row r of a 32 x 32 tile (128-byte rows, 16-byte pieces XOR-swizzled by the row: the
+            // layout of a 128-byte-swizzled tensor map), then one lane hands the tile to the TMA engine
+            unsigned char *tile = staging + (nstores & 1) * HG_TMA_TILE_BYTES;
+            if (lane == 0) tma_store_wait_read<1>();  // the store that last read this tile has finished reading
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4 *>(tile + lane * 128 + ((j ^ (lane & 7)) << 4)) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0 && row0 < M) {
+                tma_store_3d(map_d, tile, col0, row0, batch);
+                tma_store_commit();
+            }
+            ++nstores;
+            continue;
+        }
+        float *const *dsts = reinterpret_cast<float *const *>(out.dst);
+        if (out.xpose && vec_ok && full) {
+            // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
+            float *stg = reinterpret_cast<float *>(staging);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4 *>(stg + lane * HG_XPOSE_PITCH + 4 * j) =
+                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int rl = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+                const float4 val = *reinterpret_cast<const float4 *>(stg + rl * HG_XPOSE_PITCH + c4);
+                const int grow = row0 + rl;
+                if (grow < M) {
+                    for (int p = 0; p < out.ndst; ++p)  // plain stores, to local or peer-mapped memory
+                        *reinterpret_cast<float4 *>(dsts[p] + boff + (size_t)grow * out.ld + out.col_off + col0 + c4) = val;
+                }
+            }
+            __syncwarp();
+        } else if (row < M) {
+            for (int p = 0; p < out.ndst; ++p) {  // plain stores, to local or peer-mapped memory
+                float *dst = dsts[p] + boff + (size_t)row * out.ld + out.col_off + col0;
+                if (vec_ok && full) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<float4 *>(dst + 4 * j) =
+                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
+                }
+            }
+        }
+    }
+}
+
+// BN = 256: the standard tile.  BN = 128: for products with too few 128 x 256 tiles to fill the SMs (six ring
+// stages instead of four).  `idesc` carries the operand formats (fp16 or bf16) and the tile shape.
+template <int BN>
+struct HgTile {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int B_BYTES = HG_BK * BN * 2;
+    static constexpr int STAGE_BYTES = HG_A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + HG_STAGING_BYTES;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;
+};
+
+// Operands for the form that does not use tensor maps (CPA).
+struct HgRaw {
+    const uint16_t *a, *b;
+    long long stride_a, stride_b;  // elements between the matrices of a batch
+};
+constexpr int HG_CPA_WARPS = 4, HG_CPA_THREADS = HG_THREADS + HG_CPA_WARPS * 32, HG_CPA_LAG = 2;
+
+// CPA = false: operands arrive by TMA tensor loads (16-byte aligned A and B).
+// CPA = true: A and B are only 8-byte aligned -- TornadoVM arrays behind a 24-byte header, the reference launcher's
+// default mode -- which no TMA copy accepts.  Four extra warps then fill the same 128-byte-swizzled stage layout
+// with 8-byte cp.async copies (zero fill outside the matrices), keep two stages of copies in flight each, and hand
+// a stage to the MMA warp after a proxy fence; everything from the MMA on is unchanged.
+template <int BN, bool CPA>
+__global__ void __launch_bounds__(CPA ? HG_CPA_THREADS : HG_THREADS, 1)
+hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
+                const __grid_constant__ HgOut out, const __grid_constant__ HgRaw raw, int M, int N, int K, int batches, int vec_ok, int gm,
+                uint32_t idesc) {
+    using TL = HgTile<BN>;
+    constexpr int STAGES = TL::STAGES;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[HG_STAGES];
-    __shared__ __align__(8) uint64_t empty_bar[HG_STAGES];
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
     __shared__ __align__(8) uint64_t acc_full_bar[2];
     __shared__ __align__(8) uint64_t acc_empty_bar[2];
     __shared__ uint32_t tmem_base_slot;
@@ -151,14 +422,15 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     unsigned char *tiles = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = (M + HG_BM - 1) / HG_BM, tiles_n = (N + HG_BN - 1) / HG_BN;
-    const int num_tiles = tiles_m * tiles_n;
+    const int tiles_m = (M + HG_BM - 1) / HG_BM, tiles_n = (N + BN - 1) / BN;
+    const int tiles_per_matrix = tiles_m * tiles_n;
+    const int num_tiles = tiles_per_matrix * batches;
     const int k_blocks = (K + HG_BK - 1) / HG_BK;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        for (int s = 0; s < HG_STAGES; ++s) {
-            mbar_init(&full_bar[s], 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], CPA ? HG_CPA_WARPS * 32 : 1);  // CPA: one arrival per copying thread
             mbar_init(&empty_bar[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -168,9 +440,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         mbar_fence_init();
     }
     if (warp == 1) {
-        // whole warp: allocate all 512 tensor-memory columns (two 128 x 256 fp32 accumulators)
+        // whole warp: allocate the tensor-memory columns of two 128 x BN fp32 accumulators
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"(HG_TMEM_COLS)
+                     "r"(TL::TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -182,27 +454,28 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (lane == 0) {
+        if (!CPA && lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int batch = tile / tiles_per_matrix;
                 int tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
-                const int m0 = tm * HG_BM, n0 = tn * HG_BN;
+                tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
+                const int m0 = tm * HG_BM, n0 = tn * BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % HG_STAGES;
-                    const uint32_t use = it / HG_STAGES;
+                    const int s = it % STAGES;
+                    const uint32_t use = it / STAGES;
                     if (use > 0) {
                         ok = mbar_wait_abortable(&empty_bar[s], (use - 1) & 1, abortp);
                         if (!ok) break;
                     }
-                    unsigned char *a_dst = tiles + (size_t)s * HG_STAGE_BYTES;
+                    unsigned char *a_dst = tiles + (size_t)s * TL::STAGE_BYTES;
                     unsigned char *b_dst = a_dst + HG_A_BYTES;
-                    mbar_expect_tx(&full_bar[s], HG_STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, kb * HG_BK, m0, &full_bar[s]);
+                    mbar_expect_tx(&full_bar[s], TL::STAGE_BYTES);
+                    tma_load_3d(a_dst, &map_a, kb * HG_BK, m0, batch, &full_bar[s]);
 #pragma unroll
-                    for (int j = 0; j < HG_BN / 64; ++j)
-                        tma_load_2d(b_dst + j * (HG_BK * 128), &map_b, n0 + j * 64, kb * HG_BK, &full_bar[s]);
+                    for (int j = 0; j < BN / 64; ++j)
+                        tma_load_3d(b_dst + j * (HG_BK * 128), &map_b, n0 + j * 64, kb * HG_BK, batch, &full_bar[s]);
                 }
             }
         }
@@ -218,13 +491,14 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (!ok) break;
                     tc_fence_after();
                 }
-                const uint32_t d_tmem = tmem_base + acc * HG_BN;
+                const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % HG_STAGES;
-                    ok = mbar_wait_abortable(&full_bar[s], (it / HG_STAGES) & 1, abortp);
+                    const int s = it % STAGES;
+                    ok = mbar_wait_abortable(&full_bar[s], (it / STAGES) & 1, abortp);
                     if (!ok) break;
+                    if (CPA) fence_async_shared();  // the stage was written through the generic proxy
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * HG_STAGE_BYTES);
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * TL::STAGE_BYTES);
                     const uint32_t b_addr = a_addr + HG_A_BYTES;
                     // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart
                     const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
@@ -233,7 +507,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int k16 = 0; k16 < HG_BK / 16; ++k16) {
                         // A advances 16 halves = 32 bytes along K; B advances 16 k-rows = 2048 bytes
-                        tc_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), HG_IDESC,
+                        tc_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), idesc,
                                    (kb > 0 || k16 > 0) ? 1u : 0u);
                     }
                     tc_commit(&empty_bar[s]);  // arrives once the MMAs above have read this stage
@@ -241,68 +515,83 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (ok) tc_commit(&acc_full_bar[acc]);  // accumulator complete
             }
         }
-    } else {
+    } else if (CPA && warp >= 6) {
+        // ---------------- cp.async producers: warps 6..9 ----------------
+        const int ptid = threadIdx.x - HG_THREADS;
+        const uint32_t tiles_s = smem_u32(tiles);
+        uint32_t it = 0;
+        bool ok = true;
+        auto publish = [&](uint32_t done_it) {
+            // the copies of stage `done_it` have landed for this thread: make them visible to the tensor core's
+            // (async-proxy) reads, then count this thread's arrival
+            fence_async_shared();
+            mbar_arrive(&full_bar[done_it % STAGES]);
+        };
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int batch = tile / tiles_per_matrix;
+            int tm, tn;
+            tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
+            const int m0 = tm * HG_BM, n0 = tn * BN;
+            const uint16_t *A = raw.a + (size_t)batch * raw.stride_a, *B = raw.b + (size_t)batch * raw.stride_b;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t use = it / STAGES;
+                if (use > 0) {
+                    ok = mbar_wait_abortable(&empty_bar[s], (use - 1) & 1, abortp);
+                    if (!ok) break;
+                }
+                const uint32_t a_dst = tiles_s + s * TL::STAGE_BYTES, b_dst = a_dst + HG_A_BYTES;
+                const int k0 = kb * HG_BK;
+                // A tile: 128 rows x 16 pieces of 4 halves; piece p of row r sits in 16-byte chunk (p / 2) ^ (r % 8)
+#pragma unroll 4
+                for (int j = 0; j < HG_BM * 16 / (HG_CPA_WARPS * 32); ++j) {
+                    const int i = ptid + j * HG_CPA_WARPS * 32, r = i >> 4, p = i & 15;
+                    const int grow = m0 + r, gk = k0 + p * 4;
+                    const bool valid = grow < M && gk < K;
+                    cp_async_8_zfill(a_dst + r * 128 + ((((p >> 1) ^ (r & 7))) << 4) + (p & 1) * 8, valid ? A + (size_t)grow * K + gk : A, valid ? 8 : 0);
+                }
+                // B tile: BN / 64 boxes of 64 k-rows x 64 columns, each row 16 pieces
+#pragma unroll 4
+                for (int j = 0; j < (BN / 64) * 64 * 16 / (HG_CPA_WARPS * 32); ++j) {
+                    const int i = ptid + j * HG_CPA_WARPS * 32, box = i >> 10, kr = (i >> 4) & 63, p = i & 15;
+                    const int gk = k0 + kr, gn = n0 + box * 64 + p * 4;
+                    const bool valid = gk < K && gn < N;
+                    cp_async_8_zfill(b_dst + box * (HG_BK * 128) + kr * 128 + ((((p >> 1) ^ (kr & 7))) << 4) + (p & 1) * 8,
+                                     valid ? B + (size_t)gk * N + gn : B, valid ? 8 : 0);
+                }
+                cp_async_commit_group();
+                if (it >= HG_CPA_LAG) {
+                    cp_async_wait_group<HG_CPA_LAG>();  // all but the newest groups: stage it - LAG is complete
+                    publish(it - HG_CPA_LAG);
+                }
+            }
+        }
+        // drain: the last stages
+        cp_async_wait_group<0>();
+        if (ok) {
+            for (uint32_t d = it >= HG_CPA_LAG ? it - HG_CPA_LAG : 0; d < it; ++d) publish(d);
+        }
+    } else if (warp >= 2 && warp < 6) {
         // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
         const int quarter = warp & 3;
-        uint32_t local_tile = 0;
+        unsigned char *staging = tiles + (size_t)STAGES * TL::STAGE_BYTES + (warp - 2) * (HG_STAGING_BYTES / 4);
+        uint32_t local_tile = 0, nstores = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const uint32_t acc = local_tile & 1, acc_use = local_tile >> 1;
+            const int batch = tile / tiles_per_matrix;
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
-            const int m0 = tm * HG_BM, n0 = tn * HG_BN;
+            tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
             ok = __all_sync(0xffffffffu, mbar_wait_abortable(&acc_full_bar[acc], acc_use & 1, abortp));
             if (!ok) break;
             tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * HG_BN;
-#pragma unroll 1
-            for (int c = 0; c < HG_BN / 32; ++c) {
-                uint32_t v[32];
-                tc_ld_32cols(taddr + c * 32, v);
-                tc_wait_ld();
-                const int col0 = n0 + c * 32;
-                if (out.xpose && c_vec_ok && col0 + 32 <= N) {
-                    // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
-                    float *stg = reinterpret_cast<float *>(tiles + (size_t)HG_STAGES * HG_STAGE_BYTES) + (warp - 2) * 32 * HG_XPOSE_PITCH;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<float4 *>(stg + lane * HG_XPOSE_PITCH + 4 * j) =
-                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                        __uint_as_float(v[4 * j + 3]));
-                    __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int rl = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
-                        const float4 val = *reinterpret_cast<const float4 *>(stg + rl * HG_XPOSE_PITCH + c4);
-                        const int grow = row - lane + rl;
-                        if (grow < M) {
-                            for (int p = 0; p < out.ndst; ++p)  // plain stores, to local or peer-mapped memory
-                                *reinterpret_cast<float4 *>(out.dst[p] + (size_t)grow * out.ld + out.col_off + col0 + c4) = val;
-                        }
-                    }
-                    __syncwarp();
-                } else if (row < M && col0 < N) {
-                    for (int p = 0; p < out.ndst; ++p) {  // plain stores, to local or peer-mapped memory
-                        float *dst = out.dst[p] + (size_t)row * out.ld + out.col_off + col0;
-                        if (c_vec_ok && col0 + 32 <= N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                *reinterpret_cast<float4 *>(dst + 4 * j) =
-                                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
-                        }
-                    }
-                }
-            }
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+            hg_epilogue_tile<BN / 32>(out, &map_d, taddr, tm * HG_BM + quarter * 32, tn * BN, batch, M, N, vec_ok, staging, lane, nstores);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
         }
+        if (lane == 0) tma_store_wait_read<0>();  // shared memory stays valid until the last store has read it
     }
 
     // ---------------- teardown ----------------
@@ -310,7 +599,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(HG_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TL::TMEM_COLS) : "memory");
     }
 }
 
@@ -326,8 +615,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 constexpr int H2_STAGES = 6;
 constexpr int H2_B_BYTES = HG_BK * 128 * 2;                 // 16 KB: two 64-column boxes
 constexpr int H2_STAGE_BYTES = HG_A_BYTES + H2_B_BYTES;     // 32 KB per CTA and stage
-constexpr int H2_SMEM_BYTES = H2_STAGES * H2_STAGE_BYTES + 1024 + HG_XPOSE_BYTES;
-constexpr uint32_t H2_IDESC = (1u << 4) | (1u << 16) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+constexpr int H2_SMEM_BYTES = H2_STAGES * H2_STAGE_BYTES + 1024 + HG_STAGING_BYTES;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -348,11 +636,11 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load of one CTA of a pair; completion bytes go to the mbarrier at `bar_cluster_addr` (the leader's)
-__device__ __forceinline__ void tma_load_2d_pair(void *dst_smem, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+__device__ __forceinline__ void tma_load_3d_pair(void *dst_smem, const CUtensorMap *map, int x, int y, int z, uint32_t bar_cluster_addr) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
             smem_u32(dst_smem)),
-        "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr)
         : "memory");
 }
 __device__ __forceinline__ void tc2_commit_both(uint64_t *bar) {  // arrives on `bar` in both CTAs of the pair
@@ -371,8 +659,8 @@ __device__ __forceinline__ void tc2_mma_f16(uint32_t d_tmem, uint64_t a_desc, ui
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HG_THREADS, 1)
-hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ HgOut out,
-                 int M, int N, int K, int c_vec_ok, int gm) {
+hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
+                 const __grid_constant__ HgOut out, int M, int N, int K, int batches, int vec_ok, int gm, uint32_t idesc) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[H2_STAGES];   // used in the leader only
     __shared__ __align__(8) uint64_t empty_bar[H2_STAGES];  // one per CTA, signalled by the leader's commits
@@ -386,7 +674,8 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
-    const int num_tiles = tiles_m * tiles_n;
+    const int tiles_per_matrix = tiles_m * tiles_n;
+    const int num_tiles = tiles_per_matrix * batches;
     const int k_blocks = (K + HG_BK - 1) / HG_BK;
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
@@ -421,8 +710,9 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t it = 0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+                const int batch = tile / tiles_per_matrix;
                 int tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
+                tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
                 const int m0 = tm * 256 + (int)rank * 128;
                 const int n0 = tn * 256 + (int)rank * 128;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -436,9 +726,9 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     unsigned char *b_dst = a_dst + HG_A_BYTES;
                     if (leader) mbar_expect_tx(&full_bar[s], 2 * H2_STAGE_BYTES);  // bytes of both CTAs
                     const uint32_t bar = map_to_cta(&full_bar[s], 0);
-                    tma_load_2d_pair(a_dst, &map_a, kb * HG_BK, m0, bar);
-                    tma_load_2d_pair(b_dst, &map_b, n0, kb * HG_BK, bar);
-                    tma_load_2d_pair(b_dst + HG_BK * 128, &map_b, n0 + 64, kb * HG_BK, bar);
+                    tma_load_3d_pair(a_dst, &map_a, kb * HG_BK, m0, batch, bar);
+                    tma_load_3d_pair(b_dst, &map_b, n0, kb * HG_BK, batch, bar);
+                    tma_load_3d_pair(b_dst + HG_BK * 128, &map_b, n0 + 64, kb * HG_BK, batch, bar);
                 }
             }
         }
@@ -465,7 +755,7 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint64_t b_desc = make_smem_desc(a_addr + HG_A_BYTES, HG_BK * 128, 1024);
 #pragma unroll
                     for (int k16 = 0; k16 < HG_BK / 16; ++k16)
-                        tc2_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), H2_IDESC,
+                        tc2_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), idesc,
                                     (kb > 0 || k16 > 0) ? 1u : 0u);
                     tc2_commit_both(&empty_bar[s]);  // frees this stage in both CTAs
                 }
@@ -475,65 +765,24 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else {
         // ---------------- epilogue: warps 2..5 of each CTA, its own 128 rows ----------------
         const int quarter = warp & 3;
-        uint32_t local_tile = 0;
+        unsigned char *staging = tiles + (size_t)H2_STAGES * H2_STAGE_BYTES + (warp - 2) * (HG_STAGING_BYTES / 4);
+        uint32_t local_tile = 0, nstores = 0;
         bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += npairs, ++local_tile) {
             const uint32_t acc = local_tile & 1, acc_use = local_tile >> 1;
+            const int batch = tile / tiles_per_matrix;
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
-            const int m0 = tm * 256 + (int)rank * 128, n0 = tn * 256;
+            tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
             ok = __all_sync(0xffffffffu, mbar_wait_abortable(&acc_full_bar[acc], acc_use & 1, abortp));
             if (!ok) break;
             tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
-#pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
-                uint32_t v[32];
-                tc_ld_32cols(taddr + c * 32, v);
-                tc_wait_ld();
-                const int col0 = n0 + c * 32;
-                if (out.xpose && c_vec_ok && col0 + 32 <= N) {
-                    // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
-                    float *stg = reinterpret_cast<float *>(tiles + (size_t)H2_STAGES * H2_STAGE_BYTES) + (warp - 2) * 32 * HG_XPOSE_PITCH;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        *reinterpret_cast<float4 *>(stg + lane * HG_XPOSE_PITCH + 4 * j) =
-                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]),
-                                        __uint_as_float(v[4 * j + 3]));
-                    __syncwarp();
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int rl = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
-                        const float4 val = *reinterpret_cast<const float4 *>(stg + rl * HG_XPOSE_PITCH + c4);
-                        const int grow = row - lane + rl;
-                        if (grow < M) {
-                            for (int p = 0; p < out.ndst; ++p)  // plain stores, to local or peer-mapped memory
-                                *reinterpret_cast<float4 *>(out.dst[p] + (size_t)grow * out.ld + out.col_off + col0 + c4) = val;
-                        }
-                    }
-                    __syncwarp();
-                } else if (row < M && col0 < N) {
-                    for (int p = 0; p < out.ndst; ++p) {  // plain stores, to local or peer-mapped memory
-                        float *dst = out.dst[p] + (size_t)row * out.ld + out.col_off + col0;
-                        if (c_vec_ok && col0 + 32 <= N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                *reinterpret_cast<float4 *>(dst + 4 * j) =
-                                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
-                        }
-                    }
-                }
-            }
+            hg_epilogue_tile<8>(out, &map_d, taddr, tm * 256 + (int)rank * 128 + quarter * 32, tn * 256, batch, M, N, vec_ok, staging, lane, nstores);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty_bar[acc], 0));
         }
+        if (lane == 0) tma_store_wait_read<0>();  // shared memory stays valid until the last store has read it
     }
 
     // ---------------- teardown: nobody leaves while the peer may still signal or read ----------------
@@ -568,90 +817,185 @@ static EncodeTiledFn encode_tiled_fn() {
 
 int hgemm_prepare_driver() { return encode_tiled_fn() ? TB200_OK : TB200_ERR_DRIVER; }
 
-// 2-D fp16 tensor map: `inner` contiguous elements per row, `outer` rows, box of 64 x box_rows, 128-byte swizzle.
-static int make_map_f16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint32_t box_rows) {  // box: 64 x box_rows
+// 3-D tensor map over `batches` row-major matrices of `outer` rows x `inner` elements, `batch_stride` elements apart;
+// box of box_inner x box_rows x 1, 128-byte swizzle (box_inner elements = 128 bytes).
+// Encoding goes through the driver; a task dispatches the same operands again and again, so the last maps of
+// the calling thread are kept and looked up by their full key (pointer, shape, type, box).
+struct MapKey {
+    const void *base;
+    uint64_t inner, outer, batches, batch_stride;
+    uint32_t box_inner, box_rows, type;
+    bool operator==(const MapKey &o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && batches == o.batches && batch_stride == o.batch_stride &&
+               box_inner == o.box_inner && box_rows == o.box_rows && type == o.type;
+    }
+};
+struct MapCache {
+    static constexpr int N = 16;
+    MapKey key[N];
+    CUtensorMap map[N];
+    bool used[N] = {};
+    int next = 0;
+};
+static thread_local MapCache t_maps;
+
+static int make_map(CUtensorMap *map, const void *base, CUtensorMapDataType type, int elem_bytes, uint64_t inner, uint64_t outer,
+                    uint64_t batches, uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows) {
+    const MapKey key{base, inner, outer, batches, batch_stride, box_inner, box_rows, (uint32_t)type};
+    MapCache &mc = t_maps;
+    for (int i = 0; i < MapCache::N; ++i)
+        if (mc.used[i] && mc.key[i] == key) {
+            *map = mc.map[i];
+            return TB200_OK;
+        }
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return TB200_ERR_DRIVER;
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {inner * 2};
-    cuuint32_t box[2] = {64, box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_DRIVER;
+    cuuint64_t dims[3] = {inner, outer, batches};
+    // a single matrix: the third dimension has extent 1 and its stride only has to be a valid multiple of 16 bytes
+    cuuint64_t strides[2] = {inner * elem_bytes, (batches > 1 ? batch_stride : inner * outer) * elem_bytes};
+    cuuint32_t box[3] = {box_inner, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, type, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return TB200_ERR_DRIVER;
+    const int slot = mc.next;
+    mc.next = (mc.next + 1) % MapCache::N;
+    mc.key[slot] = key, mc.map[slot] = *map, mc.used[slot] = true;
+    return TB200_OK;
+}
+
+struct HgProblem {
+    int m, n, k, batches;
+    const uint16_t *a, *b;
+    long long stride_a, stride_b;  // elements between consecutive matrices (batches > 1)
+    bool bf16;
+};
+
+static int out_elem_bytes(int out_type) { return out_type == TB200_OUT_F32 ? 4 : 2; }
+
+// D = act(alpha * A * B + beta * C + bias) with the tile stores described by `out`.
+static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
+    const int m = pr.m, n = pr.n, k = pr.k;
+    out.xpose = out.ndst >= option_value(TB200_OPT_HGEMM_LINE_STORES);
+    if (m < 0 || n < 0 || k < 0 || pr.batches < 1) return TB200_ERR_INVALID_ARG;
+    if (m == 0 || n == 0) return TB200_OK;
+    if (k > 0 && (!pr.a || !pr.b)) return TB200_ERR_INVALID_ARG;
+    if (out.ndst < 1 || out.ndst > HG_MAX_DST || out.ld < n || out.col_off < 0 || out.col_off > out.ld - n) return TB200_ERR_INVALID_ARG;
+    if (out.out_type < TB200_OUT_F32 || out.out_type > TB200_OUT_BF16 || out.act < TB200_ACT_NONE || out.act > TB200_ACT_HARDSWISH) return TB200_ERR_INVALID_ARG;
+    if (pr.batches > 1 && (pr.stride_a < (long long)m * k || pr.stride_b < (long long)k * n || out.batch_stride < (long long)m * out.ld)) return TB200_ERR_INVALID_ARG;
+    if (!aligned_to(pr.a, 2) || !aligned_to(pr.b, 2)) return TB200_ERR_ALIGNMENT;
+    const int eb = out_elem_bytes(out.out_type);
+    const int per16 = 16 / eb;  // output elements per 16 bytes
+    bool vec = n % per16 == 0 && out.ld % per16 == 0 && out.col_off % per16 == 0 && out.batch_stride % per16 == 0;
+    for (int p = 0; p < out.ndst; ++p) {
+        if (!out.dst[p]) return TB200_ERR_INVALID_ARG;
+        if (!aligned_to(out.dst[p], eb)) return TB200_ERR_ALIGNMENT;
+        vec = vec && aligned_to(out.dst[p], 16);
+    }
+    if ((out.c && !aligned_to(out.c, eb)) || (out.bias && !aligned_to(out.bias, eb))) return TB200_ERR_ALIGNMENT;
+    if (out.beta != 0.f && !out.c) return TB200_ERR_INVALID_ARG;
+    out.plain = out.alpha == 1.f && out.beta == 0.f && !out.bias && out.act == TB200_ACT_NONE && out.out_type == TB200_OUT_F32;
+    int st;
+    const DeviceInfo *di = device_info(&st);
+    if (!di) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    // tensor-core path: TMA needs 16-byte aligned bases and row pitches; tiny products are not worth a 128 x 128 tile
+    // 8-byte aligned operands (an array behind a 24-byte header) take the same kernels with cp.async producers
+    const bool tma_ok = aligned_to(pr.a, 16) && aligned_to(pr.b, 16);
+    const bool tensor = k >= 32 && k % 8 == 0 && n % 8 == 0 && aligned_to(pr.a, 8) && aligned_to(pr.b, 8) && (long long)m * n >= 64 * 64 &&
+                        (pr.batches == 1 || (pr.stride_a % 8 == 0 && pr.stride_b % 8 == 0));
+    if (!tensor) {
+        // the CUDA-core kernel writes dense fp32 [m][n] matrices without an epilogue
+        if (out.ndst != 1 || out.ld != n || !out.plain || pr.bf16) return TB200_ERR_UNSUPPORTED;
+        st = ensure_kernel<gemm_generic_kernel<uint16_t>, 0>(di);
+        if (st) return st;
+        dim3 grid((n + 31) / 32, (m + 31) / 32);
+        for (int b = 0; b < pr.batches; ++b) {
+            gemm_generic_kernel<uint16_t><<<grid, 1024, 0, s>>>(m, n, k, 1.0f, pr.a + (size_t)b * pr.stride_a, pr.b + (size_t)b * pr.stride_b, 0.0f,
+                                                                reinterpret_cast<float *>(out.dst[0]) + (size_t)b * out.batch_stride);
+            st = check_launch();
+            if (st) return st;
+        }
+        return TB200_OK;
+    }
+    const CUtensorMapDataType in_type = pr.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap map_a{}, map_b{}, map_d;
+    if (tma_ok) {
+        st = make_map(&map_a, pr.a, in_type, 2, (uint64_t)k, (uint64_t)m, (uint64_t)pr.batches, (uint64_t)pr.stride_a, 64, HG_BM);
+        if (st) return st;
+        st = make_map(&map_b, pr.b, in_type, 2, (uint64_t)n, (uint64_t)k, (uint64_t)pr.batches, (uint64_t)pr.stride_b, 64, HG_BK);
+        if (st) return st;
+    }
+    const HgRaw raw{pr.a, pr.b, pr.stride_a, pr.stride_b};
+    // finished fp32 pieces of a single dense destination leave as TMA tensor stores (32 x 32 boxes)
+    out.tma_store = out.out_type == TB200_OUT_F32 && out.ndst == 1 && out.col_off == 0 && vec && n % 4 == 0;
+    if (out.tma_store) {
+        st = make_map(&map_d, out.dst[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)n, (uint64_t)m, (uint64_t)pr.batches,
+                      (uint64_t)out.batch_stride, 32, 32);
+        if (st) out.tma_store = 0;  // e.g. a row pitch the encoder does not take: plain stores
+        // a leading dimension other than n is not described by the map
+        if (out.ld != n) out.tma_store = 0;
+    }
+    if (!out.tma_store) map_d = CUtensorMap{};  // unused by the kernel
+    const int vec_ok = vec;
+    // tile rows per band: the band's A panels (rows x k halves) should take about 48 MB of the 126 MB L2
+    auto band_rows = [&](int tile_m) {
+        long long g = (48ll << 20) / ((long long)tile_m * k * 2);
+        return (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
+    };
+    const long long tiles256 = (long long)((m + 255) / 256) * ((n + 255) / 256) * pr.batches;
+    // SM pairs pay off once there are at least two waves of 256 x 256 tiles; smaller products fill the
+    // machine better with 128 x 256 or 128 x 128 tiles on single CTAs
+    if (tma_ok && option_value(TB200_OPT_HGEMM_SM_PAIRS) && tiles256 >= 2 * (di->sm_count / 2)) {
+        st = ensure_smem_optin<hgemm_tc2_kernel>(di);
+        if (st) return st;
+        const int pairs = tiles256 < di->sm_count / 2 ? (int)tiles256 : di->sm_count / 2;
+        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, pr.batches, vec_ok, band_rows(256),
+                                                                      hg_idesc(256, 256, pr.bf16));
+        return check_launch();
+    }
+    const long long tiles_wide = (long long)((m + HG_BM - 1) / HG_BM) * ((n + 255) / 256) * pr.batches;
+    const long long tiles_narrow = (long long)((m + HG_BM - 1) / HG_BM) * ((n + 127) / 128) * pr.batches;
+    // 128 x 128 tiles read as many operand bytes from shared memory per MMA as 128 x 256 tiles for half the
+    // arithmetic and run at about half the rate per SM (2048^3: 602 against 812 TFLOP/s), so they only pay when
+    // the wide tiles would leave more than half of the SMs idle
+    const bool wide = 2 * tiles_wide >= di->sm_count;
+    const long long tiles = wide ? tiles_wide : tiles_narrow;
+    const int grid = tiles < di->sm_count ? (int)tiles : di->sm_count;
+    const uint32_t idesc = hg_idesc(128, wide ? 256 : 128, pr.bf16);
+    const int gm = band_rows(HG_BM);
+    auto launch = [&](auto kernel, int threads, size_t smem_bytes) {
+        kernel<<<grid, threads, smem_bytes, s>>>(map_a, map_b, map_d, out, raw, m, n, k, pr.batches, vec_ok, gm, idesc);
+        return check_launch();
+    };
+    if (tma_ok) {
+        if (wide) {
+            st = ensure_smem_optin<hgemm_tc_kernel<256, false>>(di);
+            return st ? st : launch(hgemm_tc_kernel<256, false>, HG_THREADS, HgTile<256>::SMEM_BYTES);
+        }
+        st = ensure_smem_optin<hgemm_tc_kernel<128, false>>(di);
+        return st ? st : launch(hgemm_tc_kernel<128, false>, HG_THREADS, HgTile<128>::SMEM_BYTES);
+    }
+    if (!tma_ok && !out.tma_store) map_d = CUtensorMap{};
+    if (wide) {
+        st = ensure_smem_optin<hgemm_tc_kernel<256, true>>(di);
+        return st ? st : launch(hgemm_tc_kernel<256, true>, HG_CPA_THREADS, HgTile<256>::SMEM_BYTES);
+    }
+    st = ensure_smem_optin<hgemm_tc_kernel<128, true>>(di);
+    return st ? st : launch(hgemm_tc_kernel<128, true>, HG_CPA_THREADS, HgTile<128>::SMEM_BYTES);
 }
 
 }  // namespace tb200
 
 using namespace tb200;
 
-// C(fp32) = A(fp16) * B(fp16) with the tile stores described by `out`.
-static int hgemm_launch(int m, int n, int k, const uint16_t *a, const uint16_t *b, HgOut out, tb200_stream_t stream) {
-    out.xpose = out.ndst >= option_value(TB200_OPT_HGEMM_LINE_STORES);
+extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c, tb200_stream_t stream) {
     if (m < 0 || n < 0 || k < 0) return TB200_ERR_INVALID_ARG;
     if (m == 0 || n == 0) return TB200_OK;
-    if (k > 0 && (!a || !b)) return TB200_ERR_INVALID_ARG;
-    if (out.ndst < 1 || out.ndst > HG_MAX_DST || out.ld < n || out.col_off < 0 || out.col_off > out.ld - n) return TB200_ERR_INVALID_ARG;
-    if (!aligned_to(a, 2) || !aligned_to(b, 2)) return TB200_ERR_ALIGNMENT;
-    bool vec = n % 4 == 0 && out.ld % 4 == 0 && out.col_off % 4 == 0;
-    for (int p = 0; p < out.ndst; ++p) {
-        if (!out.dst[p]) return TB200_ERR_INVALID_ARG;
-        if (!aligned_to(out.dst[p], 4)) return TB200_ERR_ALIGNMENT;
-        vec = vec && aligned_to(out.dst[p], 16);
-    }
-    int st;
-    const DeviceInfo *di = device_info(&st);
-    if (!di) return st;
-    cudaStream_t s = (cudaStream_t)stream;
-    // tensor-core path: TMA needs 16-byte aligned bases and row pitches; tiny products are not worth a 128x256 tile
-    const bool tensor = k >= 32 && k % 8 == 0 && n % 8 == 0 && aligned_to(a, 16) && aligned_to(b, 16) &&
-                        (long long)m * n >= 64 * 64;
-    if (!tensor) {
-        // the CUDA-core kernel writes one dense [m][n] matrix
-        if (out.ndst != 1 || out.ld != n) return TB200_ERR_INVALID_ARG;
-        dim3 grid((n + 31) / 32, (m + 31) / 32);
-        st = ensure_kernel<gemm_generic_kernel<uint16_t>, 0>(di);
-        if (st) return st;
-        gemm_generic_kernel<uint16_t><<<grid, 1024, 0, s>>>(m, n, k, 1.0f, a, b, 0.0f, out.dst[0]);
-        return check_launch();
-    }
-    CUtensorMap map_a, map_b;
-    st = make_map_f16(&map_a, a, (uint64_t)k, (uint64_t)m, HG_BM);
-    if (st) return st;
-    st = make_map_f16(&map_b, b, (uint64_t)n, (uint64_t)k, HG_BK);
-    if (st) return st;
-    const int c_vec_ok = vec;
-    // tile rows per band: the band's A panels (rows x k halves) should take about 48 MB of the 126 MB L2
-    auto band_rows = [&](int tile_m) {
-        long long g = (48ll << 20) / ((long long)tile_m * k * 2);
-        return (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
-    };
-    // SM pairs pay off once there are at least two waves of 256 x 256 tiles; smaller products fill the
-    // machine better with 128 x 256 tiles on single CTAs
-    if (option_value(TB200_OPT_HGEMM_SM_PAIRS) && ((m + 255) / 256) * ((n + 255) / 256) >= 2 * (di->sm_count / 2)) {
-        // SM pairs: 256 x 256 tiles, one cluster of two CTAs each
-        st = ensure_smem_optin<hgemm_tc2_kernel>(di);
-        if (st) return st;
-        const int tiles2 = ((m + 255) / 256) * ((n + 255) / 256);
-        const int pairs = tiles2 < di->sm_count / 2 ? tiles2 : di->sm_count / 2;
-        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, out, m, n, k, c_vec_ok, band_rows(256));
-        return check_launch();
-    }
-    st = ensure_smem_optin<hgemm_tc_kernel>(di);
-    if (st) return st;
-    const int tiles = ((m + HG_BM - 1) / HG_BM) * ((n + HG_BN - 1) / HG_BN);
-    const int grid = tiles < di->sm_count ? tiles : di->sm_count;
-    hgemm_tc_kernel<<<grid, HG_THREADS, HG_SMEM_BYTES, s>>>(map_a, map_b, out, m, n, k, c_vec_ok, band_rows(HG_BM));
-    return check_launch();
-}
-
-extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c, tb200_stream_t stream) {
-    if (m > 0 && n > 0 && !c) return TB200_ERR_INVALID_ARG;
+    if (!c) return TB200_ERR_INVALID_ARG;
     HgOut out{};
-    out.dst[0] = c, out.ld = n, out.col_off = 0, out.ndst = 1;
-    if (m == 0 || n == 0) return m < 0 || n < 0 || k < 0 ? TB200_ERR_INVALID_ARG : TB200_OK;
-    return hgemm_launch(m, n, k, a, b, out, stream);
+    out.dst[0] = c, out.ld = n, out.ndst = 1, out.alpha = 1.f, out.out_type = TB200_OUT_F32;
+    return hgemm_launch(HgProblem{m, n, k, 1, a, b, 0, 0, false}, out, stream);
 }
 
 extern "C" int tb200_hgemm_f32_scatter(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *const *dst, int ndst,
@@ -659,6 +1003,22 @@ extern "C" int tb200_hgemm_f32_scatter(int m, int n, int k, const uint16_t *a, c
     if (!dst || ndst < 1 || ndst > HG_MAX_DST) return TB200_ERR_INVALID_ARG;
     HgOut out{};
     for (int p = 0; p < ndst; ++p) out.dst[p] = dst[p];
-    out.ld = ld, out.col_off = col_offset, out.ndst = ndst;
-    return hgemm_launch(m, n, k, a, b, out, stream);
+    out.ld = ld, out.col_off = col_offset, out.ndst = ndst, out.alpha = 1.f, out.out_type = TB200_OUT_F32;
+    return hgemm_launch(HgProblem{m, n, k, 1, a, b, 0, 0, false}, out, stream);
+}
+
+extern "C" int tb200_gemm_ex(int m, int n, int k, int in_type, const void *a, const void *b, int out_type, void *d, float alpha, float beta,
+                             const void *c, const void *bias, int activation, int batch_count, tb200_stream_t stream) {
+    if (in_type != TB200_IN_F16 && in_type != TB200_IN_BF16) return TB200_ERR_INVALID_ARG;
+    if (m < 0 || n < 0 || k < 0 || batch_count < 0) return TB200_ERR_INVALID_ARG;
+    if (m == 0 || n == 0 || batch_count == 0) return TB200_OK;
+    if (!d) return TB200_ERR_INVALID_ARG;
+    if (bias && batch_count > 1) return TB200_ERR_INVALID_ARG;  // one bias row per call
+    HgOut out{};
+    out.dst[0] = d, out.ld = n, out.ndst = 1, out.batch_stride = (long long)m * n;
+    out.c = beta != 0.f ? (c ? c : d) : nullptr, out.bias = bias, out.alpha = alpha, out.beta = beta;
+    out.out_type = out_type, out.act = activation;
+    HgProblem pr{m, n, k, batch_count, reinterpret_cast<const uint16_t *>(a), reinterpret_cast<const uint16_t *>(b), (long long)m * k,
+                 (long long)k * n, in_type == TB200_IN_BF16};
+    return hgemm_launch(pr, out, stream);
 }

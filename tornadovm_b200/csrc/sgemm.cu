@@ -21,7 +21,17 @@ namespace tb200 {
 constexpr int SG_BM = 128, SG_BN = 128, SG_BK = 16, SG_THREADS = 256;
 constexpr int SG_APAD = 4;  // row padding of the transposed A tile (bank spread)
 
-// Requirements: k % 4 == 0, n % 4 == 0, A and B 16-byte aligned.
+// 128-bit global load, or two 64-bit ones for operands that are only 8-byte aligned (a TornadoVM array
+// behind a 24-byte header)
+template <bool VEC4>
+__device__ __forceinline__ float4 sg_load4(const float *p) {
+    if (VEC4) return __ldg(reinterpret_cast<const float4 *>(p));
+    const float2 lo = __ldg(reinterpret_cast<const float2 *>(p)), hi = __ldg(reinterpret_cast<const float2 *>(p) + 1);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+// Requirements: k % 4 == 0, n % 4 == 0, A and B 16-byte aligned (VEC4) or 8-byte aligned.
+template <bool VEC4>
 __global__ void __launch_bounds__(SG_THREADS, 2)
 sgemm_tiled_kernel(int m, int n, int k, float alpha, const float *__restrict__ A, const float *__restrict__ B,
                    float beta, float *__restrict__ C) {
@@ -54,11 +64,9 @@ sgemm_tiled_kernel(int m, int n, int k, float alpha, const float *__restrict__ A
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int gr = bm + a_row + 64 * j, gk = k0 + a_kq;
-            ra[j] = (gr < m && gk < k) ? __ldg(reinterpret_cast<const float4 *>(A + (size_t)gr * k + gk))
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+            ra[j] = (gr < m && gk < k) ? sg_load4<VEC4>(A + (size_t)gr * k + gk) : make_float4(0.f, 0.f, 0.f, 0.f);
             const int gkb = k0 + b_row + 8 * j, gc = bn + b_col;
-            rb[j] = (gkb < k && gc < n) ? __ldg(reinterpret_cast<const float4 *>(B + (size_t)gkb * n + gc))
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+            rb[j] = (gkb < k && gc < n) ? sg_load4<VEC4>(B + (size_t)gkb * n + gc) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     };
     auto store_shared = [&](int buf) {
@@ -145,12 +153,18 @@ extern "C" int tb200_sgemm(int m, int n, int k, float alpha, const float *a, con
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool fast = k > 0 && k % 4 == 0 && n % 4 == 0 && aligned_to(a, 16) && aligned_to(b, 16) && m >= 64 && n >= 64;
+    const bool fast = k > 0 && k % 4 == 0 && n % 4 == 0 && aligned_to(a, 8) && aligned_to(b, 8) && m >= 64 && n >= 64;
     if (fast) {
         dim3 grid((n + SG_BN - 1) / SG_BN, (m + SG_BM - 1) / SG_BM);
-        st = ensure_kernel<sgemm_tiled_kernel, 0>(di);
-        if (st) return st;
-        sgemm_tiled_kernel<<<grid, SG_THREADS, 0, s>>>(m, n, k, alpha, a, b, beta, c);
+        if (aligned_to(a, 16) && aligned_to(b, 16)) {
+            st = ensure_kernel<sgemm_tiled_kernel<true>, 0>(di);
+            if (st) return st;
+            sgemm_tiled_kernel<true><<<grid, SG_THREADS, 0, s>>>(m, n, k, alpha, a, b, beta, c);
+        } else {
+            st = ensure_kernel<sgemm_tiled_kernel<false>, 0>(di);
+            if (st) return st;
+            sgemm_tiled_kernel<false><<<grid, SG_THREADS, 0, s>>>(m, n, k, alpha, a, b, beta, c);
+        }
     } else {
         dim3 grid((n + 31) / 32, (m + 31) / 32);
         st = ensure_kernel<gemm_generic_kernel<float>, 0>(di);

@@ -11,6 +11,8 @@ marshals positional arguments into one native call and checks its status.
 from __future__ import annotations
 
 import ctypes as C
+import os
+import sys
 
 from .b200 import LIBRARY_NAME, B200Options
 from .native import B200Native
@@ -68,8 +70,12 @@ class B200Context:
             self.workspace_ptr, self.workspace_bytes = out.value, required
 
 
+#: TB200_LOG=1 prints one line per dispatch to stderr (function, scalar arguments, tuning)
+_LOG = os.environ.get("TB200_LOG", "") not in ("", "0")
+
 _QUANT_FUNCTIONS = {"q8Gemv", "q8GemvBytes", "q4GemvBytes"}
 _GROUPED_FUNCTIONS = {"q8GemvBytesGrouped": "tb200_q8b_gemv_i8_grouped", "q4GemvBytesGrouped": "tb200_q4b_gemv_i8_grouped"}
+_BIAS_ACTIVATIONS = {"gemmBiasRelu": 1, "gemmBiasGelu": 2, "gemmBiasSilu": 3, "gemmBiasSigmoid": 4, "gemmBiasTanh": 5, "gemmBiasHardSwish": 6}
 _PACKED_FUNCTIONS = {"q8GemvBytesPacked": ("tb200_q8b_gemv_i8_grouped", 34), "q4GemvBytesPacked": ("tb200_q4b_gemv_i8_grouped", 18)}
 
 
@@ -87,7 +93,9 @@ class B200LibraryProvider:
 
     # operation classes of tb200_prepare (include/tornado_b200.h)
     _PREPARE_CLASS = {"sgemv": 1, "q8Gemv": 2, "q8GemvBytes": 2, "q4GemvBytes": 2, "q8GemvBytesGrouped": 2,
-                      "q4GemvBytesGrouped": 2, "q8GemvBytesPacked": 2, "q4GemvBytesPacked": 2, "sgemm": 4, "hgemmF32": 8}
+                      "q4GemvBytesGrouped": 2, "q8GemvBytesPacked": 2, "q4GemvBytesPacked": 2, "sgemm": 4, "hgemmF32": 8, "hgemm": 8, "bgemm": 8, "hgemmBatched": 8,
+                      "gemmBiasRelu": 8, "gemmBiasGelu": 8, "gemmBiasSilu": 8, "gemmBiasSigmoid": 8, "gemmBiasTanh": 8,
+                      "gemmBiasHardSwish": 8}
 
     def prepare(self, descriptor, context: B200Context) -> None:
         """Runs in the pre-launch pass, before any capture (TornadoVMInterpreter.java:1036-1055) and possibly
@@ -117,6 +125,9 @@ class B200LibraryProvider:
         scoped = isinstance(tuning, B200Options) and tuning.overlap_launches
         if scoped:
             B200Native.call("tb200_set_thread_option", 1, 1)  # TB200_OPT_OVERLAP_LAUNCHES
+        if _LOG:
+            shape = [inv.getArg(i) for i in range(len(inv._args)) if not inv.isReference(i)]
+            sys.stderr.write(f"[tb200] plan {inv.getExecutionPlanId()} dispatch {functionName}{tuple(shape)} exact_int={exact} overlap={scoped}\n")
         try:
             st = self._dispatch(lib, functionName, inv, ctx, exact)
         finally:
@@ -162,6 +173,14 @@ class B200LibraryProvider:
             st = lib.tb200_sgemm(A(0), A(1), A(2), A(3), P(4), P(5), A(6), P(7), ctx.stream)
         elif functionName == "hgemmF32":  # (m, n, k, a, b, c)
             st = lib.tb200_hgemm_f32(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
+        elif functionName in ("hgemm", "bgemm"):  # (m, n, k, alpha, a, b, beta, d): 16-bit in and out, D in place
+            t = 0 if functionName == "hgemm" else 1
+            st = lib.tb200_gemm_ex(A(0), A(1), A(2), t, P(4), P(5), 1 + t, P(7), A(3), A(6), None, None, 0, 1, ctx.stream)
+        elif functionName == "hgemmBatched":  # (m, n, k, alpha, a, b, beta, d, batchCount)
+            st = lib.tb200_gemm_ex(A(0), A(1), A(2), 0, P(4), P(5), 1, P(7), A(3), A(6), None, None, 0, A(8), ctx.stream)
+        elif functionName in _BIAS_ACTIVATIONS:  # (m, n, k, a, b, bias, d): fp16 in and out
+            st = lib.tb200_gemm_ex(A(0), A(1), A(2), 0, P(3), P(4), 1, P(6), 1.0, 0.0, None, P(5), _BIAS_ACTIVATIONS[functionName], 1,
+                                   ctx.stream)
         else:
             raise RuntimeError(f"[ERROR] B200 function not supported: {functionName}")
         return st

@@ -54,6 +54,14 @@ class CudaDevice:
     def getNativeContext(self, plan_id: int) -> int:  # noqa: N802
         return 0  # primary context, current once torch has selected the device
 
+    def nvtxRangePush(self, name: str) -> None:  # noqa: N802
+        """Host-side NVTX range around a library task (TornadoNativeStreamSupport.nvtxRangePush,
+        spi/TornadoNativeStreamSupport.java:48-63); a no-op unless a profiler is attached."""
+        torch.cuda.nvtx.range_push(name)
+
+    def nvtxRangePop(self) -> None:  # noqa: N802
+        torch.cuda.nvtx.range_pop()
+
 
 class _LibraryTask:
     def __init__(self, task_id, descriptor):
@@ -175,7 +183,13 @@ class TornadoExecutionPlan:
             params = d.getParameters()
             ptrs = [self._device_pointer(p) if isinstance(p, TornadoNativeArray) else None for p in params]
             inv = LibraryInvocation(params, ptrs, self.context, d.getTuning(), self.device, self.plan_id)
-            self.provider.dispatch(d.getFunctionName(), inv)
+            # the interpreter wraps every library dispatch in an NVTX range named library::function
+            # (TornadoVMInterpreter.java:1301-1315)
+            self.device.nvtxRangePush(f"{d.getLibraryName()}::{d.getFunctionName()}")
+            try:
+                self.provider.dispatch(d.getFunctionName(), inv)
+            finally:
+                self.device.nvtxRangePop()
 
     def execute(self):
         g = self.graph
