@@ -678,6 +678,41 @@ def run_hgemm_sharded(args):
         dist.destroy_process_group()
 
 
+def run_probe(args):
+    """--sections probe --probe FMT,MODE,BATCH | hgemm,N: a handful of launches of one kernel on a small footprint
+    (four 14336 x 4096 matrices, or one GEMM), for profiler captures."""
+    import torch
+    from tornadovm_b200.native import B200Native
+    lib = B200Native.load()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    P = lambda t: C.c_void_p(t.data_ptr())
+    S = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    what = args.probe.split(",")
+    if what[0] == "hgemm":
+        n = int(what[1])
+        a = (torch.randn((n, n), device=dev) / n**0.5).half()
+        b = (torch.randn((n, n), device=dev) / n**0.5).half()
+        c = torch.empty((n, n), device=dev)
+        for _ in range(3):
+            B200Native.call("tb200_hgemm_f32", n, n, n, P(a), P(b), P(c), S)
+    else:
+        fmt, mode, batch = what[0], what[1], int(what[2])
+        bb = 18 if fmt == "q4b" else 34
+        w = torch.randint(0, 256, (4, ROWS * (COLS // 32) * bb), dtype=torch.uint8, device=dev)
+        x = torch.randn((batch, COLS), device=dev)
+        y = torch.empty((batch, ROWS), device=dev)
+        n_ws = lib.tb200_qx_workspace_bytes(COLS, batch)
+        ws = torch.empty(n_ws, dtype=torch.uint8, device=dev)
+        for i in range(6):
+            if mode == "int":
+                B200Native.call(f"tb200_{fmt}_gemv_i8", ROWS, COLS, batch, P(w[i % 4]), P(x), P(y), P(ws), n_ws, S)
+            else:
+                B200Native.call(f"tb200_{fmt}_gemv", ROWS, COLS, batch, P(w[i % 4]), P(x), P(y), S)
+    torch.cuda.synchronize()
+    print(json.dumps({"probe": args.probe, "status": B200Native.device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -688,12 +723,15 @@ def main():
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--group", type=int, default=LAYERS, help="matrices per launch (a divisor of the 32 per step)")
     ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q8layers,q4,sgemm,hgemm; or hgemm_sharded under torch.distributed.run) and print their timings; for profiling")
+    ap.add_argument("--probe", default="q8b,int,8", help="with --sections probe: FMT,MODE,BATCH (q8b|q4b, int|f32) or hgemm,N")
     ap.add_argument("--hgemm-sizes", default="2048,4096,8192,16384")
     ap.add_argument("--hgemm-variant", default="pairs", choices=["pairs", "single"],
                     help="with --sections: 256x256 tiles on SM pairs (the default of the library) or 128x256 tiles on single SMs")
     args = ap.parse_args()
     if args.sections == "hgemm_sharded":
         run_hgemm_sharded(args)
+    elif args.sections == "probe":
+        run_probe(args)
     elif args.sections:
         import torch
         from tornadovm_b200.native import B200Native

@@ -371,6 +371,18 @@ enum tb200_activation {
 int tb200_gemm_ex(int m, int n, int k, int in_type, const void *a, const void *b, int out_type, void *d, float alpha, float beta,
                   const void *c, const void *bias, int activation, int batch_count, tb200_stream_t stream);
 
+/* ---- int8 GEMM, int32 accumulate and output -----------------------------------
+ * C(s32)[m][n] = A(s8)[m][k] * B(s8)[k][n], row-major, exact.
+ * Replaces the tile-API int8 kernel (KernelContext.mmaInt8 with MMAShape.M16N8K32,
+ * tornado-api/.../KernelContext.java:703-800; kernel and reference loop in
+ * tornado-unittests/.../kernelcontext/matrices/TestMatrixMultiplicationMMAInt8.java:70-172) on
+ * tcgen05.mma.kind::i8.  Both operands are fed K-major: B is transposed once per call into `workspace`
+ * (tb200_igemm_workspace_bytes(n, k) bytes, 16-byte aligned; provider-owned like the mat-vec workspace).
+ * Tensor-core shapes: k % 16 == 0, 16-byte aligned A, a workspace; other cases run a CUDA-core kernel. */
+size_t tb200_igemm_workspace_bytes(int n, int k);
+int tb200_igemm_s32(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
+                    tb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

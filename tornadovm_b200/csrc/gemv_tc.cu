@@ -64,7 +64,6 @@ struct TcArgs {
     int phases;    // ceil(chunks / ks)
     int max_units; // most 16-row units any CTA walks (sizes the running sums when phases > 1)
     int stages;    // bulk form: stages of the CTA-wide ring
-    int debug;     // DEBUG: 1 = no compute, 2 = no copies
 };
 
 __device__ __forceinline__ float4 ldg_f4(const float *p, bool vec) {
@@ -431,7 +430,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
 
     if (warp == TC_KS_MAX + 1) {
         // ================= producer (bulk form) =================
-        if (BULK && lane == 0 && !(args.debug & 2)) {
+        if (BULK && lane == 0) {
             // (phase, unit) and (stage, use count of the stage) advance as counters: no divisions in the loop
             int p = 0, u = 0, st = 0, use = 0;
             for (int it = 0; it < total; ++it, (++u == nunits ? (u = 0, ++p) : 0), (++st == S ? (st = 0, ++use) : 0)) {
@@ -491,7 +490,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
             const unsigned char *rp0, *sp0;
             int wp, sp;
             if (BULK) {
-                if (!(args.debug & 2) && !mbar_wait(&full_bar[st], use & 1)) break;
+                if (!mbar_wait(&full_bar[st], use & 1)) break;
                 const unsigned char *base = smem_raw + (size_t)st * stage_bytes;
                 rp0 = base + g * wpitch + warp * T::WROW, wp = wpitch;
                 sp0 = base + 16 * wpitch + g * spitch + warp * 16, sp = spitch;
@@ -505,7 +504,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
             const int r0 = row_begin + u * 16 + g;
-            if (valid && !(args.debug & 1))
+            if (valid)
                 consume_chunk<FMT, NT, FLT, DOTS>(a, rp0, rp0 + 8 * wp, sp0, sp0 + 8 * sp, t, r0, r0 + 8, row_end, kc * TC_KB, bf, xsr, unscale, acc);
             if (BULK) {
                 __syncwarp();  // every lane has read its fragments
@@ -611,8 +610,7 @@ template <int FMT, int NT, int XSRC, bool DOTS>
 static int tc_launch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap, bool bulk) {
     TcPlan p;
     if (!tc_plan<FMT, NT>(a, di, bulk, p)) return TB200_ERR_INVALID_ARG;
-    static const int dbg = getenv("TB200_TC_DEBUG") ? atoi(getenv("TB200_TC_DEBUG")) : 0;
-    TcArgs args{a, p.ks, p.phases, p.max_units, p.stages, dbg};
+    TcArgs args{a, p.ks, p.phases, p.max_units, p.stages};
     if (bulk) {
         constexpr auto kernel = qtc_gemv_kernel<FMT, NT, XSRC, true, DOTS>;
         const int st = ensure_smem_optin<kernel>(di);

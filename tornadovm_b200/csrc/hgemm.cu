@@ -95,6 +95,16 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem], M128 x N x K32, int8 inputs, int32 accumulate
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tc_ld_32cols(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
@@ -403,7 +413,11 @@ constexpr int HG_CPA_WARPS = 4, HG_CPA_THREADS = HG_THREADS + HG_CPA_WARPS * 32,
 // default mode -- which no TMA copy accepts.  Four extra warps then fill the same 128-byte-swizzled stage layout
 // with 8-byte cp.async copies (zero fill outside the matrices), keep two stages of copies in flight each, and hand
 // a stage to the MMA warp after a proxy fence; everything from the MMA on is unchanged.
-template <int BN, bool CPA>
+// I8 = true: the same pipeline for int8 operands with int32 accumulation (tcgen05.mma.kind::i8, K = 32 per
+// instruction, 128 elements per 128-byte swizzled row).  Both operands are K-major there: A[m][k] as it is, B as
+// its transpose Bt[n][k] (the caller's [k][n] matrix is transposed once into workspace memory), so a stage is
+// 128 rows of A and BN rows of Bt, 128 bytes each -- the byte sizes of the 16-bit stage.
+template <int BN, bool CPA, bool I8 = false>
 __global__ void __launch_bounds__(CPA ? HG_CPA_THREADS : HG_THREADS, 1)
 hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
                 const __grid_constant__ HgOut out, const __grid_constant__ HgRaw raw, int M, int N, int K, int batches, int vec_ok, int gm,
@@ -425,7 +439,9 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int tiles_m = (M + HG_BM - 1) / HG_BM, tiles_n = (N + BN - 1) / BN;
     const int tiles_per_matrix = tiles_m * tiles_n;
     const int num_tiles = tiles_per_matrix * batches;
-    const int k_blocks = (K + HG_BK - 1) / HG_BK;
+    constexpr int BKE = I8 ? 2 * HG_BK : HG_BK;  // elements of K per stage (128 bytes)
+    const int k_blocks = (K + BKE - 1) / BKE;
+    static_assert(!(CPA && I8), "the int8 form needs TMA-aligned operands");
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -472,10 +488,14 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     unsigned char *a_dst = tiles + (size_t)s * TL::STAGE_BYTES;
                     unsigned char *b_dst = a_dst + HG_A_BYTES;
                     mbar_expect_tx(&full_bar[s], TL::STAGE_BYTES);
-                    tma_load_3d(a_dst, &map_a, kb * HG_BK, m0, batch, &full_bar[s]);
+                    tma_load_3d(a_dst, &map_a, kb * BKE, m0, batch, &full_bar[s]);
+                    if (I8) {
+                        tma_load_3d(b_dst, &map_b, kb * BKE, n0, batch, &full_bar[s]);  // BN rows of Bt, one box
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < BN / 64; ++j)
-                        tma_load_3d(b_dst + j * (HG_BK * 128), &map_b, n0 + j * 64, kb * HG_BK, batch, &full_bar[s]);
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_3d(b_dst + j * (HG_BK * 128), &map_b, n0 + j * 64, kb * HG_BK, batch, &full_bar[s]);
+                    }
                 }
             }
         }
@@ -503,12 +523,13 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart
                     const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
                     // B: N contiguous; 64-column boxes HG_BK*128 bytes apart, 8-k-row groups 1024 bytes apart
-                    const uint64_t b_desc = make_smem_desc(b_addr, HG_BK * 128, 1024);
+                    // (int8: Bt is K-major like A)
+                    const uint64_t b_desc = I8 ? make_smem_desc(b_addr, 16, 1024) : make_smem_desc(b_addr, HG_BK * 128, 1024);
 #pragma unroll
                     for (int k16 = 0; k16 < HG_BK / 16; ++k16) {
-                        // A advances 16 halves = 32 bytes along K; B advances 16 k-rows = 2048 bytes
-                        tc_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), idesc,
-                                   (kb > 0 || k16 > 0) ? 1u : 0u);
+                        // A advances 32 bytes along K per instruction; B advances 16 k-rows = 2048 bytes (int8: 32 bytes along K)
+                        if (I8) tc_mma_i8(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+                        else tc_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
                     }
                     tc_commit(&empty_bar[s]);  // arrives once the MMAs above have read this stage
                 }
@@ -985,9 +1006,97 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     return st ? st : launch(hgemm_tc_kernel<128, true>, HG_CPA_THREADS, HgTile<128>::SMEM_BYTES);
 }
 
+// ---- int8 GEMM -----------------------------------------------------------------------------------
+// Bt[n][k] = B[k][n], bytes; 32 x 32 tiles through shared memory
+__global__ void __launch_bounds__(256) transpose_bytes_kernel(const int8_t *__restrict__ b, int8_t *__restrict__ bt, int k, int n) {
+    __shared__ int8_t tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int r = ty; r < 32; r += 8)
+        if (k0 + r < k && n0 + tx < n) tile[r][tx] = b[(size_t)(k0 + r) * n + n0 + tx];
+    __syncthreads();
+    for (int r = ty; r < 32; r += 8)
+        if (n0 + r < n && k0 + tx < k) bt[(size_t)(n0 + r) * k + k0 + tx] = tile[tx][r];
+}
+
+// any shape and alignment: one thread per output
+__global__ void __launch_bounds__(256) igemm_generic_kernel(int m, int n, int k, const int8_t *__restrict__ a, const int8_t *__restrict__ b,
+                                                            int32_t *__restrict__ c) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)m * n) return;
+    const int row = (int)(i / n), col = (int)(i - (long long)row * n);
+    int acc = 0;
+    for (int kk = 0; kk < k; ++kk) acc += (int)a[(size_t)row * k + kk] * (int)b[(size_t)kk * n + col];
+    c[i] = acc;
+}
+
+static int igemm_launch(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
+                        tb200_stream_t stream) {
+    if (m < 0 || n < 0 || k < 0) return TB200_ERR_INVALID_ARG;
+    if (m == 0 || n == 0) return TB200_OK;
+    if (!c || (k > 0 && (!a || !b))) return TB200_ERR_INVALID_ARG;
+    if (!aligned_to(c, 4)) return TB200_ERR_ALIGNMENT;
+    int st;
+    const DeviceInfo *di = device_info(&st);
+    if (!di) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool tensor = k >= 32 && k % 16 == 0 && aligned_to(a, 16) && (long long)m * n >= 64 * 64 && workspace && aligned_to(workspace, 16) &&
+                        workspace_bytes >= (size_t)n * k;
+    if (!tensor) {
+        st = ensure_kernel<igemm_generic_kernel, 0>(di);
+        if (st) return st;
+        const long long total = (long long)m * n;
+        igemm_generic_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(m, n, k, a, b, c);
+        return check_launch();
+    }
+    st = ensure_kernel<transpose_bytes_kernel, 0>(di);
+    if (st) return st;
+    int8_t *bt = reinterpret_cast<int8_t *>(workspace);
+    transpose_bytes_kernel<<<dim3((n + 31) / 32, (k + 31) / 32), 256, 0, s>>>(b, bt, k, n);
+    st = check_launch();
+    if (st) return st;
+    HgOut out{};
+    out.dst[0] = c, out.ld = n, out.ndst = 1, out.alpha = 1.f, out.out_type = TB200_OUT_F32, out.plain = 1, out.batch_stride = (long long)m * n;
+    const bool vec = n % 4 == 0 && aligned_to(c, 16);
+    const long long tiles_wide = (long long)((m + HG_BM - 1) / HG_BM) * ((n + 255) / 256);
+    const bool wide = 2 * tiles_wide >= di->sm_count;
+    const int bn = wide ? 256 : 128;
+    CUtensorMap map_a, map_b, map_d{};
+    st = make_map(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)k, (uint64_t)m, 1, 0, 128, HG_BM);
+    if (st) return st;
+    st = make_map(&map_b, bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)k, (uint64_t)n, 1, 0, 128, (uint32_t)bn);
+    if (st) return st;
+    out.tma_store = vec;
+    if (out.tma_store && make_map(&map_d, c, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)n, (uint64_t)m, 1, 0, 32, 32) != TB200_OK) out.tma_store = 0;
+    // kind::i8: D format 2 = S32 at [4,6), A and B format 1 = signed 8-bit at [7,10) and [10,13), both K-major
+    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(HG_BM >> 4) << 24);
+    const long long tiles = (long long)((m + HG_BM - 1) / HG_BM) * ((n + bn - 1) / bn);
+    const int grid = tiles < di->sm_count ? (int)tiles : di->sm_count;
+    long long g = (48ll << 20) / ((long long)HG_BM * k);
+    const int gm = (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
+    const HgRaw raw{};
+    if (wide) {
+        st = ensure_smem_optin<hgemm_tc_kernel<256, false, true>>(di);
+        if (st) return st;
+        hgemm_tc_kernel<256, false, true><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, raw, m, n, k, 1, vec, gm, idesc);
+    } else {
+        st = ensure_smem_optin<hgemm_tc_kernel<128, false, true>>(di);
+        if (st) return st;
+        hgemm_tc_kernel<128, false, true><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, raw, m, n, k, 1, vec, gm, idesc);
+    }
+    return check_launch();
+}
+
 }  // namespace tb200
 
 using namespace tb200;
+
+extern "C" size_t tb200_igemm_workspace_bytes(int n, int k) { return n > 0 && k > 0 ? (size_t)n * k : 0; }
+
+extern "C" int tb200_igemm_s32(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
+                               tb200_stream_t stream) {
+    return igemm_launch(m, n, k, a, b, c, workspace, workspace_bytes, stream);
+}
 
 extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c, tb200_stream_t stream) {
     if (m < 0 || n < 0 || k < 0) return TB200_ERR_INVALID_ARG;
