@@ -18,6 +18,7 @@ struct QGemvArgs {
     float *y;                // [batch][rows]; may be null when dots is set
     int32_t *dots;           // optional [rows][cols/32] (batch 1, int mode)
     int rows, cols, batch;
+    int wshift;              // block-layout ring kernels: w modulo 16 (0, or 8 behind a 24-byte array header)
 };
 
 // Several matrices of one shape sharing the activation vectors, and several destinations for every

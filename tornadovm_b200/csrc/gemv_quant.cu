@@ -464,6 +464,7 @@ struct RingTraits {
     static constexpr int BB = FMT == FMT_Q4B ? 18 : 34;   // bytes per block
     static constexpr int PW = BB / 2;                     // 32-bit words per block pair
     static constexpr int CB = kChunkBlocks * BB;          // bytes per full row chunk (4352 / 2304)
+    static constexpr int CBS = CB + 16;                   // ring bytes per row chunk: a chunk may sit 8 bytes into its slot
     static constexpr int QW = FMT == FMT_Q4B ? 4 : 8;     // quant words per block
     static constexpr int CPL = 64;                        // contiguous columns per lane and pair
     static constexpr int PIECES = (CB / 16 + 31) / 32;    // 16-byte pieces per lane and row chunk (9 / 5)
@@ -494,6 +495,7 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     using T = RingTraits<FMT>;
     constexpr bool INT = MODE != MODE_FLOAT;
     static_assert(STAGES >= 2 && STAGES <= 4, "ring depth");
+    static_assert(T::PIECES * 32 >= T::CB / 16 + 1, "a shifted chunk is one piece longer");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int cols = a.cols;
     const int bpr = cols / 32;
@@ -511,8 +513,12 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     float *xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
     int *xsum = reinterpret_cast<int *>(xs_scales + B * bpr);
     const uint32_t ring_off = (uint32_t)(((size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 8 + 127) & ~(size_t)127);
-    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * T::CB;
+    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * T::CBS;
     const uint32_t ring_s = smem_u32(ring);
+    // Weights 8 bytes past a 16-byte boundary (an array behind a 24-byte header; every row chunk then is): the chunk
+    // keeps that phase in its ring slot -- its first and last 8 bytes travel as 8-byte copies, the rest as the
+    // same aligned 16-byte pieces
+    const uint32_t wsh = (uint32_t)a.wshift;
 
     // ---- issue side ------------------------------------------------------------------
     int ig = g_begin, ich = 0;
@@ -524,19 +530,29 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int vrow = min(row_begin + ig * R + r, row_end - 1);
-                const unsigned char *src;
+                const unsigned char *src;  // the 16-byte aligned address at or below this lane's first piece
                 if constexpr (GROUPED) {
                     int m = im;
                     while (vrow >= grp->row_start[m + 1]) ++m;  // vrow < row_start[count]
                     if (r == 0) im = m;  // the later chunks of this group start from its first row again
-                    src = grp->w[m] + (size_t)(vrow - grp->row_start[m]) * row_bytes + (size_t)ich * T::CB + lane * 16;
+                    src = grp->w[m] + (size_t)(vrow - grp->row_start[m]) * row_bytes + (size_t)ich * T::CB + lane * 16 - wsh;
                 } else {
-                    src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16;
+                    src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16 - wsh;
                 }
-                const uint32_t dst = ring_s + (st * R + r) * T::CB + lane * 16;
+                const uint32_t dst = ring_s + (st * R + r) * T::CBS + lane * 16;
+                if (wsh == 0) {
 #pragma unroll
-                for (int i = 0; i < T::PIECES; ++i)
-                    if (lane + 32 * i < npieces) cp_async_16(dst + i * 512, src + i * 512);
+                    for (int i = 0; i < T::PIECES; ++i)
+                        if (lane + 32 * i < npieces) cp_async_16(dst + i * 512, src + i * 512);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < T::PIECES; ++i) {
+                        const int idx = lane + 32 * i;
+                        if (idx == 0) cp_async_8(dst + 8, src + 8);
+                        else if (idx < npieces) cp_async_16(dst + i * 512, src + i * 512);
+                        else if (idx == npieces) cp_async_8(dst + i * 512, src + i * 512);
+                    }
+                }
             }
             if (++ich == nch) ich = 0, ++ig;
         }
@@ -614,7 +630,7 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
             uint32_t qa[R][T::QW], qb[R][T::QW];
 #pragma unroll
             for (int r = 0; r < R; ++r)
-                load_pair<FMT>(reinterpret_cast<const uint32_t *>(ring + (st * R + r) * T::CB) + pair * T::PW, scale[r], qa[r], qb[r]);
+                load_pair<FMT>(reinterpret_cast<const uint32_t *>(ring + (st * R + r) * T::CBS + wsh) + pair * T::PW, scale[r], qa[r], qb[r]);
             if (INT) {
                 const uint4 *xq16 = reinterpret_cast<const uint4 *>(smem_raw);
 #pragma unroll
@@ -876,7 +892,7 @@ static size_t ring_smem_bytes(int cols) {
     const size_t slots = (size_t)((cols + 2047) / 2048) * 2048 / (Cfg::INT ? 16 : 4);
     size_t off = (size_t)B * slots * 16 + (Cfg::INT ? (size_t)B * (cols / 32) * 8 : 0);  // + scales + block sums
     off = (off + 127) & ~(size_t)127;
-    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * T::CB;
+    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * T::CBS;
 }
 
 template <int FMT, int B, int MODE, bool DOTS>
@@ -1025,18 +1041,21 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     }
     // ring: every row chunk starts on a 16-byte boundary and is a whole number of 16-byte units
     // split layout: 128-bit loads need 16-byte aligned rows (cols % 32 == 0 keeps the phase)
+    // block layouts: weights 8 bytes past a 16-byte boundary keep that phase inside the ring
     Path path = PATH_GENERIC;
-    if (aligned_to(a.w, 16)) {
-        if (FMT == FMT_Q8S) path = PATH_Q8S_DIRECT;
-        else if (a.cols % 256 == 0) path = PATH_RING;
+    a.wshift = 0;
+    if (FMT == FMT_Q8S) {
+        if (aligned_to(a.w, 16)) path = PATH_Q8S_DIRECT;
+    } else if (aligned_to(a.w, 8) && a.cols % 256 == 0) {
+        path = PATH_RING, a.wshift = (int)((uintptr_t)a.w & 15);
     }
     // Tensor-core kernel with the activations in registers (gemv_tc.cu): integer mode from
     // TB200_OPT_INT_TENSOR_CORE_MIN_BATCH vectors on, float mode from the measured batch on, and every batch
-    // when the weights are only 8-byte aligned (an array behind a 24-byte header), where the alternative is
-    // the byte-load kernel.
+    // when split-layout operands are only 8-byte aligned (arrays behind a 24-byte header), where the alternative
+    // is the byte-load kernel.
     const bool overlap = option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0;
     if (option_value(TB200_OPT_TC_REGISTER_KERNEL)) {
-        const bool only8 = !aligned_to(a.w, 16) || (FMT == FMT_Q8S && a.scales && !aligned_to(a.scales, 16));
+        const bool only8 = FMT == FMT_Q8S && (!aligned_to(a.w, 16) || (a.scales && !aligned_to(a.scales, 16)));
         if (MODE == MODE_FLOAT) {
             const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 from the measured batch on, 2 always
             const int min_batch = float_tc >= 2 || only8 ? 1 : (FMT == FMT_Q8S ? 1 : 2);
@@ -1195,7 +1214,7 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
         if (!blocks[m] || shape.rows[m] < 0) return TB200_ERR_INVALID_ARG;
         if (shape.row_off[m] < 0 || shape.ld[m] < shape.rows[m] || shape.row_off[m] > shape.ld[m] - shape.rows[m]) return TB200_ERR_INVALID_ARG;
         if (!aligned_to(blocks[m], 2)) return TB200_ERR_ALIGNMENT;
-        fast = fast && aligned_to(blocks[m], 16);
+        fast = fast && aligned_to(blocks[m], 8) && (((uintptr_t)blocks[m] ^ (uintptr_t)blocks[0]) & 15) == 0;  // one phase, 0 or 8
         grp.w[m] = reinterpret_cast<const uint8_t *>(blocks[m]);
         grp.row_start[m] = (int)total;
         grp.out_off[m] = shape.out_off[m], grp.ld[m] = shape.ld[m], grp.row_off[m] = shape.row_off[m];
@@ -1227,7 +1246,7 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
     cudaStream_t s = (cudaStream_t)stream;
-    QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, (int)total, cols, batch};
+    QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, (int)total, cols, batch, (int)((uintptr_t)blocks[0] & 15)};
     if (fast && batch <= 4 && fast_batch_fits<FMT, MODE_INT>(cols, batch, PATH_RING, di)) {
         if ((long long)batch * cols <= kFusedQuantMaxElems) return launch_ring_grouped_b<FMT, MODE_INT_FUSED>(a, grp, di, s);
         int8_t *xq;

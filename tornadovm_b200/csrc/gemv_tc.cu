@@ -46,15 +46,10 @@ template <int FMT>
 struct TcTraits {
     static constexpr int BB = FMT == FMT_Q4B ? 18 : (FMT == FMT_Q8B ? 34 : 32);
     static constexpr int WROW = TC_KB * BB;                           // weight bytes per row and chunk (272 / 144 / 256)
-    static constexpr int PITCH = FMT == FMT_Q8S ? 272 : WROW;        // split layout: + the chunk's 8 fp16 scales
-    static constexpr int STAGE = 16 * PITCH;
 };
 
 template <int FMT, int NT>
 struct TcConfig {
-    // cp.async form: ring stages per warp, sized so that rings + partial buffers fit in 227 KB
-    static constexpr int STAGES = FMT == FMT_Q4B ? 4 : (NT == 1 ? 3 : 2);
-    static constexpr size_t RING = (size_t)TC_KS_MAX * STAGES * TcTraits<FMT>::STAGE;
     static constexpr size_t PARTIAL = (size_t)TC_NB * TC_KS_MAX * NT * 512;
 };
 
@@ -63,7 +58,9 @@ struct TcArgs {
     int ks;        // consumer warps in use (K chunks per phase)
     int phases;    // ceil(chunks / ks)
     int max_units; // most 16-row units any CTA walks (sizes the running sums when phases > 1)
-    int stages;    // bulk form: stages of the CTA-wide ring
+    int stages;    // stages of the CTA-wide ring
+    int wshift;    // 0, or 8 when the weights sit 8 bytes past a 16-byte boundary (an array behind a 24-byte header)
+    int sshift;    // the same for the scale array of the split layout
 };
 
 __device__ __forceinline__ float4 ldg_f4(const float *p, bool vec) {
@@ -320,12 +317,6 @@ __device__ __forceinline__ void consume_chunk(const QGemvArgs &a, const unsigned
     }
 }
 
-__host__ __device__ constexpr bool row_div_exact(int ppr, uint32_t rdiv) {
-    for (uint32_t i = 0; i < 16u * ppr; ++i)
-        if (((i * rdiv) >> 16) != i / ppr) return false;
-    return true;
-}
-
 // Shared-memory pitch of a row that holds `ks` chunks of `wrow` bytes: padded so that the eight rows a warp
 // reads together start 4 banks apart (wrow is 16 modulo 128 for the block formats, 0 for the split quants)
 __host__ __device__ __forceinline__ int tc_row_pitch(int ks, int wrow) {
@@ -333,28 +324,27 @@ __host__ __device__ __forceinline__ int tc_row_pitch(int ks, int wrow) {
     return raw + (((raw / 4 + 4) % 32) % 8 == 4 ? 16 : 32);
 }
 
-// BULK = true (16-byte aligned weights): the weights of a unit -- 16 consecutive rows, one contiguous piece of
-// global memory per phase -- arrive in a CTA-wide ring as one bulk async copy per row (TMA engine, evict-first),
-// issued by one thread of an eighteenth warp; every consumer warp reads its own chunk of the 16 rows and
-// releases the stage through an mbarrier.  Global memory is therefore read in long sequential runs, and no
-// consumer spends issue slots on copies.
-// BULK = false (weights only 8-byte aligned: a TornadoVM array behind a 24-byte header): every warp copies its
-// own (unit, chunk) pieces with 8-byte cp.async into a ring of its own.
-template <int FMT, int NT, int XSRC, bool BULK, bool DOTS>
+// The weights of a unit -- 16 consecutive rows, one contiguous piece of global memory per phase -- arrive in a
+// CTA-wide ring as one bulk async copy per row (TMA engine, evict-first), issued by one thread of an eighteenth
+// warp; every consumer warp reads its own chunk of the 16 rows and releases the stage through an mbarrier.  Global
+// memory is therefore read in long sequential runs, and no consumer spends issue slots on copies.
+// Weights that sit 8 bytes past a 16-byte boundary (a TornadoVM array behind a 24-byte header) keep that phase in
+// shared memory: the bulk copy moves the 16-byte aligned middle of a row, and two lanes of the copy warp add the
+// row's first and last 8 bytes with 8-byte cp.async copies that arrive on the same mbarrier.
+template <int FMT, int NT, int XSRC, bool DOTS>
 __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_constant__ TcArgs args) {
     using T = TcTraits<FMT>;
     constexpr bool FLT = XSRC == X_FLOAT;
-    constexpr int S8 = TcConfig<FMT, NT>::STAGES;  // ring depth of the cp.async form
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[TC_MAX_STAGES];   // bulk form: a stage has landed
-    __shared__ __align__(8) uint64_t empty_bar[TC_MAX_STAGES];  // bulk form: every consumer is done with a stage
+    __shared__ __align__(8) uint64_t full_bar[TC_MAX_STAGES];   // a stage has landed
+    __shared__ __align__(8) uint64_t empty_bar[TC_MAX_STAGES];  // every consumer is done with a stage
     __shared__ __align__(8) uint64_t pfull_bar[TC_NB];          // partial tiles of an item are complete
     __shared__ __align__(8) uint64_t pempty_bar[TC_NB];
 
     const QGemvArgs &a = args.g;
     const int cols = a.cols, rows = a.rows;
     const int bpr = cols / 32, nch = bpr / TC_KB;
-    const int KS = args.ks, phases = args.phases, S = BULK ? args.stages : S8;
+    const int KS = args.ks, phases = args.phases, S = args.stages;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
@@ -364,16 +354,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
     const int total = nunits * phases;  // items every warp walks: (phase, unit), phase-major
     const size_t row_bytes = (size_t)bpr * T::BB;
 
-    // bulk form: stage = [16 rows x wpitch weights][split layout: 16 rows x spitch scales]
+    // stage = [16 rows x wpitch weights][split layout: 16 rows x spitch scales]; both pitches leave at least 16 bytes
+    // beyond a row's data, so a row shifted by 8 bytes still fits
     const int wpitch = tc_row_pitch(KS, T::WROW), spitch = FMT == FMT_Q8S ? KS * 16 + 16 : 0;
-    const int stage_bytes = BULK ? 16 * (wpitch + spitch) : T::STAGE;
-    const size_t ring_bytes = BULK ? (size_t)S * stage_bytes : (size_t)TC_KS_MAX * S8 * T::STAGE;
+    const int stage_bytes = 16 * (wpitch + spitch);
+    const size_t ring_bytes = (size_t)S * stage_bytes;
+    const bool shifted = (args.wshift | args.sshift) != 0;
     float4 *partial = reinterpret_cast<float4 *>(smem_raw + ((ring_bytes + 127) & ~(size_t)127));  // [buffer][warp][tile][lane]
     float4 *ysum = partial + (size_t)TC_NB * TC_KS_MAX * NT * 32;                                  // [unit][tile][lane], phases > 1
 
     if (tid == 0) {
         for (int i = 0; i < TC_MAX_STAGES; ++i) {
-            mbar_init(&full_bar[i], 1);
+            mbar_init(&full_bar[i], shifted ? 33 : 1);  // the copy thread, + every lane of its warp for the row ends
             mbar_init(&empty_bar[i], KS);
         }
         for (int i = 0; i < TC_NB; ++i) {
@@ -386,70 +378,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
 
     const bool consumer = warp < KS;
 
-    // ---- cp.async form: this warp's own ring, primed before anything else (weights do not depend on the
-    // kernel before this one) ----
-    unsigned char *ring = smem_raw + (size_t)warp * S8 * T::STAGE;
-    const uint32_t ring_s = smem_u32(ring);
-    constexpr int PPR = T::PITCH / 8, WPR = T::WROW / 8, NPJ = (16 * PPR + 31) / 32;
-    constexpr uint32_t RDIV = 65536 / PPR + 1;  // piece / PPR == (piece * RDIV) >> 16 for piece < 16 * PPR
-    static_assert(row_div_exact(PPR, RDIV), "row index by multiplication");
-    auto issue = [&](int it) {
-        // lane l copies pieces l, l + 32, ... of the stage's 16 x PPR pieces: consecutive lanes take consecutive
-        // pieces of a row
-        if (!BULK && consumer && it < total) {
-            const int p = it / nunits, u = it - p * nunits;
-            const int kc = p * KS + warp;
-            if (kc < nch) {
-                const int row_first = row_begin + u * 16;
-                const int nrows = min(16, row_end - row_first);
-                const uint32_t dst = ring_s + (it % S8) * T::STAGE;
-                const unsigned char *src = a.w + (size_t)row_first * row_bytes + (size_t)kc * T::WROW;
-#pragma unroll
-                for (int j = 0; j < NPJ; ++j) {
-                    const uint32_t i = lane + 32 * j;
-                    const uint32_t r = (i * RDIV) >> 16, pp = i - r * PPR;
-                    if ((NPJ * 32 == 16 * PPR || i < 16 * PPR) && (int)r < nrows) {
-                        const unsigned char *from;
-                        if (FMT == FMT_Q8S && pp >= WPR) {
-                            if (DOTS) continue;  // the block-dot entry passes no scales
-                            from = reinterpret_cast<const unsigned char *>(a.scales + (size_t)(row_first + r) * bpr + (size_t)kc * TC_KB) + (pp - WPR) * 8;
-                        } else {
-                            from = src + (size_t)r * row_bytes + pp * 8;
-                        }
-                        cp_async_8(dst + i * 8, from);
-                    }
-                }
-            }
-        }
-        if (!BULK) cp_async_commit();
-    };
-    if (!BULK) {
-#pragma unroll
-        for (int s = 0; s < S8 - 1; ++s) issue(s);
-    }
-
     if (warp == TC_KS_MAX + 1) {
-        // ================= producer (bulk form) =================
-        if (BULK && lane == 0) {
+        // ================= producer =================
+        if (lane == 0 || shifted) {
+            const bool has_scales = FMT == FMT_Q8S && !DOTS;
+            const uint32_t wcut = args.wshift ? 16u : 0u, scut = args.sshift ? 16u : 0u;  // bytes of a row the bulk copy leaves out
             // (phase, unit) and (stage, use count of the stage) advance as counters: no divisions in the loop
             int p = 0, u = 0, st = 0, use = 0;
             for (int it = 0; it < total; ++it, (++u == nunits ? (u = 0, ++p) : 0), (++st == S ? (st = 0, ++use) : 0)) {
-                if (use > 0 && !mbar_wait(&empty_bar[st], (use - 1) & 1)) break;
+                if (use > 0) {
+                    bool ok = lane != 0 || mbar_wait(&empty_bar[st], (use - 1) & 1);
+                    if (shifted) ok = __shfl_sync(0xffffffffu, ok, 0) != 0;  // also orders the other lanes' copies after the wait
+                    if (!ok) break;
+                }
                 const int row_first = row_begin + u * 16;
                 const int nrows = min(16, row_end - row_first);
                 const int nvalid = min(KS, nch - p * KS);
-                const uint32_t wbytes = (uint32_t)nvalid * T::WROW, sbytes = (FMT == FMT_Q8S && !DOTS) ? (uint32_t)nvalid * 16 : 0;
+                const uint32_t wbytes = (uint32_t)nvalid * T::WROW, sbytes = has_scales ? (uint32_t)nvalid * 16 : 0;
                 unsigned char *dst = smem_raw + (size_t)st * stage_bytes;
-                mbar_expect_tx(&full_bar[st], (uint32_t)nrows * (wbytes + sbytes));
                 const unsigned char *src = a.w + (size_t)row_first * row_bytes + (size_t)p * KS * T::WROW;
-                for (int r = 0; r < nrows; ++r) {
-                    bulk_g2s_stream(dst + (size_t)r * wpitch, src + (size_t)r * row_bytes, wbytes, &full_bar[st]);
-                    if (sbytes)
-                        bulk_g2s_stream(dst + 16 * (size_t)wpitch + (size_t)r * spitch,
-                                        reinterpret_cast<const unsigned char *>(a.scales + (size_t)(row_first + r) * bpr + (size_t)p * KS * TC_KB),
-                                        sbytes, &full_bar[st]);
+                const unsigned char *ssrc = has_scales ? reinterpret_cast<const unsigned char *>(a.scales + (size_t)row_first * bpr + (size_t)p * KS * TC_KB) : nullptr;
+                if (lane == 0) {
+                    mbar_expect_tx(&full_bar[st], (uint32_t)nrows * (wbytes - wcut + (sbytes ? sbytes - scut : 0)));
+                    for (int r = 0; r < nrows; ++r) {
+                        // the 16-byte aligned part of the row, at the same phase in shared memory as in global memory
+                        bulk_g2s_stream(dst + (size_t)r * wpitch + wcut, src + (size_t)r * row_bytes + (wcut >> 1), wbytes - wcut, &full_bar[st]);
+                        if (sbytes)
+                            bulk_g2s_stream(dst + 16 * (size_t)wpitch + (size_t)r * spitch + scut, ssrc + (size_t)r * bpr * 2 + (scut >> 1), sbytes - scut,
+                                            &full_bar[st]);
+                    }
+                }
+                if (shifted) {
+                    // lane 2r copies the first 8 bytes of row r, lane 2r + 1 its last 8 bytes
+                    const int r = lane >> 1, last = lane & 1;
+                    if (r < nrows) {
+                        if (args.wshift) {
+                            const uint32_t off = last ? wbytes - 8 : 0u;  // relative to the row's first byte
+                            cp_async_8(smem_u32(dst + (size_t)r * wpitch + 8 + off), src + (size_t)r * row_bytes + off);
+                        }
+                        if (args.sshift && sbytes) {
+                            const uint32_t off = last ? sbytes - 8 : 0u;
+                            cp_async_8(smem_u32(dst + 16 * (size_t)wpitch + (size_t)r * spitch + 8 + off), ssrc + (size_t)r * bpr * 2 + off);
+                        }
+                    }
+                    // counts as this lane's arrival once its copies above have landed (at once if it made none)
+                    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[st])) : "memory");
                 }
             }
+            if (shifted) asm volatile("cp.async.wait_all;" ::: "memory");
         }
         return;
     }
@@ -465,7 +441,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
         float acc[NT][4];
         float unscale[2][NT];  // float mode: 2^e of vector 4j + t for each half chunk
         int phase_loaded = -1;
-        int p = 0, u = 0, st = 0, use = 0;  // (phase, unit) of the item; bulk form: its stage and the stage's use count
+        int p = 0, u = 0, st = 0, use = 0;  // (phase, unit) of the item, its stage and the stage's use count
         for (int it = 0; it < total; ++it, (++u == nunits ? (u = 0, ++p) : 0), (++st == S ? (st = 0, ++use) : 0)) {
             const int kc = p * KS + warp;
             const bool valid = kc < nch;  // the last phase may have fewer chunks than warps
@@ -487,29 +463,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
                 }
                 phase_loaded = p;
             }
-            const unsigned char *rp0, *sp0;
-            int wp, sp;
-            if (BULK) {
-                if (!mbar_wait(&full_bar[st], use & 1)) break;
-                const unsigned char *base = smem_raw + (size_t)st * stage_bytes;
-                rp0 = base + g * wpitch + warp * T::WROW, wp = wpitch;
-                sp0 = base + 16 * wpitch + g * spitch + warp * 16, sp = spitch;
-            } else {
-                cp_async_wait<S8 - 2>();
-                __syncwarp();       // item `it` has landed for every lane; every lane is done with item it - 1
-                issue(it + S8 - 1); // refills the stage of item it - 1
-                rp0 = ring + (size_t)st * T::STAGE + g * T::PITCH, wp = T::PITCH;  // S == S8 here
-                sp0 = rp0 + 256, sp = T::PITCH;
-            }
+            if (!mbar_wait(&full_bar[st], use & 1)) break;
+            const unsigned char *base = smem_raw + (size_t)st * stage_bytes;
+            const unsigned char *rp0 = base + g * wpitch + warp * T::WROW + args.wshift;
+            const unsigned char *sp0 = base + 16 * wpitch + g * spitch + warp * 16 + args.sshift;
+            const int wp = wpitch, sp = spitch;
 #pragma unroll
             for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
             const int r0 = row_begin + u * 16 + g;
             if (valid)
                 consume_chunk<FMT, NT, FLT, DOTS>(a, rp0, rp0 + 8 * wp, sp0, sp0 + 8 * sp, t, r0, r0 + 8, row_end, kc * TC_KB, bf, xsr, unscale, acc);
-            if (BULK) {
-                __syncwarp();  // every lane has read its fragments
-                if (lane == 0) mbar_arrive(&empty_bar[st]);
-            }
+            __syncwarp();  // every lane has read its fragments
+            if (lane == 0) mbar_arrive(&empty_bar[st]);
             if (!DOTS) {
                 // hand the partial tile to the reducer
                 const int buf = it % TC_NB;
@@ -523,7 +488,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
                 if (lane == 0) mbar_arrive(&pfull_bar[buf]);
             }
         }
-        if (!BULK) cp_async_wait<0>();
     } else if (!DOTS) {
         // ================= reducer =================
         int p = 0, u = 0;
@@ -581,7 +545,7 @@ struct TcPlan {
 };
 
 template <int FMT, int NT>
-static bool tc_plan(const QGemvArgs &a, const DeviceInfo *di, bool bulk, TcPlan &p) {
+static bool tc_plan(const QGemvArgs &a, const DeviceInfo *di, TcPlan &p) {
     using T = TcTraits<FMT>;
     using Cfg = TcConfig<FMT, NT>;
     const int nch = a.cols / 256;
@@ -593,39 +557,25 @@ static bool tc_plan(const QGemvArgs &a, const DeviceInfo *di, bool bulk, TcPlan 
     p.max_units = (rows_per_cta + 15) / 16 + 1;
     const size_t tail = Cfg::PARTIAL + (p.phases > 1 ? (size_t)p.max_units * NT * 512 : 0) + 128;
     const size_t limit = (size_t)di->max_smem_optin - 1024;  // the kernel's static shared memory and slack
-    if (bulk) {
-        const size_t stage = 16 * ((size_t)tc_row_pitch(p.ks, T::WROW) + (FMT == FMT_Q8S ? p.ks * 16 + 16 : 0));
-        if (tail + 2 * stage > limit) return false;
-        const size_t n = (limit - tail) / stage;
-        p.stages = (int)(n > TC_MAX_STAGES ? TC_MAX_STAGES : n);
-        p.smem = (size_t)p.stages * stage + tail;
-    } else {
-        p.stages = Cfg::STAGES;
-        p.smem = Cfg::RING + tail;
-    }
+    const size_t stage = 16 * ((size_t)tc_row_pitch(p.ks, T::WROW) + (FMT == FMT_Q8S ? p.ks * 16 + 16 : 0));
+    if (tail + 2 * stage > limit) return false;
+    const size_t n = (limit - tail) / stage;
+    p.stages = (int)(n > TC_MAX_STAGES ? TC_MAX_STAGES : n);
+    p.smem = (size_t)p.stages * stage + tail;
     return p.smem <= limit;
 }
 
 template <int FMT, int NT, int XSRC, bool DOTS>
-static int tc_launch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap, bool bulk) {
+static int tc_launch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
     TcPlan p;
-    if (!tc_plan<FMT, NT>(a, di, bulk, p)) return TB200_ERR_INVALID_ARG;
-    TcArgs args{a, p.ks, p.phases, p.max_units, p.stages};
-    if (bulk) {
-        constexpr auto kernel = qtc_gemv_kernel<FMT, NT, XSRC, true, DOTS>;
-        const int st = ensure_smem_optin<kernel>(di);
-        if (st) return st;
-        return launch_kernel(kernel, dim3(p.grid), dim3(TC_THREADS), p.smem, s, overlap, args);
-    }
-    constexpr auto kernel = qtc_gemv_kernel<FMT, NT, XSRC, false, DOTS>;
+    if (!tc_plan<FMT, NT>(a, di, p)) return TB200_ERR_INVALID_ARG;
+    // pointers are 0 or 8 modulo 16 here (tc_eligible)
+    const int wshift = (int)((uintptr_t)a.w & 15), sshift = (FMT == FMT_Q8S && a.scales) ? (int)((uintptr_t)a.scales & 15) : 0;
+    TcArgs args{a, p.ks, p.phases, p.max_units, p.stages, wshift, sshift};
+    constexpr auto kernel = qtc_gemv_kernel<FMT, NT, XSRC, DOTS>;
     const int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
     return launch_kernel(kernel, dim3(p.grid), dim3(TC_THREADS), p.smem, s, overlap, args);
-}
-
-template <int FMT>
-static bool tc_bulk(const QGemvArgs &a) {
-    return aligned_to(a.w, 16) && !(FMT == FMT_Q8S && a.scales && !aligned_to(a.scales, 16));
 }
 
 template <int FMT>
@@ -638,23 +588,22 @@ static bool tc_eligible(int mode, const QGemvArgs &a, const DeviceInfo *di) {
     if (a.dots ? mode != MODE_INT : !a.y) return false;
     const bool two = mode == MODE_FLOAT ? a.batch > 4 : a.batch > 8;
     TcPlan p;
-    return two ? tc_plan<FMT, 2>(a, di, tc_bulk<FMT>(a), p) : tc_plan<FMT, 1>(a, di, tc_bulk<FMT>(a), p);
+    return two ? tc_plan<FMT, 2>(a, di, p) : tc_plan<FMT, 1>(a, di, p);
 }
 
 template <int FMT>
 static int tc_dispatch(int mode, const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
-    const bool bulk = tc_bulk<FMT>(a);  // true: bulk copies into a CTA-wide ring; false: 8-byte cp.async per warp
     if (a.dots)
-        return a.batch <= 8 ? tc_launch<FMT, 1, X_INT_WS, true>(a, di, s, overlap, bulk)
-                            : tc_launch<FMT, 2, X_INT_WS, true>(a, di, s, overlap, bulk);
+        return a.batch <= 8 ? tc_launch<FMT, 1, X_INT_WS, true>(a, di, s, overlap)
+                            : tc_launch<FMT, 2, X_INT_WS, true>(a, di, s, overlap);
     if (mode == MODE_FLOAT)
-        return a.batch <= 4 ? tc_launch<FMT, 1, X_FLOAT, false>(a, di, s, overlap, bulk)
-                            : tc_launch<FMT, 2, X_FLOAT, false>(a, di, s, overlap, bulk);
+        return a.batch <= 4 ? tc_launch<FMT, 1, X_FLOAT, false>(a, di, s, overlap)
+                            : tc_launch<FMT, 2, X_FLOAT, false>(a, di, s, overlap);
     if (mode == MODE_INT)
-        return a.batch <= 8 ? tc_launch<FMT, 1, X_INT_WS, false>(a, di, s, overlap, bulk)
-                            : tc_launch<FMT, 2, X_INT_WS, false>(a, di, s, overlap, bulk);
-    return a.batch <= 8 ? tc_launch<FMT, 1, X_INT_FUSED, false>(a, di, s, overlap, bulk)
-                        : tc_launch<FMT, 2, X_INT_FUSED, false>(a, di, s, overlap, bulk);
+        return a.batch <= 8 ? tc_launch<FMT, 1, X_INT_WS, false>(a, di, s, overlap)
+                            : tc_launch<FMT, 2, X_INT_WS, false>(a, di, s, overlap);
+    return a.batch <= 8 ? tc_launch<FMT, 1, X_INT_FUSED, false>(a, di, s, overlap)
+                        : tc_launch<FMT, 2, X_INT_FUSED, false>(a, di, s, overlap);
 }
 
 bool qtc_eligible(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di) {
