@@ -219,12 +219,13 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             for batch in (1, 4, 8):
                 x = torch.randn((batch, COLS), device=dev)
                 yb = torch.empty((batch, ROWS), device=dev)
-                ws_n = lib.tb200_qx_workspace_bytes(COLS, batch)
+                # the provider hands its context workspace to both modes: int8 activations + scales, or fp16 pairs
+                ws_n = max(lib.tb200_qx_workspace_bytes(COLS, batch), lib.tb200_fx_workspace_bytes(COLS, batch))
                 ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
                 by = algorithmic_bytes(ROWS, COLS, batch)
                 runs = {
-                    f"q8_split_f32_b{batch}": lambda i: lib.tb200_q8_gemv(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), S),
-                    f"q8_blocks_f32_b{batch}": lambda i: lib.tb200_q8b_gemv(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), S),
+                    f"q8_split_f32_b{batch}": lambda i: lib.tb200_q8_gemv_ws(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), P(ws), ws_n, S),
+                    f"q8_blocks_f32_b{batch}": lambda i: lib.tb200_q8b_gemv_ws(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), P(ws), ws_n, S),
                     f"q8_split_int_b{batch}": lambda i: lib.tb200_q8_gemv_i8(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), P(ws), ws_n, S),
                     f"q8_blocks_int_b{batch}": lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), P(ws), ws_n, S),
                 }
@@ -278,13 +279,13 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             for batch in (1, 4, 16):
                 xs = {c: torch.randn((batch, c), device=dev) for c in (4096, 14336)}
                 ys = {r: torch.empty((batch, r), device=dev) for r in (4096, 1024, 14336, 128256)}
-                ws_n = lib.tb200_qx_workspace_bytes(14336, batch)
+                ws_n = max(lib.tb200_qx_workspace_bytes(14336, batch), lib.tb200_fx_workspace_bytes(14336, batch))
                 ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
                 by = sum(algorithmic_bytes(r, c, batch, 18) for r, c in shapes)
 
                 def sweep_f(i):
                     for (r, c), w in zip(shapes, wsets[i & 1]):
-                        lib.tb200_q4b_gemv(r, c, batch, P(w), P(xs[c]), P(ys[r]), S)
+                        lib.tb200_q4b_gemv_ws(r, c, batch, P(w), P(xs[c]), P(ys[r]), P(ws), ws_n, S)
 
                 def sweep_i(i):
                     for (r, c), w in zip(shapes, wsets[i & 1]):
@@ -336,19 +337,21 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 bh = (torch.randn((n, n), device=dev) / n**0.5).half()
                 ch = torch.empty((n, n), device=dev)
                 t = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, P(ah), P(bh), P(ch), S), 3, period=2)
+                t24 = None
+                if n == 8192:
+                    # A, B and C behind a 24-byte header (8 modulo 16), timed like the aligned product and next to it
+                    raw = [torch.empty(n * n * e + 16, dtype=torch.uint8, device=dev) for e in (2, 2, 4)]
+                    raw[0][8:8 + n * n * 2].copy_(ah.view(torch.uint8).reshape(-1))
+                    raw[1][8:8 + n * n * 2].copy_(bh.view(torch.uint8).reshape(-1))
+                    pa, pb, pc = (C.c_void_p(r.data_ptr() + 8) for r in raw)
+                    t24 = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, pa, pb, pc, S), 3, period=2)
+                    del raw
                 # a longer run (about 100 launches) next to the burst figure: the clock settles under sustained tensor load
                 t_long = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, P(ah), P(bh), P(ch), S), 50 if n <= 8192 else 10, period=2)
                 out[f"hgemm_{n}"] = {"TFLOP/s": 2 * n**3 / t / 1e12, "frac_tensor": 2 * n**3 / t / 1e12 / tensor_peak, "ms": t * 1e3,
                                      "sustained_TFLOP/s": 2 * n**3 / t_long / 1e12}
-                if n == 8192:
-                    # A and B behind a 24-byte header (8 modulo 16): the cp.async producers replace the TMA loads
-                    raw = [torch.empty(n * n * 2 + 16, dtype=torch.uint8, device=dev) for _ in range(2)]
-                    raw[0][8:8 + n * n * 2].copy_(ah.view(torch.uint8).reshape(-1))
-                    raw[1][8:8 + n * n * 2].copy_(bh.view(torch.uint8).reshape(-1))
-                    pa, pb = (C.c_void_p(r.data_ptr() + 8) for r in raw)
-                    t24 = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, pa, pb, P(ch), S), 3, period=2)
+                if t24 is not None:
                     out[f"hgemm_{n}_header24"] = {"TFLOP/s": 2 * n**3 / t24 / 1e12, "frac_tensor": 2 * n**3 / t24 / 1e12 / tensor_peak, "ms": t24 * 1e3}
-                    del raw
                 if n == 4096:
                     # fused epilogue and 16-bit output on the same product: D(fp16) = gelu(A*B + bias)
                     dh = torch.empty((n, n), dtype=torch.float16, device=dev)

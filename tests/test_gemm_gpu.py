@@ -114,6 +114,53 @@ def test_hgemm_matches_reference_loop(lib, m, n, k, header):
     assert not np.isnan(got).any() and dc.guard_intact()
 
 
+@pytest.mark.parametrize("ha,hb,hc", [(24, 24, 24), (24, 16, 16), (16, 24, 16), (16, 16, 24), (24, 24, 16)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (200, 264, 72), (384, 1000, 520)])
+def test_hgemm_operands_behind_24_byte_headers(lib, m, n, k, ha, hb, hc):
+    """Arrays 8 bytes past a 16-byte boundary, in every combination, with NaN bit patterns right in front of A and B
+    and an infinity at the end of A's first row: nothing outside a row may leak into its results."""
+    import torch
+    r = o.JavaRandom(7)
+    mul = 1.0 / np.sqrt(k)
+    a, b = r.gaussian_f16(m * k, mul), r.gaussian_f16(k * n, mul)
+    a = a.copy()
+    a[k - 1] = 0x7C00  # +inf as the last element of row 0: row 0 becomes inf / nan, row 1 must not
+    da, db, dc = DevBuf(a, ha), DevBuf(b, hb), out_buf(m * n, header=hc)
+    da.t[:ha] = 0xFF  # NaN halves in front of the arrays
+    db.t[:hb] = 0xFF
+    _ok(lib.tb200_hgemm_f32(m, n, k, da.ptr, db.ptr, dc.ptr, stream_ptr()), lib)
+    sync_and_check(lib)
+    got = dc.numpy().reshape(m, n)
+    ref = o.hgemm_ref(np.ascontiguousarray(a[k:]), b, m - 1, n, k)
+    assert np.isfinite(got[1:]).all()
+    assert o.rel_l2(got[1:], ref) <= REL_L2_FP16
+    assert not np.isfinite(got[0]).all()  # the infinity did arrive in its own row
+    raw = dc.t.cpu().numpy()
+    assert (raw[:hc] == 0xA5).all() and (raw[hc + dc.nbytes:] == 0xA5).all()
+
+
+def test_hgemm_header_24_large(lib):
+    """4096 x 4096 x 1024 behind 24-byte headers against an fp32 product of the same halves."""
+    import torch
+    m, n, k = 4096, 4096, 1024
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = (torch.randn((m, k), device="cuda", generator=g) / k**0.5).half()
+    b = (torch.randn((k, n), device="cuda", generator=g) / k**0.5).half()
+    raw = [torch.full((t.numel() * t.element_size() + 32,), 0xFF, dtype=torch.uint8, device="cuda") for t in (a, b)]
+    craw = torch.full((m * n * 4 + 32,), 0xFF, dtype=torch.uint8, device="cuda")
+    base = [(t.data_ptr() + 15) // 16 * 16 + 8 for t in (raw[0], raw[1], craw)]  # 8 modulo 16
+    offs = [bb - t.data_ptr() for bb, t in zip(base, (raw[0], raw[1], craw))]
+    raw[0][offs[0]:offs[0] + a.numel() * 2].copy_(a.view(torch.uint8).reshape(-1))
+    raw[1][offs[1]:offs[1] + b.numel() * 2].copy_(b.view(torch.uint8).reshape(-1))
+    _ok(lib.tb200_hgemm_f32(m, n, k, C.c_void_p(base[0]), C.c_void_p(base[1]), C.c_void_p(base[2]), stream_ptr()), lib)
+    sync_and_check(lib)
+    got = craw[offs[2]:offs[2] + m * n * 4].view(torch.float32).reshape(m, n)
+    want = a.float() @ b.float()
+    assert torch.isfinite(got).all()
+    assert ((got - want).norm() / want.norm()).item() <= 1e-4
+    assert (craw[:offs[2]] == 0xFF).all() and (craw[offs[2] + m * n * 4:] == 0xFF).all()
+
+
 def test_gemm_argument_errors(lib):
     d = DevBuf(np.zeros(64, np.float32))
     assert lib.tb200_sgemm(-1, 2, 2, 1.0, d.ptr, d.ptr, 0.0, d.ptr, stream_ptr()) == -1

@@ -19,6 +19,7 @@ struct QGemvArgs {
     int32_t *dots;           // optional [rows][cols/32] (batch 1, int mode)
     int rows, cols, batch;
     int wshift;              // block-layout ring kernels: w modulo 16 (0, or 8 behind a 24-byte array header)
+    int xlayout;             // int mode, tensor-core kernel: 0 = xq[batch][cols], xs[batch][cols/32]; 1 = xq[block][batch][32], xs[block][batch]
 };
 
 // Several matrices of one shape sharing the activation vectors, and several destinations for every
@@ -130,6 +131,7 @@ int qtc_dispatch(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di, cu
 // ---- helpers of gemv_quant.cu used by the allocation-free entry point ----
 int split_workspace(int cols, int batch, void *workspace, size_t workspace_bytes, int8_t **xq, float **xs);
 int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s);
+int quantize_x_layout(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s, bool interleaved);
 int q8s_gemv_quantised(const QGemvArgs &a, tb200_stream_t stream);
 
 }  // namespace tb200

@@ -792,9 +792,13 @@ __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_grouped_kernel(const QG
 // Activation quantiser: one warp per 32-element block.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) quantize_x_kernel(const float *__restrict__ x, int8_t *__restrict__ xq,
-                                                         float *__restrict__ xs, int nblocks) {
+                                                         float *__restrict__ xs, int nblocks, int bpr, int batch) {
+    // batch = 0: xq[vector][cols], xs[vector][cols / 32] (the layout of the public entries).
+    // batch > 0: xq[block][vector][32], xs[block][vector] -- what the tensor-core mat-vec chained to this kernel reads:
+    // the vectors of a column tile lie next to one another.
     const int lane = threadIdx.x & 31;
     const int wpc = blockDim.x / 32;
+    pdl_launch_dependents();  // a mat-vec chained to this kernel may start and request its weights now
     for (int blk = blockIdx.x * wpc + (threadIdx.x >> 5); blk < nblocks; blk += gridDim.x * wpc) {
         const float v = x[(size_t)blk * 32 + lane];
         float m = fabsf(v);
@@ -802,8 +806,54 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float *__restrict
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         const float scale = (m == 0.0f) ? 1.0f : __fdiv_rn(m, 127.0f);
         const float inv = __fdiv_rn(1.0f, scale);
-        xq[(size_t)blk * 32 + lane] = (int8_t)quantize_byte(v, inv);
-        if (lane == 0) xs[blk] = scale;
+        size_t at = (size_t)blk;
+        if (batch > 0) {
+            const int n = blk / bpr, b = blk - n * bpr;
+            at = (size_t)b * batch + n;
+        }
+        xq[at * 32 + lane] = (int8_t)quantize_byte(v, inv);
+        if (lane == 0) xs[at] = scale;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Activation splitter of the float mode: one warp per half chunk (128 columns) of one vector.  Writes what the
+// tensor-core mat-vec otherwise derives in every CTA: x * 2^-e as fp16 hi + lo (e from the largest magnitude of the
+// half chunk) into two planes [batch][cols], and 2^e per half chunk -- operation for operation the arithmetic of
+// the in-kernel conversion, so both forms give the same bits.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) split_x_kernel(const float *__restrict__ x, uint16_t *__restrict__ planes, float *__restrict__ unscale,
+                                                      int nhalf, int hpr, int batch) {
+    // planes[block][vector][hi 32 | lo 32] and unscale[half chunk][vector]: the vectors of a column tile lie next to
+    // one another, as the tensor-core mat-vec reads them
+    const int lane = threadIdx.x & 31;
+    const int wpc = blockDim.x / 32;
+    pdl_launch_dependents();  // the mat-vec chained to this kernel may start and request its weights now
+    for (int hc = blockIdx.x * wpc + (threadIdx.x >> 5); hc < nhalf; hc += gridDim.x * wpc) {
+        const float *p = x + (size_t)hc * 128 + lane * 4;  // vectors are contiguous and cols % 128 == 0: hc runs over all of them
+        const float v[4] = {p[0], p[1], p[2], p[3]};
+        float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        int e = ((__float_as_int(m) >> 23) & 0xFF) - 127;
+        if (m == 0.f || e > 127) e = 0;
+        e = e < -126 ? -126 : (e > 126 ? 126 : e);
+        const float prescale = __int_as_float((127 - e) << 23);
+        uint32_t h[2], l[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float w0 = v[2 * i] * prescale, w1 = v[2 * i + 1] * prescale;
+            const __half2 hh = __floats2half2_rn(w0, w1);
+            const float2 back = __half22float2(hh);
+            const __half2 ll = __floats2half2_rn(w0 - back.x, w1 - back.y);
+            h[i] = *reinterpret_cast<const uint32_t *>(&hh), l[i] = *reinterpret_cast<const uint32_t *>(&ll);
+        }
+        const int n = hc / hpr, hcv = hc - n * hpr;         // vector and its half chunk
+        const int blk = hcv * 4 + (lane >> 3);              // 32-block of this lane's four values
+        uint16_t *dst = planes + ((size_t)blk * batch + n) * 64 + (lane & 7) * 4;
+        *reinterpret_cast<uint2 *>(dst) = make_uint2(h[0], h[1]);
+        *reinterpret_cast<uint2 *>(dst + 32) = make_uint2(l[0], l[1]);
+        if (lane == 0) unscale[(size_t)hcv * batch + n] = __int_as_float((127 + e) << 23);
     }
 }
 
@@ -1064,16 +1114,51 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
             if ((float_tc || only8) && a.batch >= min_batch && qtc_eligible(FMT, MODE_FLOAT, p, di)) {
                 // at most eight vectors (sixteen fp16 columns) per pass over the weights
                 const int passes = (a.batch + 7) / 8, each = (a.batch + passes - 1) / passes;
+                // With a workspace the fp16 pairs are made once by a kernel of their own instead of once per CTA of
+                // the mat-vec (which costs a third of its run time at 8 vectors); the mat-vec is chained to that
+                // kernel by a programmatic dependent launch, like the integer mode to its quantiser.
+                const bool split_ws = xq_ws && xs_ws;
+                if (split_ws) {
+                    uint16_t *planes = reinterpret_cast<uint16_t *>(xq_ws);
+                    st = ensure_kernel<split_x_kernel, KERNEL_MAX_CARVEOUT>(di);
+                    if (st) return st;
+                    for (int b0 = 0; b0 < a.batch; b0 += each) {
+                        // the vectors of a pass: [block][vector][hi | lo]
+                        const int nb = a.batch - b0 < each ? a.batch - b0 : each;
+                        const int nhalf = nb * (a.cols / 128);
+                        split_x_kernel<<<(nhalf + 7) / 8, 256, 0, s>>>(a.x + (size_t)b0 * a.cols, planes + (size_t)b0 * a.cols * 2, xs_ws + (size_t)b0 * (a.cols / 128), nhalf,
+                                                                       a.cols / 128, nb);
+                        st = check_launch();
+                        if (st) return st;
+                    }
+                }
                 for (int b0 = 0; b0 < a.batch; b0 += each) {
                     p.batch = a.batch - b0 < each ? a.batch - b0 : each;
                     p.x = a.x + (size_t)b0 * a.cols, p.y = a.y + (size_t)b0 * a.rows;
-                    st = qtc_dispatch(FMT, MODE_FLOAT, p, di, s, overlap && b0 == 0);
+                    if (split_ws) {
+                        p.xq = xq_ws + (size_t)b0 * a.cols * 4, p.xs = xs_ws + (size_t)b0 * (a.cols / 128);
+                        st = qtc_dispatch(FMT, MODE_FLOAT, p, di, s, b0 == 0);  // chained to the splitter
+                    } else {
+                        st = qtc_dispatch(FMT, MODE_FLOAT, p, di, s, overlap && b0 == 0);
+                    }
                     if (st) return st;
                 }
                 return TB200_OK;
             }
         } else if (a.batch >= (only8 ? 1 : option_value(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH)) && (!DOTS || a.batch == 1) &&
                    qtc_eligible(FMT, MODE, a, di)) {
+            if (MODE == MODE_INT_FUSED && xq_ws && xs_ws) {
+                // Quantising inside the mat-vec means every one of its CTAs converts all the vectors (measured: 5 us
+                // of a 14 us launch at 8 vectors, during which the weight ring fills up and the copies stall).  The
+                // activations are therefore quantised once by a small kernel of their own, and the mat-vec is chained
+                // to it with a programmatic dependent launch: it starts while the quantiser runs, requests its first
+                // weights, and waits for the quantiser only where it reads the int8 activations.
+                st = quantize_x_layout(a.cols, a.batch, a.x, xq_ws, xs_ws, s, true);
+                if (st) return st;
+                QGemvArgs b = a;
+                b.x = nullptr, b.xq = xq_ws, b.xs = xs_ws, b.xlayout = 1;
+                return qtc_dispatch(FMT, MODE_INT, b, di, s, true);
+            }
             // MODE_INT follows the quantiser kernel in plain stream order; the fused form may overlap its predecessor
             return qtc_dispatch(FMT, MODE, a, di, s, MODE == MODE_INT_FUSED && overlap);
         }
@@ -1151,7 +1236,10 @@ int split_workspace(int cols, int batch, void *workspace, size_t workspace_bytes
     return TB200_OK;
 }
 
-int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s) {
+int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s) { return quantize_x_layout(cols, batch, x, xq, xs, s, false); }
+
+// interleaved: xq[block][vector][32], xs[block][vector] (see quantize_x_kernel)
+int quantize_x_layout(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaStream_t s, bool interleaved) {
     if (!x) return TB200_ERR_INVALID_ARG;
     if (!aligned_to(x, 4)) return TB200_ERR_ALIGNMENT;
     int st;
@@ -1167,7 +1255,7 @@ int quantize_x(int cols, int batch, const float *x, int8_t *xq, float *xs, cudaS
     // driver would switch the carve-out for this small kernel and back, draining the SMs twice (about 15 us).
     st = ensure_kernel<quantize_x_kernel, KERNEL_MAX_CARVEOUT>(di);
     if (st) return st;
-    quantize_x_kernel<<<grid, 256, 0, s>>>(x, xq, xs, nblocks);
+    quantize_x_kernel<<<grid, 256, 0, s>>>(x, xq, xs, nblocks, cols / 32, interleaved ? batch : 0);
     return check_launch();
 }
 
@@ -1333,6 +1421,55 @@ extern "C" int tb200_q4b_gemv(int rows, int cols, int batch, const uint8_t *bloc
     if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
     QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
     return qgemv_dispatch<FMT_Q4B, MODE_FLOAT, false>(a, nullptr, nullptr, stream);
+}
+
+// float mode with a workspace for the split activations
+static int split_float_workspace(int cols, int batch, void *workspace, size_t workspace_bytes, int8_t **planes, float **unscale) {
+    *planes = nullptr, *unscale = nullptr;
+    if (!workspace) return workspace_bytes ? TB200_ERR_INVALID_ARG : TB200_OK;  // no workspace: conversion inside the mat-vec
+    if (cols < 0 || batch < 1) return TB200_ERR_INVALID_ARG;
+    if (!aligned_to(workspace, 16)) return TB200_ERR_ALIGNMENT;
+    if (workspace_bytes < tb200_fx_workspace_bytes(cols, batch)) return TB200_ERR_WORKSPACE;
+    *planes = reinterpret_cast<int8_t *>(workspace);
+    *unscale = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + (((size_t)cols * batch * 4 + 15) & ~(size_t)15));
+    return TB200_OK;
+}
+
+extern "C" size_t tb200_fx_workspace_bytes(int cols, int batch) {
+    if (cols < 0 || batch < 0) return 0;
+    return (((size_t)cols * batch * 4 + 15) & ~(size_t)15) + (size_t)((cols + 127) / 128) * batch * sizeof(float);
+}
+
+extern "C" int tb200_q8_gemv_ws(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x, float *y,
+                                void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
+    int8_t *planes;
+    float *unscale;
+    const int st = split_float_workspace(cols, batch, workspace, workspace_bytes, &planes, &unscale);
+    if (st) return st;
+    QGemvArgs a{reinterpret_cast<const uint8_t *>(q), scales, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
+    return qgemv_dispatch<FMT_Q8S, MODE_FLOAT, false>(a, planes, unscale, stream);
+}
+
+extern "C" int tb200_q8b_gemv_ws(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y, void *workspace,
+                                 size_t workspace_bytes, tb200_stream_t stream) {
+    if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
+    int8_t *planes;
+    float *unscale;
+    const int st = split_float_workspace(cols, batch, workspace, workspace_bytes, &planes, &unscale);
+    if (st) return st;
+    QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
+    return qgemv_dispatch<FMT_Q8B, MODE_FLOAT, false>(a, planes, unscale, stream);
+}
+
+extern "C" int tb200_q4b_gemv_ws(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y, void *workspace,
+                                 size_t workspace_bytes, tb200_stream_t stream) {
+    if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
+    int8_t *planes;
+    float *unscale;
+    const int st = split_float_workspace(cols, batch, workspace, workspace_bytes, &planes, &unscale);
+    if (st) return st;
+    QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
+    return qgemv_dispatch<FMT_Q4B, MODE_FLOAT, false>(a, planes, unscale, stream);
 }
 
 extern "C" size_t tb200_qx_workspace_bytes(int cols, int batch) {

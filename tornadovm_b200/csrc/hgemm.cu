@@ -70,13 +70,6 @@ template <int N>
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// 8-byte asynchronous copy with zero fill: src_bytes = 0 writes zeros (out-of-range pieces of a tile)
-__device__ __forceinline__ void cp_async_8_zfill(uint32_t dst_smem, const void *src, uint32_t src_bytes) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -156,6 +149,19 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tm = band * gm + (in_band - tn * rows_here);
 }
 
+// The same walk for a product whose last tile column is narrow (at most half a tile wide: a ragged N, or the four
+// columns a shifted B adds): those tiles come after all the others, so that they fall to the CTAs that have a tile
+// less than the rest instead of costing every CTA's schedule a whole tile.
+__device__ __forceinline__ void tile_coords_edge(int tile, int tiles_m, int tiles_n, int gm, bool edge_last, int &tm, int &tn) {
+    if (!edge_last) return tile_coords(tile, tiles_m, tiles_n, gm, tm, tn);
+    const int main_tiles = tiles_m * (tiles_n - 1);
+    if (tile >= main_tiles) {
+        tn = tiles_n - 1, tm = tile - main_tiles;
+        return;
+    }
+    tile_coords(tile, tiles_m, tiles_n - 1, gm, tm, tn);
+}
+
 // Instruction descriptor, kind::f16: D fp32, A/B fp16 or bf16, A K-major, B MN-major (N contiguous).
 //   [4,6) D format 1 = F32   [7,10) A format 0 = F16, 1 = BF16   [10,13) B format likewise
 //   bit 15 A major (0 = K)   bit 16 B major (1 = MN)   [17,23) N >> 3   [24,29) M >> 4
@@ -211,13 +217,15 @@ __device__ __forceinline__ float hg_activate(float x) {
     return x;
 }
 
-// 32 consecutive elements of the output type starting at element index i of p, as floats (all lanes may read the
-// same elements: one broadcast transaction per load)
+// Elements lo .. hi - 1 of the 32 consecutive elements of the output type that start at element index i of p, as
+// floats (all lanes may read the same elements: one broadcast transaction per load).  `rows_vec`: row pitches keep
+// the 16-byte phase of the base pointer; the base itself is checked here, because an array behind a 24-byte
+// header starts 8 bytes off.
 template <int OUT>
-__device__ __forceinline__ void hg_load32(const void *p, size_t i, int valid, bool vec, float (&f)[32]) {
+__device__ __forceinline__ void hg_load32(const void *p, long long i, int lo, int hi, bool rows_vec, float (&f)[32]) {
     if (OUT == TB200_OUT_F32) {
         const float *q = reinterpret_cast<const float *>(p) + i;
-        if (vec && valid == 32) {
+        if (rows_vec && lo == 0 && hi == 32 && ((uintptr_t)q & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float4 v = __ldg(reinterpret_cast<const float4 *>(q) + j);
@@ -225,12 +233,12 @@ __device__ __forceinline__ void hg_load32(const void *p, size_t i, int valid, bo
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = j < valid ? __ldg(q + j) : 0.f;
+            for (int j = 0; j < 32; ++j) f[j] = (j >= lo && j < hi) ? __ldg(q + j) : 0.f;
         }
     } else {
         const uint16_t *q = reinterpret_cast<const uint16_t *>(p) + i;
         auto cvt = [](uint16_t h) { return OUT == TB200_OUT_F16 ? half_bits_to_float(h) : __uint_as_float((uint32_t)h << 16); };
-        if (vec && valid == 32) {
+        if (rows_vec && lo == 0 && hi == 32 && ((uintptr_t)q & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint4 v = __ldg(reinterpret_cast<const uint4 *>(q) + j);
@@ -240,26 +248,26 @@ __device__ __forceinline__ void hg_load32(const void *p, size_t i, int valid, bo
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = j < valid ? cvt(__ldg(q + j)) : 0.f;
+            for (int j = 0; j < 32; ++j) f[j] = (j >= lo && j < hi) ? cvt(__ldg(q + j)) : 0.f;
         }
     }
 }
 
 // v = act(alpha * v + beta * C + bias) on the lane's 32 accumulator values (bit patterns of floats)
 template <int OUT, int ACT>
-__device__ __forceinline__ void hg_fuse32(uint32_t (&v)[32], const HgOut &out, size_t at, int col0, int valid, bool row_ok, bool vec) {
+__device__ __forceinline__ void hg_fuse32(uint32_t (&v)[32], const HgOut &out, long long at, int col0, int lo, int hi, bool row_ok, bool vec) {
     float x[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) x[j] = out.alpha * __uint_as_float(v[j]);
     if (out.beta != 0.f && out.c && row_ok) {
         float c[32];
-        hg_load32<OUT>(out.c, at, valid, vec, c);
+        hg_load32<OUT>(out.c, at, lo, hi, vec, c);
 #pragma unroll
         for (int j = 0; j < 32; ++j) x[j] = fmaf(out.beta, c[j], x[j]);
     }
     if (out.bias) {
         float b[32];
-        hg_load32<OUT>(out.bias, (size_t)col0, valid, vec, b);
+        hg_load32<OUT>(out.bias, (long long)col0, lo, hi, vec, b);
 #pragma unroll
         for (int j = 0; j < 32; ++j) x[j] += b[j];
     }
@@ -268,15 +276,15 @@ __device__ __forceinline__ void hg_fuse32(uint32_t (&v)[32], const HgOut &out, s
 }
 
 template <int OUT>
-__device__ __forceinline__ void hg_fuse32_act(uint32_t (&v)[32], const HgOut &out, size_t at, int col0, int valid, bool row_ok, bool vec) {
+__device__ __forceinline__ void hg_fuse32_act(uint32_t (&v)[32], const HgOut &out, long long at, int col0, int lo, int hi, bool row_ok, bool vec) {
     switch (out.act) {
-        case TB200_ACT_RELU: return hg_fuse32<OUT, TB200_ACT_RELU>(v, out, at, col0, valid, row_ok, vec);
-        case TB200_ACT_GELU: return hg_fuse32<OUT, TB200_ACT_GELU>(v, out, at, col0, valid, row_ok, vec);
-        case TB200_ACT_SILU: return hg_fuse32<OUT, TB200_ACT_SILU>(v, out, at, col0, valid, row_ok, vec);
-        case TB200_ACT_SIGMOID: return hg_fuse32<OUT, TB200_ACT_SIGMOID>(v, out, at, col0, valid, row_ok, vec);
-        case TB200_ACT_TANH: return hg_fuse32<OUT, TB200_ACT_TANH>(v, out, at, col0, valid, row_ok, vec);
-        case TB200_ACT_HARDSWISH: return hg_fuse32<OUT, TB200_ACT_HARDSWISH>(v, out, at, col0, valid, row_ok, vec);
-        default: return hg_fuse32<OUT, TB200_ACT_NONE>(v, out, at, col0, valid, row_ok, vec);
+        case TB200_ACT_RELU: return hg_fuse32<OUT, TB200_ACT_RELU>(v, out, at, col0, lo, hi, row_ok, vec);
+        case TB200_ACT_GELU: return hg_fuse32<OUT, TB200_ACT_GELU>(v, out, at, col0, lo, hi, row_ok, vec);
+        case TB200_ACT_SILU: return hg_fuse32<OUT, TB200_ACT_SILU>(v, out, at, col0, lo, hi, row_ok, vec);
+        case TB200_ACT_SIGMOID: return hg_fuse32<OUT, TB200_ACT_SIGMOID>(v, out, at, col0, lo, hi, row_ok, vec);
+        case TB200_ACT_TANH: return hg_fuse32<OUT, TB200_ACT_TANH>(v, out, at, col0, lo, hi, row_ok, vec);
+        case TB200_ACT_HARDSWISH: return hg_fuse32<OUT, TB200_ACT_HARDSWISH>(v, out, at, col0, lo, hi, row_ok, vec);
+        default: return hg_fuse32<OUT, TB200_ACT_NONE>(v, out, at, col0, lo, hi, row_ok, vec);
     }
 }
 
@@ -287,54 +295,62 @@ __device__ __forceinline__ uint16_t hg_to_out16(float x, int out_type) {
 
 // Epilogue of one warp for one accumulator tile: NCHUNK pieces of 32 rows (one per lane) x 32 columns.
 //   taddr     tensor-memory address of the warp's lane quarter, first column of the tile's accumulator
-//   row0      first row of the warp's 32 rows, n0 first column of the tile, batch index of the matrix
+//   row0      first row of the warp's 32 rows, n0 first column of the tile (-4 for the first tile of a product whose
+//             B sits 8 bytes past a 16-byte boundary), batch index of the matrix
+//   rows_vec  row pitches, column offset and batch stride keep the 16-byte phase of a destination's base pointer;
+//             the pointers themselves are checked here (an array behind a 24-byte header starts 8 bytes off)
 //   staging   this warp's part of the staging area (HG_STAGING_BYTES / 4 bytes, 1024-byte aligned)
 //   nstores   running count of this warp's TMA stores (selects the staging tile)
 template <int NCHUNK>
 __device__ __forceinline__ void hg_epilogue_tile(const HgOut &out, const CUtensorMap *map_d, uint32_t taddr, int row0, int n0, int batch,
-                                                 int M, int N, int vec_ok, unsigned char *staging, int lane, uint32_t &nstores) {
+                                                 int M, int N, int rows_vec, unsigned char *staging, int lane, uint32_t &nstores) {
     const int row = row0 + lane;
-    const size_t boff = (size_t)batch * out.batch_stride;
+    const long long boff = (long long)batch * out.batch_stride;
 #pragma unroll 1
     for (int c = 0; c < NCHUNK; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= N || col0 + 32 <= 0) continue;  // warp-uniform; columns beyond the matrix were not even multiplied
         uint32_t v[32];
         tc_ld_32cols(taddr + c * 32, v);
         tc_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (col0 >= N) continue;  // warp-uniform
-        const bool full = col0 + 32 <= N;
+        const int lo = col0 < 0 ? -col0 : 0, hi = col0 + 32 <= N ? 32 : N - col0;  // columns col0 + lo .. col0 + hi - 1 exist
+        const bool full = lo == 0 && hi == 32;
+        const long long at = boff + (long long)row * out.ld + out.col_off + col0;  // element index of (row, col0)
         if (!out.plain) {
-            const size_t at = boff + (size_t)row * out.ld + out.col_off + col0;
-            const int valid = full ? 32 : N - col0;
-            if (out.out_type == TB200_OUT_F32) hg_fuse32_act<TB200_OUT_F32>(v, out, at, col0, valid, row < M, vec_ok != 0);
-            else if (out.out_type == TB200_OUT_F16) hg_fuse32_act<TB200_OUT_F16>(v, out, at, col0, valid, row < M, vec_ok != 0);
-            else hg_fuse32_act<TB200_OUT_BF16>(v, out, at, col0, valid, row < M, vec_ok != 0);
+            if (out.out_type == TB200_OUT_F32) hg_fuse32_act<TB200_OUT_F32>(v, out, at, col0, lo, hi, row < M, rows_vec != 0);
+            else if (out.out_type == TB200_OUT_F16) hg_fuse32_act<TB200_OUT_F16>(v, out, at, col0, lo, hi, row < M, rows_vec != 0);
+            else hg_fuse32_act<TB200_OUT_BF16>(v, out, at, col0, lo, hi, row < M, rows_vec != 0);
         }
         if (out.out_type != TB200_OUT_F32) {
             // 16-bit outputs: the lane's 32 values are 64 contiguous bytes of its row
             if (row < M) {
                 for (int p = 0; p < out.ndst; ++p) {
-                    uint16_t *dst = reinterpret_cast<uint16_t *>(out.dst[p]) + boff + (size_t)row * out.ld + out.col_off + col0;
-                    if (vec_ok && full) {
+                    uint16_t *dst = reinterpret_cast<uint16_t *>(out.dst[p]) + at;
+                    const uintptr_t phase = (uintptr_t)dst & 15;
+                    if (rows_vec && full && (phase & 7) == 0) {
+                        uint32_t w[16];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint32_t w[4];
+                        for (int i = 0; i < 16; ++i)
+                            w[i] = (uint32_t)hg_to_out16(__uint_as_float(v[2 * i]), out.out_type) |
+                                   ((uint32_t)hg_to_out16(__uint_as_float(v[2 * i + 1]), out.out_type) << 16);
+                        if (phase == 0) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                w[i] = (uint32_t)hg_to_out16(__uint_as_float(v[8 * j + 2 * i]), out.out_type) |
-                                       ((uint32_t)hg_to_out16(__uint_as_float(v[8 * j + 2 * i + 1]), out.out_type) << 16);
-                            *reinterpret_cast<uint4 *>(dst + 8 * j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4 *>(dst + 8 * j) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) *reinterpret_cast<uint2 *>(dst + 4 * j) = make_uint2(w[2 * j], w[2 * j + 1]);
                         }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] = hg_to_out16(__uint_as_float(v[j]), out.out_type);
+                            if (j >= lo && j < hi) dst[j] = hg_to_out16(__uint_as_float(v[j]), out.out_type);
                     }
                 }
             }
             continue;
         }
         if (out.tma_store) {
+            // (the host enables this only for columns that start at 0 and 16-byte aligned destinations)
             // lane r writes row r of a 32 x 32 tile (128-byte rows, 16-byte pieces XOR-swizzled by the row: the
             // layout of a 128-byte-swizzled tensor map), then one lane hands the tile to the TMA engine
             unsigned char *tile = staging + (nstores & 1) * HG_TMA_TILE_BYTES;
@@ -353,37 +369,61 @@ __device__ __forceinline__ void hg_epilogue_tile(const HgOut &out, const CUtenso
             continue;
         }
         float *const *dsts = reinterpret_cast<float *const *>(out.dst);
-        if (out.xpose && vec_ok && full) {
-            // through shared memory: lane r wrote row r, now eight lanes store one row's 128 bytes
+        // whole 128-byte lines per row through the transposition buffer: for several destinations, and for a
+        // destination 8 bytes past a 16-byte boundary (an array behind a 24-byte header), where the alternative is
+        // one 8-byte store per lane and row.  All rows share the phase of the base pointer (rows_vec).
+        uintptr_t phase = (uintptr_t)(dsts[0] + at) & 15;
+        for (int p = 1; p < out.ndst; ++p)
+            if ((((uintptr_t)(dsts[p] + at)) & 15) != phase) phase = 1;  // mixed
+        if (rows_vec && full && ((phase == 0 && out.xpose) || phase == 8)) {
             float *stg = reinterpret_cast<float *>(staging);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
                 *reinterpret_cast<float4 *>(stg + lane * HG_XPOSE_PITCH + 4 * j) =
                     make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
             __syncwarp();
+            if (phase == 0) {
+                // eight lanes store one row's 128 bytes
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int rl = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
-                const float4 val = *reinterpret_cast<const float4 *>(stg + rl * HG_XPOSE_PITCH + c4);
-                const int grow = row0 + rl;
-                if (grow < M) {
-                    for (int p = 0; p < out.ndst; ++p)  // plain stores, to local or peer-mapped memory
-                        *reinterpret_cast<float4 *>(dsts[p] + boff + (size_t)grow * out.ld + out.col_off + col0 + c4) = val;
+                for (int i = 0; i < 8; ++i) {
+                    const int rl = i * 4 + (lane >> 3), c4 = (lane & 7) * 4;
+                    const float4 val = *reinterpret_cast<const float4 *>(stg + rl * HG_XPOSE_PITCH + c4);
+                    const int grow = row0 + rl;
+                    if (grow < M) {
+                        for (int p = 0; p < out.ndst; ++p)  // plain stores, to local or peer-mapped memory
+                            *reinterpret_cast<float4 *>(dsts[p] + boff + (long long)grow * out.ld + out.col_off + col0 + c4) = val;
+                    }
+                }
+            } else {
+                // sixteen lanes store one row's 128 bytes as 8-byte pieces
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int rl = i * 2 + (lane >> 4), c2 = (lane & 15) * 2;
+                    const float2 val = *reinterpret_cast<const float2 *>(stg + rl * HG_XPOSE_PITCH + c2);
+                    const int grow = row0 + rl;
+                    if (grow < M) {
+                        for (int p = 0; p < out.ndst; ++p)
+                            *reinterpret_cast<float2 *>(dsts[p] + boff + (long long)grow * out.ld + out.col_off + col0 + c2) = val;
+                    }
                 }
             }
             __syncwarp();
         } else if (row < M) {
             for (int p = 0; p < out.ndst; ++p) {  // plain stores, to local or peer-mapped memory
-                float *dst = dsts[p] + boff + (size_t)row * out.ld + out.col_off + col0;
-                if (vec_ok && full) {
+                float *dst = dsts[p] + at;
+                const uintptr_t phase = (uintptr_t)dst & 15;
+                if (rows_vec && full && phase == 0) {
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         *reinterpret_cast<float4 *>(dst + 4 * j) =
                             make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                } else if (rows_vec && full && phase == 8) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) *reinterpret_cast<float2 *>(dst + 2 * j) = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (col0 + j < N) dst[j] = __uint_as_float(v[j]);
+                        if (j >= lo && j < hi) dst[j] = __uint_as_float(v[j]);
                 }
             }
         }
@@ -401,27 +441,24 @@ struct HgTile {
     static constexpr uint32_t TMEM_COLS = 2 * BN;
 };
 
-// Operands for the form that does not use tensor maps (CPA).
-struct HgRaw {
-    const uint16_t *a, *b;
-    long long stride_a, stride_b;  // elements between the matrices of a batch
-};
-constexpr int HG_CPA_WARPS = 4, HG_CPA_THREADS = HG_THREADS + HG_CPA_WARPS * 32, HG_CPA_LAG = 2;
-
-// CPA = false: operands arrive by TMA tensor loads (16-byte aligned A and B).
-// CPA = true: A and B are only 8-byte aligned -- TornadoVM arrays behind a 24-byte header, the reference launcher's
-// default mode -- which no TMA copy accepts.  Four extra warps then fill the same 128-byte-swizzled stage layout
-// with 8-byte cp.async copies (zero fill outside the matrices), keep two stages of copies in flight each, and hand
-// a stage to the MMA warp after a proxy fence; everything from the MMA on is unchanged.
+// Operands 8 bytes past a 16-byte boundary (TornadoVM arrays behind a 24-byte header, the reference launcher's
+// default mode) cannot be the base of a tensor map, and a TMA copy cannot start 8 bytes into a 16-byte unit either.
+// The maps are therefore laid over the aligned address 8 bytes (4 elements) BELOW the array, which shifts the
+// matrix by four elements along its contiguous dimension, and the kernel works in the shifted coordinates:
+//   A (K contiguous): element k of a row appears at k' = k + kshift; K blocks cover k' = 0 .. K + kshift - 1, the rows
+//     of B are fetched from k' - kshift (a negative row coordinate is filled with zeros), and the kshift halves in
+//     front of every row of the first K block -- bytes that belong to the previous row or lie before the array --
+//     are overwritten with zeros in shared memory before the first MMA reads them;
+//   B (N contiguous): column n appears at n' = n + nshift; tiles cover n' = 0 .. N + nshift - 1 and the epilogue
+//     stores tile column n' to column n' - nshift, skipping the nshift columns in front of the first tile.
 // I8 = true: the same pipeline for int8 operands with int32 accumulation (tcgen05.mma.kind::i8, K = 32 per
 // instruction, 128 elements per 128-byte swizzled row).  Both operands are K-major there: A[m][k] as it is, B as
 // its transpose Bt[n][k] (the caller's [k][n] matrix is transposed once into workspace memory), so a stage is
 // 128 rows of A and BN rows of Bt, 128 bytes each -- the byte sizes of the 16-bit stage.
-template <int BN, bool CPA, bool I8 = false>
-__global__ void __launch_bounds__(CPA ? HG_CPA_THREADS : HG_THREADS, 1)
+template <int BN, bool I8 = false>
+__global__ void __launch_bounds__(HG_THREADS, 1)
 hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
-                const __grid_constant__ HgOut out, const __grid_constant__ HgRaw raw, int M, int N, int K, int batches, int vec_ok, int gm,
-                uint32_t idesc) {
+                const __grid_constant__ HgOut out, int M, int N, int K, int batches, int rows_vec, int gm, uint32_t idesc, int kshift, int nshift) {
     using TL = HgTile<BN>;
     constexpr int STAGES = TL::STAGES;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -436,17 +473,18 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     unsigned char *tiles = reinterpret_cast<unsigned char *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = (M + HG_BM - 1) / HG_BM, tiles_n = (N + BN - 1) / BN;
+    const int tiles_m = (M + HG_BM - 1) / HG_BM, tiles_n = (N + nshift + BN - 1) / BN;
     const int tiles_per_matrix = tiles_m * tiles_n;
     const int num_tiles = tiles_per_matrix * batches;
     constexpr int BKE = I8 ? 2 * HG_BK : HG_BK;  // elements of K per stage (128 bytes)
-    const int k_blocks = (K + BKE - 1) / BKE;
-    static_assert(!(CPA && I8), "the int8 form needs TMA-aligned operands");
+    const int k_blocks = (K + kshift + BKE - 1) / BKE;
+    const int edge_cols = (N + nshift) - (tiles_n - 1) * BN;  // columns of the last tile column
+    const bool edge_last = !I8 && batches == 1 && tiles_n > 1 && edge_cols <= BN / 2;
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], CPA ? HG_CPA_WARPS * 32 : 1);  // CPA: one arrival per copying thread
+            mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -470,13 +508,13 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
-        if (!CPA && lane == 0) {
+        if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int batch = tile / tiles_per_matrix;
                 int tm, tn;
-                tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
+                tile_coords_edge(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, edge_last, tm, tn);
                 const int m0 = tm * HG_BM, n0 = tn * BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -487,110 +525,81 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     unsigned char *a_dst = tiles + (size_t)s * TL::STAGE_BYTES;
                     unsigned char *b_dst = a_dst + HG_A_BYTES;
-                    mbar_expect_tx(&full_bar[s], TL::STAGE_BYTES);
-                    tma_load_3d(a_dst, &map_a, kb * BKE, m0, batch, &full_bar[s]);
                     if (I8) {
+                        mbar_expect_tx(&full_bar[s], TL::STAGE_BYTES);
+                        tma_load_3d(a_dst, &map_a, kb * BKE, m0, batch, &full_bar[s]);
                         tma_load_3d(b_dst, &map_b, kb * BKE, n0, batch, &full_bar[s]);  // BN rows of Bt, one box
                     } else {
+                        // a tile at the right edge fetches only the 64-column boxes that hold columns of the matrix
+                        const int boxes = min(BN / 64, (N + nshift - n0 + 63) / 64);
+                        mbar_expect_tx(&full_bar[s], HG_A_BYTES + boxes * (HG_BK * 128));
+                        tma_load_3d(a_dst, &map_a, kb * BKE, m0, batch, &full_bar[s]);
 #pragma unroll
                         for (int j = 0; j < BN / 64; ++j)
-                            tma_load_3d(b_dst + j * (HG_BK * 128), &map_b, n0 + j * 64, kb * HG_BK, batch, &full_bar[s]);
+                            if (j < boxes) tma_load_3d(b_dst + j * (HG_BK * 128), &map_b, n0 + j * 64, kb * HG_BK - kshift, batch, &full_bar[s]);
                     }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // one lane issues; with a shifted A the whole warp walks the loop, because all lanes clear the bytes in
+        // front of the rows of every tile's first K block
+        if (lane == 0 || kshift) {
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
                 const uint32_t acc = local_tile & 1, acc_use = local_tile >> 1;
                 if (acc_use > 0) {
                     ok = mbar_wait_abortable(&acc_empty_bar[acc], (acc_use - 1) & 1, abortp);
+                    if (kshift) ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
                 }
                 const uint32_t d_tmem = tmem_base + acc * BN;
+                // a tile at the right edge multiplies only as many columns (a multiple of 16) as the matrix has left
+                uint32_t idesc_tile = idesc;
+                if (!I8) {
+                    const int tile_in_matrix = tile - (tile / tiles_per_matrix) * tiles_per_matrix;
+                    int tm, tn;
+                    tile_coords_edge(tile_in_matrix, tiles_m, tiles_n, gm, edge_last, tm, tn);
+                    const int left = N + nshift - tn * BN;
+                    if (left < BN) idesc_tile = (idesc & ~(0x3Fu << 17)) | ((uint32_t)(((left + 15) & ~15) >> 3) << 17);
+                }
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     ok = mbar_wait_abortable(&full_bar[s], (it / STAGES) & 1, abortp);
+                    if (kshift) ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
-                    if (CPA) fence_async_shared();  // the stage was written through the generic proxy
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * TL::STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + HG_A_BYTES;
-                    // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart
-                    const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
-                    // B: N contiguous; 64-column boxes HG_BK*128 bytes apart, 8-k-row groups 1024 bytes apart
-                    // (int8: Bt is K-major like A)
-                    const uint64_t b_desc = I8 ? make_smem_desc(b_addr, 16, 1024) : make_smem_desc(b_addr, HG_BK * 128, 1024);
+                    unsigned char *a_tile = tiles + (size_t)s * TL::STAGE_BYTES;
+                    if (kshift && kb == 0) {
+                        // row r keeps its first 16-byte piece at position r % 8 of its 128 bytes (128-byte swizzle);
+                        // the first 8 bytes of that piece are the four halves in front of the row
 #pragma unroll
-                    for (int k16 = 0; k16 < HG_BK / 16; ++k16) {
-                        // A advances 32 bytes along K per instruction; B advances 16 k-rows = 2048 bytes (int8: 32 bytes along K)
-                        if (I8) tc_mma_i8(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
-                        else tc_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+                        for (int r = lane; r < HG_BM; r += 32) *reinterpret_cast<uint2 *>(a_tile + r * 128 + ((r & 7) << 4)) = make_uint2(0u, 0u);
+                        fence_async_shared();  // generic-proxy writes before the tensor core's reads
+                        __syncwarp();
                     }
-                    tc_commit(&empty_bar[s]);  // arrives once the MMAs above have read this stage
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t a_addr = smem_u32(a_tile);
+                        const uint32_t b_addr = a_addr + HG_A_BYTES;
+                        // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart
+                        const uint64_t a_desc = make_smem_desc(a_addr, 16, 1024);
+                        // B: N contiguous; 64-column boxes HG_BK*128 bytes apart, 8-k-row groups 1024 bytes apart
+                        // (int8: Bt is K-major like A)
+                        const uint64_t b_desc = I8 ? make_smem_desc(b_addr, 16, 1024) : make_smem_desc(b_addr, HG_BK * 128, 1024);
+#pragma unroll
+                        for (int k16 = 0; k16 < HG_BK / 16; ++k16) {
+                            // A advances 32 bytes along K per instruction; B advances 16 k-rows = 2048 bytes (int8: 32 bytes along K)
+                            if (I8) tc_mma_i8(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc_tile, (kb > 0 || k16 > 0) ? 1u : 0u);
+                            else tc_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), idesc_tile, (kb > 0 || k16 > 0) ? 1u : 0u);
+                        }
+                        tc_commit(&empty_bar[s]);  // arrives once the MMAs above have read this stage
+                    }
                 }
-                if (ok) tc_commit(&acc_full_bar[acc]);  // accumulator complete
+                if (ok && lane == 0) tc_commit(&acc_full_bar[acc]);  // accumulator complete
             }
-        }
-    } else if (CPA && warp >= 6) {
-        // ---------------- cp.async producers: warps 6..9 ----------------
-        const int ptid = threadIdx.x - HG_THREADS;
-        const uint32_t tiles_s = smem_u32(tiles);
-        uint32_t it = 0;
-        bool ok = true;
-        auto publish = [&](uint32_t done_it) {
-            // the copies of stage `done_it` have landed for this thread: make them visible to the tensor core's
-            // (async-proxy) reads, then count this thread's arrival
-            fence_async_shared();
-            mbar_arrive(&full_bar[done_it % STAGES]);
-        };
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int batch = tile / tiles_per_matrix;
-            int tm, tn;
-            tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
-            const int m0 = tm * HG_BM, n0 = tn * BN;
-            const uint16_t *A = raw.a + (size_t)batch * raw.stride_a, *B = raw.b + (size_t)batch * raw.stride_b;
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                const int s = it % STAGES;
-                const uint32_t use = it / STAGES;
-                if (use > 0) {
-                    ok = mbar_wait_abortable(&empty_bar[s], (use - 1) & 1, abortp);
-                    if (!ok) break;
-                }
-                const uint32_t a_dst = tiles_s + s * TL::STAGE_BYTES, b_dst = a_dst + HG_A_BYTES;
-                const int k0 = kb * HG_BK;
-                // A tile: 128 rows x 16 pieces of 4 halves; piece p of row r sits in 16-byte chunk (p / 2) ^ (r % 8)
-#pragma unroll 4
-                for (int j = 0; j < HG_BM * 16 / (HG_CPA_WARPS * 32); ++j) {
-                    const int i = ptid + j * HG_CPA_WARPS * 32, r = i >> 4, p = i & 15;
-                    const int grow = m0 + r, gk = k0 + p * 4;
-                    const bool valid = grow < M && gk < K;
-                    cp_async_8_zfill(a_dst + r * 128 + ((((p >> 1) ^ (r & 7))) << 4) + (p & 1) * 8, valid ? A + (size_t)grow * K + gk : A, valid ? 8 : 0);
-                }
-                // B tile: BN / 64 boxes of 64 k-rows x 64 columns, each row 16 pieces
-#pragma unroll 4
-                for (int j = 0; j < (BN / 64) * 64 * 16 / (HG_CPA_WARPS * 32); ++j) {
-                    const int i = ptid + j * HG_CPA_WARPS * 32, box = i >> 10, kr = (i >> 4) & 63, p = i & 15;
-                    const int gk = k0 + kr, gn = n0 + box * 64 + p * 4;
-                    const bool valid = gk < K && gn < N;
-                    cp_async_8_zfill(b_dst + box * (HG_BK * 128) + kr * 128 + ((((p >> 1) ^ (kr & 7))) << 4) + (p & 1) * 8,
-                                     valid ? B + (size_t)gk * N + gn : B, valid ? 8 : 0);
-                }
-                cp_async_commit_group();
-                if (it >= HG_CPA_LAG) {
-                    cp_async_wait_group<HG_CPA_LAG>();  // all but the newest groups: stage it - LAG is complete
-                    publish(it - HG_CPA_LAG);
-                }
-            }
-        }
-        // drain: the last stages
-        cp_async_wait_group<0>();
-        if (ok) {
-            for (uint32_t d = it >= HG_CPA_LAG ? it - HG_CPA_LAG : 0; d < it; ++d) publish(d);
         }
     } else if (warp >= 2 && warp < 6) {
         // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
@@ -602,12 +611,12 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t acc = local_tile & 1, acc_use = local_tile >> 1;
             const int batch = tile / tiles_per_matrix;
             int tm, tn;
-            tile_coords(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, tm, tn);
+            tile_coords_edge(tile - batch * tiles_per_matrix, tiles_m, tiles_n, gm, edge_last, tm, tn);
             ok = __all_sync(0xffffffffu, mbar_wait_abortable(&acc_full_bar[acc], acc_use & 1, abortp));
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-            hg_epilogue_tile<BN / 32>(out, &map_d, taddr, tm * HG_BM + quarter * 32, tn * BN, batch, M, N, vec_ok, staging, lane, nstores);
+            hg_epilogue_tile<BN / 32>(out, &map_d, taddr, tm * HG_BM + quarter * 32, tn * BN - nshift, batch, M, N, rows_vec, staging, lane, nstores);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
@@ -681,7 +690,7 @@ __device__ __forceinline__ void tc2_mma_f16(uint32_t d_tmem, uint64_t a_desc, ui
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HG_THREADS, 1)
 hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
-                 const __grid_constant__ HgOut out, int M, int N, int K, int batches, int vec_ok, int gm, uint32_t idesc) {
+                 const __grid_constant__ HgOut out, int M, int N, int K, int batches, int rows_vec, int gm, uint32_t idesc) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[H2_STAGES];   // used in the leader only
     __shared__ __align__(8) uint64_t empty_bar[H2_STAGES];  // one per CTA, signalled by the leader's commits
@@ -798,7 +807,7 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
-            hg_epilogue_tile<8>(out, &map_d, taddr, tm * 256 + (int)rank * 128 + quarter * 32, tn * 256, batch, M, N, vec_ok, staging, lane, nstores);
+            hg_epilogue_tile<8>(out, &map_d, taddr, tm * 256 + (int)rank * 128 + quarter * 32, tn * 256, batch, M, N, rows_vec, staging, lane, nstores);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty_bar[acc], 0));
@@ -838,16 +847,17 @@ static EncodeTiledFn encode_tiled_fn() {
 
 int hgemm_prepare_driver() { return encode_tiled_fn() ? TB200_OK : TB200_ERR_DRIVER; }
 
-// 3-D tensor map over `batches` row-major matrices of `outer` rows x `inner` elements, `batch_stride` elements apart;
-// box of box_inner x box_rows x 1, 128-byte swizzle (box_inner elements = 128 bytes).
+// 3-D tensor map over `batches` row-major matrices of `outer` rows x `inner` elements, rows `pitch` elements apart
+// (0: inner; a shifted matrix is 4 elements wider than its pitch, so its rows overlap) and matrices `batch_stride`
+// elements apart; box of box_inner x box_rows x 1, 128-byte swizzle (box_inner elements = 128 bytes).
 // Encoding goes through the driver; a task dispatches the same operands again and again, so the last maps of
 // the calling thread are kept and looked up by their full key (pointer, shape, type, box).
 struct MapKey {
     const void *base;
-    uint64_t inner, outer, batches, batch_stride;
+    uint64_t inner, outer, batches, batch_stride, pitch;
     uint32_t box_inner, box_rows, type;
     bool operator==(const MapKey &o) const {
-        return base == o.base && inner == o.inner && outer == o.outer && batches == o.batches && batch_stride == o.batch_stride &&
+        return base == o.base && inner == o.inner && outer == o.outer && batches == o.batches && batch_stride == o.batch_stride && pitch == o.pitch &&
                box_inner == o.box_inner && box_rows == o.box_rows && type == o.type;
     }
 };
@@ -861,8 +871,9 @@ struct MapCache {
 static thread_local MapCache t_maps;
 
 static int make_map(CUtensorMap *map, const void *base, CUtensorMapDataType type, int elem_bytes, uint64_t inner, uint64_t outer,
-                    uint64_t batches, uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows) {
-    const MapKey key{base, inner, outer, batches, batch_stride, box_inner, box_rows, (uint32_t)type};
+                    uint64_t batches, uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows, uint64_t pitch = 0) {
+    if (!pitch) pitch = inner;
+    const MapKey key{base, inner, outer, batches, batch_stride, pitch, box_inner, box_rows, (uint32_t)type};
     MapCache &mc = t_maps;
     for (int i = 0; i < MapCache::N; ++i)
         if (mc.used[i] && mc.key[i] == key) {
@@ -873,7 +884,7 @@ static int make_map(CUtensorMap *map, const void *base, CUtensorMapDataType type
     if (!fn) return TB200_ERR_DRIVER;
     cuuint64_t dims[3] = {inner, outer, batches};
     // a single matrix: the third dimension has extent 1 and its stride only has to be a valid multiple of 16 bytes
-    cuuint64_t strides[2] = {inner * elem_bytes, (batches > 1 ? batch_stride : inner * outer) * elem_bytes};
+    cuuint64_t strides[2] = {pitch * elem_bytes, (batches > 1 ? batch_stride : pitch * outer) * elem_bytes};
     cuuint32_t box[3] = {box_inner, box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(map, type, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -907,11 +918,13 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     if (!aligned_to(pr.a, 2) || !aligned_to(pr.b, 2)) return TB200_ERR_ALIGNMENT;
     const int eb = out_elem_bytes(out.out_type);
     const int per16 = 16 / eb;  // output elements per 16 bytes
-    bool vec = n % per16 == 0 && out.ld % per16 == 0 && out.col_off % per16 == 0 && out.batch_stride % per16 == 0;
+    // row pitches keep the 16-byte phase of a destination; the kernel looks at the pointers themselves
+    const bool rows_vec = n % per16 == 0 && out.ld % per16 == 0 && out.col_off % per16 == 0 && out.batch_stride % per16 == 0;
+    bool dst_aligned = true;
     for (int p = 0; p < out.ndst; ++p) {
         if (!out.dst[p]) return TB200_ERR_INVALID_ARG;
         if (!aligned_to(out.dst[p], eb)) return TB200_ERR_ALIGNMENT;
-        vec = vec && aligned_to(out.dst[p], 16);
+        dst_aligned = dst_aligned && aligned_to(out.dst[p], 16);
     }
     if ((out.c && !aligned_to(out.c, eb)) || (out.bias && !aligned_to(out.bias, eb))) return TB200_ERR_ALIGNMENT;
     if (out.beta != 0.f && !out.c) return TB200_ERR_INVALID_ARG;
@@ -920,9 +933,8 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
     cudaStream_t s = (cudaStream_t)stream;
-    // tensor-core path: TMA needs 16-byte aligned bases and row pitches; tiny products are not worth a 128 x 128 tile
-    // 8-byte aligned operands (an array behind a 24-byte header) take the same kernels with cp.async producers
-    const bool tma_ok = aligned_to(pr.a, 16) && aligned_to(pr.b, 16);
+    // tensor-core path: row pitches of 16 bytes and operands at 0 or 8 modulo 16 (an array behind a 16- or a 24-byte
+    // header); tiny products are not worth a 128 x 128 tile
     const bool tensor = k >= 32 && k % 8 == 0 && n % 8 == 0 && aligned_to(pr.a, 8) && aligned_to(pr.b, 8) && (long long)m * n >= 64 * 64 &&
                         (pr.batches == 1 || (pr.stride_a % 8 == 0 && pr.stride_b % 8 == 0));
     if (!tensor) {
@@ -939,17 +951,18 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
         }
         return TB200_OK;
     }
+    // operands 8 bytes past a 16-byte boundary: maps over the aligned address below, matrices shifted by 4 elements
+    const int kshift = aligned_to(pr.a, 16) ? 0 : 4, nshift = aligned_to(pr.b, 16) ? 0 : 4;
+    const bool aligned = kshift == 0 && nshift == 0;
     const CUtensorMapDataType in_type = pr.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap map_a{}, map_b{}, map_d;
-    if (tma_ok) {
-        st = make_map(&map_a, pr.a, in_type, 2, (uint64_t)k, (uint64_t)m, (uint64_t)pr.batches, (uint64_t)pr.stride_a, 64, HG_BM);
-        if (st) return st;
-        st = make_map(&map_b, pr.b, in_type, 2, (uint64_t)n, (uint64_t)k, (uint64_t)pr.batches, (uint64_t)pr.stride_b, 64, HG_BK);
-        if (st) return st;
-    }
-    const HgRaw raw{pr.a, pr.b, pr.stride_a, pr.stride_b};
-    // finished fp32 pieces of a single dense destination leave as TMA tensor stores (32 x 32 boxes)
-    out.tma_store = out.out_type == TB200_OUT_F32 && out.ndst == 1 && out.col_off == 0 && vec && n % 4 == 0;
+    CUtensorMap map_a, map_b, map_d;
+    st = make_map(&map_a, pr.a - kshift, in_type, 2, (uint64_t)(k + kshift), (uint64_t)m, (uint64_t)pr.batches, (uint64_t)pr.stride_a, 64, HG_BM, (uint64_t)k);
+    if (st) return st;
+    st = make_map(&map_b, pr.b - nshift, in_type, 2, (uint64_t)(n + nshift), (uint64_t)k, (uint64_t)pr.batches, (uint64_t)pr.stride_b, 64, HG_BK, (uint64_t)n);
+    if (st) return st;
+    // finished fp32 pieces of a single dense, 16-byte aligned destination leave as TMA tensor stores (32 x 32 boxes);
+    // shifted columns would start the first store at a negative coordinate
+    out.tma_store = out.out_type == TB200_OUT_F32 && out.ndst == 1 && out.col_off == 0 && rows_vec && dst_aligned && n % 4 == 0 && nshift == 0;
     if (out.tma_store) {
         st = make_map(&map_d, out.dst[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)n, (uint64_t)m, (uint64_t)pr.batches,
                       (uint64_t)out.batch_stride, 32, 32);
@@ -958,7 +971,6 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
         if (out.ld != n) out.tma_store = 0;
     }
     if (!out.tma_store) map_d = CUtensorMap{};  // unused by the kernel
-    const int vec_ok = vec;
     // tile rows per band: the band's A panels (rows x k halves) should take about 48 MB of the 126 MB L2
     auto band_rows = [&](int tile_m) {
         long long g = (48ll << 20) / ((long long)tile_m * k * 2);
@@ -966,17 +978,18 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     };
     const long long tiles256 = (long long)((m + 255) / 256) * ((n + 255) / 256) * pr.batches;
     // SM pairs pay off once there are at least two waves of 256 x 256 tiles; smaller products fill the
-    // machine better with 128 x 256 or 128 x 128 tiles on single CTAs
-    if (tma_ok && option_value(TB200_OPT_HGEMM_SM_PAIRS) && tiles256 >= 2 * (di->sm_count / 2)) {
+    // machine better with 128 x 256 or 128 x 128 tiles on single CTAs (and so do shifted operands, whose
+    // clearing of the bytes in front of A's rows stays inside one CTA there)
+    if (aligned && option_value(TB200_OPT_HGEMM_SM_PAIRS) && tiles256 >= 2 * (di->sm_count / 2)) {
         st = ensure_smem_optin<hgemm_tc2_kernel>(di);
         if (st) return st;
         const int pairs = tiles256 < di->sm_count / 2 ? (int)tiles256 : di->sm_count / 2;
-        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, pr.batches, vec_ok, band_rows(256),
+        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, pr.batches, (int)rows_vec, band_rows(256),
                                                                       hg_idesc(256, 256, pr.bf16));
         return check_launch();
     }
-    const long long tiles_wide = (long long)((m + HG_BM - 1) / HG_BM) * ((n + 255) / 256) * pr.batches;
-    const long long tiles_narrow = (long long)((m + HG_BM - 1) / HG_BM) * ((n + 127) / 128) * pr.batches;
+    const long long tiles_wide = (long long)((m + HG_BM - 1) / HG_BM) * ((n + nshift + 255) / 256) * pr.batches;
+    const long long tiles_narrow = (long long)((m + HG_BM - 1) / HG_BM) * ((n + nshift + 127) / 128) * pr.batches;
     // 128 x 128 tiles read as many operand bytes from shared memory per MMA as 128 x 256 tiles for half the
     // arithmetic and run at about half the rate per SM (2048^3: 602 against 812 TFLOP/s), so they only pay when
     // the wide tiles would leave more than half of the SMs idle
@@ -985,25 +998,16 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     const int grid = tiles < di->sm_count ? (int)tiles : di->sm_count;
     const uint32_t idesc = hg_idesc(128, wide ? 256 : 128, pr.bf16);
     const int gm = band_rows(HG_BM);
-    auto launch = [&](auto kernel, int threads, size_t smem_bytes) {
-        kernel<<<grid, threads, smem_bytes, s>>>(map_a, map_b, map_d, out, raw, m, n, k, pr.batches, vec_ok, gm, idesc);
-        return check_launch();
-    };
-    if (tma_ok) {
-        if (wide) {
-            st = ensure_smem_optin<hgemm_tc_kernel<256, false>>(di);
-            return st ? st : launch(hgemm_tc_kernel<256, false>, HG_THREADS, HgTile<256>::SMEM_BYTES);
-        }
-        st = ensure_smem_optin<hgemm_tc_kernel<128, false>>(di);
-        return st ? st : launch(hgemm_tc_kernel<128, false>, HG_THREADS, HgTile<128>::SMEM_BYTES);
-    }
-    if (!tma_ok && !out.tma_store) map_d = CUtensorMap{};
     if (wide) {
-        st = ensure_smem_optin<hgemm_tc_kernel<256, true>>(di);
-        return st ? st : launch(hgemm_tc_kernel<256, true>, HG_CPA_THREADS, HgTile<256>::SMEM_BYTES);
+        st = ensure_smem_optin<hgemm_tc_kernel<256>>(di);
+        if (st) return st;
+        hgemm_tc_kernel<256><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, pr.batches, (int)rows_vec, gm, idesc, kshift, nshift);
+    } else {
+        st = ensure_smem_optin<hgemm_tc_kernel<128>>(di);
+        if (st) return st;
+        hgemm_tc_kernel<128><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, pr.batches, (int)rows_vec, gm, idesc, kshift, nshift);
     }
-    st = ensure_smem_optin<hgemm_tc_kernel<128, true>>(di);
-    return st ? st : launch(hgemm_tc_kernel<128, true>, HG_CPA_THREADS, HgTile<128>::SMEM_BYTES);
+    return check_launch();
 }
 
 // ---- int8 GEMM -----------------------------------------------------------------------------------
@@ -1074,15 +1078,14 @@ static int igemm_launch(int m, int n, int k, const int8_t *a, const int8_t *b, i
     const int grid = tiles < di->sm_count ? (int)tiles : di->sm_count;
     long long g = (48ll << 20) / ((long long)HG_BM * k);
     const int gm = (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
-    const HgRaw raw{};
     if (wide) {
-        st = ensure_smem_optin<hgemm_tc_kernel<256, false, true>>(di);
+        st = ensure_smem_optin<hgemm_tc_kernel<256, true>>(di);
         if (st) return st;
-        hgemm_tc_kernel<256, false, true><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, raw, m, n, k, 1, vec, gm, idesc);
+        hgemm_tc_kernel<256, true><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
     } else {
-        st = ensure_smem_optin<hgemm_tc_kernel<128, false, true>>(di);
+        st = ensure_smem_optin<hgemm_tc_kernel<128, true>>(di);
         if (st) return st;
-        hgemm_tc_kernel<128, false, true><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, raw, m, n, k, 1, vec, gm, idesc);
+        hgemm_tc_kernel<128, true><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
     }
     return check_launch();
 }
