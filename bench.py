@@ -219,13 +219,12 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             for batch in (1, 4, 8):
                 x = torch.randn((batch, COLS), device=dev)
                 yb = torch.empty((batch, ROWS), device=dev)
-                # the provider hands its context workspace to both modes: int8 activations + scales, or fp16 pairs
-                ws_n = max(lib.tb200_qx_workspace_bytes(COLS, batch), lib.tb200_fx_workspace_bytes(COLS, batch))
+                ws_n = lib.tb200_qx_workspace_bytes(COLS, batch)
                 ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
                 by = algorithmic_bytes(ROWS, COLS, batch)
                 runs = {
-                    f"q8_split_f32_b{batch}": lambda i: lib.tb200_q8_gemv_ws(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), P(ws), ws_n, S),
-                    f"q8_blocks_f32_b{batch}": lambda i: lib.tb200_q8b_gemv_ws(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), P(ws), ws_n, S),
+                    f"q8_split_f32_b{batch}": lambda i: lib.tb200_q8_gemv(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), S),
+                    f"q8_blocks_f32_b{batch}": lambda i: lib.tb200_q8b_gemv(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), S),
                     f"q8_split_int_b{batch}": lambda i: lib.tb200_q8_gemv_i8(ROWS, COLS, batch, P(q[i & 3]), P(sc[i & 3]), P(x), P(yb), P(ws), ws_n, S),
                     f"q8_blocks_int_b{batch}": lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, batch, P(blocks[i & 3]), P(x), P(yb), P(ws), ws_n, S),
                 }
@@ -279,13 +278,13 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             for batch in (1, 4, 16):
                 xs = {c: torch.randn((batch, c), device=dev) for c in (4096, 14336)}
                 ys = {r: torch.empty((batch, r), device=dev) for r in (4096, 1024, 14336, 128256)}
-                ws_n = max(lib.tb200_qx_workspace_bytes(14336, batch), lib.tb200_fx_workspace_bytes(14336, batch))
+                ws_n = lib.tb200_qx_workspace_bytes(14336, batch)
                 ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
                 by = sum(algorithmic_bytes(r, c, batch, 18) for r, c in shapes)
 
                 def sweep_f(i):
                     for (r, c), w in zip(shapes, wsets[i & 1]):
-                        lib.tb200_q4b_gemv_ws(r, c, batch, P(w), P(xs[c]), P(ys[r]), P(ws), ws_n, S)
+                        lib.tb200_q4b_gemv(r, c, batch, P(w), P(xs[c]), P(ys[r]), S)
 
                 def sweep_i(i):
                     for (r, c), w in zip(shapes, wsets[i & 1]):

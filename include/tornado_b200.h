@@ -163,25 +163,6 @@ int tb200_q8b_gemv(int rows, int cols, int batch, const uint8_t *blocks, const f
 int tb200_q4b_gemv(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y,
                    tb200_stream_t stream);
 
-/* ---- float mode with scratch memory for several activation vectors -----------
- * The same products as tb200_q8_gemv / tb200_q8b_gemv / tb200_q4b_gemv (bit for
- * bit), for callers that can hand over scratch memory -- a provider's context
- * workspace (CutlassLibraryProvider.java:40-61 keeps one).  From two vectors on
- * the kernel multiplies on the tensor cores with every activation as an fp16
- * pair; without scratch memory each of its CTAs derives the pairs itself, with
- * it a small kernel derives them once per call:
- *   workspace contents (internal)  per pass of at most 8 vectors and per
- *   32-block the vectors' fp16 hi and lo parts side by side, then one fp32
- *   factor per vector and 128 columns
- * A null workspace (and 0 bytes) is allowed and means the plain entry. */
-size_t tb200_fx_workspace_bytes(int cols, int batch);
-int tb200_q8_gemv_ws(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x, float *y,
-                     void *workspace, size_t workspace_bytes, tb200_stream_t stream);
-int tb200_q8b_gemv_ws(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y, void *workspace,
-                      size_t workspace_bytes, tb200_stream_t stream);
-int tb200_q4b_gemv_ws(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y, void *workspace,
-                      size_t workspace_bytes, tb200_stream_t stream);
-
 /* ---- integer path ("exact-int mode") ----------------------------------------
  * Activations are quantised on the device to int8 with one fp32 scale per
  * 32-element block, scale = max|x|/127 (1 when the block is all zero),
@@ -196,8 +177,8 @@ int tb200_q4b_gemv_ws(int rows, int cols, int batch, const uint8_t *blocks, cons
  *   tb200_quantize_x writes  int8 xq[batch][cols], then float xs[batch][cols/32]
  *   (xs starts at the next multiple of 16 bytes after xq); the *_gemv_i8 entries
  *   use the same bytes as scratch in an order of their own.  From two vectors on
- *   they quantise with a small kernel of their own and chain the mat-vec to it
- *   with a programmatic dependent launch. */
+ *   (up to eight) they quantise with a small kernel of their own and chain the
+ *   mat-vec to it with a programmatic dependent launch. */
 size_t tb200_qx_workspace_bytes(int cols, int batch);
 int tb200_quantize_x(int cols, int batch, const float *x, void *workspace, size_t workspace_bytes,
                      tb200_stream_t stream);

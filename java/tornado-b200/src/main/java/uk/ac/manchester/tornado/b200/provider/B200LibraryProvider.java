@@ -87,9 +87,8 @@ public final class B200LibraryProvider implements TornadoLibraryProvider {
         String function = descriptor.getFunctionName();
         B200Native.checkStatus(B200Native.prepare(prepareClass(function)), "prepare");
         Object[] p = descriptor.getParameters();
-        if (isQuantised(function)) { // integer mode: int8 activations and scales; float mode: the activations as fp16 pairs
-            boolean exact = descriptor.getTuning() instanceof B200Options options && options.exactInt;
-            ((B200Context) context).growWorkspace(exact ? B200Native.qxWorkspaceBytes((int) p[1], (int) p[2]) : B200Native.fxWorkspaceBytes((int) p[1], (int) p[2]));
+        if (isQuantised(function) && descriptor.getTuning() instanceof B200Options options && options.exactInt) {
+            ((B200Context) context).growWorkspace(B200Native.qxWorkspaceBytes((int) p[1], (int) p[2]));
         }
         if (function.endsWith("Grouped") || function.endsWith("Packed")) { // (count, rows, cols, batch, ...): integer mode whatever the tuning
             ((B200Context) context).growWorkspace(B200Native.qxWorkspaceBytes((int) p[2], (int) p[3]));
@@ -137,7 +136,7 @@ public final class B200LibraryProvider implements TornadoLibraryProvider {
                     ? B200Native.q8GemvI8((int) inv.getArg(0), (int) inv.getArg(1), (int) inv.getArg(2), inv.getDevicePointer(3), inv.getDevicePointer(4), //
                             inv.getDevicePointer(5), inv.getDevicePointer(6), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream) //
                     : B200Native.q8Gemv((int) inv.getArg(0), (int) inv.getArg(1), (int) inv.getArg(2), inv.getDevicePointer(3), inv.getDevicePointer(4), //
-                            inv.getDevicePointer(5), inv.getDevicePointer(6), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream);
+                            inv.getDevicePointer(5), inv.getDevicePointer(6), ctx.stream);
             // (rows, cols, batch, blocks, x, y)
             case "q8GemvBytes", "q4GemvBytes" -> {
                 int kind = functionName.equals("q8GemvBytes") ? 0 : 1;
@@ -145,7 +144,7 @@ public final class B200LibraryProvider implements TornadoLibraryProvider {
                         ? B200Native.blockGemvI8(kind, (int) inv.getArg(0), (int) inv.getArg(1), (int) inv.getArg(2), inv.getDevicePointer(3), //
                                 inv.getDevicePointer(4), inv.getDevicePointer(5), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream) //
                         : B200Native.blockGemv(kind, (int) inv.getArg(0), (int) inv.getArg(1), (int) inv.getArg(2), inv.getDevicePointer(3), //
-                                inv.getDevicePointer(4), inv.getDevicePointer(5), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream);
+                                inv.getDevicePointer(4), inv.getDevicePointer(5), ctx.stream);
             }
             // (count, rows, cols, batch, x, y, blocks...)
             case "q8GemvBytesGrouped", "q4GemvBytesGrouped" -> {

@@ -42,7 +42,6 @@ public final class B200Native {
     private static MethodHandle sgemm;
     private static MethodHandle hgemmF32;
     private static MethodHandle qxWorkspaceBytes;
-    private static MethodHandle fxWorkspaceBytes;
     private static MethodHandle deviceMalloc;
     private static MethodHandle deviceFree;
     private static MethodHandle statusString;
@@ -68,14 +67,14 @@ public final class B200Native {
         } catch (IllegalArgumentException e) {
             throw new TornadoRuntimeException("[ERROR] Unable to load libtornado_b200.so: " + e.getMessage());
         }
+        FunctionDescriptor gemvF = FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG);
         FunctionDescriptor gemvI = FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG);
         sgemv = handle("tb200_sgemv", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG));
-        // float mode: the entries that take the context workspace for the activations' fp16 pairs
-        q8Gemv = handle("tb200_q8_gemv_ws", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG));
+        q8Gemv = handle("tb200_q8_gemv", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG));
         q8GemvI8 = handle("tb200_q8_gemv_i8", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG));
-        q8bGemv = handle("tb200_q8b_gemv_ws", gemvI);
+        q8bGemv = handle("tb200_q8b_gemv", gemvF);
         q8bGemvI8 = handle("tb200_q8b_gemv_i8", gemvI);
-        q4bGemv = handle("tb200_q4b_gemv_ws", gemvI);
+        q4bGemv = handle("tb200_q4b_gemv", gemvF);
         q4bGemvI8 = handle("tb200_q4b_gemv_i8", gemvI);
         // int tb200_q8b_gemv_i8_grouped(count, rows, cols, batch, blocks**, x, dst**, npeers, half_stride, epoch, rows_total, row_offset, ws, ws_bytes, stream)
         FunctionDescriptor grouped = FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, ADDRESS, JAVA_LONG, ADDRESS, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_INT,
@@ -85,7 +84,6 @@ public final class B200Native {
         sgemm = handle("tb200_sgemm", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_FLOAT, JAVA_LONG, JAVA_LONG, JAVA_FLOAT, JAVA_LONG, JAVA_LONG));
         hgemmF32 = handle("tb200_hgemm_f32", FunctionDescriptor.of(JAVA_INT, JAVA_INT, JAVA_INT, JAVA_INT, JAVA_LONG, JAVA_LONG, JAVA_LONG, JAVA_LONG));
         qxWorkspaceBytes = handle("tb200_qx_workspace_bytes", FunctionDescriptor.of(JAVA_LONG, JAVA_INT, JAVA_INT));
-        fxWorkspaceBytes = handle("tb200_fx_workspace_bytes", FunctionDescriptor.of(JAVA_LONG, JAVA_INT, JAVA_INT));
         deviceMalloc = handle("tb200_device_malloc", FunctionDescriptor.of(JAVA_INT, JAVA_LONG, ADDRESS));
         deviceFree = handle("tb200_device_free", FunctionDescriptor.of(JAVA_INT, JAVA_LONG));
         statusString = handle("tb200_status_string", FunctionDescriptor.of(ADDRESS, JAVA_INT));
@@ -110,9 +108,9 @@ public final class B200Native {
         }
     }
 
-    public static int q8Gemv(int rows, int cols, int batch, long q, long scales, long x, long y, long workspace, long workspaceBytes, long stream) {
+    public static int q8Gemv(int rows, int cols, int batch, long q, long scales, long x, long y, long stream) {
         try {
-            return (int) q8Gemv.invokeExact(rows, cols, batch, q, scales, x, y, workspace, workspaceBytes, stream);
+            return (int) q8Gemv.invokeExact(rows, cols, batch, q, scales, x, y, stream);
         } catch (Throwable t) {
             throw wrap(t);
         }
@@ -127,9 +125,9 @@ public final class B200Native {
     }
 
     /** kind: 0 = Q8_0 34-byte blocks, 1 = Q4_0 18-byte blocks. */
-    public static int blockGemv(int kind, int rows, int cols, int batch, long blocks, long x, long y, long workspace, long workspaceBytes, long stream) {
+    public static int blockGemv(int kind, int rows, int cols, int batch, long blocks, long x, long y, long stream) {
         try {
-            return (int) (kind == 0 ? q8bGemv : q4bGemv).invokeExact(rows, cols, batch, blocks, x, y, workspace, workspaceBytes, stream);
+            return (int) (kind == 0 ? q8bGemv : q4bGemv).invokeExact(rows, cols, batch, blocks, x, y, stream);
         } catch (Throwable t) {
             throw wrap(t);
         }
@@ -173,14 +171,6 @@ public final class B200Native {
     public static long qxWorkspaceBytes(int cols, int batch) {
         try {
             return (long) qxWorkspaceBytes.invokeExact(cols, batch);
-        } catch (Throwable t) {
-            throw wrap(t);
-        }
-    }
-
-    public static long fxWorkspaceBytes(int cols, int batch) {
-        try {
-            return (long) fxWorkspaceBytes.invokeExact(cols, batch);
         } catch (Throwable t) {
             throw wrap(t);
         }

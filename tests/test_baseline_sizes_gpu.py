@@ -268,60 +268,6 @@ def test_float_mode_activation_range(lib, scale, fmt, batch):
         assert o.rel_l2(got[b], want) <= REL_L2_FP32, (b, o.rel_l2(got[b], want))
 
 
-@pytest.mark.parametrize("fmt", ["q8", "q8b", "q4b"])
-@pytest.mark.parametrize("batch", [1, 2, 5, 8, 16])
-@pytest.mark.parametrize("rows,cols", [(200, 4096), (96, 14336), (64, 160)])
-def test_float_mode_workspace_entries_give_the_same_bits(lib, fmt, batch, rows, cols):
-    """tb200_*_gemv_ws (activations split into fp16 pairs once, by a kernel of their own) against tb200_*_gemv (every
-    CTA splits them itself): the same bits, for magnitudes from 1e-20 to 1e20 within one batch; and against the
-    oracle."""
-    if fmt == "q4b":
-        blocks, _, x = o.make_q4(rows, cols, batch)
-    else:
-        q, s, x = o.make_q8(rows, cols, batch)
-        blocks = o.q8_pack_blocks(q, s)
-    x = x.reshape(batch, cols).copy()
-    x[0] *= np.float32(1e-20)
-    x[-1] *= np.float32(1e20)
-    x[batch // 2, ::5] *= np.float32(3e-5)
-    x = np.ascontiguousarray(x.ravel())
-    dx, dy, dz = DevBuf(x), out_buf(rows * batch), out_buf(rows * batch)
-    nws = lib.tb200_fx_workspace_bytes(cols, batch)
-    assert nws >= 4 * cols * batch
-    ws = DevBuf(np.zeros(nws, np.uint8))
-    if fmt == "q8":
-        dq, ds = DevBuf(q), DevBuf(s)
-        _ok(lib.tb200_q8_gemv(rows, cols, batch, dq.ptr, ds.ptr, dx.ptr, dy.ptr, stream_ptr()), lib)
-        _ok(lib.tb200_q8_gemv_ws(rows, cols, batch, dq.ptr, ds.ptr, dx.ptr, dz.ptr, ws.ptr, nws, stream_ptr()), lib)
-    else:
-        dq = DevBuf(blocks)
-        plain, with_ws = (lib.tb200_q8b_gemv, lib.tb200_q8b_gemv_ws) if fmt == "q8b" else (lib.tb200_q4b_gemv, lib.tb200_q4b_gemv_ws)
-        _ok(plain(rows, cols, batch, dq.ptr, dx.ptr, dy.ptr, stream_ptr()), lib)
-        _ok(with_ws(rows, cols, batch, dq.ptr, dx.ptr, dz.ptr, ws.ptr, nws, stream_ptr()), lib)
-    sync_and_check(lib)
-    a, b = dy.numpy().reshape(batch, rows), dz.numpy().reshape(batch, rows)
-    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
-    assert dz.guard_intact() and ws.guard_intact() and dx.guard_intact()
-    for v in range(batch):
-        xb = x[v * cols:(v + 1) * cols]
-        want = o.q4_gemv_f64(blocks, xb, cols, rows) if fmt == "q4b" else o.q8_gemv_f64(q, s, xb, cols, rows)
-        assert o.rel_l2(b[v], want) <= REL_L2_FP32
-
-
-def test_float_mode_workspace_argument_errors(lib):
-    rows, cols, batch = 64, 4096, 4
-    q, s, x = o.make_q8(rows, cols, batch)
-    dq, dx, dy = DevBuf(o.q8_pack_blocks(q, s)), DevBuf(x), out_buf(rows * batch)
-    nws = lib.tb200_fx_workspace_bytes(cols, batch)
-    ws = DevBuf(np.zeros(nws, np.uint8))
-    assert lib.tb200_q8b_gemv_ws(rows, cols, batch, dq.ptr, dx.ptr, dy.ptr, ws.ptr, nws - 1, stream_ptr()) == -3  # TB200_ERR_WORKSPACE
-    assert lib.tb200_q8b_gemv_ws(rows, cols, batch, dq.ptr, dx.ptr, dy.ptr, C.c_void_p(ws.ptr.value + 4), nws, stream_ptr()) == -2
-    assert lib.tb200_q8b_gemv_ws(rows, cols, batch, dq.ptr, dx.ptr, dy.ptr, None, 0, stream_ptr()) == 0  # no workspace: the plain entry
-    sync_and_check(lib)
-    want = o.q8_gemv_f64(q, s, x[:cols], cols, rows)
-    assert o.rel_l2(dy.numpy().reshape(batch, rows)[0], want) <= REL_L2_FP32
-
-
 # --------------------------------------------------------------------------- FP16 GEMM sweep sizes
 @pytest.mark.parametrize("n", [4096, 8192, 16384])
 def test_hgemm_sweep_sizes_rows_sampled(lib, n):

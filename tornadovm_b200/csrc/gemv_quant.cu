@@ -464,7 +464,6 @@ struct RingTraits {
     static constexpr int BB = FMT == FMT_Q4B ? 18 : 34;   // bytes per block
     static constexpr int PW = BB / 2;                     // 32-bit words per block pair
     static constexpr int CB = kChunkBlocks * BB;          // bytes per full row chunk (4352 / 2304)
-    static constexpr int CBS = CB + 16;                   // ring bytes per row chunk: a chunk may sit 8 bytes into its slot
     static constexpr int QW = FMT == FMT_Q4B ? 4 : 8;     // quant words per block
     static constexpr int CPL = 64;                        // contiguous columns per lane and pair
     static constexpr int PIECES = (CB / 16 + 31) / 32;    // 16-byte pieces per lane and row chunk (9 / 5)
@@ -489,7 +488,7 @@ __device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], 
     for (int i = 0; i < QW; ++i) qb[i] = wds[QW + 1 + i];
 }
 
-template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, bool GROUPED>
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, bool GROUPED, bool SH8>
 __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupArgs *grp) {
     // GROUPED: a.rows counts the rows of all matrices laid end to end; a.w and a.y are unused
     using T = RingTraits<FMT>;
@@ -513,12 +512,15 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     float *xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
     int *xsum = reinterpret_cast<int *>(xs_scales + B * bpr);
     const uint32_t ring_off = (uint32_t)(((size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 8 + 127) & ~(size_t)127);
-    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * T::CBS;
+    // SH8: ring slots are 128 bytes longer and a chunk starts 8 bytes into its slot (see below)
+    constexpr int CBS = SH8 ? T::CB + 128 : T::CB;
+    unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * CBS;
     const uint32_t ring_s = smem_u32(ring);
-    // Weights 8 bytes past a 16-byte boundary (an array behind a 24-byte header; every row chunk then is): the chunk
-    // keeps that phase in its ring slot -- its first and last 8 bytes travel as 8-byte copies, the rest as the
-    // same aligned 16-byte pieces
-    const uint32_t wsh = (uint32_t)a.wshift;
+    // SH8: weights 8 bytes past a 16-byte boundary (an array behind a 24-byte header; every row chunk then is).  The
+    // chunk keeps that phase in its ring slot -- its first and last 8 bytes travel as 8-byte copies, the rest as the
+    // same aligned 16-byte pieces.  A template parameter, not a run-time value: the aligned form keeps its 128-byte
+    // aligned slots and its instruction count (a run-time shift measured 10 % slower on aligned weights).
+    constexpr uint32_t wsh = SH8 ? 8u : 0u;
 
     // ---- issue side ------------------------------------------------------------------
     int ig = g_begin, ich = 0;
@@ -539,8 +541,8 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                 } else {
                     src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16 - wsh;
                 }
-                const uint32_t dst = ring_s + (st * R + r) * T::CBS + lane * 16;
-                if (wsh == 0) {
+                const uint32_t dst = ring_s + (st * R + r) * CBS + lane * 16;
+                if constexpr (!SH8) {
 #pragma unroll
                     for (int i = 0; i < T::PIECES; ++i)
                         if (lane + 32 * i < npieces) cp_async_16(dst + i * 512, src + i * 512);
@@ -630,7 +632,7 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
             uint32_t qa[R][T::QW], qb[R][T::QW];
 #pragma unroll
             for (int r = 0; r < R; ++r)
-                load_pair<FMT>(reinterpret_cast<const uint32_t *>(ring + (st * R + r) * T::CBS + wsh) + pair * T::PW, scale[r], qa[r], qb[r]);
+                load_pair<FMT>(reinterpret_cast<const uint32_t *>(ring + (st * R + r) * CBS + wsh) + pair * T::PW, scale[r], qa[r], qb[r]);
             if (INT) {
                 const uint4 *xq16 = reinterpret_cast<const uint4 *>(smem_raw);
 #pragma unroll
@@ -778,14 +780,14 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     }
 }
 
-template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES>
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, bool SH8 = false>
 __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
-    qblk_gemv_body<FMT, B, R, MODE, DOTS, STAGES, false>(a, nullptr);
+    qblk_gemv_body<FMT, B, R, MODE, DOTS, STAGES, false, SH8>(a, nullptr);
 }
 
-template <int FMT, int B, int R, int MODE, int STAGES>
+template <int FMT, int B, int R, int MODE, int STAGES, bool SH8 = false>
 __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_grouped_kernel(const QGemvArgs a, const __grid_constant__ QGroupArgs grp) {
-    qblk_gemv_body<FMT, B, R, MODE, false, STAGES, true>(a, &grp);
+    qblk_gemv_body<FMT, B, R, MODE, false, STAGES, true, SH8>(a, &grp);
 }
 
 // ---------------------------------------------------------------------------
@@ -813,47 +815,6 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float *__restrict
         }
         xq[at * 32 + lane] = (int8_t)quantize_byte(v, inv);
         if (lane == 0) xs[at] = scale;
-    }
-}
-
-// ---------------------------------------------------------------------------
-// Activation splitter of the float mode: one warp per half chunk (128 columns) of one vector.  Writes what the
-// tensor-core mat-vec otherwise derives in every CTA: x * 2^-e as fp16 hi + lo (e from the largest magnitude of the
-// half chunk) into two planes [batch][cols], and 2^e per half chunk -- operation for operation the arithmetic of
-// the in-kernel conversion, so both forms give the same bits.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) split_x_kernel(const float *__restrict__ x, uint16_t *__restrict__ planes, float *__restrict__ unscale,
-                                                      int nhalf, int hpr, int batch) {
-    // planes[block][vector][hi 32 | lo 32] and unscale[half chunk][vector]: the vectors of a column tile lie next to
-    // one another, as the tensor-core mat-vec reads them
-    const int lane = threadIdx.x & 31;
-    const int wpc = blockDim.x / 32;
-    pdl_launch_dependents();  // the mat-vec chained to this kernel may start and request its weights now
-    for (int hc = blockIdx.x * wpc + (threadIdx.x >> 5); hc < nhalf; hc += gridDim.x * wpc) {
-        const float *p = x + (size_t)hc * 128 + lane * 4;  // vectors are contiguous and cols % 128 == 0: hc runs over all of them
-        const float v[4] = {p[0], p[1], p[2], p[3]};
-        float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        int e = ((__float_as_int(m) >> 23) & 0xFF) - 127;
-        if (m == 0.f || e > 127) e = 0;
-        e = e < -126 ? -126 : (e > 126 ? 126 : e);
-        const float prescale = __int_as_float((127 - e) << 23);
-        uint32_t h[2], l[2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const float w0 = v[2 * i] * prescale, w1 = v[2 * i + 1] * prescale;
-            const __half2 hh = __floats2half2_rn(w0, w1);
-            const float2 back = __half22float2(hh);
-            const __half2 ll = __floats2half2_rn(w0 - back.x, w1 - back.y);
-            h[i] = *reinterpret_cast<const uint32_t *>(&hh), l[i] = *reinterpret_cast<const uint32_t *>(&ll);
-        }
-        const int n = hc / hpr, hcv = hc - n * hpr;         // vector and its half chunk
-        const int blk = hcv * 4 + (lane >> 3);              // 32-block of this lane's four values
-        uint16_t *dst = planes + ((size_t)blk * batch + n) * 64 + (lane & 7) * 4;
-        *reinterpret_cast<uint2 *>(dst) = make_uint2(h[0], h[1]);
-        *reinterpret_cast<uint2 *>(dst + 32) = make_uint2(l[0], l[1]);
-        if (lane == 0) unscale[(size_t)hcv * batch + n] = __int_as_float((127 + e) << 23);
     }
 }
 
@@ -936,20 +897,20 @@ struct RingConfig {
 };
 
 template <int FMT, int B, int MODE>
-static size_t ring_smem_bytes(int cols) {
+static size_t ring_smem_bytes(int cols, bool sh8 = false) {
     using T = RingTraits<FMT>;
     using Cfg = RingConfig<FMT, B, MODE>;
     const size_t slots = (size_t)((cols + 2047) / 2048) * 2048 / (Cfg::INT ? 16 : 4);
     size_t off = (size_t)B * slots * 16 + (Cfg::INT ? (size_t)B * (cols / 32) * 8 : 0);  // + scales + block sums
     off = (off + 127) & ~(size_t)127;
-    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * T::CBS;
+    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * (T::CB + (sh8 ? 128 : 0));
 }
 
-template <int FMT, int B, int MODE, bool DOTS>
-static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+template <int FMT, int B, int MODE, bool DOTS, bool SH8>
+static int launch_ring_sh(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     using Cfg = RingConfig<FMT, B, MODE>;
-    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols);
-    constexpr auto kernel = qblk_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES>;
+    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols, SH8);
+    constexpr auto kernel = qblk_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES, SH8>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
     // at most one resident wave, sized so that all warps own (nearly) the same number of rows
@@ -957,15 +918,31 @@ static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s)
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a);
 }
 
-template <int FMT, int B, int MODE>
-static int launch_ring_grouped(const QGemvArgs &a, const QGroupArgs &grp, const DeviceInfo *di, cudaStream_t s) {
+// weights 8 bytes past a 16-byte boundary: a kernel of their own for one vector (more vectors go to the tensor-core
+// kernel, which handles the phase itself)
+template <int FMT, int B, int MODE, bool DOTS>
+static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
+    if constexpr (B == 1) {
+        if (a.wshift) return launch_ring_sh<FMT, B, MODE, DOTS, true>(a, di, s);
+    }
+    if (a.wshift) return TB200_ERR_ALIGNMENT;  // not reached: the dispatcher keeps such launches off this path
+    return launch_ring_sh<FMT, B, MODE, DOTS, false>(a, di, s);
+}
+
+template <int FMT, int B, int MODE, bool SH8>
+static int launch_ring_grouped_sh(const QGemvArgs &a, const QGroupArgs &grp, const DeviceInfo *di, cudaStream_t s) {
     using Cfg = RingConfig<FMT, B, MODE>;
-    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols);
-    constexpr auto kernel = qblk_gemv_grouped_kernel<FMT, B, Cfg::R, MODE, Cfg::STAGES>;
+    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols, SH8);
+    constexpr auto kernel = qblk_gemv_grouped_kernel<FMT, B, Cfg::R, MODE, Cfg::STAGES, SH8>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
     const int grid = balanced_ctas(a.rows, Cfg::R, di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem));
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a, grp);
+}
+
+template <int FMT, int B, int MODE>
+static int launch_ring_grouped(const QGemvArgs &a, const QGroupArgs &grp, const DeviceInfo *di, cudaStream_t s) {
+    return a.wshift ? launch_ring_grouped_sh<FMT, B, MODE, true>(a, grp, di, s) : launch_ring_grouped_sh<FMT, B, MODE, false>(a, grp, di, s);
 }
 
 template <int FMT, int MODE>
@@ -1096,7 +1073,7 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     a.wshift = 0;
     if (FMT == FMT_Q8S) {
         if (aligned_to(a.w, 16)) path = PATH_Q8S_DIRECT;
-    } else if (aligned_to(a.w, 8) && a.cols % 256 == 0) {
+    } else if (a.cols % 256 == 0 && (aligned_to(a.w, 16) || (aligned_to(a.w, 8) && a.batch == 1))) {
         path = PATH_RING, a.wshift = (int)((uintptr_t)a.w & 15);
     }
     // Tensor-core kernel with the activations in registers (gemv_tc.cu): integer mode from
@@ -1114,45 +1091,23 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
             if ((float_tc || only8) && a.batch >= min_batch && qtc_eligible(FMT, MODE_FLOAT, p, di)) {
                 // at most eight vectors (sixteen fp16 columns) per pass over the weights
                 const int passes = (a.batch + 7) / 8, each = (a.batch + passes - 1) / passes;
-                // With a workspace the fp16 pairs are made once by a kernel of their own instead of once per CTA of
-                // the mat-vec (which costs a third of its run time at 8 vectors); the mat-vec is chained to that
-                // kernel by a programmatic dependent launch, like the integer mode to its quantiser.
-                const bool split_ws = xq_ws && xs_ws;
-                if (split_ws) {
-                    uint16_t *planes = reinterpret_cast<uint16_t *>(xq_ws);
-                    st = ensure_kernel<split_x_kernel, KERNEL_MAX_CARVEOUT>(di);
-                    if (st) return st;
-                    for (int b0 = 0; b0 < a.batch; b0 += each) {
-                        // the vectors of a pass: [block][vector][hi | lo]
-                        const int nb = a.batch - b0 < each ? a.batch - b0 : each;
-                        const int nhalf = nb * (a.cols / 128);
-                        split_x_kernel<<<(nhalf + 7) / 8, 256, 0, s>>>(a.x + (size_t)b0 * a.cols, planes + (size_t)b0 * a.cols * 2, xs_ws + (size_t)b0 * (a.cols / 128), nhalf,
-                                                                       a.cols / 128, nb);
-                        st = check_launch();
-                        if (st) return st;
-                    }
-                }
                 for (int b0 = 0; b0 < a.batch; b0 += each) {
                     p.batch = a.batch - b0 < each ? a.batch - b0 : each;
                     p.x = a.x + (size_t)b0 * a.cols, p.y = a.y + (size_t)b0 * a.rows;
-                    if (split_ws) {
-                        p.xq = xq_ws + (size_t)b0 * a.cols * 4, p.xs = xs_ws + (size_t)b0 * (a.cols / 128);
-                        st = qtc_dispatch(FMT, MODE_FLOAT, p, di, s, b0 == 0);  // chained to the splitter
-                    } else {
-                        st = qtc_dispatch(FMT, MODE_FLOAT, p, di, s, overlap && b0 == 0);
-                    }
+                    st = qtc_dispatch(FMT, MODE_FLOAT, p, di, s, overlap && b0 == 0);
                     if (st) return st;
                 }
                 return TB200_OK;
             }
         } else if (a.batch >= (only8 ? 1 : option_value(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH)) && (!DOTS || a.batch == 1) &&
                    qtc_eligible(FMT, MODE, a, di)) {
-            if (MODE == MODE_INT_FUSED && xq_ws && xs_ws) {
+            if (MODE == MODE_INT_FUSED && xq_ws && xs_ws && a.batch <= 8) {
                 // Quantising inside the mat-vec means every one of its CTAs converts all the vectors (measured: 5 us
-                // of a 14 us launch at 8 vectors, during which the weight ring fills up and the copies stall).  The
-                // activations are therefore quantised once by a small kernel of their own, and the mat-vec is chained
-                // to it with a programmatic dependent launch: it starts while the quantiser runs, requests its first
-                // weights, and waits for the quantiser only where it reads the int8 activations.
+                // of a 14 us launch at 8 vectors, during which the weight ring fills up and the copies stall).  Up to
+                // 8 vectors the activations are therefore quantised once by a small kernel of their own, and the
+                // mat-vec is chained to it with a programmatic dependent launch: it starts while the quantiser runs,
+                // requests its first weights, and waits for the quantiser only where it reads the int8 activations.
+                // (With two column tiles the fused form measured faster: 24.6 against 31 us at 16 vectors.)
                 st = quantize_x_layout(a.cols, a.batch, a.x, xq_ws, xs_ws, s, true);
                 if (st) return st;
                 QGemvArgs b = a;
@@ -1421,55 +1376,6 @@ extern "C" int tb200_q4b_gemv(int rows, int cols, int batch, const uint8_t *bloc
     if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
     QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
     return qgemv_dispatch<FMT_Q4B, MODE_FLOAT, false>(a, nullptr, nullptr, stream);
-}
-
-// float mode with a workspace for the split activations
-static int split_float_workspace(int cols, int batch, void *workspace, size_t workspace_bytes, int8_t **planes, float **unscale) {
-    *planes = nullptr, *unscale = nullptr;
-    if (!workspace) return workspace_bytes ? TB200_ERR_INVALID_ARG : TB200_OK;  // no workspace: conversion inside the mat-vec
-    if (cols < 0 || batch < 1) return TB200_ERR_INVALID_ARG;
-    if (!aligned_to(workspace, 16)) return TB200_ERR_ALIGNMENT;
-    if (workspace_bytes < tb200_fx_workspace_bytes(cols, batch)) return TB200_ERR_WORKSPACE;
-    *planes = reinterpret_cast<int8_t *>(workspace);
-    *unscale = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(workspace) + (((size_t)cols * batch * 4 + 15) & ~(size_t)15));
-    return TB200_OK;
-}
-
-extern "C" size_t tb200_fx_workspace_bytes(int cols, int batch) {
-    if (cols < 0 || batch < 0) return 0;
-    return (((size_t)cols * batch * 4 + 15) & ~(size_t)15) + (size_t)((cols + 127) / 128) * batch * sizeof(float);
-}
-
-extern "C" int tb200_q8_gemv_ws(int rows, int cols, int batch, const int8_t *q, const uint16_t *scales, const float *x, float *y,
-                                void *workspace, size_t workspace_bytes, tb200_stream_t stream) {
-    int8_t *planes;
-    float *unscale;
-    const int st = split_float_workspace(cols, batch, workspace, workspace_bytes, &planes, &unscale);
-    if (st) return st;
-    QGemvArgs a{reinterpret_cast<const uint8_t *>(q), scales, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT_Q8S, MODE_FLOAT, false>(a, planes, unscale, stream);
-}
-
-extern "C" int tb200_q8b_gemv_ws(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y, void *workspace,
-                                 size_t workspace_bytes, tb200_stream_t stream) {
-    if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
-    int8_t *planes;
-    float *unscale;
-    const int st = split_float_workspace(cols, batch, workspace, workspace_bytes, &planes, &unscale);
-    if (st) return st;
-    QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT_Q8B, MODE_FLOAT, false>(a, planes, unscale, stream);
-}
-
-extern "C" int tb200_q4b_gemv_ws(int rows, int cols, int batch, const uint8_t *blocks, const float *x, float *y, void *workspace,
-                                 size_t workspace_bytes, tb200_stream_t stream) {
-    if (blocks && !aligned_to(blocks, 2)) return TB200_ERR_ALIGNMENT;
-    int8_t *planes;
-    float *unscale;
-    const int st = split_float_workspace(cols, batch, workspace, workspace_bytes, &planes, &unscale);
-    if (st) return st;
-    QGemvArgs a{blocks, nullptr, x, nullptr, nullptr, y, nullptr, rows, cols, batch};
-    return qgemv_dispatch<FMT_Q4B, MODE_FLOAT, false>(a, planes, unscale, stream);
 }
 
 extern "C" size_t tb200_qx_workspace_bytes(int cols, int batch) {

@@ -32,33 +32,15 @@ TB200_TU_STATUS(gemv_tc)
 
 namespace tb200 {
 
-#ifdef TB200_TC_TRACE
-__device__ unsigned long long g_tc_trace[2][64];
-#define TC_TRACE(slot)                                                                                                  \
-    do {                                                                                                                \
-        if (lane == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) g_tc_trace[blockIdx.x ? 1 : 0][slot] = clock64(); \
-    } while (0)
-#else
-#define TC_TRACE(slot)
-#endif
-
 constexpr int TC_KS_MAX = 16;                       // consumer warps = K chunks in flight per unit
 constexpr int TC_THREADS = (TC_KS_MAX + 2) * 32;    // + the reducing warp + the copy-issuing warp
 constexpr int TC_MAX_STAGES = 8;
 constexpr int TC_KB = 8;                            // blocks per K chunk
 constexpr int TC_NB = 2;                            // partial-tile buffers between consumers and reducer
-#ifndef TC_PER_TILE_HANDOFF
-#define TC_PER_TILE_HANDOFF 1
-#endif
-constexpr bool TC_PER_TILE = TC_PER_TILE_HANDOFF != 0;  // experiment switch
-#ifndef TC_UNROLLED_REDUCER
-#define TC_UNROLLED_REDUCER 1
-#endif
 
 constexpr int X_INT_WS = 0;     // int8 activations and their scales read from global memory (already quantised)
 constexpr int X_INT_FUSED = 1;  // fp32 activations quantised per 32-block while they are loaded
 constexpr int X_FLOAT = 2;      // fp32 activations split into fp16 hi + lo
-constexpr int X_FLOAT_WS = 3;   // the same split read from a workspace that a separate kernel filled once per call
 
 template <int FMT>
 struct TcTraits {
@@ -68,7 +50,7 @@ struct TcTraits {
 
 template <int FMT, int NT>
 struct TcConfig {
-    static constexpr size_t PARTIAL = (size_t)TC_NB * TC_KS_MAX * 512 * (TC_PER_TILE ? 1 : NT);  // tiles of an item are handed over one after the other
+    static constexpr size_t PARTIAL = (size_t)TC_NB * TC_KS_MAX * NT * 512;
 };
 
 struct TcArgs {
@@ -225,30 +207,6 @@ __device__ __forceinline__ void load_x_quantised(const QGemvArgs &a, int blk0, i
         for (int j = 0; j < NT; ++j) xsr[kb][j][0] *= wfix, xsr[kb][j][1] *= wfix;
 }
 
-// Split activations from the workspace of split_x_kernel: per 32-block and vector 32 fp16 hi parts followed by 32 fp16
-// lo parts, [block][vector][2][32] (prescaled per half chunk of 128 columns), and unscale[half chunk][vector].
-// Column g of tile j is the hi (g even) or lo (g odd) part of vector 4j + g / 2: the fragments are loaded straight
-// into their registers, the four vectors of a tile from 512 contiguous bytes.
-template <int NT>
-__device__ __forceinline__ void load_x_split(const QGemvArgs &a, int blk0, int lane, uint32_t (&bf)[TC_KB][NT][4], float (&unscale)[2][NT]) {
-    const int g = lane >> 2, t = lane & 3;
-    const uint16_t *planes = reinterpret_cast<const uint16_t *>(a.xq);
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        const int n = j * 4 + (g >> 1);
-#pragma unroll
-        for (int kb = 0; kb < TC_KB; ++kb) {
-            const uint16_t *p = planes + (((size_t)(blk0 + kb) * a.batch + n) * 2 + (g & 1)) * 32 + 4 * t;
-            uint2 v0 = make_uint2(0u, 0u), v1 = make_uint2(0u, 0u);
-            if (n < a.batch) v0 = __ldg(reinterpret_cast<const uint2 *>(p)), v1 = __ldg(reinterpret_cast<const uint2 *>(p + 16));
-            bf[kb][j][0] = v0.x, bf[kb][j][1] = v0.y, bf[kb][j][2] = v1.x, bf[kb][j][3] = v1.y;
-        }
-        const int nu = j * 4 + t;  // columns 2t and 2t + 1 of the accumulator belong to vector 4j + t
-#pragma unroll
-        for (int half = 0; half < 2; ++half) unscale[half][j] = nu < a.batch ? __ldg(a.xs + (size_t)(blk0 / TC_HB + half) * a.batch + nu) : 0.f;
-    }
-}
-
 // A fragments (rows g and g + 8 of the unit, block kb of the warp's chunk) and the two rows' block scales.
 // rp0 / rp1 point at the chunk's weight bytes of the two rows, sp0 / sp1 (split layout) at its eight fp16 scales.
 template <int FMT>
@@ -379,7 +337,7 @@ __host__ __device__ __forceinline__ int tc_row_pitch(int ks, int wrow) {
 template <int FMT, int NT, int XSRC, bool DOTS>
 __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_constant__ TcArgs args) {
     using T = TcTraits<FMT>;
-    constexpr bool FLT = XSRC == X_FLOAT || XSRC == X_FLOAT_WS;
+    constexpr bool FLT = XSRC == X_FLOAT;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[TC_MAX_STAGES];   // a stage has landed
     __shared__ __align__(8) uint64_t empty_bar[TC_MAX_STAGES];  // every consumer is done with a stage
@@ -405,8 +363,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
     const int stage_bytes = 16 * (wpitch + spitch);
     const size_t ring_bytes = (size_t)S * stage_bytes;
     const bool shifted = (args.wshift | args.sshift) != 0;
-    float4 *partial = reinterpret_cast<float4 *>(smem_raw + ((ring_bytes + 127) & ~(size_t)127));  // [buffer][warp][lane]
-    float4 *ysum = partial + (size_t)TC_NB * TC_KS_MAX * 32 * (TC_PER_TILE ? 1 : NT);                                  // [unit][tile][lane], phases > 1
+    float4 *partial = reinterpret_cast<float4 *>(smem_raw + ((ring_bytes + 127) & ~(size_t)127));  // [buffer][warp][tile][lane]
+    float4 *ysum = partial + (size_t)TC_NB * TC_KS_MAX * NT * 32;                                  // [unit][tile][lane], phases > 1
 
     if (tid == 0) {
         for (int i = 0; i < TC_MAX_STAGES; ++i) {
@@ -419,12 +377,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
         }
         mbar_fence_init();
     }
-    if (warp == 0) TC_TRACE(0);
     __syncthreads();  // barriers exist before the producer's first copy can signal one
-    if (warp == 0) TC_TRACE(1);
-#ifdef TB200_TC_TRACE
-    if (tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) g_tc_trace[blockIdx.x ? 1 : 0][62] = qg_timer_ns();
-#endif
 
     const bool consumer = warp < KS;
 
@@ -475,7 +428,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
                 // counts as this lane's arrival once its copies above have landed (at once if it made none)
                 asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[st])) : "memory");
             }
-            if (it < 10) TC_TRACE(50 + it);
         }
         if (shifted) asm volatile("cp.async.wait_all;" ::: "memory");
         return;
@@ -483,7 +435,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
 
     pdl_launch_dependents();
     pdl_wait();  // activations and outputs may belong to the kernel before this one
-    if (warp == 0) TC_TRACE(2);
 
     if (warp < TC_KS_MAX) {
         if (!consumer) return;  // fewer K chunks than warps: no barrier below counts this warp
@@ -502,25 +453,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
                 if (valid) {
                     if constexpr (XSRC == X_INT_WS) {
                         load_x_quantised<FMT, NT>(a, kc * TC_KB, lane, bf, xsr);
-                    } else if constexpr (XSRC == X_FLOAT_WS) {
-                        load_x_split<NT>(a, kc * TC_KB, lane, bf, unscale);
                     } else {
-                        // all of a tile's loads are in flight before the first conversion: one round trip per tile
-                        float4 xraw[2][TC_HB][2];  // fp32 activations of the chunk's two halves on their way into fragments
+                        // half a chunk at a time: requesting both halves before the first conversion measured slower
+                        // (the fragments under construction and 64 raw values do not fit the register budget)
+                        float4 xraw[TC_HB][2];  // fp32 activations of half a chunk on their way into fragments
 #pragma unroll
-                        for (int j = 0; j < NT; ++j) {
-                            load_x_raw<XSRC>(a, kc * TC_KB, lane, j, xraw[0]);
-                            load_x_raw<XSRC>(a, kc * TC_KB + TC_HB, lane, j, xraw[1]);
-                            unscale[0][j] = convert_x<FMT, NT, XSRC>(a, lane, j, 0, xraw[0], bf, xsr);
-                            unscale[1][j] = convert_x<FMT, NT, XSRC>(a, lane, j, 1, xraw[1], bf, xsr);
-                        }
+                        for (int j = 0; j < NT; ++j)
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                load_x_raw<XSRC>(a, kc * TC_KB + half * TC_HB, lane, j, xraw);
+                                unscale[half][j] = convert_x<FMT, NT, XSRC>(a, lane, j, half, xraw, bf, xsr);
+                            }
                     }
                 }
                 phase_loaded = p;
-                if (warp == 0 && it == 0) TC_TRACE(3);
             }
             if (!mbar_wait(&full_bar[st], use & 1)) break;
-            if (warp == 0 && it < 10) TC_TRACE(4 + 3 * it);
             const unsigned char *base = smem_raw + (size_t)st * stage_bytes;
             const unsigned char *rp0 = base + g * wpitch + warp * T::WROW + args.wshift;
             const unsigned char *sp0 = base + 16 * wpitch + g * spitch + warp * 16 + args.sshift;
@@ -532,92 +480,63 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
                 consume_chunk<FMT, NT, FLT, DOTS>(a, rp0, rp0 + 8 * wp, sp0, sp0 + 8 * sp, t, r0, r0 + 8, row_end, kc * TC_KB, bf, xsr, unscale, acc);
             __syncwarp();  // every lane has read its fragments
             if (lane == 0) mbar_arrive(&empty_bar[st]);
-            if (warp == 0 && it < 10) TC_TRACE(5 + 3 * it);
             if (!DOTS) {
-                // hand the partial tiles to the reducer, one column tile per hand-over (two buffers in rotation: the
-                // shared memory this saves is a third stage of the weight ring when there are two tiles)
-                bool ok = true;
+                // hand the partial tiles to the reducer
+                const int buf = it % TC_NB;
+                if (it >= TC_NB && !mbar_wait(&pempty_bar[buf], ((it / TC_NB) - 1) & 1)) break;
+                if (valid) {
 #pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    const int h = TC_PER_TILE ? it * NT + j : it, buf = h % TC_NB;
-                    const size_t slot = TC_PER_TILE ? (size_t)(buf * TC_KS_MAX + warp) : (size_t)((buf * TC_KS_MAX + warp) * NT + j);
-                    if ((TC_PER_TILE || j == 0) && h >= TC_NB && !mbar_wait(&pempty_bar[buf], ((h / TC_NB) - 1) & 1)) {
-                        ok = false;
-                        break;
-                    }
-                    if (valid) partial[slot * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-                    if (TC_PER_TILE || j == NT - 1) {
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&pfull_bar[buf]);
-                    }
+                    for (int j = 0; j < NT; ++j)
+                        partial[((size_t)(buf * TC_KS_MAX + warp) * NT + j) * 32 + lane] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
                 }
-                if (!ok) break;
-                if (warp == 0 && it < 10) TC_TRACE(6 + 3 * it);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&pfull_bar[buf]);
             }
         }
     } else if (!DOTS) {
         // ================= reducer =================
         int p = 0, u = 0;
-        bool ok = true;
-        for (int it = 0; it < total && ok; ++it, (++u == nunits ? (u = 0, ++p) : 0)) {
+        for (int it = 0; it < total; ++it, (++u == nunits ? (u = 0, ++p) : 0)) {
+            const int buf = it % TC_NB;
+            if (!mbar_wait(&pfull_bar[buf], (it / TC_NB) & 1)) break;
             const int nvalid = min(KS, nch - p * KS);
+            float4 sum[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                sum[j] = (phases > 1 && p > 0) ? ysum[((size_t)u * NT + j) * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int w = 0; w < nvalid; ++w) {  // fixed order: the result does not depend on warp timing
+                    const float4 v = partial[((size_t)(buf * TC_KS_MAX + w) * NT + j) * 32 + lane];
+                    sum[j].x += v.x, sum[j].y += v.y, sum[j].z += v.z, sum[j].w += v.w;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pempty_bar[buf]);
+            if (p + 1 < phases) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) ysum[((size_t)u * NT + j) * 32 + lane] = sum[j];
+                continue;
+            }
             const int r0 = row_begin + u * 16 + g, r1 = r0 + 8;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const int h = TC_PER_TILE ? it * NT + j : it, buf = h % TC_NB;
-                if ((TC_PER_TILE || j == 0) && !mbar_wait(&pfull_bar[buf], (h / TC_NB) & 1)) {
-                    ok = false;
-                    break;
-                }
-                float4 sum = (phases > 1 && p > 0) ? ysum[((size_t)u * NT + j) * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
-                // all partial tiles are requested before the first addition (one shared-memory round trip instead of
-                // sixteen); they are added in warp order, so the result does not depend on warp timing
-#if TC_UNROLLED_REDUCER
-                float4 v[TC_KS_MAX];
-#pragma unroll
-                for (int w = 0; w < TC_KS_MAX; ++w) {
-                    const size_t slot = TC_PER_TILE ? (size_t)(buf * TC_KS_MAX + w) : (size_t)((buf * TC_KS_MAX + w) * NT + j);
-                    v[w] = w < nvalid ? partial[slot * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-                for (int w = 0; w < TC_KS_MAX; ++w) sum.x += v[w].x, sum.y += v[w].y, sum.z += v[w].z, sum.w += v[w].w;
-#else
-                for (int w = 0; w < nvalid; ++w) {
-                    const size_t slot = TC_PER_TILE ? (size_t)(buf * TC_KS_MAX + w) : (size_t)((buf * TC_KS_MAX + w) * NT + j);
-                    const float4 v = partial[slot * 32 + lane];
-                    sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
-                }
-#endif
-                if (TC_PER_TILE || j == NT - 1) {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&pempty_bar[buf]);
-                }
-                if (p + 1 < phases) {
-                    ysum[((size_t)u * NT + j) * 32 + lane] = sum;
-                    continue;
-                }
                 if (FLT) {
                     const int n = j * 4 + t;
                     if (n < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n * rows + r0] = sum.x;
-                        if (r1 < row_end) a.y[(size_t)n * rows + r1] = sum.z;
+                        if (r0 < row_end) a.y[(size_t)n * rows + r0] = sum[j].x;
+                        if (r1 < row_end) a.y[(size_t)n * rows + r1] = sum[j].z;
                     }
                 } else {
                     const int n0 = j * 8 + 2 * t, n1 = n0 + 1;
                     if (n0 < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n0 * rows + r0] = sum.x;
-                        if (r1 < row_end) a.y[(size_t)n0 * rows + r1] = sum.z;
+                        if (r0 < row_end) a.y[(size_t)n0 * rows + r0] = sum[j].x;
+                        if (r1 < row_end) a.y[(size_t)n0 * rows + r1] = sum[j].z;
                     }
                     if (n1 < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n1 * rows + r0] = sum.y;
-                        if (r1 < row_end) a.y[(size_t)n1 * rows + r1] = sum.w;
+                        if (r0 < row_end) a.y[(size_t)n1 * rows + r0] = sum[j].y;
+                        if (r1 < row_end) a.y[(size_t)n1 * rows + r1] = sum[j].w;
                     }
                 }
             }
-            if (it < 10) TC_TRACE(40 + it);
-#ifdef TB200_TC_TRACE
-            if (lane == 0 && it == total - 1 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) g_tc_trace[blockIdx.x ? 1 : 0][63] = qg_timer_ns();
-#endif
         }
     }
 }
@@ -670,7 +589,7 @@ static bool tc_eligible(int mode, const QGemvArgs &a, const DeviceInfo *di) {
     if (FMT == FMT_Q8S && !a.dots && (!a.scales || !aligned_to(a.scales, 8))) return false;
     const int cap = mode == MODE_FLOAT ? 8 : kMaxBatch;
     if (a.batch < 1 || a.batch > cap) return false;
-    if (mode == MODE_INT ? !a.xq : (!a.xq && (!a.x || !aligned_to(a.x, 4)))) return false;  // float mode: x, or its split form in a.xq / a.xs
+    if (mode == MODE_INT ? !a.xq : (!a.x || !aligned_to(a.x, 4))) return false;
     if (a.dots ? mode != MODE_INT : !a.y) return false;
     const bool two = mode == MODE_FLOAT ? a.batch > 4 : a.batch > 8;
     TcPlan p;
@@ -682,9 +601,6 @@ static int tc_dispatch(int mode, const QGemvArgs &a, const DeviceInfo *di, cudaS
     if (a.dots)
         return a.batch <= 8 ? tc_launch<FMT, 1, X_INT_WS, true>(a, di, s, overlap)
                             : tc_launch<FMT, 2, X_INT_WS, true>(a, di, s, overlap);
-    if (mode == MODE_FLOAT && a.xq)  // split activations in a workspace (a.xq: fp16 planes, a.xs: unscale factors)
-        return a.batch <= 4 ? tc_launch<FMT, 1, X_FLOAT_WS, false>(a, di, s, overlap)
-                            : tc_launch<FMT, 2, X_FLOAT_WS, false>(a, di, s, overlap);
     if (mode == MODE_FLOAT)
         return a.batch <= 4 ? tc_launch<FMT, 1, X_FLOAT, false>(a, di, s, overlap)
                             : tc_launch<FMT, 2, X_FLOAT, false>(a, di, s, overlap);
@@ -706,9 +622,6 @@ int qtc_dispatch(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di, cu
 
 }  // namespace tb200
 
-#ifdef TB200_TC_TRACE
-extern "C" int tb200_tc_trace(unsigned long long *out) { return (int)cudaMemcpyFromSymbol(out, tb200::g_tc_trace, sizeof(tb200::g_tc_trace)); }
-#endif
 
 extern "C" int tb200_blockdots_i32_batched(int format, int rows, int cols, int batch, const void *weights, const int8_t *xq,
                                            int32_t *dots, tb200_stream_t stream) {

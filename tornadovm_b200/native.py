@@ -32,10 +32,6 @@ SIGNATURES = {
     "tb200_q8_gemv": (_I, [_I, _I, _I, _P, _P, _P, _P, _P]),
     "tb200_q8b_gemv": (_I, [_I, _I, _I, _P, _P, _P, _P]),
     "tb200_q4b_gemv": (_I, [_I, _I, _I, _P, _P, _P, _P]),
-    "tb200_fx_workspace_bytes": (_Z, [_I, _I]),
-    "tb200_q8_gemv_ws": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _Z, _P]),
-    "tb200_q8b_gemv_ws": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
-    "tb200_q4b_gemv_ws": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_qx_workspace_bytes": (_Z, [_I, _I]),
     "tb200_quantize_x": (_I, [_I, _I, _P, _P, _Z, _P]),
     "tb200_q8_gemv_i8": (_I, [_I, _I, _I, _P, _P, _P, _P, _P, _Z, _P]),

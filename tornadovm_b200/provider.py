@@ -105,13 +105,9 @@ class B200LibraryProvider:
         fn = descriptor.getFunctionName()
         tuning = descriptor.getTuning()
         B200Native.call("tb200_prepare", self._PREPARE_CLASS.get(fn, 0))
-        if fn in _QUANT_FUNCTIONS:  # (rows, cols, batch, ...)
+        if fn in _QUANT_FUNCTIONS and isinstance(tuning, B200Options) and tuning.exact_int:
             p = descriptor.getParameters()
-            lib = B200Native.load()
-            if isinstance(tuning, B200Options) and tuning.exact_int:
-                need = lib.tb200_qx_workspace_bytes(int(p[1]), int(p[2]))  # int8 activations and their scales
-            else:
-                need = lib.tb200_fx_workspace_bytes(int(p[1]), int(p[2]))  # float mode: the activations as fp16 pairs
+            need = B200Native.load().tb200_qx_workspace_bytes(int(p[1]), int(p[2]))
             context.grow_workspace(int(need))
         if fn in _PACKED_FUNCTIONS:  # (count, rows, cols, batch, blocks, x, y)
             p = descriptor.getParameters()
@@ -150,17 +146,17 @@ class B200LibraryProvider:
             if exact:
                 st = lib.tb200_q8_gemv_i8(A(0), A(1), A(2), P(3), P(4), P(5), P(6), *ws, ctx.stream)
             else:
-                st = lib.tb200_q8_gemv_ws(A(0), A(1), A(2), P(3), P(4), P(5), P(6), *ws, ctx.stream)
+                st = lib.tb200_q8_gemv(A(0), A(1), A(2), P(3), P(4), P(5), P(6), ctx.stream)
         elif functionName == "q8GemvBytes":  # (rows, cols, batch, blocks, x, y)
             if exact:
                 st = lib.tb200_q8b_gemv_i8(A(0), A(1), A(2), P(3), P(4), P(5), *ws, ctx.stream)
             else:
-                st = lib.tb200_q8b_gemv_ws(A(0), A(1), A(2), P(3), P(4), P(5), *ws, ctx.stream)
+                st = lib.tb200_q8b_gemv(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
         elif functionName == "q4GemvBytes":
             if exact:
                 st = lib.tb200_q4b_gemv_i8(A(0), A(1), A(2), P(3), P(4), P(5), *ws, ctx.stream)
             else:
-                st = lib.tb200_q4b_gemv_ws(A(0), A(1), A(2), P(3), P(4), P(5), *ws, ctx.stream)
+                st = lib.tb200_q4b_gemv(A(0), A(1), A(2), P(3), P(4), P(5), ctx.stream)
         elif functionName in _GROUPED_FUNCTIONS:  # (count, rows, cols, batch, x, y, blocks...)
             count = A(0)
             blocks = (C.c_void_p * count)(*[P(6 + m) for m in range(count)])
