@@ -23,6 +23,7 @@ fixed).
 from __future__ import annotations
 
 import argparse
+import datetime
 import ctypes as C
 import json
 import os
@@ -413,7 +414,7 @@ def run_gpu_arm(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     lib = B200Native.load()  # raises if libtornado_b200.so is missing
     hbm_peak, tensor_peak, peak_kind = measured_peaks()
 
@@ -678,7 +679,7 @@ def run_hgemm_sharded(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     _, tensor_peak, _ = measured_peaks()
     out = measure_hgemm_sharded(torch, dist, [int(v) for v in args.hgemm_sizes.split(",")], dev, world, rank, tensor_peak)
     if rank == 0:

@@ -5,6 +5,7 @@ mat-vec whose kernel stores its outputs into every GPU's buffer (consecutive ste
 activations, so output slots are reused; ragged row shards), and the column-sharded FP16 GEMM whose epilogue
 stores every tile to every GPU.  Plain peer loads and stores only.
 """
+import datetime
 import os
 import sys
 
@@ -24,7 +25,8 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    # a short collective time-out: a rank that fails must not keep the others (and the GPUs) waiting for minutes
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     ok = True
 
     # ---- grouped Q8_0 / Q4_0 mat-vec, rows sharded (the last rank owns fewer rows) ----
