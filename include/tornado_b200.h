@@ -386,6 +386,17 @@ size_t tb200_igemm_workspace_bytes(int n, int k);
 int tb200_igemm_s32(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
                     tb200_stream_t stream);
 
+/* ---- fp8 GEMM, fp32 accumulate and output --------------------------------------
+ * C(f32)[m][n] = A(fp8)[m][k] * B(fp8)[k][n], row-major; both operands in the same OCP format.
+ * Replaces the tile-API fp8 kernels (KernelContext.mmaFP8E4M3 / mmaFP8E5M2 with MMAShape.M16N8K32; kernels,
+ * reference loops and tolerance 1e-3 in
+ * tornado-unittests/.../kernelcontext/matrices/TestMatrixMultiplicationMMAFP8.java:80-248, :415-430; byte
+ * formats of tornado-api/.../types/FP8.java) on tcgen05.mma.kind::f8f6f4.  Workspace and shape rules as for
+ * tb200_igemm_s32. */
+enum tb200_fp8_format { TB200_FP8_E4M3 = 0, TB200_FP8_E5M2 = 1 };
+int tb200_fp8gemm_f32(int m, int n, int k, int format, const uint8_t *a, const uint8_t *b, float *c, void *workspace,
+                      size_t workspace_bytes, tb200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -369,3 +369,52 @@ def gemm_epilogue_ref(prod, act="none", alpha=1.0, beta=0.0, c=None, bias=None):
     if bias is not None:
         x = x + np.asarray(bias, np.float64)[None, :]
     return activation_ref(x, act)
+
+
+# -- fp8 (OCP E4M3 / E5M2), restated from tornado-api/.../types/FP8.java:44-80 and the OCP 8-bit float specification ----
+def fp8_decode_table(fmt: str) -> np.ndarray:
+    """float32 value of every byte.  E4M3: bias 7, subnormals m * 2^-9, no infinity, S.1111.111 = NaN, max 448
+    (FP8.java:41, :52-76).  E5M2: bias 15, IEEE-like (the upper byte of an fp16), max 57344 (FP8.java:43)."""
+    out = np.empty(256, np.float32)
+    for b in range(256):
+        sign = -1.0 if b & 0x80 else 1.0
+        if fmt == "e4m3":
+            e, m = (b >> 3) & 15, b & 7
+            if e == 0:
+                v = m * 2.0 ** -9
+            elif e == 15 and m == 7:
+                v = float("nan")
+            else:
+                v = (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        elif fmt == "e5m2":
+            e, m = (b >> 2) & 31, b & 3
+            if e == 0:
+                v = m * 2.0 ** -16
+            elif e == 31:
+                v = float("inf") if m == 0 else float("nan")
+            else:
+                v = (1.0 + m / 4.0) * 2.0 ** (e - 15)
+        else:
+            raise ValueError(fmt)
+        out[b] = sign * v
+    return out
+
+
+def fp8_encode_exact(values: np.ndarray, fmt: str) -> np.ndarray:
+    """Bytes of values that the format represents exactly (the reference's test inputs, multiples of 0.25 in
+    [-2, 2): TestMatrixMultiplicationMMAFP8.java:433-439); raises on any other value."""
+    table = fp8_decode_table(fmt)
+    lookup = {}
+    for b in range(256):
+        v = float(table[b])
+        if v == v and abs(v) != float("inf") and v not in lookup:  # +0 before -0, finite only
+            lookup[v] = b
+    return np.array([lookup[float(v)] for v in np.asarray(values, np.float32).ravel()], np.uint8)
+
+
+def fp8_gemm_ref(a: np.ndarray, b: np.ndarray, m: int, n: int, k: int, fmt: str) -> np.ndarray:
+    """gemmReferenceE4M3 / gemmReferenceE5M2 (TestMatrixMultiplicationMMAFP8.java:226-248): decode, multiply,
+    accumulate.  Accumulated in float64 here; for the reference's exactly representable inputs every partial sum is
+    exact in fp32 as well, so the order and the width of the accumulator do not matter (:420-423)."""
+    t = fp8_decode_table(fmt).astype(np.float64)
+    return (t[np.asarray(a, np.uint8).reshape(m, k)] @ t[np.asarray(b, np.uint8).reshape(k, n)])

@@ -191,3 +191,21 @@ def test_q8_blockdots_and_combine():
     assert np.allclose(y, ref, rtol=1e-12)
     # the int path approximates the float path to quantisation accuracy
     assert o.rel_l2(y, o.q8_gemv_f64(q, s, x, cols, rows)) < 2e-2
+
+
+def test_fp8_tables_match_the_reference_formats():
+    """Constants and encodings of tornado-api/.../types/FP8.java:41-43, :52-76."""
+    e4, e5 = o.fp8_decode_table("e4m3"), o.fp8_decode_table("e5m2")
+    assert e4[0x7E] == 448.0 and e4[0xFE] == -448.0 and np.isnan(e4[0x7F]) and np.isnan(e4[0xFF])  # max normal, the one NaN
+    assert e4[0x38] == 1.0 and e4[0x01] == 2.0 ** -9 and e4[0x08] == 2.0 ** -6 and e4[0x00] == 0.0
+    assert np.isfinite(e4[:0x7F]).all() and (np.diff(e4[:0x7F]) > 0).all()  # monotonic: no infinity below the NaN
+    assert e5[0x7B] == 57344.0 and np.isinf(e5[0x7C]) and np.isnan(e5[0x7D]) and e5[0x3C] == 1.0 and e5[0x01] == 2.0 ** -16
+    # E5M2 is the upper byte of an IEEE half
+    halves = (np.arange(256, dtype=np.uint16) << 8).view(np.float16).astype(np.float32)
+    assert np.array_equal(np.nan_to_num(halves, nan=7.0), np.nan_to_num(e5, nan=7.0))
+    # the reference's test values are exact in both formats, and the all-halves case gives K * 0.25
+    vals = (np.arange(16) - 8) * 0.25
+    for fmt, table in (("e4m3", e4), ("e5m2", e5)):
+        assert np.array_equal(table[o.fp8_encode_exact(vals, fmt)], vals.astype(np.float32))
+    half = o.fp8_encode_exact(np.full(16 * 32, 0.5), "e4m3")
+    assert np.array_equal(o.fp8_gemm_ref(half, half, 16, 16, 32, "e4m3"), np.full((16, 16), 8.0))

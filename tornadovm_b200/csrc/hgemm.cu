@@ -98,6 +98,16 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem], M128 x N x K32, fp8 inputs (E4M3 or E5M2 by the descriptor), fp32 accumulate
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tc_ld_32cols(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
@@ -451,11 +461,12 @@ struct HgTile {
 //     are overwritten with zeros in shared memory before the first MMA reads them;
 //   B (N contiguous): column n appears at n' = n + nshift; tiles cover n' = 0 .. N + nshift - 1 and the epilogue
 //     stores tile column n' to column n' - nshift, skipping the nshift columns in front of the first tile.
-// I8 = true: the same pipeline for int8 operands with int32 accumulation (tcgen05.mma.kind::i8, K = 32 per
-// instruction, 128 elements per 128-byte swizzled row).  Both operands are K-major there: A[m][k] as it is, B as
-// its transpose Bt[n][k] (the caller's [k][n] matrix is transposed once into workspace memory), so a stage is
-// 128 rows of A and BN rows of Bt, 128 bytes each -- the byte sizes of the 16-bit stage.
-template <int BN, bool I8 = false>
+// K8 = 1 / 2: the same pipeline for 8-bit operands -- int8 with int32 accumulation (tcgen05.mma.kind::i8) or fp8
+// with fp32 accumulation (kind::f8f6f4, E4M3 / E5M2 chosen by the instruction descriptor); K = 32 per instruction,
+// 128 elements per 128-byte swizzled row.  Both operands are K-major there: A[m][k] as it is, B as its transpose
+// Bt[n][k] (the caller's [k][n] matrix is transposed once into workspace memory), so a stage is 128 rows of A and
+// BN rows of Bt, 128 bytes each -- the byte sizes of the 16-bit stage.
+template <int BN, int K8 = 0>
 __global__ void __launch_bounds__(HG_THREADS, 1)
 hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
                 const __grid_constant__ HgOut out, int M, int N, int K, int batches, int rows_vec, int gm, uint32_t idesc, int kshift, int nshift) {
@@ -476,6 +487,7 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int tiles_m = (M + HG_BM - 1) / HG_BM, tiles_n = (N + nshift + BN - 1) / BN;
     const int tiles_per_matrix = tiles_m * tiles_n;
     const int num_tiles = tiles_per_matrix * batches;
+    constexpr bool I8 = K8 != 0;                  // 8-bit operands
     constexpr int BKE = I8 ? 2 * HG_BK : HG_BK;  // elements of K per stage (128 bytes)
     const int k_blocks = (K + kshift + BKE - 1) / BKE;
     const int edge_cols = (N + nshift) - (tiles_n - 1) * BN;  // columns of the last tile column
@@ -592,7 +604,8 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                         for (int k16 = 0; k16 < HG_BK / 16; ++k16) {
                             // A advances 32 bytes along K per instruction; B advances 16 k-rows = 2048 bytes (int8: 32 bytes along K)
-                            if (I8) tc_mma_i8(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc_tile, (kb > 0 || k16 > 0) ? 1u : 0u);
+                            if (K8 == 1) tc_mma_i8(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc_tile, (kb > 0 || k16 > 0) ? 1u : 0u);
+                            else if (K8 == 2) tc_mma_f8(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 2), idesc_tile, (kb > 0 || k16 > 0) ? 1u : 0u);
                             else tc_mma_f16(d_tmem, a_desc + (uint64_t)(k16 * 2), b_desc + (uint64_t)(k16 * 128), idesc_tile, (kb > 0 || k16 > 0) ? 1u : 0u);
                         }
                         tc_commit(&empty_bar[s]);  // arrives once the MMAs above have read this stage
@@ -1010,7 +1023,7 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     return check_launch();
 }
 
-// ---- int8 GEMM -----------------------------------------------------------------------------------
+// ---- int8 and fp8 GEMM ---------------------------------------------------------------------------
 // Bt[n][k] = B[k][n], bytes; 32 x 32 tiles through shared memory
 __global__ void __launch_bounds__(256) transpose_bytes_kernel(const int8_t *__restrict__ b, int8_t *__restrict__ bt, int k, int n) {
     __shared__ int8_t tile[32][33];
@@ -1023,18 +1036,38 @@ __global__ void __launch_bounds__(256) transpose_bytes_kernel(const int8_t *__re
         if (n0 + r < n && k0 + tx < k) bt[(size_t)(n0 + r) * k + k0 + tx] = tile[tx][r];
 }
 
-// any shape and alignment: one thread per output
-__global__ void __launch_bounds__(256) igemm_generic_kernel(int m, int n, int k, const int8_t *__restrict__ a, const int8_t *__restrict__ b,
-                                                            int32_t *__restrict__ c) {
+// fp8 byte -> float: E5M2 is the upper byte of an fp16; E4M3 has bias 7, subnormals m * 2^-9 and one NaN (S.1111.111)
+__device__ __forceinline__ float fp8_to_float(uint8_t v, int e5m2) {
+    if (e5m2) return half_bits_to_float((uint16_t)((uint16_t)v << 8));
+    const int sign = v >> 7, e = (v >> 3) & 15, mant = v & 7;
+    float r;
+    if (e == 0) r = ldexpf((float)mant, -9);
+    else if (e == 15 && mant == 7) r = __int_as_float(0x7fc00000);
+    else r = ldexpf(1.0f + (float)mant * 0.125f, e - 7);
+    return sign ? -r : r;
+}
+
+// any shape and alignment: one thread per output (KIND 1: int8 -> int32, 2: fp8 -> fp32 accumulated in k order)
+template <int KIND>
+__global__ void __launch_bounds__(256) gemm8_generic_kernel(int m, int n, int k, const uint8_t *__restrict__ a, const uint8_t *__restrict__ b,
+                                                            void *__restrict__ c, int e5m2) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)m * n) return;
     const int row = (int)(i / n), col = (int)(i - (long long)row * n);
-    int acc = 0;
-    for (int kk = 0; kk < k; ++kk) acc += (int)a[(size_t)row * k + kk] * (int)b[(size_t)kk * n + col];
-    c[i] = acc;
+    if (KIND == 1) {
+        int acc = 0;
+        for (int kk = 0; kk < k; ++kk) acc += (int)(int8_t)a[(size_t)row * k + kk] * (int)(int8_t)b[(size_t)kk * n + col];
+        reinterpret_cast<int32_t *>(c)[i] = acc;
+    } else {
+        float acc = 0.f;
+        for (int kk = 0; kk < k; ++kk) acc = fmaf(fp8_to_float(a[(size_t)row * k + kk], e5m2), fp8_to_float(b[(size_t)kk * n + col], e5m2), acc);
+        reinterpret_cast<float *>(c)[i] = acc;
+    }
 }
 
-static int igemm_launch(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
+// KIND 1: int8 x int8 -> int32 (tcgen05.mma.kind::i8); KIND 2: fp8 x fp8 -> fp32 (kind::f8f6f4, format 0 = E4M3, 1 = E5M2)
+template <int KIND>
+static int gemm8_launch(int m, int n, int k, const uint8_t *a, const uint8_t *b, void *c, int e5m2, void *workspace, size_t workspace_bytes,
                         tb200_stream_t stream) {
     if (m < 0 || n < 0 || k < 0) return TB200_ERR_INVALID_ARG;
     if (m == 0 || n == 0) return TB200_OK;
@@ -1047,16 +1080,16 @@ static int igemm_launch(int m, int n, int k, const int8_t *a, const int8_t *b, i
     const bool tensor = k >= 32 && k % 16 == 0 && aligned_to(a, 16) && (long long)m * n >= 64 * 64 && workspace && aligned_to(workspace, 16) &&
                         workspace_bytes >= (size_t)n * k;
     if (!tensor) {
-        st = ensure_kernel<igemm_generic_kernel, 0>(di);
+        st = ensure_kernel<gemm8_generic_kernel<KIND>, 0>(di);
         if (st) return st;
         const long long total = (long long)m * n;
-        igemm_generic_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(m, n, k, a, b, c);
+        gemm8_generic_kernel<KIND><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(m, n, k, a, b, c, e5m2);
         return check_launch();
     }
     st = ensure_kernel<transpose_bytes_kernel, 0>(di);
     if (st) return st;
     int8_t *bt = reinterpret_cast<int8_t *>(workspace);
-    transpose_bytes_kernel<<<dim3((n + 31) / 32, (k + 31) / 32), 256, 0, s>>>(b, bt, k, n);
+    transpose_bytes_kernel<<<dim3((n + 31) / 32, (k + 31) / 32), 256, 0, s>>>(reinterpret_cast<const int8_t *>(b), bt, k, n);
     st = check_launch();
     if (st) return st;
     HgOut out{};
@@ -1070,22 +1103,24 @@ static int igemm_launch(int m, int n, int k, const int8_t *a, const int8_t *b, i
     if (st) return st;
     st = make_map(&map_b, bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)k, (uint64_t)n, 1, 0, 128, (uint32_t)bn);
     if (st) return st;
-    out.tma_store = vec;
+    out.tma_store = vec;  // 32-bit results of either kind leave as they are
     if (out.tma_store && make_map(&map_d, c, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)n, (uint64_t)m, 1, 0, 32, 32) != TB200_OK) out.tma_store = 0;
-    // kind::i8: D format 2 = S32 at [4,6), A and B format 1 = signed 8-bit at [7,10) and [10,13), both K-major
-    const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(HG_BM >> 4) << 24);
+    // instruction descriptor, both operands K-major: D format at [4,6) (1 = F32, 2 = S32), A and B formats at [7,10) and
+    // [10,13) (kind::i8: 1 = signed 8-bit; kind::f8f6f4: 0 = E4M3, 1 = E5M2), N >> 3 at [17,23), M >> 4 at [24,29)
+    const uint32_t fmt = KIND == 1 ? 1u : (e5m2 ? 1u : 0u);
+    const uint32_t idesc = ((KIND == 1 ? 2u : 1u) << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(HG_BM >> 4) << 24);
     const long long tiles = (long long)((m + HG_BM - 1) / HG_BM) * ((n + bn - 1) / bn);
     const int grid = tiles < di->sm_count ? (int)tiles : di->sm_count;
     long long g = (48ll << 20) / ((long long)HG_BM * k);
     const int gm = (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
     if (wide) {
-        st = ensure_smem_optin<hgemm_tc_kernel<256, true>>(di);
+        st = ensure_smem_optin<hgemm_tc_kernel<256, KIND>>(di);
         if (st) return st;
-        hgemm_tc_kernel<256, true><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
+        hgemm_tc_kernel<256, KIND><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
     } else {
-        st = ensure_smem_optin<hgemm_tc_kernel<128, true>>(di);
+        st = ensure_smem_optin<hgemm_tc_kernel<128, KIND>>(di);
         if (st) return st;
-        hgemm_tc_kernel<128, true><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
+        hgemm_tc_kernel<128, KIND><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
     }
     return check_launch();
 }
@@ -1098,7 +1133,13 @@ extern "C" size_t tb200_igemm_workspace_bytes(int n, int k) { return n > 0 && k 
 
 extern "C" int tb200_igemm_s32(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
                                tb200_stream_t stream) {
-    return igemm_launch(m, n, k, a, b, c, workspace, workspace_bytes, stream);
+    return gemm8_launch<1>(m, n, k, reinterpret_cast<const uint8_t *>(a), reinterpret_cast<const uint8_t *>(b), c, 0, workspace, workspace_bytes, stream);
+}
+
+extern "C" int tb200_fp8gemm_f32(int m, int n, int k, int format, const uint8_t *a, const uint8_t *b, float *c, void *workspace,
+                                 size_t workspace_bytes, tb200_stream_t stream) {
+    if (format != TB200_FP8_E4M3 && format != TB200_FP8_E5M2) return TB200_ERR_INVALID_ARG;
+    return gemm8_launch<2>(m, n, k, a, b, c, format == TB200_FP8_E5M2, workspace, workspace_bytes, stream);
 }
 
 extern "C" int tb200_hgemm_f32(int m, int n, int k, const uint16_t *a, const uint16_t *b, float *c, tb200_stream_t stream) {

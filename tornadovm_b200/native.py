@@ -59,6 +59,7 @@ SIGNATURES = {
     "tb200_gemm_ex": (_I, [_I, _I, _I, _I, _P, _P, _I, _P, _F, _F, _P, _P, _I, _I, _P]),
     "tb200_igemm_workspace_bytes": (_Z, [_I, _I]),
     "tb200_igemm_s32": (_I, [_I, _I, _I, _P, _P, _P, _P, _Z, _P]),
+    "tb200_fp8gemm_f32": (_I, [_I, _I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "tb200_hgemm_f32_scatter": (_I, [_I, _I, _I, _P, _P, _P, _I, C.c_longlong, C.c_longlong, _P]),
 }
 
