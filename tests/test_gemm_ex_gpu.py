@@ -112,6 +112,29 @@ def test_gemm_batched(lib, batches, m, n, k, out_type):
     assert dd.guard_intact()
 
 
+@pytest.mark.parametrize("in_type,out_type", [(IN_F16, OUT_F16), (IN_BF16, OUT_BF16), (IN_F16, OUT_F32)])
+@pytest.mark.parametrize("batches,m,n,k", [(1, 300, 264, 136), (1, 256, 512, 256), (3, 136, 200, 96)])
+def test_gemm_ex_every_array_behind_a_24_byte_header(lib, in_type, out_type, batches, m, n, k):
+    """TornadoVM's default array header: A, B, C, bias and D all 8 bytes past a 16-byte boundary, with the fused
+    epilogue act(alpha*A*B + beta*C + bias), typed outputs and batches."""
+    a, b, af, bf = _operands(m, n, k, in_type, 33, batches)
+    c = _to_out(o.JavaRandom(34).uniform_f32(batches * m * n, -1, 1), out_type)
+    bias = _to_out(o.JavaRandom(35).uniform_f32(n, -1, 1), out_type)
+    da, db, dc, dbias = DevBuf(a, 24), DevBuf(b, 24), DevBuf(c, 24), DevBuf(bias, 24)
+    dd = out_buf(batches * m * n, np.float32 if out_type == OUT_F32 else np.uint16, header=24)
+    use_bias = batches == 1  # a batched call takes no bias row
+    _ok(lib.tb200_gemm_ex(m, n, k, in_type, da.ptr, db.ptr, out_type, dd.ptr, 0.75, 0.5, dc.ptr, dbias.ptr if use_bias else None, ACTS["silu"], batches,
+                          stream_ptr()), lib)
+    sync_and_check(lib)
+    got = _from_out(dd.numpy(), out_type).reshape(batches, m, n)
+    cf = _from_out(c, out_type).reshape(batches, m, n)
+    for i in range(batches):
+        prod = _product(af[i * m * k:(i + 1) * m * k], bf[i * k * n:(i + 1) * k * n], m, n, k)
+        want = o.gemm_epilogue_ref(prod, "silu", 0.75, 0.5, cf[i], bias=_from_out(bias, out_type) if use_bias else None)
+        assert o.rel_l2(got[i], want) <= REL_L2[out_type], (i, o.rel_l2(got[i], want))
+    assert dd.guard_intact() and dc.guard_intact() and dbias.guard_intact()
+
+
 def test_gemm_ex_equals_plain_entry_and_argument_errors(lib):
     m, n, k = 256, 384, 128
     a, b = o.make_hgemm(m, n, k, 3)

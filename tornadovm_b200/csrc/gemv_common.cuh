@@ -50,6 +50,12 @@ struct QGroupArgs {
 };
 
 __device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
+// four unsigned bytes of a times four signed bytes of b
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 
 // floor(v * inv + 0.5) as the low byte of the result (a signed byte), for |v * inv| <= 127: the rule of
 // quantizeKernelContext (MatrixVectorRowMajor.java:349-354) without the conversion unit.  Adding 1.5 * 2^23 with

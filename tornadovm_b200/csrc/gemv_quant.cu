@@ -656,15 +656,18 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                                 d1 = dp4a_s8(qb[r][i], xw[8 + i], d1);
                             }
                         } else {
+                            // high nibbles stay where they are: as unsigned bytes they are 16 x the nibble, so their
+                            // dot is a multiple of 16 and the shift below is exact (saves a shift per word)
+                            int h0 = 0, h1 = 0;
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 d0 = dp4a_s8(qa[r][i] & 0x0F0F0F0Fu, xw[i], d0);
-                                d0 = dp4a_s8((qa[r][i] >> 4) & 0x0F0F0F0Fu, xw[4 + i], d0);
+                                h0 = dp4a_u8s8(qa[r][i] & 0xF0F0F0F0u, xw[4 + i], h0);
                                 d1 = dp4a_s8(qb[r][i] & 0x0F0F0F0Fu, xw[8 + i], d1);
-                                d1 = dp4a_s8((qb[r][i] >> 4) & 0x0F0F0F0Fu, xw[12 + i], d1);
+                                h1 = dp4a_u8s8(qb[r][i] & 0xF0F0F0F0u, xw[12 + i], h1);
                             }
-                            d0 -= 8 * xsm.x;
-                            d1 -= 8 * xsm.y;
+                            d0 += (h0 >> 4) - 8 * xsm.x;
+                            d1 += (h1 >> 4) - 8 * xsm.y;
                         }
                         if (DOTS && b == 0 && row0 + r < row_end) {
                             int32_t *dp = a.dots + (size_t)(row0 + r) * bpr + blk0;
