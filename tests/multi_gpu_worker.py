@@ -45,9 +45,12 @@ def main():
         shards = [torch.from_numpy(np.ascontiguousarray(b[r0 * row_bytes:r1 * row_bytes])).to(dev) for b, _, _ in mats]
         op = ShardedGroupedGemv(rows, cols, batch, shards, fmt, per_launch=2, nslots=2)
         try:
-            for step in range(6):
+            xh = torch.empty((batch, cols)).pin_memory()  # one pinned buffer: the graph-replayed steps read it in place
+            for step in range(8):
                 x = o.JavaRandom(900 + step).gaussian_f32(batch * cols)
-                got = op.run(torch.from_numpy(x).reshape(batch, cols).pin_memory()).numpy().copy()
+                xh.copy_(torch.from_numpy(x).reshape(batch, cols))
+                # plain steps first, then steps replayed from the per-slot CUDA graphs (captured at steps 3 and 4)
+                got = op.run(xh, graph=step >= 3).numpy().copy()
                 for m, (blocks, q, s) in enumerate(mats):
                     for b in range(batch):
                         xq, xs = o.quantize_x_block(np.ascontiguousarray(x[b * cols:(b + 1) * cols]))

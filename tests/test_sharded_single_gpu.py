@@ -27,6 +27,10 @@ def test_sharded_grouped_gemv_one_rank_matches_single_launches():
         xh = torch.from_numpy(x).reshape(1, cols).pin_memory()
         for _ in range(3):
             y = op.run(xh).clone()
+        # the same step replayed from a CUDA graph gives the same bits
+        for _ in range(3):
+            yg = op.run(xh, graph=True).clone()
+        assert torch.equal(yg, y)
         ws_n = lib.tb200_qx_workspace_bytes(cols, 1)
         ws = torch.empty(ws_n, dtype=torch.uint8, device="cuda")
         xd = xh.cuda()

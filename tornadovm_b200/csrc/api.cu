@@ -17,6 +17,23 @@ int tu_status_gemv_tc(int *);
 int tu_status_sgemm(int *);
 int tu_status_hgemm(int *);
 int tu_status_peer(int *);
+int tu_status_read_async_api(int *);
+int tu_status_clear_api();
+int tu_status_read_async_gemv_f32(int *);
+int tu_status_clear_gemv_f32();
+int tu_status_read_async_gemv_quant(int *);
+int tu_status_clear_gemv_quant();
+int tu_status_read_async_gemv_mma(int *);
+int tu_status_clear_gemv_mma();
+int tu_status_read_async_gemv_tc(int *);
+int tu_status_clear_gemv_tc();
+int tu_status_read_async_sgemm(int *);
+int tu_status_clear_sgemm();
+int tu_status_read_async_hgemm(int *);
+int tu_status_clear_hgemm();
+int tu_status_read_async_peer(int *);
+int tu_status_clear_peer();
+
 
 // ---- options ---------------------------------------------------------------------------------
 constexpr int kNumOptions = 8;  // option ids are 1 .. kNumOptions - 1
@@ -236,25 +253,49 @@ extern "C" int tb200_version(void) { return TB200_VERSION; }
 extern "C" int tb200_device_status_of(int op_classes, int *status_out) {
     if (!status_out) return TB200_ERR_INVALID_ARG;
     struct Reader {
-        int (*fn)(int *);
+        int (*read_async)(int *);
+        int (*clear)();
         int op_class;
     };
-    const Reader readers[] = {{tu_status_api, TB200_PREPARE_ALL},
-                              {tu_status_gemv_f32, TB200_PREPARE_GEMV_F32},
-                              {tu_status_gemv_quant, TB200_PREPARE_GEMV_QUANT},
-                              {tu_status_gemv_mma, TB200_PREPARE_GEMV_QUANT},
-                              {tu_status_gemv_tc, TB200_PREPARE_GEMV_QUANT},
-                              {tu_status_sgemm, TB200_PREPARE_GEMM_F32},
-                              {tu_status_hgemm, TB200_PREPARE_GEMM_F16},
-                              {tu_status_peer, TB200_PREPARE_PEER}};
+    static const Reader readers[] = {{tu_status_read_async_api, tu_status_clear_api, TB200_PREPARE_ALL},
+                                     {tu_status_read_async_gemv_f32, tu_status_clear_gemv_f32, TB200_PREPARE_GEMV_F32},
+                                     {tu_status_read_async_gemv_quant, tu_status_clear_gemv_quant, TB200_PREPARE_GEMV_QUANT},
+                                     {tu_status_read_async_gemv_mma, tu_status_clear_gemv_mma, TB200_PREPARE_GEMV_QUANT},
+                                     {tu_status_read_async_gemv_tc, tu_status_clear_gemv_tc, TB200_PREPARE_GEMV_QUANT},
+                                     {tu_status_read_async_sgemm, tu_status_clear_sgemm, TB200_PREPARE_GEMM_F32},
+                                     {tu_status_read_async_hgemm, tu_status_clear_hgemm, TB200_PREPARE_GEMM_F16},
+                                     {tu_status_read_async_peer, tu_status_clear_peer, TB200_PREPARE_PEER}};
+    constexpr int kReaders = sizeof(readers) / sizeof(readers[0]);
+    // One word per translation unit: the reads are enqueued together into pinned memory and waited for once (a
+    // host class calls this after every step; eight blocking copies cost more than the step's launch).
+    static std::mutex mutex;
+    static int *pinned = nullptr;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!pinned) {
+        void *p = nullptr;
+        cudaError_t e = cudaHostAlloc(&p, kReaders * sizeof(int), cudaHostAllocPortable);
+        if (e != cudaSuccess) return (int)e;
+        pinned = static_cast<int *>(p);
+    }
     if (op_classes == 0) op_classes = TB200_PREPARE_ALL;
+    bool selected[kReaders];
+    for (int i = 0; i < kReaders; ++i) {
+        const Reader &r = readers[i];
+        selected[i] = r.op_class != TB200_PREPARE_ALL ? (r.op_class & op_classes) != 0 : op_classes == TB200_PREPARE_ALL;
+        pinned[i] = 0;
+        if (selected[i]) {
+            const int st = r.read_async(pinned + i);
+            if (st) return st;
+        }
+    }
+    cudaError_t e = cudaStreamSynchronize(0);
+    if (e != cudaSuccess) return (int)e;
     int combined = 0;
-    for (const Reader &r : readers) {
-        if (r.op_class != TB200_PREPARE_ALL ? !(r.op_class & op_classes) : op_classes != TB200_PREPARE_ALL) continue;
-        int v = 0;
-        const int st = r.fn(&v);  // read and clear, like cudaGetLastError
+    for (int i = 0; i < kReaders; ++i) {
+        if (!selected[i] || pinned[i] == 0) continue;
+        if (combined == 0) combined = pinned[i];
+        const int st = readers[i].clear();  // read and clear, like cudaGetLastError
         if (st) return st;
-        if (v != 0 && combined == 0) combined = v;
     }
     *status_out = combined;
     return TB200_OK;

@@ -113,6 +113,7 @@ static inline int resident_ctas(const DeviceInfo *di, int threads, size_t smem) 
 // Exports this translation unit's status word (read, and clear when set).
 #define TB200_TU_STATUS(name)                                                                   \
     namespace tb200 {                                                                           \
+    /* read and clear */                                                                        \
     int tu_status_##name(int *value) {                                                          \
         int v = 0;                                                                              \
         cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));                 \
@@ -124,6 +125,15 @@ static inline int resident_ctas(const DeviceInfo *di, int threads, size_t smem) 
         }                                                                                       \
         *value = v;                                                                             \
         return TB200_OK;                                                                        \
+    }                                                                                           \
+    /* the same in two steps, so that one synchronisation serves several units: enqueue the read */ \
+    /* into pinned memory on the legacy stream, and clear after the caller has synchronised */   \
+    int tu_status_read_async_##name(int *pinned) {                                              \
+        return (int)cudaMemcpyFromSymbolAsync(pinned, g_device_status, sizeof(int), 0, cudaMemcpyDeviceToHost, 0); \
+    }                                                                                           \
+    int tu_status_clear_##name() {                                                              \
+        const int zero = 0;                                                                     \
+        return (int)cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));                    \
     }                                                                                           \
     }
 

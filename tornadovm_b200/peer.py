@@ -150,6 +150,7 @@ class ShardedGroupedGemv:
         self.fn_sync = getattr(self.lib, self.fn_name + "_sync")
         assert self.world == 1 or rows >= self.world * 1 and self.local_rows >= 1, "every rank needs at least one row"
         self.steps = 0  # steps enqueued so far; step s writes slot s % nslots
+        self._step_graphs = {}  # (slot, download, host pointer) -> (captured step, its output slot)
 
     def launch(self) -> torch.Tensor:
         """Enqueue one step.  With several ranks the kernels carry the hand-shake: the first launch of the step
@@ -188,20 +189,45 @@ class ShardedGroupedGemv:
         if status != 0:
             raise TornadoB200Error(f"{self.fn_name} (step {self.steps})", status, B200Native.status_string(status))
 
-    def run(self, x_host: torch.Tensor, download: bool = True) -> torch.Tensor:
+    def run(self, x_host: torch.Tensor, download: bool = True, graph: bool = False) -> torch.Tensor:
         """One step end to end.  ``download=False`` leaves the gathered result on the device (returned as the
-        device tensor): a rank whose consumer reads it there need not copy it to the host."""
-        with torch.cuda.stream(self.stream):
-            self.x_dev.copy_(x_host, non_blocking=True)
-            y = self.launch()
-            self.wait()
-            if download:
-                self.y_host.copy_(y, non_blocking=True)
+        device tensor): a rank whose consumer reads it there need not copy it to the host.  ``graph=True`` replays
+        the step (upload, launches, hand-shake, download) from a CUDA graph captured on first use -- one per output
+        slot, because the slot a step writes follows the step count -- the way a TornadoVM plan ``withCUDAGraph()``
+        replays its tasks; ``x_host`` must then be the same pinned tensor on every call."""
+        if graph:
+            slot = self.steps % self.nslots if self.world > 1 else 0
+            key = (slot, bool(download), x_host.data_ptr())
+            entry = self._step_graphs.get(key)
+            if entry is None:
+                self.stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                steps_before = self.steps
+                with torch.cuda.graph(g, stream=self.stream):
+                    self.x_dev.copy_(x_host, non_blocking=True)
+                    y = self.launch()
+                    self.wait()
+                    if download:
+                        self.y_host.copy_(y, non_blocking=True)
+                self.steps = steps_before  # capture enqueued nothing; the replay below is the step
+                entry = self._step_graphs[key] = (g, y)
+            g, y = entry
+            with torch.cuda.stream(self.stream):
+                g.replay()
+            self.steps += 1
+        else:
+            with torch.cuda.stream(self.stream):
+                self.x_dev.copy_(x_host, non_blocking=True)
+                y = self.launch()
+                self.wait()
+                if download:
+                    self.y_host.copy_(y, non_blocking=True)
         self.stream.synchronize()
         self.check()
         return self.y_host if download else y
 
     def close(self) -> None:
         self.stream.synchronize()
+        self._step_graphs = {}
         self.halves = None
         self.slab.close()
