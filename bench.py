@@ -475,6 +475,13 @@ def run_gpu_arm(args):
                 step_graph = None
             barrier()
         with ClockSampler(local) as clocks:
+            if world > 1:
+                # The ranks leave the host barrier up to a few hundred microseconds apart, which a 20-step region of
+                # about a millisecond would count as step time on the early ranks.  One untimed step and its peer
+                # wait in front of the start event align the GPUs themselves: the wait kernel returns on every rank
+                # only when every rank has announced that step, and the timed launches are already enqueued behind it.
+                op.launch()
+                op.wait()
             e0.record(stream)
             if step_graph is not None:
                 step_graph.replay()

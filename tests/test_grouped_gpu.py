@@ -32,16 +32,16 @@ def _case(fmt, rows, cols, batch, count):
     return mats, x
 
 
-def _single(lib, fmt, rows, cols, batch, dw, dx):
+def _single(lib, fmt, rows, cols, batch, dw, dx, dp4a=True):
     dy = out_buf(rows * batch)
     n = lib.tb200_qx_workspace_bytes(cols, batch)
     ws = DevBuf(np.zeros(max(n, 16), np.uint8))
     fn = lib.tb200_q8b_gemv_i8 if fmt == "q8b" else lib.tb200_q4b_gemv_i8
-    # Bit-for-bit comparisons need the same fp32 summation order, i.e. the same kernel family: the grouped launch
-    # runs the dp4a kernel, so the single launch is kept on it for this call (from two vectors on it would otherwise
-    # take the tensor-core kernel; that kernel's exact block dots and its results have their own tests).  Above four
-    # vectors the grouped entry itself falls back to one ordinary launch per matrix, with the default choice.
-    if batch <= 4:
+    # Bit-for-bit comparisons need the same fp32 summation order, i.e. the same kernel family.  Grouped launches
+    # with several destinations or a hand-shake run the dp4a kernel, so the single launch is kept on it for those
+    # (dp4a=True; from two vectors on it would otherwise take the tensor-core kernel).  A grouped launch into one
+    # local buffer takes the tensor-core kernel itself from two vectors on, like the single launch (dp4a=False).
+    if dp4a and batch <= 4:
         assert lib.tb200_set_thread_option(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH, 17) == 0
     try:
         assert fn(rows, cols, batch, dw.ptr, dx.ptr, dy.ptr, ws.ptr, n, stream_ptr()) == 0
@@ -66,7 +66,7 @@ def test_grouped_equals_one_launch_per_matrix(lib, fmt, rows, cols, batch, count
     sync_and_check(lib)
     got = dy.numpy().reshape(count, batch, rows)
     for m in range(count):
-        want = _single(lib, fmt, rows, cols, batch, dws[m], dx)
+        want = _single(lib, fmt, rows, cols, batch, dws[m], dx, dp4a=False)
         assert np.array_equal(got[m], want), (m, np.abs(got[m] - want).max())
     assert dy.guard_intact()
 
@@ -235,7 +235,7 @@ def test_grouped_rows_of_different_shapes_equal_one_launch_per_matrix(lib, fmt, 
         if r == 0:
             assert np.isnan(dys[m].numpy()).all()  # untouched
             continue
-        want = _single(lib, fmt, r, cols, batch, dws[m], dx)
+        want = _single(lib, fmt, r, cols, batch, dws[m], dx, dp4a=False)
         got = dys[m].numpy()[:batch * r].reshape(batch, r)
         assert np.array_equal(got, want), (m, r)
         assert dys[m].guard_intact()

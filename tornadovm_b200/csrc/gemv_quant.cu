@@ -1292,6 +1292,34 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
     cudaStream_t s = (cudaStream_t)stream;
+    // Two to eight vectors into one local buffer: the tensor-core mat-vec per matrix (it outruns the dp4a ring kernel
+    // from two vectors on), all behind ONE quantiser launch and chained to one another, so that each starts
+    // requesting its weights while its predecessor drains.
+    if (batch >= option_value(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH) && batch <= 8 && npeers == 1 && !epoch && !gs.flags &&
+        option_value(TB200_OPT_TC_REGISTER_KERNEL) && workspace) {
+        bool tc = true;
+        for (int m = 0; m < count && tc; ++m) {
+            QGemvArgs one{grp.w[m], nullptr, nullptr, reinterpret_cast<const int8_t *>(workspace), nullptr, dst[0], nullptr, shape.rows[m] > 0 ? shape.rows[m] : 1,
+                          cols, batch};
+            tc = shape.ld[m] == shape.rows[m] && qtc_eligible(FMT, MODE_INT, one, di);
+        }
+        if (tc) {
+            int8_t *xq;
+            float *xs;
+            st = split_workspace(cols, batch, workspace, workspace_bytes, &xq, &xs);
+            if (st) return st;
+            st = quantize_x_layout(cols, batch, x, xq, xs, s, true);
+            if (st) return st;
+            for (int m = 0; m < count; ++m) {
+                if (shape.rows[m] == 0) continue;
+                QGemvArgs one{grp.w[m], nullptr, nullptr, xq, xs, dst[0] + shape.out_off[m] + shape.row_off[m], nullptr, shape.rows[m], cols, batch};
+                one.xlayout = 1;
+                st = qtc_dispatch(FMT, MODE_INT, one, di, s, true);
+                if (st) return st;
+            }
+            return TB200_OK;
+        }
+    }
     QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, (int)total, cols, batch, (int)((uintptr_t)blocks[0] & 15)};
     if (fast && batch <= 4 && fast_batch_fits<FMT, MODE_INT>(cols, batch, PATH_RING, di)) {
         if ((long long)batch * cols <= kFusedQuantMaxElems) return launch_ring_grouped_b<FMT, MODE_INT_FUSED>(a, grp, di, s);
