@@ -640,6 +640,8 @@ def measure_hgemm_sharded(torch, dist, sizes, dev, world, rank, tensor_peak):
         can_fuse = n % (8 * world) == 0
         op = ShardedHgemm(n, n, n, a, b_local, fused=can_fuse, layout="auto")
 
+        align = torch.zeros(1, device=dev)
+
         def timed(fn, reps=10):
             for _ in range(3):
                 fn()
@@ -647,6 +649,11 @@ def measure_hgemm_sharded(torch, dist, sizes, dev, world, rank, tensor_peak):
                 dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if world > 1:
+                # the ranks leave the host barrier at slightly different times; a tiny collective in front of the
+                # start event aligns the GPUs themselves (it completes on a rank only when every rank has entered)
+                with torch.cuda.stream(op.stream):
+                    dist.all_reduce(align)
             e0.record(op.stream)
             for _ in range(reps):
                 fn()
