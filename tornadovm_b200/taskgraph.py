@@ -213,22 +213,29 @@ class TornadoExecutionPlan:
                 self._d2h_pairs = [(self._host_slab[off:off + n], self._dev_slab[off:off + n]) for off, n in self._merge(out)]
                 self._d2h_bytes = sum(n for _, n in out)
             else:
-                for dst, src in self._h2d_pairs:
-                    dst.copy_(src, non_blocking=True)
                 h2d = self._h2d_bytes
             if self._use_graph:
                 if self._cuda_graph is None:
-                    # as in the reference (TornadoVMInterpreter.java:462-476), the FIRST dispatch of every task
-                    # already happens inside the capture: everything capture-unsafe was done by prepare()
+                    # as in the reference (TornadoVMInterpreter.java:462-476), the capture region spans the whole
+                    # bytecode sequence of an execution -- the every-execution transfers in, the FIRST dispatch of
+                    # every task and the transfers out; everything capture-unsafe was done by prepare().  The host
+                    # side of every transfer is the pinned slab, whose addresses never change.
                     self.stream.synchronize()
                     self._cuda_graph = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(self._cuda_graph, stream=self.stream):
+                        for dst, src in self._h2d_pairs:
+                            dst.copy_(src, non_blocking=True)
                         self._launch_all()
+                        for dst, src in self._d2h_pairs:
+                            dst.copy_(src, non_blocking=True)
                 self._cuda_graph.replay()
             else:
+                if not first:
+                    for dst, src in self._h2d_pairs:
+                        dst.copy_(src, non_blocking=True)
                 self._launch_all()
-            for dst, src in self._d2h_pairs:
-                dst.copy_(src, non_blocking=True)
+                for dst, src in self._d2h_pairs:
+                    dst.copy_(src, non_blocking=True)
             d2h = self._d2h_bytes
             self.stream.synchronize()
         self.h2d_bytes_last, self.d2h_bytes_last = h2d, d2h
