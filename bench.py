@@ -269,7 +269,29 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 t = timeit(lambda i: lib.tb200_q8b_gemv_i8_grouped(grp, ROWS, COLS, 1, wp[i], P(x), dp[i], 1, 0, None, ROWS, 0, None, 0, S),
                            10, period=LAYERS // grp)
                 out[f"q8_blocks_int_b1_{grp}_per_launch"] = {"GB/s": grp * by / t / 1e9, "frac_hbm": grp * by / t / 1e9 / hbm_peak, "us": t * 1e6}
+            # the same 32 matrices as payloads behind the reference's 24-byte array header: every matrix, the vector
+            # and the outputs start 8 bytes off a 16-byte boundary (a matrix is a multiple of 16 bytes long, so all
+            # share the phase); one launch per 8 matrices
+            mat_bytes = ROWS * (COLS // 32) * 34
+            raw = torch.empty(LAYERS * mat_bytes + 16, dtype=torch.uint8, device=dev)
+            base = 8 + (-raw.data_ptr()) % 16
+            raw[base:base + LAYERS * mat_bytes].copy_(blocks.view(-1))
             del blocks
+            xr = torch.empty(COLS + 4, device=dev)
+            xo = (8 + (-xr.data_ptr()) % 16) // 4
+            xr[xo:xo + COLS].copy_(x.view(-1))
+            yr = torch.empty(LAYERS * ROWS + 4, device=dev)
+            yo = (8 + (-yr.data_ptr()) % 16) // 4
+            grp = 8
+            wp = [(C.c_void_p * grp)(*[raw.data_ptr() + base + (c * grp + m) * mat_bytes for m in range(grp)]) for c in range(LAYERS // grp)]
+            dp = [(C.c_void_p * 1)(yr.data_ptr() + 4 * (yo + c * grp * ROWS)) for c in range(LAYERS // grp)]
+            xp = C.c_void_p(xr.data_ptr() + 4 * xo)
+            t = timeit(lambda i: lib.tb200_q8b_gemv_i8_grouped(grp, ROWS, COLS, 1, wp[i], xp, dp[i], 1, 0, None, ROWS, 0, None, 0, S),
+                       10, period=LAYERS // grp)
+            out["q8_blocks_int_b1_8_per_launch_header24"] = {"GB/s": grp * by / t / 1e9, "frac_hbm": grp * by / t / 1e9 / hbm_peak, "us": t * 1e6}
+            same = bool(torch.equal(yr[yo:yo + LAYERS * ROWS].view(LAYERS, ROWS), yl))
+            out["q8_blocks_int_b1_8_per_launch_header24"]["same_bits_as_aligned"] = same
+            del raw
         if "q4" in sections:
             # Q4_0 Llama-3-8B-shaped layer sweep: 7 projections + the output projection
             shapes = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336), (128256, 4096)]
