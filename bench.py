@@ -232,9 +232,9 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 for name, fn in runs.items():
                     t = timeit(fn, 10)
                     out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
-            # the same block matrices behind a 24-byte array header (the reference launcher's JVM mode): element
-            # pointers are 8 modulo 16
-            shifted = torch.empty(blocks.numel() + 16, dtype=torch.uint8, device=dev)
+            # the same block matrices behind a 24-byte array header (the reference launcher's JVM mode) in an aligned
+            # buffer: element pointers are 24 modulo 128, i.e. 8 modulo 16
+            shifted = torch.empty(blocks.numel() + 32, dtype=torch.uint8, device=dev)
             per = blocks[0].numel()
             for batch in (1, 8):
                 x = torch.randn((batch, COLS), device=dev)
@@ -242,9 +242,9 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 ws_n = lib.tb200_qx_workspace_bytes(COLS, batch)
                 ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
                 by = algorithmic_bytes(ROWS, COLS, batch)
-                base = shifted.data_ptr() + 8
+                base = shifted.data_ptr() + 24
                 for i in range(4):
-                    shifted[8 + i * per:8 + (i + 1) * per].copy_(blocks[i].reshape(-1))
+                    shifted[24 + i * per:24 + (i + 1) * per].copy_(blocks[i].reshape(-1))
                 t = timeit(lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, batch, C.c_void_p(base + (i & 3) * per), P(x), P(yb), P(ws), ws_n, S), 10)
                 out[f"q8_blocks_int_b{batch}_header24"] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
             del q, sc, blocks, shifted
@@ -269,19 +269,19 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 t = timeit(lambda i: lib.tb200_q8b_gemv_i8_grouped(grp, ROWS, COLS, 1, wp[i], P(x), dp[i], 1, 0, None, ROWS, 0, None, 0, S),
                            10, period=LAYERS // grp)
                 out[f"q8_blocks_int_b1_{grp}_per_launch"] = {"GB/s": grp * by / t / 1e9, "frac_hbm": grp * by / t / 1e9 / hbm_peak, "us": t * 1e6}
-            # the same 32 matrices as payloads behind the reference's 24-byte array header: every matrix, the vector
-            # and the outputs start 8 bytes off a 16-byte boundary (a matrix is a multiple of 16 bytes long, so all
-            # share the phase); one launch per 8 matrices
+            # the same 32 matrices as payloads behind the reference's 24-byte array header in 256-byte aligned
+            # buffers: every matrix, the vector and the outputs start 24 bytes past a 128-byte line (a matrix is a
+            # multiple of 128 bytes long, so all share the phase); one launch per 8 matrices
             mat_bytes = ROWS * (COLS // 32) * 34
-            raw = torch.empty(LAYERS * mat_bytes + 16, dtype=torch.uint8, device=dev)
-            base = 8 + (-raw.data_ptr()) % 16
+            raw = torch.empty(LAYERS * mat_bytes + 256, dtype=torch.uint8, device=dev)
+            base = 24 + (-raw.data_ptr()) % 128
             raw[base:base + LAYERS * mat_bytes].copy_(blocks.view(-1))
             del blocks
-            xr = torch.empty(COLS + 4, device=dev)
-            xo = (8 + (-xr.data_ptr()) % 16) // 4
+            xr = torch.empty(COLS + 64, device=dev)
+            xo = (24 + (-xr.data_ptr()) % 128) // 4
             xr[xo:xo + COLS].copy_(x.view(-1))
-            yr = torch.empty(LAYERS * ROWS + 4, device=dev)
-            yo = (8 + (-yr.data_ptr()) % 16) // 4
+            yr = torch.empty(LAYERS * ROWS + 64, device=dev)
+            yo = (24 + (-yr.data_ptr()) % 128) // 4
             grp = 8
             wp = [(C.c_void_p * grp)(*[raw.data_ptr() + base + (c * grp + m) * mat_bytes for m in range(grp)]) for c in range(LAYERS // grp)]
             dp = [(C.c_void_p * 1)(yr.data_ptr() + 4 * (yo + c * grp * ROWS)) for c in range(LAYERS // grp)]
@@ -345,10 +345,10 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             out["sgemm_4096"] = {"TFLOP/s": 2 * 4096**3 / t / 1e12, "ms": t * 1e3, "sustained_TFLOP/s": 2 * 4096**3 / t_long / 1e12,
                                  "sm_mhz_sustained": mhz, "frac_ffma_at_clock": (2 * 4096**3 / t_long / 1e12) / (sms * 128 * 2 * mhz * 1e-6) if mhz else None}
             # operands behind a 24-byte header: 8 modulo 16
-            raw = [torch.empty(4096 * 4096 * 4 + 16, dtype=torch.uint8, device=dev) for _ in range(3)]
-            pa, pb, pc = (r.data_ptr() + 8 for r in raw)
-            raw[0][8:8 + a.numel() * 4].copy_(a.view(torch.uint8).reshape(-1))
-            raw[1][8:8 + bm.numel() * 4].copy_(bm.view(torch.uint8).reshape(-1))
+            raw = [torch.empty(4096 * 4096 * 4 + 32, dtype=torch.uint8, device=dev) for _ in range(3)]
+            pa, pb, pc = (r.data_ptr() + 24 for r in raw)
+            raw[0][24:24 + a.numel() * 4].copy_(a.view(torch.uint8).reshape(-1))
+            raw[1][24:24 + bm.numel() * 4].copy_(bm.view(torch.uint8).reshape(-1))
             t24 = timeit(lambda i: lib.tb200_sgemm(4096, 4096, 4096, C.c_float(1.0), C.c_void_p(pa), C.c_void_p(pb), C.c_float(0.0), C.c_void_p(pc), S), 3, period=2)
             out["sgemm_4096_header24"] = {"TFLOP/s": 2 * 4096**3 / t24 / 1e12, "ms": t24 * 1e3}
             del raw
@@ -362,10 +362,10 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 t24 = None
                 if n == 8192:
                     # A, B and C behind a 24-byte header (8 modulo 16), timed like the aligned product and next to it
-                    raw = [torch.empty(n * n * e + 16, dtype=torch.uint8, device=dev) for e in (2, 2, 4)]
-                    raw[0][8:8 + n * n * 2].copy_(ah.view(torch.uint8).reshape(-1))
-                    raw[1][8:8 + n * n * 2].copy_(bh.view(torch.uint8).reshape(-1))
-                    pa, pb, pc = (C.c_void_p(r.data_ptr() + 8) for r in raw)
+                    raw = [torch.empty(n * n * e + 32, dtype=torch.uint8, device=dev) for e in (2, 2, 4)]
+                    raw[0][24:24 + n * n * 2].copy_(ah.view(torch.uint8).reshape(-1))
+                    raw[1][24:24 + n * n * 2].copy_(bh.view(torch.uint8).reshape(-1))
+                    pa, pb, pc = (C.c_void_p(r.data_ptr() + 24) for r in raw)
                     t24 = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, pa, pb, pc, S), 3, period=2)
                     del raw
                 # a longer run (about 100 launches) next to the burst figure: the clock settles under sustained tensor load
@@ -555,6 +555,7 @@ def run_gpu_arm(args):
     # ---- end to end through the public API, host buffers ---------------------------------------------------
     e2e_steps = args.steps
     if world == 1:
+        import numpy as np
         from tornadovm_b200.arrays import ByteArray, FloatArray
         from tornadovm_b200.b200 import B200, B200Options
         from tornadovm_b200.taskgraph import CudaDevice, DataTransferMode, TaskGraph, TornadoExecutionPlan
@@ -563,23 +564,38 @@ def run_gpu_arm(args):
         wa = [ByteArray(blocks[c * group:(c + 1) * group].cpu().numpy().ravel()) for c in range(LAYERS // group)]
         xa = FloatArray(op.x_dev.cpu().numpy())
         ya = [FloatArray(group * ROWS * BATCH) for _ in range(LAYERS // group)]
-        opts = B200Options(exact_int=True, overlap_launches=True)
-        tg = TaskGraph("q8decode").transferToDevice(DataTransferMode.FIRST_EXECUTION, *wa) \
-            .transferToDevice(DataTransferMode.EVERY_EXECUTION, xa)
-        for c in range(LAYERS // group):
-            tg.libraryTask(f"g{c}", B200.q8GemvBytesPacked, group, ROWS, COLS, BATCH, wa[c], xa, ya[c], opts)
-        tg.transferToHost(DataTransferMode.EVERY_EXECUTION, *ya)
-        with TornadoExecutionPlan(tg, CudaDevice(local)).withCUDAGraph() as plan:
-            for _ in range(max(args.warmup, 3)):
-                plan.execute()
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            for _ in range(e2e_steps):
-                plan.execute()
-            torch.cuda.synchronize()
-            e2e_s = time.perf_counter() - t0
-            h2d, d2h = plan.h2d_bytes_last, plan.d2h_bytes_last
-        api = "TaskGraph.libraryTask(B200.q8GemvBytesPacked) + TornadoExecutionPlan.withCUDAGraph().execute()"
+
+        def plan_seconds(host_results):
+            """Seconds per execute() of the step as one task graph; the outputs of the last execution."""
+            opts = B200Options(exact_int=True, overlap_launches=True, host_results=host_results)
+            tg = TaskGraph("q8decode").transferToDevice(DataTransferMode.FIRST_EXECUTION, *wa) \
+                .transferToDevice(DataTransferMode.EVERY_EXECUTION, xa)
+            for c in range(LAYERS // group):
+                tg.libraryTask(f"g{c}", B200.q8GemvBytesPacked, group, ROWS, COLS, BATCH, wa[c], xa, ya[c], opts)
+            tg.transferToHost(DataTransferMode.EVERY_EXECUTION, *ya)
+            with TornadoExecutionPlan(tg, CudaDevice(local)).withCUDAGraph() as plan:
+                for _ in range(max(args.warmup, 3)):
+                    plan.execute()
+                torch.cuda.synchronize()
+                for y in ya:
+                    y.numpy()[:] = float("nan")
+                t0 = time.perf_counter()
+                for _ in range(e2e_steps):
+                    plan.execute()
+                torch.cuda.synchronize()
+                s = (time.perf_counter() - t0) / e2e_steps
+                return s, plan.h2d_bytes_last, plan.d2h_bytes_last, [y.numpy().copy() for y in ya]
+
+        # the plan that copies the outputs back after the launches, then the one whose kernels store every result into
+        # the output arrays' pinned host segments themselves (B200Options.host_results); the second is the e2e figure
+        copy_s, _, _, copy_out = plan_seconds(False)
+        e2e_s, h2d, d2h, host_out = plan_seconds(True)
+        if not all(np.array_equal(a, b) for a, b in zip(copy_out, host_out)):
+            raise SystemExit("e2e: the host-stored results differ from the copied ones")
+        del copy_out, host_out
+        e2e_s *= e2e_steps
+        api = ("TaskGraph.libraryTask(B200.q8GemvBytesPacked, B200Options(host_results=True)) + "
+               "TornadoExecutionPlan.withCUDAGraph().execute()")
     else:
         xh = torch.randn((BATCH, COLS)).pin_memory()
         # the job's result reaches the host once: rank 0 downloads the gathered outputs, the other ranks (whose
@@ -618,7 +634,8 @@ def run_gpu_arm(args):
                    "mode": "int (fp32 activations quantised to int8 per 32-block inside the kernel, exact int32 block dots)",
                    "launch": f"{LAYERS // group} grouped launch(es) per step, programmatic dependent launches" + (", timed steps replayed from one CUDA graph" if world > 1 else "")},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s / e2e_steps * 1e3, "api": api},
+                "ms_per_step": e2e_s / e2e_steps * 1e3, "api": api,
+                **({"copy_back_ms_per_step": copy_s * 1e3, "copy_back_value": total_bytes / copy_s / 1e9} if world == 1 else {})},
         "gpu_launches": gpu_launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_GEMV * group if world == 1 else None,

@@ -71,6 +71,32 @@ def test_grouped_equals_one_launch_per_matrix(lib, fmt, rows, cols, batch, count
     assert dy.guard_intact()
 
 
+@pytest.mark.parametrize("header", [8, 16, 24, 40, 64, 72, 112, 120])
+@pytest.mark.parametrize("fmt,cols", [("q8b", 4096), ("q4b", 2048), ("q8b", 6144), ("q4b", 14336), ("q8b", 1280)])
+def test_weights_at_every_byte_phase(lib, fmt, cols, header):
+    """The ring kernels keep the byte phase of the weights (the offset from the 128-byte line below them) inside their
+    ring slots.  Every multiple of 8, in a grouped launch and in one launch per matrix: the same bits as with weights on
+    a 128-byte boundary, which the other tests hold against the oracle; nothing outside the matrices is needed (each
+    sits in a buffer of its own, so the bytes in front of the first row and behind the last one are poison)."""
+    rows, batch, count = 37, 1, 3
+    mats, x = _case(fmt, rows, cols, batch, count)
+    dx = DevBuf(x)
+    fn = lib.tb200_q8b_gemv_i8_grouped if fmt == "q8b" else lib.tb200_q4b_gemv_i8_grouped
+    results = []
+    for h in (128, header):
+        dws, dy = [DevBuf(m, h) for m in mats], out_buf(count * rows)
+        assert all(d.ptr.value % 128 == h % 128 for d in dws)
+        st = fn(count, rows, cols, batch, _ptr_array(dws), dx.ptr, _ptr_array([dy]), 1, 0, None, rows, 0, None, 0, stream_ptr())
+        assert st == 0, lib.tb200_status_string(st)
+        sync_and_check(lib)
+        one = np.stack([_single(lib, fmt, rows, cols, batch, dws[m], dx)[0] for m in range(count)])
+        results.append((dy.numpy().reshape(count, rows), one))
+        assert dy.guard_intact()
+    assert np.array_equal(results[0][0], results[1][0])
+    assert np.array_equal(results[0][1], results[1][1])
+    assert np.array_equal(results[0][0], results[0][1])
+
+
 def test_grouped_against_oracle(lib):
     rows, cols, count = 96, 4096, 4
     dws, want = [], []

@@ -235,3 +235,58 @@ def test_two_layer_mlp_of_fused_gemm_tasks():
     g_ref = o.sgemm_seq(xh, w1h, m, n1, k)
     for i in range(3):
         assert np.abs(gd.to_float32().reshape(3, m, n1)[i] - g_ref).max() <= 0.05
+
+
+@pytest.mark.parametrize("header", [16, 24])
+@pytest.mark.parametrize("fmt", ["q8", "q4"])
+@pytest.mark.parametrize("batch", [1, 2])
+def test_packed_results_stored_on_the_host_by_the_kernel(header, fmt, batch):
+    """B200Options(host_results=True): the packed mat-vec stores into the output array's pinned host segment as well
+    as into its device buffer, and the plan issues no copy back for that array.  Same bits as the plan that copies,
+    over executions with changing activations (the later ones replayed from the captured graph), and the integer
+    block dots of the oracle.  Two vectors take a one-destination kernel: there the plan keeps its copy."""
+    count, rows, cols = 3, 130, 1024
+    mats = []
+    for m in range(count):
+        if fmt == "q8":
+            q, s, _ = o.make_q8(rows, cols, batch, 40 + m)
+            mats.append((o.q8_pack_blocks(q, s), q, s))
+        else:
+            blocks, s, _ = o.make_q4(rows, cols, batch, 40 + m)
+            mats.append((blocks, None, s))
+    packed_h = np.concatenate([b for b, _, _ in mats])
+    factory = B200.q8GemvBytesPacked if fmt == "q8" else B200.q4GemvBytesPacked
+    results = {}
+    for host_results in (False, True):
+        packed, x = ByteArray(packed_h, header), FloatArray(cols * batch, header)
+        y, z = FloatArray(count * batch * rows, header), FloatArray(rows, header)
+        opts = B200Options(exact_int=True, overlap_launches=True, host_results=host_results)
+        tg = (TaskGraph("packed")
+              .transferToDevice(DataTransferMode.FIRST_EXECUTION, packed)
+              .transferToDevice(DataTransferMode.EVERY_EXECUTION, x)
+              .libraryTask("g", factory, count, rows, cols, batch, packed, x, y, opts)
+              # a second task whose output always travels by copy
+              .libraryTask("one", factory, 1, rows, cols, 1, packed, x, z, B200Options(exact_int=True))
+              .transferToHost(DataTransferMode.EVERY_EXECUTION, y, z))
+        got = []
+        with TornadoExecutionPlan(tg).withCUDAGraph() as plan:
+            for it in range(4):
+                x.numpy()[:] = o.JavaRandom(300 + it).gaussian_f32(cols * batch)
+                y.numpy()[:] = np.nan
+                z.numpy()[:] = np.nan
+                plan.execute()
+                got.append((y.numpy().copy(), z.numpy().copy()))
+                assert plan.d2h_bytes_last == y.nbytes_with_header + z.nbytes_with_header
+            skipped = [key for key in plan._d2h_cache if id(y) in key]
+            assert bool(skipped) == (host_results and batch == 1)
+            assert y.getSize() == count * batch * rows  # the header on the host is untouched
+        results[host_results] = got
+        xs = x.numpy()
+        for m, (blocks, q, s) in enumerate(mats):
+            for b in range(batch):
+                xq, xsc = o.quantize_x_block(np.ascontiguousarray(xs[b * cols:(b + 1) * cols]))
+                dots = o.q8_blockdots_i32(q, xq, cols, rows) if fmt == "q8" else o.q4_blockdots_i32(blocks, xq, cols, rows)
+                want = o.blockdots_combine_f64(dots, s, xsc, cols // 32, rows)
+                assert o.rel_l2(got[-1][0].reshape(count, batch, rows)[m, b], want) <= 1e-5
+    for (ya, za), (yb, zb) in zip(results[False], results[True]):
+        assert np.array_equal(ya, yb) and np.array_equal(za, zb)

@@ -18,7 +18,7 @@ struct QGemvArgs {
     float *y;                // [batch][rows]; may be null when dots is set
     int32_t *dots;           // optional [rows][cols/32] (batch 1, int mode)
     int rows, cols, batch;
-    int wshift;              // block-layout ring kernels: w modulo 16 (0, or 8 behind a 24-byte array header)
+    int wshift;              // block-layout ring kernels: byte phase of every row chunk (w modulo 128 or modulo 16)
     int xlayout;             // int mode, tensor-core kernel: 0 = xq[batch][cols], xs[batch][cols/32]; 1 = xq[block][batch][32], xs[block][batch]
 };
 
@@ -72,6 +72,10 @@ constexpr int MODE_INT_FUSED = 2; // int8 activations quantised in the prologue 
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src_gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src_gmem) : "memory");
+}
+// 16-byte piece of which only the first `src_bytes` are read from global memory; the rest of the piece is zero-filled
+__device__ __forceinline__ void cp_async_16_partial(uint32_t dst_smem, const void *src_gmem, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src_gmem), "r"(src_bytes) : "memory");
 }
 // 8-byte form (through L1): for operands that are only 8-byte aligned
 __device__ __forceinline__ void cp_async_8(uint32_t dst_smem, const void *src_gmem) {

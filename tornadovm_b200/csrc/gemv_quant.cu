@@ -488,13 +488,13 @@ __device__ __forceinline__ void load_pair(const uint32_t *p, float (&scale)[2], 
     for (int i = 0; i < QW; ++i) qb[i] = wds[QW + 1 + i];
 }
 
-template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, bool GROUPED, bool SH8>
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, bool GROUPED, int SHR>
 __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupArgs *grp) {
     // GROUPED: a.rows counts the rows of all matrices laid end to end; a.w and a.y are unused
     using T = RingTraits<FMT>;
     constexpr bool INT = MODE != MODE_FLOAT;
     static_assert(STAGES >= 2 && STAGES <= 4, "ring depth");
-    static_assert(T::PIECES * 32 >= T::CB / 16 + 1, "a shifted chunk is one piece longer");
+    static_assert(T::PIECES * 32 * 16 >= T::CB + 128 && T::CB % 128 == 0, "a shifted chunk starts up to 120 bytes into its slot");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int cols = a.cols;
     const int bpr = cols / 32;
@@ -512,15 +512,18 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     float *xs_scales = reinterpret_cast<float *>(smem_raw + (size_t)B * slots * 16);
     int *xsum = reinterpret_cast<int *>(xs_scales + B * bpr);
     const uint32_t ring_off = (uint32_t)(((size_t)B * slots * 16 + (size_t)(INT ? B * bpr : 0) * 8 + 127) & ~(size_t)127);
-    // SH8: ring slots are 128 bytes longer and a chunk starts 8 bytes into its slot (see below)
-    constexpr int CBS = SH8 ? T::CB + 128 : T::CB;
+    // SHR: ring slots are 128 bytes longer and a chunk starts a.wshift bytes into its slot (see below)
+    constexpr int CBS = SHR ? T::CB + 128 : T::CB;
     unsigned char *ring = smem_raw + ring_off + (size_t)warp * STAGES * R * CBS;
     const uint32_t ring_s = smem_u32(ring);
-    // SH8: weights 8 bytes past a 16-byte boundary (an array behind a 24-byte header; every row chunk then is).  The
-    // chunk keeps that phase in its ring slot -- its first and last 8 bytes travel as 8-byte copies, the rest as the
-    // same aligned 16-byte pieces.  A template parameter, not a run-time value: the aligned form keeps its 128-byte
-    // aligned slots and its instruction count (a run-time shift measured 10 % slower on aligned weights).
-    constexpr uint32_t wsh = SH8 ? 8u : 0u;
+    // SHR: every row chunk starts a.wshift bytes (a multiple of 8 below 128) past a 128-byte boundary -- weights behind
+    // an array header of 16 or 24 bytes in a 256-byte aligned buffer.  A warp's 32 pieces of 16 bytes then would span
+    // five 128-byte lines instead of four (measured: 12-17 % more time per launch).  The chunk therefore keeps its
+    // phase inside the ring slot: the pieces are the aligned 16-byte units of the lines that hold the chunk, the ones
+    // wholly outside it are skipped and, at an 8-byte phase (SHR == 2), the first and last travel as 8-byte copies.
+    // Template parameters: the aligned form keeps its slots and its instruction count, and the 16-byte phases do not
+    // carry the 8-byte copies (the Q4_0 kernels are bound by their instruction count).
+    const uint32_t wsh = SHR ? (uint32_t)a.wshift : 0u;
 
     // ---- issue side ------------------------------------------------------------------
     int ig = g_begin, ich = 0;
@@ -529,30 +532,59 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
         if (ig < g_end) {
             const int nblk = min(kChunkBlocks, bpr - ich * kChunkBlocks);
             const int npieces = nblk * T::BB / 16;  // nblk is a multiple of 8: whole 16-byte pieces
+            // SHR: the chunk's bytes are [wsh, hi) of its slot
+            const uint32_t hi = wsh + 16u * npieces, lo_up = (wsh + 15u) & ~15u;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 const int vrow = min(row_begin + ig * R + r, row_end - 1);
-                const unsigned char *src;  // the 16-byte aligned address at or below this lane's first piece
+                const unsigned char *src;  // this lane's first piece; SHR: counted from the boundary below the chunk
+                bool first;                // the chunk starts at the first byte of its matrix
                 if constexpr (GROUPED) {
                     int m = im;
                     while (vrow >= grp->row_start[m + 1]) ++m;  // vrow < row_start[count]
                     if (r == 0) im = m;  // the later chunks of this group start from its first row again
                     src = grp->w[m] + (size_t)(vrow - grp->row_start[m]) * row_bytes + (size_t)ich * T::CB + lane * 16 - wsh;
+                    first = vrow == grp->row_start[m] && ich == 0;
                 } else {
                     src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16 - wsh;
+                    first = vrow == 0 && ich == 0;
                 }
                 const uint32_t dst = ring_s + (st * R + r) * CBS + lane * 16;
-                if constexpr (!SH8) {
+                if constexpr (!SHR) {
 #pragma unroll
                     for (int i = 0; i < T::PIECES; ++i)
                         if (lane + 32 * i < npieces) cp_async_16(dst + i * 512, src + i * 512);
-                } else {
+                } else if constexpr (SHR == 1) {
 #pragma unroll
                     for (int i = 0; i < T::PIECES; ++i) {
-                        const int idx = lane + 32 * i;
-                        if (idx == 0) cp_async_8(dst + 8, src + 8);
-                        else if (idx < npieces) cp_async_16(dst + i * 512, src + i * 512);
-                        else if (idx == npieces) cp_async_8(dst + i * 512, src + i * 512);
+                        // the chunk starts inside the first 128 bytes of its slot: only the first round of pieces can
+                        // lie in front of it (the later rounds keep the aligned form's single comparison)
+                        const uint32_t p = (uint32_t)(lane + 32 * i) * 16u;
+                        if ((i > 0 || p >= wsh) && p < hi) cp_async_16(dst + i * 512, src + i * 512);
+                    }
+                } else if constexpr (FMT == FMT_Q8B) {
+                    // 8-byte phase: the chunk begins and ends in the middle of a piece; its first and last 8 bytes
+                    // travel as copies of their own (two more copy instructions per chunk, which the Q8_0 kernels,
+                    // bound by memory, do not notice: measured 303 against 314 us for the form below)
+                    const uint32_t hi_dn = hi - 8u;
+#pragma unroll
+                    for (int i = 0; i < T::PIECES; ++i) {
+                        const uint32_t p = (uint32_t)(lane + 32 * i) * 16u;
+                        if ((i > 0 || p >= lo_up) && p < hi_dn) cp_async_16(dst + i * 512, src + i * 512);
+                        else if (i == 0 && p + 8 == wsh) cp_async_8(dst + 8, src + 8);
+                        else if (p == hi_dn) cp_async_8(dst + i * 512, src + i * 512);
+                    }
+                } else {
+                    // 8-byte phase, Q4_0 (bound by its instruction count: 220 against 242 us for the form above): the
+                    // last piece is a 16-byte copy that reads 8 bytes only; the first one brings the 8 bytes in front
+                    // of the chunk along (the end of the row before) -- except at the first byte of a matrix, where
+                    // nothing in front of it is read and the first 8 bytes travel as a copy of their own.
+                    const uint32_t lo = first ? lo_up : wsh - 8u;
+#pragma unroll
+                    for (int i = 0; i < T::PIECES; ++i) {
+                        const uint32_t p = (uint32_t)(lane + 32 * i) * 16u;
+                        if ((i > 0 || p >= lo) && p < hi) cp_async_16_partial(dst + i * 512, src + i * 512, min(16u, hi - p));
+                        else if (i == 0 && first && p + 8 == wsh) cp_async_8(dst + 8, src + 8);
                     }
                 }
             }
@@ -783,14 +815,14 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
     }
 }
 
-template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, bool SH8 = false>
+template <int FMT, int B, int R, int MODE, bool DOTS, int STAGES, int SHR = 0>
 __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_kernel(QGemvArgs a) {
-    qblk_gemv_body<FMT, B, R, MODE, DOTS, STAGES, false, SH8>(a, nullptr);
+    qblk_gemv_body<FMT, B, R, MODE, DOTS, STAGES, false, SHR>(a, nullptr);
 }
 
-template <int FMT, int B, int R, int MODE, int STAGES, bool SH8 = false>
+template <int FMT, int B, int R, int MODE, int STAGES, int SHR = 0>
 __global__ void __launch_bounds__(kQ8SThreads) qblk_gemv_grouped_kernel(const QGemvArgs a, const __grid_constant__ QGroupArgs grp) {
-    qblk_gemv_body<FMT, B, R, MODE, false, STAGES, true, SH8>(a, &grp);
+    qblk_gemv_body<FMT, B, R, MODE, false, STAGES, true, SHR>(a, &grp);
 }
 
 // ---------------------------------------------------------------------------
@@ -900,20 +932,20 @@ struct RingConfig {
 };
 
 template <int FMT, int B, int MODE>
-static size_t ring_smem_bytes(int cols, bool sh8 = false) {
+static size_t ring_smem_bytes(int cols, bool shifted = false) {
     using T = RingTraits<FMT>;
     using Cfg = RingConfig<FMT, B, MODE>;
     const size_t slots = (size_t)((cols + 2047) / 2048) * 2048 / (Cfg::INT ? 16 : 4);
     size_t off = (size_t)B * slots * 16 + (Cfg::INT ? (size_t)B * (cols / 32) * 8 : 0);  // + scales + block sums
     off = (off + 127) & ~(size_t)127;
-    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * (T::CB + (sh8 ? 128 : 0));
+    return off + (size_t)kQ8SWarps * Cfg::STAGES * Cfg::R * (T::CB + (shifted ? 128 : 0));
 }
 
-template <int FMT, int B, int MODE, bool DOTS, bool SH8>
+template <int FMT, int B, int MODE, bool DOTS, int SHR>
 static int launch_ring_sh(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     using Cfg = RingConfig<FMT, B, MODE>;
-    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols, SH8);
-    constexpr auto kernel = qblk_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES, SH8>;
+    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols, SHR != 0);
+    constexpr auto kernel = qblk_gemv_kernel<FMT, B, Cfg::R, MODE, DOTS, Cfg::STAGES, SHR>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
     // at most one resident wave, sized so that all warps own (nearly) the same number of rows
@@ -921,22 +953,31 @@ static int launch_ring_sh(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t
     return launch_kernel(kernel, dim3(grid), dim3(kQ8SThreads), smem, s, option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0, a);
 }
 
-// weights 8 bytes past a 16-byte boundary: a kernel of their own for one vector (more vectors go to the tensor-core
-// kernel, which handles the phase itself)
+// Byte phase of the row chunks of a block matrix for the ring kernels: the offset from the 128-byte boundary below
+// when every row keeps it (rows that are whole 128-byte lines), else the offset from the 16-byte boundary (0 or 8).
+template <int FMT>
+static int ring_phase(const void *w, int cols) {
+    const size_t row_bytes = (size_t)(cols / 32) * RingTraits<FMT>::BB;
+    return (int)((uintptr_t)w & (row_bytes % 128 == 0 ? 127 : 15));
+}
+
+// weights off a 128-byte boundary: a kernel of their own for one vector (more vectors go to the tensor-core
+// kernel, whose bulk copies do not depend on the phase)
 template <int FMT, int B, int MODE, bool DOTS>
 static int launch_ring(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s) {
     if constexpr (B == 1) {
-        if (a.wshift) return launch_ring_sh<FMT, B, MODE, DOTS, true>(a, di, s);
+        if (a.wshift & 8) return launch_ring_sh<FMT, B, MODE, DOTS, 2>(a, di, s);
+        if (a.wshift) return launch_ring_sh<FMT, B, MODE, DOTS, 1>(a, di, s);
     }
-    if (a.wshift) return TB200_ERR_ALIGNMENT;  // not reached: the dispatcher keeps such launches off this path
-    return launch_ring_sh<FMT, B, MODE, DOTS, false>(a, di, s);
+    if (a.wshift & 15) return TB200_ERR_ALIGNMENT;  // not reached: the dispatcher keeps such launches off this path
+    return launch_ring_sh<FMT, B, MODE, DOTS, 0>(a, di, s);
 }
 
-template <int FMT, int B, int MODE, bool SH8>
+template <int FMT, int B, int MODE, int SHR>
 static int launch_ring_grouped_sh(const QGemvArgs &a, const QGroupArgs &grp, const DeviceInfo *di, cudaStream_t s) {
     using Cfg = RingConfig<FMT, B, MODE>;
-    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols, SH8);
-    constexpr auto kernel = qblk_gemv_grouped_kernel<FMT, B, Cfg::R, MODE, Cfg::STAGES, SH8>;
+    const size_t smem = ring_smem_bytes<FMT, B, MODE>(a.cols, SHR != 0);
+    constexpr auto kernel = qblk_gemv_grouped_kernel<FMT, B, Cfg::R, MODE, Cfg::STAGES, SHR>;
     int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
     const int grid = balanced_ctas(a.rows, Cfg::R, di->sm_count * resident_ctas<kernel>(di, kQ8SThreads, smem));
@@ -945,7 +986,9 @@ static int launch_ring_grouped_sh(const QGemvArgs &a, const QGroupArgs &grp, con
 
 template <int FMT, int B, int MODE>
 static int launch_ring_grouped(const QGemvArgs &a, const QGroupArgs &grp, const DeviceInfo *di, cudaStream_t s) {
-    return a.wshift ? launch_ring_grouped_sh<FMT, B, MODE, true>(a, grp, di, s) : launch_ring_grouped_sh<FMT, B, MODE, false>(a, grp, di, s);
+    if (a.wshift & 8) return launch_ring_grouped_sh<FMT, B, MODE, 2>(a, grp, di, s);
+    if (a.wshift) return launch_ring_grouped_sh<FMT, B, MODE, 1>(a, grp, di, s);
+    return launch_ring_grouped_sh<FMT, B, MODE, 0>(a, grp, di, s);
 }
 
 template <int FMT, int MODE>
@@ -1077,7 +1120,7 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
     if (FMT == FMT_Q8S) {
         if (aligned_to(a.w, 16)) path = PATH_Q8S_DIRECT;
     } else if (a.cols % 256 == 0 && (aligned_to(a.w, 16) || (aligned_to(a.w, 8) && a.batch == 1))) {
-        path = PATH_RING, a.wshift = (int)((uintptr_t)a.w & 15);
+        path = PATH_RING, a.wshift = ring_phase<FMT>(a.w, a.cols);
     }
     // Tensor-core kernel with the activations in registers (gemv_tc.cu): integer mode from
     // TB200_OPT_INT_TENSOR_CORE_MIN_BATCH vectors on, float mode from the measured batch on, and every batch
@@ -1255,12 +1298,14 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
     if (!aligned_to(x, 4) || (epoch && !aligned_to(epoch, 4))) return TB200_ERR_ALIGNMENT;
     QGroupArgs grp{};
     bool fast = cols % 256 == 0 && cols > 0;
+    bool same_line_phase = true;  // every matrix starts at the same offset from a 128-byte boundary
     long long total = 0;
     for (int m = 0; m < count; ++m) {
         if (!blocks[m] || shape.rows[m] < 0) return TB200_ERR_INVALID_ARG;
         if (shape.row_off[m] < 0 || shape.ld[m] < shape.rows[m] || shape.row_off[m] > shape.ld[m] - shape.rows[m]) return TB200_ERR_INVALID_ARG;
         if (!aligned_to(blocks[m], 2)) return TB200_ERR_ALIGNMENT;
         fast = fast && aligned_to(blocks[m], 8) && (((uintptr_t)blocks[m] ^ (uintptr_t)blocks[0]) & 15) == 0;  // one phase, 0 or 8
+        same_line_phase = same_line_phase && (((uintptr_t)blocks[m] ^ (uintptr_t)blocks[0]) & 127) == 0;
         grp.w[m] = reinterpret_cast<const uint8_t *>(blocks[m]);
         grp.row_start[m] = (int)total;
         grp.out_off[m] = shape.out_off[m], grp.ld[m] = shape.ld[m], grp.row_off[m] = shape.row_off[m];
@@ -1320,7 +1365,8 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
             return TB200_OK;
         }
     }
-    QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, (int)total, cols, batch, (int)((uintptr_t)blocks[0] & 15)};
+    QGemvArgs a{nullptr, nullptr, x, nullptr, nullptr, nullptr, nullptr, (int)total, cols, batch,
+                same_line_phase ? ring_phase<FMT>(blocks[0], cols) : (int)((uintptr_t)blocks[0] & 15)};
     if (fast && batch <= 4 && fast_batch_fits<FMT, MODE_INT>(cols, batch, PATH_RING, di)) {
         if ((long long)batch * cols <= kFusedQuantMaxElems) return launch_ring_grouped_b<FMT, MODE_INT_FUSED>(a, grp, di, s);
         int8_t *xq;

@@ -453,8 +453,11 @@ struct HgTile {
 
 // Operands 8 bytes past a 16-byte boundary (TornadoVM arrays behind a 24-byte header, the reference launcher's
 // default mode) cannot be the base of a tensor map, and a TMA copy cannot start 8 bytes into a 16-byte unit either.
-// The maps are therefore laid over the aligned address 8 bytes (4 elements) BELOW the array, which shifts the
-// matrix by four elements along its contiguous dimension, and the kernel works in the shifted coordinates:
+// And operands that are 16-byte aligned but off a 128-byte line (the same arrays behind a 16-byte header) make every
+// 128-byte row of a TMA box straddle two lines (measured at 8192^3: 842 instead of 1350 TFLOP/s).  The maps are
+// therefore laid over an aligned address BELOW the array -- the 128-byte line boundary when every row keeps the phase,
+// else the 16-byte boundary -- which shifts the matrix by kshift / nshift elements (a multiple of 4 below 64) along
+// its contiguous dimension, and the kernel works in the shifted coordinates:
 //   A (K contiguous): element k of a row appears at k' = k + kshift; K blocks cover k' = 0 .. K + kshift - 1, the rows
 //     of B are fetched from k' - kshift (a negative row coordinate is filled with zeros), and the kshift halves in
 //     front of every row of the first K block -- bytes that belong to the previous row or lie before the array --
@@ -585,10 +588,16 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (!ok) break;
                     unsigned char *a_tile = tiles + (size_t)s * TL::STAGE_BYTES;
                     if (kshift && kb == 0) {
-                        // row r keeps its first 16-byte piece at position r % 8 of its 128 bytes (128-byte swizzle);
-                        // the first 8 bytes of that piece are the four halves in front of the row
+                        // row r keeps its 16-byte piece j at position j ^ (r % 8) of its 128 bytes (128-byte swizzle);
+                        // the first 2 * kshift bytes of the row (whole pieces, then possibly the first 8 bytes of the
+                        // next one) are the halves in front of the row
+                        const int zfull = kshift >> 3, zhalf = kshift & 4;
 #pragma unroll
-                        for (int r = lane; r < HG_BM; r += 32) *reinterpret_cast<uint2 *>(a_tile + r * 128 + ((r & 7) << 4)) = make_uint2(0u, 0u);
+                        for (int r = lane; r < HG_BM; r += 32) {
+                            unsigned char *rowp = a_tile + r * 128;
+                            for (int j = 0; j < zfull; ++j) *reinterpret_cast<uint4 *>(rowp + ((j ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                            if (zhalf) *reinterpret_cast<uint2 *>(rowp + ((zfull ^ (r & 7)) << 4)) = make_uint2(0u, 0u);
+                        }
                         fence_async_shared();  // generic-proxy writes before the tensor core's reads
                         __syncwarp();
                     }
@@ -964,8 +973,14 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
         }
         return TB200_OK;
     }
-    // operands 8 bytes past a 16-byte boundary: maps over the aligned address below, matrices shifted by 4 elements
-    const int kshift = aligned_to(pr.a, 16) ? 0 : 4, nshift = aligned_to(pr.b, 16) ? 0 : 4;
+    // operands off a 128-byte line (arrays behind a 16- or 24-byte header in an aligned buffer): maps over the line
+    // boundary below when every row keeps the phase (row pitch and batch stride are whole lines), else over the
+    // 16-byte boundary below; the matrices are shifted by that many elements
+    auto shift_of = [&](const uint16_t *p, long long row_elems, long long stride_elems) {
+        const bool lines = row_elems % 64 == 0 && (pr.batches == 1 || stride_elems % 64 == 0);
+        return (int)(((uintptr_t)p & (lines ? 127 : 15)) / 2);
+    };
+    const int kshift = shift_of(pr.a, k, pr.stride_a), nshift = shift_of(pr.b, n, pr.stride_b);
     const bool aligned = kshift == 0 && nshift == 0;
     const CUtensorMapDataType in_type = pr.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap map_a, map_b, map_d;

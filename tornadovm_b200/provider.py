@@ -21,9 +21,24 @@ from .native import B200Native
 class LibraryInvocation:
     """spi/LibraryInvocation.java:54-97."""
 
-    def __init__(self, args, device_pointers, context, tuning=None, device=None, plan_id=0):
+    def __init__(self, args, device_pointers, context, tuning=None, device=None, plan_id=0, host_pointers=None):
         self._args, self._ptrs, self._ctx = list(args), list(device_pointers), context
         self._tuning, self._device, self._plan = tuning, device, plan_id
+        # An extension of the reference's invocation object: for an argument that the graph copies to the host after
+        # every execution, the address of the payload in the array's own host segment, when that segment is pinned
+        # and mapped into the device's address space (None otherwise).
+        self._host_ptrs = list(host_pointers) if host_pointers is not None else [None] * len(self._args)
+        self._host_delivered = set()
+
+    def getHostPointer(self, i):  # noqa: N802
+        return self._host_ptrs[i]
+
+    def markHostDelivered(self, i) -> None:  # noqa: N802
+        """The dispatch stored argument i's results into the host segment itself: no copy back is needed."""
+        self._host_delivered.add(i)
+
+    def hostDelivered(self):  # noqa: N802
+        return frozenset(self._host_delivered)
 
     def getArg(self, i):  # noqa: N802
         return self._args[i]
@@ -69,6 +84,8 @@ class B200Context:
                 raise RuntimeError(f"[ERROR] Unable to allocate B200 workspace of {required} bytes")
             self.workspace_ptr, self.workspace_bytes = out.value, required
 
+
+TB200_ERR_INVALID_ARG = -1  # include/tornado_b200.h
 
 #: TB200_LOG=1 prints one line per dispatch to stderr (function, scalar arguments, tuning)
 _LOG = os.environ.get("TB200_LOG", "") not in ("", "0")
@@ -167,8 +184,21 @@ class B200LibraryProvider:
             native, block_bytes = _PACKED_FUNCTIONS[functionName]
             count, per = A(0), A(1) * (A(2) // 32) * block_bytes
             blocks = (C.c_void_p * count)(*[P(4) + m * per for m in range(count)])
-            dst = (C.c_void_p * 1)(P(6))
-            st = getattr(lib, native)(count, A(1), A(2), A(3), blocks, P(5), dst, 1, 0, None, A(1), 0, *ws, ctx.stream)
+            tuning = inv.getTuning()
+            host = inv.getHostPointer(6) if isinstance(tuning, B200Options) and tuning.host_results and A(3) == 1 else None
+            st = TB200_ERR_INVALID_ARG
+            if host:
+                # two destinations: the device buffer and the array's host segment (plain stores over PCIe while the
+                # launch runs).  One vector only: there the same kernel runs whatever the number of destinations, so
+                # the option never changes a result bit.  Shapes that only the one-destination kernels cover are
+                # refused before anything is launched and take the call below.
+                dst = (C.c_void_p * 2)(P(6), host)
+                st = getattr(lib, native)(count, A(1), A(2), A(3), blocks, P(5), dst, 2, 0, None, A(1), 0, *ws, ctx.stream)
+                if st == 0:
+                    inv.markHostDelivered(6)
+            if not host or st == TB200_ERR_INVALID_ARG:
+                dst = (C.c_void_p * 1)(P(6))
+                st = getattr(lib, native)(count, A(1), A(2), A(3), blocks, P(5), dst, 1, 0, None, A(1), 0, *ws, ctx.stream)
         elif functionName == "sgemm":  # (m, n, k, alpha, a, b, beta, c)
             st = lib.tb200_sgemm(A(0), A(1), A(2), A(3), P(4), P(5), A(6), P(7), ctx.stream)
         elif functionName == "hgemmF32":  # (m, n, k, a, b, c)

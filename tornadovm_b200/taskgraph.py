@@ -17,12 +17,14 @@ Device memory, streams and copies are PyTorch's; nothing here computes.
 """
 from __future__ import annotations
 
+import ctypes as C
 import enum
 import itertools
 
 import torch
 
 from .arrays import TornadoNativeArray
+from .descriptor import Access
 from .provider import B200LibraryProvider, LibraryInvocation
 
 
@@ -111,6 +113,7 @@ class TornadoExecutionPlan:
         self._executions = 0
         self._use_graph = False
         self._cuda_graph = None
+        self._replay = None
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
 
@@ -178,11 +181,17 @@ class TornadoExecutionPlan:
         return out
 
     def _launch_all(self):
+        # arrays copied back after every execution: their host segment (pinned, device-mapped) is offered to the
+        # provider, which may let its kernel store the results there itself
+        every_out = {id(arr) for mode, arr in self.graph.to_host if mode is DataTransferMode.EVERY_EXECUTION}
+        delivered = {}
         for t in self.graph.tasks:
             d = t.descriptor
             params = d.getParameters()
             ptrs = [self._device_pointer(p) if isinstance(p, TornadoNativeArray) else None for p in params]
-            inv = LibraryInvocation(params, ptrs, self.context, d.getTuning(), self.device, self.plan_id)
+            host = [self._buffer(p)[1].data_ptr() + p.header if isinstance(p, TornadoNativeArray) and id(p) in every_out else None
+                    for p in params]
+            inv = LibraryInvocation(params, ptrs, self.context, d.getTuning(), self.device, self.plan_id, host_pointers=host)
             # the interpreter wraps every library dispatch in an NVTX range named library::function
             # (TornadoVMInterpreter.java:1301-1315)
             self.device.nvtxRangePush(f"{d.getLibraryName()}::{d.getFunctionName()}")
@@ -190,10 +199,51 @@ class TornadoExecutionPlan:
                 self.provider.dispatch(d.getFunctionName(), inv)
             finally:
                 self.device.nvtxRangePop()
+            # the host copy of an array is current only if the LAST task that writes it delivered it
+            access = list(d.getAccess())
+            for i, p in enumerate(params):
+                if isinstance(p, TornadoNativeArray) and (i >= len(access) or access[i] is not Access.READ_ONLY):
+                    delivered[id(p)] = i in inv.hostDelivered()
+        return {k for k, v in delivered.items() if v}
+
+    def _copy_back(self, delivered):
+        """Device->host copies of an execution: every output array whose results no kernel stored on the host."""
+        key = frozenset(delivered)
+        if key not in self._d2h_cache:
+            out = [(self._buffer(arr)[2], arr.nbytes_with_header) for _, arr in self.graph.to_host if id(arr) not in key]
+            self._d2h_cache[key] = [(self._host_slab[off:off + n], self._dev_slab[off:off + n]) for off, n in self._merge(out)]
+        for dst, src in self._d2h_cache[key]:
+            dst.copy_(src, non_blocking=True)
+
+    def _bind_replay(self):
+        """Replaying an execution is one cudaGraphLaunch on the plan's stream and one stream synchronisation, as in
+        the reference's interpreter (a JNI call each).  Returns a callable that issues exactly those two calls on the
+        instantiated graph, or None when the runtime library or the graph's handle cannot be reached (the plan then
+        replays through torch, which also selects the device and the stream around the launch)."""
+        try:
+            rt = C.CDLL("libcudart.so.12")
+            launch, sync = rt.cudaGraphLaunch, rt.cudaStreamSynchronize
+            launch.argtypes, launch.restype = [C.c_void_p, C.c_void_p], C.c_int
+            sync.argtypes, sync.restype = [C.c_void_p], C.c_int
+            exec_handle = C.c_void_p(self._cuda_graph.raw_cuda_graph_exec())
+        except (OSError, AttributeError, RuntimeError):
+            return None
+        stream = C.c_void_p(self.stream.cuda_stream)
+
+        def replay():
+            st = launch(exec_handle, stream) or sync(stream)
+            if st:
+                raise RuntimeError(f"[ERROR] replay of the captured execution failed with CUDA status {st}")
+        return replay
 
     def execute(self):
         g = self.graph
         first = self._executions == 0
+        if self._replay is not None and torch.cuda.current_device() == self.device.index:
+            self._replay()
+            self.h2d_bytes_last, self.d2h_bytes_last = self._h2d_bytes, self._d2h_bytes
+            self._executions += 1
+            return self
         with torch.cuda.device(self.device.index), torch.cuda.stream(self.stream):
             if first:
                 self._layout()
@@ -209,9 +259,9 @@ class TornadoExecutionPlan:
                          if mode is DataTransferMode.EVERY_EXECUTION]
                 self._h2d_pairs = [(self._dev_slab[off:off + n], self._host_slab[off:off + n]) for off, n in self._merge(every)]
                 self._h2d_bytes = sum(n for _, n in every)
-                out = [(self._buffer(arr)[2], arr.nbytes_with_header) for _, arr in g.to_host]
-                self._d2h_pairs = [(self._host_slab[off:off + n], self._dev_slab[off:off + n]) for off, n in self._merge(out)]
-                self._d2h_bytes = sum(n for _, n in out)
+                # bytes that reach the host per execution, whether a copy or a kernel's own stores move them
+                self._d2h_bytes = sum(arr.nbytes_with_header for _, arr in g.to_host)
+                self._d2h_cache = {}
             else:
                 h2d = self._h2d_bytes
             if self._use_graph:
@@ -225,17 +275,16 @@ class TornadoExecutionPlan:
                     with torch.cuda.graph(self._cuda_graph, stream=self.stream):
                         for dst, src in self._h2d_pairs:
                             dst.copy_(src, non_blocking=True)
-                        self._launch_all()
-                        for dst, src in self._d2h_pairs:
-                            dst.copy_(src, non_blocking=True)
-                self._cuda_graph.replay()
+                        self._copy_back(self._launch_all())
+                    self._cuda_graph.replay()
+                    self._replay = self._bind_replay()
+                else:
+                    self._cuda_graph.replay()
             else:
                 if not first:
                     for dst, src in self._h2d_pairs:
                         dst.copy_(src, non_blocking=True)
-                self._launch_all()
-                for dst, src in self._d2h_pairs:
-                    dst.copy_(src, non_blocking=True)
+                self._copy_back(self._launch_all())
             d2h = self._d2h_bytes
             self.stream.synchronize()
         self.h2d_bytes_last, self.d2h_bytes_last = h2d, d2h
@@ -250,6 +299,7 @@ class TornadoExecutionPlan:
             self.context = None
         self._buffers.clear()
         self._dev_slab = None
+        self._replay = None
         self._cuda_graph = None
 
     def __enter__(self):
