@@ -14,7 +14,10 @@
  *     0 of a TornadoVM off-heap array, i.e. buffer base + array header
  *     (tornado-runtime/.../interpreter/TornadoVMInterpreter.java:1260-1266);
  *     the header is 16 or 24 bytes, so 8-byte alignment is all that is
- *     guaranteed; 16-byte aligned pointers take the fast path;
+ *     guaranteed, and a payload normally sits 16 or 24 bytes past a 128-byte
+ *     line of its (256-byte aligned) buffer: the block-layout mat-vec kernels
+ *     and the tensor-core GEMMs run from the line boundary below their
+ *     operands, so that these offsets cost no extra memory transactions;
  *   - scalars are passed by value; `stream` is the CUstream / cudaStream_t of
  *     the execution plan (TornadoNativeStreamSupport.getNativeStream);
  *   - the CUDA context of the plan must be current on the calling thread;
@@ -226,15 +229,20 @@ int tb200_static_scratch_address(void **in_use, void **fresh);
  *
  * blocks[m] is matrix m (host array of device pointers).  Every result is stored
  * to each of the `npeers` (<= 8) destination buffers dst[p] (host array of device
- * pointers: this GPU's buffer and, mapped with tb200_ipc_open, its peers'), at
+ * pointers: this GPU's buffer and, mapped with tb200_ipc_open, its peers'; pinned
+ * host memory mapped into the device's address space is a destination like any
+ * other -- the kernel's stores then deliver the results to the host while the
+ * launch runs, and they are visible there once the stream has been synchronised), at
  *     dst[p][half * half_stride + (m * batch + b) * rows_total + row_offset + r]
  * where `half` is the low bit of *epoch (0 when epoch is NULL): two halves let a
  * GPU fill the next step's outputs while a peer still reads this step's.  With
  * npeers = 1, rows_total = rows, row_offset = 0, epoch = NULL this is a plain
  * grouped mat-vec with y[count][batch][rows].
- * One launch needs batch <= 4, cols % 256 == 0 and 16-byte aligned matrices;
- * other cases are accepted only with a single local destination (one launch per
- * matrix).  The workspace is used when batch * cols > 16384 (see above). */
+ * One launch needs batch <= 4, cols % 256 == 0 and matrices that share one
+ * 8-byte aligned phase modulo 16 (any offset from a 128-byte line runs at the
+ * same rate when rows are whole 128-byte lines, cols % 2048 == 0, and all
+ * matrices share it); other cases are accepted only with a single local
+ * destination (one launch per matrix).  The workspace is used when batch * cols > 16384 (see above). */
 int tb200_q8b_gemv_i8_grouped(int count, int rows, int cols, int batch, const void *const *blocks, const float *x,
                               float *const *dst, int npeers, long long half_stride, const unsigned *epoch, int rows_total,
                               int row_offset, void *workspace, size_t workspace_bytes, tb200_stream_t stream);
