@@ -359,21 +359,28 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                 bh = (torch.randn((n, n), device=dev) / n**0.5).half()
                 ch = torch.empty((n, n), device=dev)
                 t = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, P(ah), P(bh), P(ch), S), 3, period=2)
-                t24 = None
+                t24 = t16 = None
                 if n == 8192:
-                    # A, B and C behind a 24-byte header (8 modulo 16), timed like the aligned product and next to it
+                    # A, B and C behind a 16- and a 24-byte header in aligned buffers (payloads 16 / 24 bytes past a
+                    # 128-byte line; 24 is also 8 modulo 16), timed like the aligned product and next to it
                     raw = [torch.empty(n * n * e + 32, dtype=torch.uint8, device=dev) for e in (2, 2, 4)]
-                    raw[0][24:24 + n * n * 2].copy_(ah.view(torch.uint8).reshape(-1))
-                    raw[1][24:24 + n * n * 2].copy_(bh.view(torch.uint8).reshape(-1))
-                    pa, pb, pc = (C.c_void_p(r.data_ptr() + 24) for r in raw)
-                    t24 = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, pa, pb, pc, S), 3, period=2)
+                    for hdr in (16, 24):
+                        raw[0][hdr:hdr + n * n * 2].copy_(ah.view(torch.uint8).reshape(-1))
+                        raw[1][hdr:hdr + n * n * 2].copy_(bh.view(torch.uint8).reshape(-1))
+                        pa, pb, pc = (C.c_void_p(r.data_ptr() + hdr) for r in raw)
+                        th = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, pa, pb, pc, S), 3, period=2)
+                        if hdr == 16:
+                            t16 = th
+                        else:
+                            t24 = th
                     del raw
                 # a longer run (about 100 launches) next to the burst figure: the clock settles under sustained tensor load
                 t_long = timeit(lambda i: lib.tb200_hgemm_f32(n, n, n, P(ah), P(bh), P(ch), S), 50 if n <= 8192 else 10, period=2)
                 out[f"hgemm_{n}"] = {"TFLOP/s": 2 * n**3 / t / 1e12, "frac_tensor": 2 * n**3 / t / 1e12 / tensor_peak, "ms": t * 1e3,
                                      "sustained_TFLOP/s": 2 * n**3 / t_long / 1e12}
-                if t24 is not None:
-                    out[f"hgemm_{n}_header24"] = {"TFLOP/s": 2 * n**3 / t24 / 1e12, "frac_tensor": 2 * n**3 / t24 / 1e12 / tensor_peak, "ms": t24 * 1e3}
+                for hdr, th in ((16, t16), (24, t24)):
+                    if th is not None:
+                        out[f"hgemm_{n}_header{hdr}"] = {"TFLOP/s": 2 * n**3 / th / 1e12, "frac_tensor": 2 * n**3 / th / 1e12 / tensor_peak, "ms": th * 1e3}
                 if n == 4096:
                     # fused epilogue and 16-bit output on the same product: D(fp16) = gelu(A*B + bias)
                     dh = torch.empty((n, n), dtype=torch.float16, device=dev)

@@ -139,25 +139,31 @@ def test_hgemm_operands_behind_24_byte_headers(lib, m, n, k, ha, hb, hc):
     assert (raw[:hc] == 0xA5).all() and (raw[hc + dc.nbytes:] == 0xA5).all()
 
 
-def test_hgemm_header_24_large(lib):
-    """4096 x 4096 x 1024 behind 24-byte headers against an fp32 product of the same halves."""
+@pytest.mark.parametrize("offset", [8, 16, 24, 48, 72, 112])
+def test_hgemm_large_at_byte_offsets(lib, offset):
+    """4096 x 4096 x 1024 with A, B and C `offset` bytes past a 128-byte line (16 and 24: arrays behind a header in an
+    aligned buffer) against an fp32 product of the same halves.  Multiples of 16 run on SM pairs, the others on single
+    CTAs.  Everything around the matrices is NaN, and row 0 of A ends in an infinity: what lies in front of a row
+    (the end of the row before, or the bytes before the matrix) must not reach any product."""
     import torch
     m, n, k = 4096, 4096, 1024
     g = torch.Generator(device="cuda").manual_seed(5)
     a = (torch.randn((m, k), device="cuda", generator=g) / k**0.5).half()
     b = (torch.randn((k, n), device="cuda", generator=g) / k**0.5).half()
-    raw = [torch.full((t.numel() * t.element_size() + 32,), 0xFF, dtype=torch.uint8, device="cuda") for t in (a, b)]
-    craw = torch.full((m * n * 4 + 32,), 0xFF, dtype=torch.uint8, device="cuda")
-    base = [(t.data_ptr() + 15) // 16 * 16 + 8 for t in (raw[0], raw[1], craw)]  # 8 modulo 16
+    a[0, k - 1] = float("inf")
+    raw = [torch.full((t.numel() * t.element_size() + 512,), 0xFF, dtype=torch.uint8, device="cuda") for t in (a, b)]
+    craw = torch.full((m * n * 4 + 512,), 0xFF, dtype=torch.uint8, device="cuda")
+    base = [(t.data_ptr() + 127) // 128 * 128 + offset for t in (raw[0], raw[1], craw)]
     offs = [bb - t.data_ptr() for bb, t in zip(base, (raw[0], raw[1], craw))]
     raw[0][offs[0]:offs[0] + a.numel() * 2].copy_(a.view(torch.uint8).reshape(-1))
     raw[1][offs[1]:offs[1] + b.numel() * 2].copy_(b.view(torch.uint8).reshape(-1))
     _ok(lib.tb200_hgemm_f32(m, n, k, C.c_void_p(base[0]), C.c_void_p(base[1]), C.c_void_p(base[2]), stream_ptr()), lib)
     sync_and_check(lib)
     got = craw[offs[2]:offs[2] + m * n * 4].view(torch.float32).reshape(m, n)
-    want = a.float() @ b.float()
-    assert torch.isfinite(got).all()
-    assert ((got - want).norm() / want.norm()).item() <= 1e-4
+    want = a[1:].float() @ b.float()
+    assert torch.isfinite(got[1:]).all()
+    assert not torch.isfinite(got[0]).all()  # the infinity did arrive in its own row
+    assert ((got[1:] - want).norm() / want.norm()).item() <= 1e-4
     assert (craw[:offs[2]] == 0xFF).all() and (craw[offs[2] + m * n * 4:] == 0xFF).all()
 
 

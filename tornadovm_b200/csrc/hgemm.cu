@@ -711,8 +711,14 @@ __device__ __forceinline__ void tc2_mma_f16(uint32_t d_tmem, uint64_t a_desc, ui
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(HG_THREADS, 1)
-hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d,
-                 const __grid_constant__ HgOut out, int M, int N, int K, int batches, int rows_vec, int gm, uint32_t idesc) {
+hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_d, const __grid_constant__ HgOut out, int M, int N, int K, int batches, int rows_vec,
+                 int gm, uint32_t idesc, int kshift, int nshift) {
+    // Shifted operands (see hgemm_tc_kernel): map_a and map_b lie over the 128-byte line below A and B.  Only
+    // 16-byte aligned A (kshift a multiple of 8): the first K block of A then comes through map_a0, which lies over
+    // A itself, from column -kshift -- the TMA engine fills the columns in front of the row with zeros, so no CTA has
+    // to clear anything in shared memory (with A 8 bytes off, four halves per row would still have to be cleared, in
+    // both CTAs, before the leader's MMA: those products take the single-CTA kernel).
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[H2_STAGES];   // used in the leader only
     __shared__ __align__(8) uint64_t empty_bar[H2_STAGES];  // one per CTA, signalled by the leader's commits
@@ -725,10 +731,10 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
-    const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
+    const int tiles_m = (M + 255) / 256, tiles_n = (N + nshift + 255) / 256;
     const int tiles_per_matrix = tiles_m * tiles_n;
     const int num_tiles = tiles_per_matrix * batches;
-    const int k_blocks = (K + HG_BK - 1) / HG_BK;
+    const int k_blocks = (K + kshift + HG_BK - 1) / HG_BK;
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
@@ -778,9 +784,10 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     unsigned char *b_dst = a_dst + HG_A_BYTES;
                     if (leader) mbar_expect_tx(&full_bar[s], 2 * H2_STAGE_BYTES);  // bytes of both CTAs
                     const uint32_t bar = map_to_cta(&full_bar[s], 0);
-                    tma_load_3d_pair(a_dst, &map_a, kb * HG_BK, m0, batch, bar);
-                    tma_load_3d_pair(b_dst, &map_b, n0, kb * HG_BK, batch, bar);
-                    tma_load_3d_pair(b_dst + HG_BK * 128, &map_b, n0 + 64, kb * HG_BK, batch, bar);
+                    if (kb == 0 && kshift) tma_load_3d_pair(a_dst, &map_a0, -kshift, m0, batch, bar);
+                    else tma_load_3d_pair(a_dst, &map_a, kb * HG_BK, m0, batch, bar);
+                    tma_load_3d_pair(b_dst, &map_b, n0, kb * HG_BK - kshift, batch, bar);
+                    tma_load_3d_pair(b_dst + HG_BK * 128, &map_b, n0 + 64, kb * HG_BK - kshift, batch, bar);
                 }
             }
         }
@@ -829,7 +836,7 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
-            hg_epilogue_tile<8>(out, &map_d, taddr, tm * 256 + (int)rank * 128 + quarter * 32, tn * 256, batch, M, N, rows_vec, staging, lane, nstores);
+            hg_epilogue_tile<8>(out, &map_d, taddr, tm * 256 + (int)rank * 128 + quarter * 32, tn * 256 - nshift, batch, M, N, rows_vec, staging, lane, nstores);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty_bar[acc], 0));
@@ -981,7 +988,6 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
         return (int)(((uintptr_t)p & (lines ? 127 : 15)) / 2);
     };
     const int kshift = shift_of(pr.a, k, pr.stride_a), nshift = shift_of(pr.b, n, pr.stride_b);
-    const bool aligned = kshift == 0 && nshift == 0;
     const CUtensorMapDataType in_type = pr.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap map_a, map_b, map_d;
     st = make_map(&map_a, pr.a - kshift, in_type, 2, (uint64_t)(k + kshift), (uint64_t)m, (uint64_t)pr.batches, (uint64_t)pr.stride_a, 64, HG_BM, (uint64_t)k);
@@ -1004,16 +1010,21 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
         long long g = (48ll << 20) / ((long long)tile_m * k * 2);
         return (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
     };
-    const long long tiles256 = (long long)((m + 255) / 256) * ((n + 255) / 256) * pr.batches;
+    const long long tiles256 = (long long)((m + 255) / 256) * ((n + nshift + 255) / 256) * pr.batches;
     // SM pairs pay off once there are at least two waves of 256 x 256 tiles; smaller products fill the
-    // machine better with 128 x 256 or 128 x 128 tiles on single CTAs (and so do shifted operands, whose
-    // clearing of the bytes in front of A's rows stays inside one CTA there)
-    if (aligned && option_value(TB200_OPT_HGEMM_SM_PAIRS) && tiles256 >= 2 * (di->sm_count / 2)) {
+    // machine better with 128 x 256 or 128 x 128 tiles on single CTAs (and so does an A 8 bytes off a 16-byte
+    // boundary, whose clearing of the bytes in front of the rows stays inside one CTA there)
+    if (kshift % 8 == 0 && option_value(TB200_OPT_HGEMM_SM_PAIRS) && tiles256 >= 2 * (di->sm_count / 2)) {
         st = ensure_smem_optin<hgemm_tc2_kernel>(di);
         if (st) return st;
+        CUtensorMap map_a0 = map_a;  // first K block of a shifted A: a map over A itself (see the kernel)
+        if (kshift) {
+            st = make_map(&map_a0, pr.a, in_type, 2, (uint64_t)k, (uint64_t)m, (uint64_t)pr.batches, (uint64_t)pr.stride_a, 64, HG_BM);
+            if (st) return st;
+        }
         const int pairs = tiles256 < di->sm_count / 2 ? (int)tiles256 : di->sm_count / 2;
-        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, pr.batches, (int)rows_vec, band_rows(256),
-                                                                      hg_idesc(256, 256, pr.bf16));
+        hgemm_tc2_kernel<<<2 * pairs, HG_THREADS, H2_SMEM_BYTES, s>>>(map_a, map_a0, map_b, map_d, out, m, n, k, pr.batches, (int)rows_vec,
+                                                                      band_rows(256), hg_idesc(256, 256, pr.bf16), kshift, nshift);
         return check_launch();
     }
     const long long tiles_wide = (long long)((m + HG_BM - 1) / HG_BM) * ((n + nshift + 255) / 256) * pr.batches;
