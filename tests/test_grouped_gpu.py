@@ -97,6 +97,29 @@ def test_weights_at_every_byte_phase(lib, fmt, cols, header):
     assert np.array_equal(results[0][0], results[0][1])
 
 
+@pytest.mark.parametrize("header", [16, 24, 128])
+def test_widest_rows_that_fit_the_ring(lib, header):
+    """Four vectors of 18432 columns fill the shared memory of the ring kernel to the last byte when the weights sit on
+    a 128-byte line; off the line the ring slots are 128 bytes longer.  Either way the launch is accepted and equals
+    one launch per matrix."""
+    rows, cols, batch, count = 9, 18432, 4, 2
+    mats, x = _case("q8b", rows, cols, batch, count)
+    dws, dx, dy = [DevBuf(m, header) for m in mats], DevBuf(x), out_buf(count * batch * rows)
+    n = lib.tb200_qx_workspace_bytes(cols, batch)
+    ws = DevBuf(np.zeros(max(n, 16), np.uint8))
+    assert lib.tb200_set_thread_option(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH, 17) == 0
+    try:
+        st = lib.tb200_q8b_gemv_i8_grouped(count, rows, cols, batch, _ptr_array(dws), dx.ptr, _ptr_array([dy]), 1, 0, None, rows, 0,
+                                           ws.ptr, n, stream_ptr())
+        assert st == 0, lib.tb200_status_string(st)
+        sync_and_check(lib)
+    finally:
+        lib.tb200_clear_thread_options()
+    got = dy.numpy().reshape(count, batch, rows)
+    for m in range(count):
+        assert np.array_equal(got[m], _single(lib, "q8b", rows, cols, batch, dws[m], dx))
+
+
 def test_grouped_against_oracle(lib):
     rows, cols, count = 96, 4096, 4
     dws, want = [], []

@@ -1019,15 +1019,16 @@ template <int FMT, int MODE>
 static bool fast_batch_fits(int cols, int batch, Path path, const DeviceInfo *di) {
     const size_t limit = (size_t)di->max_smem_optin - 1024;
     if (path == PATH_RING) {
+        // sized for the form with shifted ring slots (128 bytes more per slot), which weights off a 128-byte line take
         switch (batch) {
-            case 1: return ring_smem_bytes<FMT, 1, MODE>(cols) <= limit;
-            case 2: return ring_smem_bytes<FMT, 2, MODE>(cols) <= limit;
-            case 3: return ring_smem_bytes<FMT, 3, MODE>(cols) <= limit;
-            case 4: return ring_smem_bytes<FMT, 4, MODE>(cols) <= limit;
-            case 5: return ring_smem_bytes<FMT, 5, MODE>(cols) <= limit;
-            case 6: return ring_smem_bytes<FMT, 6, MODE>(cols) <= limit;
-            case 7: return ring_smem_bytes<FMT, 7, MODE>(cols) <= limit;
-            case 8: return ring_smem_bytes<FMT, 8, MODE>(cols) <= limit;
+            case 1: return ring_smem_bytes<FMT, 1, MODE>(cols, true) <= limit;
+            case 2: return ring_smem_bytes<FMT, 2, MODE>(cols, true) <= limit;
+            case 3: return ring_smem_bytes<FMT, 3, MODE>(cols, true) <= limit;
+            case 4: return ring_smem_bytes<FMT, 4, MODE>(cols, true) <= limit;
+            case 5: return ring_smem_bytes<FMT, 5, MODE>(cols, true) <= limit;
+            case 6: return ring_smem_bytes<FMT, 6, MODE>(cols, true) <= limit;
+            case 7: return ring_smem_bytes<FMT, 7, MODE>(cols, true) <= limit;
+            case 8: return ring_smem_bytes<FMT, 8, MODE>(cols, true) <= limit;
             default: return false;
         }
     }
