@@ -781,28 +781,40 @@ def run_probe(args):
     P = lambda t: C.c_void_p(t.data_ptr())
     S = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     what = args.probe.split(",")
+    off = args.probe_offset  # operands this many bytes past a 128-byte line (16 / 24: behind a TornadoVM array header)
+
+    def placed(t):
+        """A copy of t's bytes `off` bytes past a 128-byte line; (keep-alive buffer, pointer)."""
+        raw = torch.empty(t.numel() * t.element_size() + 256, dtype=torch.uint8, device=dev)
+        at = (-raw.data_ptr()) % 128 + off
+        raw[at:at + t.numel() * t.element_size()].copy_(t.contiguous().view(torch.uint8).reshape(-1))
+        return raw, C.c_void_p(raw.data_ptr() + at)
     if what[0] == "hgemm":
         n = int(what[1])
         a = (torch.randn((n, n), device=dev) / n**0.5).half()
         b = (torch.randn((n, n), device=dev) / n**0.5).half()
         c = torch.empty((n, n), device=dev)
+        (ka, pa), (kb, pb), (kc, pc) = placed(a), placed(b), placed(c)
         for _ in range(3):
-            B200Native.call("tb200_hgemm_f32", n, n, n, P(a), P(b), P(c), S)
+            B200Native.call("tb200_hgemm_f32", n, n, n, pa, pb, pc, S)
     else:
         fmt, mode, batch = what[0], what[1], int(what[2])
         bb = 18 if fmt == "q4b" else 34
         w = torch.randint(0, 256, (4, ROWS * (COLS // 32) * bb), dtype=torch.uint8, device=dev)
+        keep, pw = placed(w)
+        per = w[0].numel()
+        del w
         x = torch.randn((batch, COLS), device=dev)
         y = torch.empty((batch, ROWS), device=dev)
         n_ws = lib.tb200_qx_workspace_bytes(COLS, batch)
         ws = torch.empty(n_ws, dtype=torch.uint8, device=dev)
         for i in range(6):
             if mode == "int":
-                B200Native.call(f"tb200_{fmt}_gemv_i8", ROWS, COLS, batch, P(w[i % 4]), P(x), P(y), P(ws), n_ws, S)
+                B200Native.call(f"tb200_{fmt}_gemv_i8", ROWS, COLS, batch, C.c_void_p(pw.value + (i % 4) * per), P(x), P(y), P(ws), n_ws, S)
             else:
-                B200Native.call(f"tb200_{fmt}_gemv", ROWS, COLS, batch, P(w[i % 4]), P(x), P(y), S)
+                B200Native.call(f"tb200_{fmt}_gemv", ROWS, COLS, batch, C.c_void_p(pw.value + (i % 4) * per), P(x), P(y), S)
     torch.cuda.synchronize()
-    print(json.dumps({"probe": args.probe, "status": B200Native.device_status()}))
+    print(json.dumps({"probe": args.probe, "offset": off, "status": B200Native.device_status()}))
 
 
 def main():
@@ -816,6 +828,7 @@ def main():
     ap.add_argument("--group", type=int, default=LAYERS, help="matrices per launch (a divisor of the 32 per step)")
     ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q8layers,q4,sgemm,hgemm; or hgemm_sharded under torch.distributed.run) and print their timings; for profiling")
     ap.add_argument("--probe", default="q8b,int,8", help="with --sections probe: FMT,MODE,BATCH (q8b|q4b, int|f32) or hgemm,N")
+    ap.add_argument("--probe-offset", type=int, default=0, help="with --sections probe: bytes between a 128-byte line and the operands (a multiple of 8)")
     ap.add_argument("--hgemm-sizes", default="2048,4096,8192,16384")
     ap.add_argument("--hgemm-variant", default="pairs", choices=["pairs", "single"],
                     help="with --sections: 256x256 tiles on SM pairs (the default of the library) or 128x256 tiles on single SMs")

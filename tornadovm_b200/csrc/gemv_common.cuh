@@ -73,10 +73,6 @@ constexpr int MODE_INT_FUSED = 2; // int8 activations quantised in the prologue 
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void *src_gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src_gmem) : "memory");
 }
-// 16-byte piece of which only the first `src_bytes` are read from global memory; the rest of the piece is zero-filled
-__device__ __forceinline__ void cp_async_16_partial(uint32_t dst_smem, const void *src_gmem, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src_gmem), "r"(src_bytes) : "memory");
-}
 // 8-byte form (through L1): for operands that are only 8-byte aligned
 __device__ __forceinline__ void cp_async_8(uint32_t dst_smem, const void *src_gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst_smem), "l"(src_gmem) : "memory");

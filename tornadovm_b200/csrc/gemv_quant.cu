@@ -538,16 +538,13 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
             for (int r = 0; r < R; ++r) {
                 const int vrow = min(row_begin + ig * R + r, row_end - 1);
                 const unsigned char *src;  // this lane's first piece; SHR: counted from the boundary below the chunk
-                bool first;                // the chunk starts at the first byte of its matrix
                 if constexpr (GROUPED) {
                     int m = im;
                     while (vrow >= grp->row_start[m + 1]) ++m;  // vrow < row_start[count]
                     if (r == 0) im = m;  // the later chunks of this group start from its first row again
                     src = grp->w[m] + (size_t)(vrow - grp->row_start[m]) * row_bytes + (size_t)ich * T::CB + lane * 16 - wsh;
-                    first = vrow == grp->row_start[m] && ich == 0;
                 } else {
                     src = a.w + (size_t)vrow * row_bytes + (size_t)ich * T::CB + lane * 16 - wsh;
-                    first = vrow == 0 && ich == 0;
                 }
                 const uint32_t dst = ring_s + (st * R + r) * CBS + lane * 16;
                 if constexpr (!SHR) {
@@ -562,29 +559,19 @@ __device__ __forceinline__ void qblk_gemv_body(const QGemvArgs a, const QGroupAr
                         const uint32_t p = (uint32_t)(lane + 32 * i) * 16u;
                         if ((i > 0 || p >= wsh) && p < hi) cp_async_16(dst + i * 512, src + i * 512);
                     }
-                } else if constexpr (FMT == FMT_Q8B) {
-                    // 8-byte phase: the chunk begins and ends in the middle of a piece; its first and last 8 bytes
-                    // travel as copies of their own (two more copy instructions per chunk, which the Q8_0 kernels,
-                    // bound by memory, do not notice: measured 303 against 314 us for the form below)
+                } else {
+                    // 8-byte phase: the chunk begins and ends in the middle of a piece.  Its first and last 8 bytes
+                    // travel as 8-byte copies, both in ONE instruction of lanes 0 and 1 (a comparison in every round
+                    // of pieces instead cost the Q4_0 kernel, which is bound by its instruction count, 20 %)
                     const uint32_t hi_dn = hi - 8u;
 #pragma unroll
                     for (int i = 0; i < T::PIECES; ++i) {
                         const uint32_t p = (uint32_t)(lane + 32 * i) * 16u;
                         if ((i > 0 || p >= lo_up) && p < hi_dn) cp_async_16(dst + i * 512, src + i * 512);
-                        else if (i == 0 && p + 8 == wsh) cp_async_8(dst + 8, src + 8);
-                        else if (p == hi_dn) cp_async_8(dst + i * 512, src + i * 512);
                     }
-                } else {
-                    // 8-byte phase, Q4_0 (bound by its instruction count: 220 against 242 us for the form above): the
-                    // last piece is a 16-byte copy that reads 8 bytes only; the first one brings the 8 bytes in front
-                    // of the chunk along (the end of the row before) -- except at the first byte of a matrix, where
-                    // nothing in front of it is read and the first 8 bytes travel as a copy of their own.
-                    const uint32_t lo = first ? lo_up : wsh - 8u;
-#pragma unroll
-                    for (int i = 0; i < T::PIECES; ++i) {
-                        const uint32_t p = (uint32_t)(lane + 32 * i) * 16u;
-                        if ((i > 0 || p >= lo) && p < hi) cp_async_16_partial(dst + i * 512, src + i * 512, min(16u, hi - p));
-                        else if (i == 0 && first && p + 8 == wsh) cp_async_8(dst + 8, src + 8);
+                    if (lane < 2) {
+                        const uint32_t at = lane ? hi_dn : wsh;  // offset of the 8 bytes from the line below the chunk
+                        cp_async_8(dst - lane * 16 + at, src - lane * 16 + at);
                     }
                 }
             }
