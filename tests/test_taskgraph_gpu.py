@@ -1,4 +1,6 @@
 """The library tasks driven the way TornadoVM drives them: TaskGraph -> plan -> provider -> C ABI."""
+import functools
+
 import numpy as np
 import pytest
 
@@ -256,28 +258,33 @@ def test_packed_results_stored_on_the_host_by_the_kernel(header, fmt, batch):
             mats.append((blocks, None, s))
     packed_h = np.concatenate([b for b, _, _ in mats])
     factory = B200.q8GemvBytesPacked if fmt == "q8" else B200.q4GemvBytesPacked
+    grouped = B200.q8GemvBytesGrouped if fmt == "q8" else B200.q4GemvBytesGrouped
     results = {}
     for host_results in (False, True):
         packed, x = ByteArray(packed_h, header), FloatArray(cols * batch, header)
-        y, z = FloatArray(count * batch * rows, header), FloatArray(rows, header)
+        y, z, u = FloatArray(count * batch * rows, header), FloatArray(rows, header), FloatArray(2 * batch * rows, header)
+        sep = [ByteArray(mats[m][0], header) for m in range(2)]  # the grouped form: one array per matrix
         opts = B200Options(exact_int=True, overlap_launches=True, host_results=host_results)
         tg = (TaskGraph("packed")
-              .transferToDevice(DataTransferMode.FIRST_EXECUTION, packed)
+              .transferToDevice(DataTransferMode.FIRST_EXECUTION, packed, *sep)
               .transferToDevice(DataTransferMode.EVERY_EXECUTION, x)
               .libraryTask("g", factory, count, rows, cols, batch, packed, x, y, opts)
+              .libraryTask("s", functools.partial(grouped, options=opts), rows, cols, batch, x, u, *sep)
               # a second task whose output always travels by copy
               .libraryTask("one", factory, 1, rows, cols, 1, packed, x, z, B200Options(exact_int=True))
-              .transferToHost(DataTransferMode.EVERY_EXECUTION, y, z))
+              .transferToHost(DataTransferMode.EVERY_EXECUTION, y, z, u))
         got = []
         with TornadoExecutionPlan(tg).withCUDAGraph() as plan:
             for it in range(4):
                 x.numpy()[:] = o.JavaRandom(300 + it).gaussian_f32(cols * batch)
-                y.numpy()[:] = np.nan
-                z.numpy()[:] = np.nan
+                for out in (y, z, u):
+                    out.numpy()[:] = np.nan
                 plan.execute()
-                got.append((y.numpy().copy(), z.numpy().copy()))
-                assert plan.d2h_bytes_last == y.nbytes_with_header + z.nbytes_with_header
-            skipped = [key for key in plan._d2h_cache if id(y) in key]
+                got.append((y.numpy().copy(), z.numpy().copy(), u.numpy().copy()))
+                assert plan.d2h_bytes_last == y.nbytes_with_header + z.nbytes_with_header + u.nbytes_with_header
+                # the grouped task multiplies the first two matrices of the packed one
+                assert np.array_equal(got[-1][2], got[-1][0][:2 * batch * rows])
+            skipped = [key for key in plan._d2h_cache if id(y) in key and id(u) in key]
             assert bool(skipped) == (host_results and batch == 1)
             assert y.getSize() == count * batch * rows  # the header on the host is untouched
         results[host_results] = got
@@ -288,5 +295,5 @@ def test_packed_results_stored_on_the_host_by_the_kernel(header, fmt, batch):
                 dots = o.q8_blockdots_i32(q, xq, cols, rows) if fmt == "q8" else o.q4_blockdots_i32(blocks, xq, cols, rows)
                 want = o.blockdots_combine_f64(dots, s, xsc, cols // 32, rows)
                 assert o.rel_l2(got[-1][0].reshape(count, batch, rows)[m, b], want) <= 1e-5
-    for (ya, za), (yb, zb) in zip(results[False], results[True]):
-        assert np.array_equal(ya, yb) and np.array_equal(za, zb)
+    for (ya, za, ua), (yb, zb, ub) in zip(results[False], results[True]):
+        assert np.array_equal(ya, yb) and np.array_equal(za, zb) and np.array_equal(ua, ub)

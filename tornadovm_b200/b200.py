@@ -28,7 +28,7 @@ class B200Options:
     kernels of the plan overlap (each prefetches its weights while the kernel
     before it drains), which requires that no task writes a weight array
     immediately before the mat-vec that reads it; ``host_results`` lets the
-    packed mat-vec kernels store every result into the output array's pinned,
+    grouped and packed mat-vec kernels store every result into the output array's pinned,
     device-mapped host segment as well as into its device buffer, when the
     graph copies that array to the host after every execution -- the plan
     then has no device-to-host copy left to issue for it."""

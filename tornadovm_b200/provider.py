@@ -177,28 +177,12 @@ class B200LibraryProvider:
         elif functionName in _GROUPED_FUNCTIONS:  # (count, rows, cols, batch, x, y, blocks...)
             count = A(0)
             blocks = (C.c_void_p * count)(*[P(6 + m) for m in range(count)])
-            dst = (C.c_void_p * 1)(P(5))
-            st = getattr(lib, _GROUPED_FUNCTIONS[functionName])(count, A(1), A(2), A(3), blocks, P(4), dst, 1, 0, None, A(1), 0, *ws,
-                                                                ctx.stream)
+            st = B200LibraryProvider._grouped(lib, _GROUPED_FUNCTIONS[functionName], inv, ctx, blocks, x_index=4, y_index=5)
         elif functionName in _PACKED_FUNCTIONS:  # (count, rows, cols, batch, blocks, x, y)
             native, block_bytes = _PACKED_FUNCTIONS[functionName]
             count, per = A(0), A(1) * (A(2) // 32) * block_bytes
             blocks = (C.c_void_p * count)(*[P(4) + m * per for m in range(count)])
-            tuning = inv.getTuning()
-            host = inv.getHostPointer(6) if isinstance(tuning, B200Options) and tuning.host_results and A(3) == 1 else None
-            st = TB200_ERR_INVALID_ARG
-            if host:
-                # two destinations: the device buffer and the array's host segment (plain stores over PCIe while the
-                # launch runs).  One vector only: there the same kernel runs whatever the number of destinations, so
-                # the option never changes a result bit.  Shapes that only the one-destination kernels cover are
-                # refused before anything is launched and take the call below.
-                dst = (C.c_void_p * 2)(P(6), host)
-                st = getattr(lib, native)(count, A(1), A(2), A(3), blocks, P(5), dst, 2, 0, None, A(1), 0, *ws, ctx.stream)
-                if st == 0:
-                    inv.markHostDelivered(6)
-            if not host or st == TB200_ERR_INVALID_ARG:
-                dst = (C.c_void_p * 1)(P(6))
-                st = getattr(lib, native)(count, A(1), A(2), A(3), blocks, P(5), dst, 1, 0, None, A(1), 0, *ws, ctx.stream)
+            st = B200LibraryProvider._grouped(lib, native, inv, ctx, blocks, x_index=5, y_index=6)
         elif functionName == "sgemm":  # (m, n, k, alpha, a, b, beta, c)
             st = lib.tb200_sgemm(A(0), A(1), A(2), A(3), P(4), P(5), A(6), P(7), ctx.stream)
         elif functionName == "hgemmF32":  # (m, n, k, a, b, c)
@@ -214,6 +198,27 @@ class B200LibraryProvider:
         else:
             raise RuntimeError(f"[ERROR] B200 function not supported: {functionName}")
         return st
+
+    @staticmethod
+    def _grouped(lib, native, inv, ctx, blocks, x_index, y_index) -> int:
+        """One grouped launch of len(blocks) matrices; arguments 0..3 of the task are count, rows, cols, batch."""
+        P, A = inv.getDevicePointer, inv.getArg
+        fn, ws = getattr(lib, native), (ctx.workspace_ptr, ctx.workspace_bytes)
+        tuning = inv.getTuning()
+        host = inv.getHostPointer(y_index) if isinstance(tuning, B200Options) and tuning.host_results and A(3) == 1 else None
+        if host:
+            # two destinations: the device buffer and the array's host segment (plain stores over PCIe while the
+            # launch runs).  One vector only: there the same kernel runs whatever the number of destinations, so
+            # the option never changes a result bit.  Shapes that only the one-destination kernels cover are
+            # refused before anything is launched and take the call below.
+            dst = (C.c_void_p * 2)(P(y_index), host)
+            st = fn(A(0), A(1), A(2), A(3), blocks, P(x_index), dst, 2, 0, None, A(1), 0, *ws, ctx.stream)
+            if st == 0:
+                inv.markHostDelivered(y_index)
+            if st != TB200_ERR_INVALID_ARG:
+                return st
+        dst = (C.c_void_p * 1)(P(y_index))
+        return fn(A(0), A(1), A(2), A(3), blocks, P(x_index), dst, 1, 0, None, A(1), 0, *ws, ctx.stream)
 
     def destroyContext(self, context: B200Context) -> None:  # noqa: N802
         if context.workspace_ptr:
