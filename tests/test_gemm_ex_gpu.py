@@ -135,6 +135,38 @@ def test_gemm_ex_every_array_behind_a_24_byte_header(lib, in_type, out_type, bat
     assert dd.guard_intact() and dc.guard_intact() and dbias.guard_intact()
 
 
+@pytest.mark.parametrize("header", [8, 16, 24, 40, 100, 120, 128])
+@pytest.mark.parametrize("batches,m,n,k", [(1, 300, 288, 136), (1, 130, 1024, 64), (3, 136, 224, 96), (1, 128, 32, 64)])
+def test_fp32_results_at_every_offset_from_a_line(lib, header, batches, m, n, k):
+    """fp32 results whose rows are whole 128-byte lines (n % 32 == 0) into a destination `header` bytes past a line:
+    the epilogue stores along the destination's lines (whole lines as TMA stores, the first and last segment of a tile
+    and the matrix edges as 8-byte pieces).  Fused epilogue with C and bias at the same offset, ragged rows, several
+    tile columns, batches; a 4-byte phase (header 100) takes the per-element stores.  Nothing around D is written."""
+    a, b, af, bf = _operands(m, n, k, IN_F16, 51, batches)
+    c = _to_out(o.JavaRandom(52).uniform_f32(batches * m * n, -1, 1), OUT_F32)
+    bias = _to_out(o.JavaRandom(53).uniform_f32(n, -1, 1), OUT_F32)
+    da, db, dc, dbias = DevBuf(a, 16), DevBuf(b, 16), DevBuf(c, header), DevBuf(bias, header)
+    dd = out_buf(batches * m * n, np.float32, header=header)
+    use_bias = batches == 1
+    _ok(lib.tb200_gemm_ex(m, n, k, IN_F16, da.ptr, db.ptr, OUT_F32, dd.ptr, 1.25, -0.5, dc.ptr, dbias.ptr if use_bias else None, ACTS["tanh"], batches,
+                          stream_ptr()), lib)
+    sync_and_check(lib)
+    got = dd.numpy().astype(np.float64).reshape(batches, m, n)
+    cf = c.astype(np.float64).reshape(batches, m, n)
+    for i in range(batches):
+        prod = _product(af[i * m * k:(i + 1) * m * k], bf[i * k * n:(i + 1) * k * n], m, n, k)
+        want = o.gemm_epilogue_ref(prod, "tanh", 1.25, -0.5, cf[i], bias=bias.astype(np.float64) if use_bias else None)
+        assert o.rel_l2(got[i], want) <= REL_L2[OUT_F32], (i, o.rel_l2(got[i], want))
+    assert dd.guard_intact() and dc.guard_intact()
+    # the plain product into the same place: bit for bit what it is on a line
+    if batches == 1:
+        plain = [out_buf(m * n, np.float32, header=h) for h in (128, header)]
+        for d in plain:
+            _ok(lib.tb200_hgemm_f32(m, n, k, da.ptr, db.ptr, d.ptr, stream_ptr()), lib)
+        sync_and_check(lib)
+        assert np.array_equal(plain[0].numpy(), plain[1].numpy()) and plain[1].guard_intact()
+
+
 def test_gemm_ex_equals_plain_entry_and_argument_errors(lib):
     m, n, k = 256, 384, 128
     a, b = o.make_hgemm(m, n, k, 3)

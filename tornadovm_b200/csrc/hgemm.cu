@@ -200,6 +200,10 @@ struct HgOut {
     int out_type;   // tb200_gemm_out
     int act;        // tb200_activation
     int tma_store;  // fp32, one dense destination: pieces leave shared memory as TMA tensor stores
+    int line_shift; // >= 0: fp32, one destination off a 128-byte line: stores follow the destination's lines (see
+                    // hg_epilogue_lines); the number of floats between a line boundary and the first column of a tile
+    int line_tma;   // ... and whole lines leave as TMA stores through a map that starts line_cs floats below the
+    int line_cs;    // destination (on the line boundary below it)
     int plain;      // alpha == 1, beta == 0, no bias, no activation, fp32: the accumulator is stored as it is
 };
 
@@ -303,6 +307,95 @@ __device__ __forceinline__ uint16_t hg_to_out16(float x, int out_type) {
     return __bfloat16_as_ushort(__float2bfloat16_rn(x));
 }
 
+// fp32 results into ONE destination whose tile columns do not start on a 128-byte line (an array behind a 16- or
+// 24-byte header, or columns shifted with B).  Storing each 32 x 32 piece where it falls writes every row as 128
+// bytes that straddle two lines, with part-written 32-byte sectors at both ends; measured on products whose
+// epilogue dominates (K = 256, 8192 x 8192 results): 304 us through 8-byte stores at an 8-byte phase and 115 us
+// through TMA stores 16 bytes off a line, against 75 us on a line.  Here the stores follow the destination's lines
+// instead: the warp's two staging tiles form a sliding window over the row -- piece c of the accumulator writes its
+// first 32 - sh columns behind the sh columns that piece c - 1 left in tile c % 2, and its last sh columns into the
+// other tile -- and tile c % 2 then leaves as whole 128-byte lines: one TMA tensor store through a map laid over the
+// line boundary below the destination (a dense destination), else eight lanes per row, 16 bytes each.  Only the
+// first and the last segment of a tile (and segments cut by the matrix edge) are partial and leave as 8-byte pieces.
+//   sh        floats between the line boundary below and the tile's first column (even, 0 .. 30), the same for all tiles
+template <int NCHUNK>
+__device__ __forceinline__ void hg_epilogue_lines(const HgOut &out, const CUtensorMap *map_d, uint32_t taddr, int row0, int n0, int batch, int M,
+                                                  int N, int rows_vec, unsigned char *staging, int lane) {
+    const int row = row0 + lane;
+    const int sh = out.line_shift;
+    const long long boff = (long long)batch * out.batch_stride;
+    float *dst = reinterpret_cast<float *>(out.dst[0]);
+#pragma unroll 1
+    for (int c = 0; c <= NCHUNK; ++c) {
+        const int col0 = n0 + c * 32;
+        if (c < NCHUNK && col0 < N && col0 + 32 > 0) {  // warp-uniform; columns beyond the matrix were not even multiplied
+            uint32_t v[32];
+            tc_ld_32cols(taddr + c * 32, v);
+            tc_wait_ld();
+            if (!out.plain) {
+                const int lo = col0 < 0 ? -col0 : 0, hi = col0 + 32 <= N ? 32 : N - col0;
+                const long long at = boff + (long long)row * out.ld + out.col_off + col0;
+                hg_fuse32_act<TB200_OUT_F32>(v, out, at, col0, lo, hi, row < M, rows_vec != 0);
+            }
+            // the TMA stores that read the two tiles (segments c - 1 and c - 2) were issued before the accumulator was read
+            if (out.line_tma) {
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+            }
+            // lane r writes row r: column i of the piece goes to position (sh + i) % 32 of tile (c + (sh + i) / 32) % 2
+            // (rows of 128 bytes, 16-byte units XOR-swizzled by the row: the layout of a 128-byte-swizzled tensor map)
+            if ((sh & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    const int q = sh + i, pos = q & 31;
+                    unsigned char *tile = staging + ((c + (q >> 5)) & 1) * HG_TMA_TILE_BYTES;
+                    *reinterpret_cast<uint4 *>(tile + lane * 128 + (((pos >> 2) ^ (lane & 7)) << 4)) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int q = sh + i, pos = q & 31;
+                    unsigned char *tile = staging + ((c + (q >> 5)) & 1) * HG_TMA_TILE_BYTES;
+                    *reinterpret_cast<uint2 *>(tile + lane * 128 + (((pos >> 2) ^ (lane & 7)) << 4) + (pos & 3) * 4) = make_uint2(v[i], v[i + 1]);
+                }
+            }
+            if (out.line_tma) fence_async_shared();  // generic-proxy writes before the TMA engine's reads
+        }
+        __syncwarp();
+        // segment c: tile columns 32 c - sh .. 32 c - sh + 31, of which this tile owns [own_lo, own_hi)
+        const int colbase = n0 + c * 32 - sh;
+        const int own_lo = c == 0 ? sh : 0, own_hi = c == NCHUNK ? sh : 32;
+        const int jlo = max(own_lo, -colbase), jhi = min(own_hi, N - colbase);  // both even
+        const unsigned char *tile = staging + (c & 1) * HG_TMA_TILE_BYTES;
+        if (jlo == 0 && jhi == 32 && out.line_tma) {
+            // x = column + line_cs is a multiple of 32: whole lines; rows beyond M are clipped by the map
+            if (lane == 0 && row0 < M) {
+                tma_store_3d(map_d, tile, colbase + out.line_cs, row0, batch);
+                tma_store_commit();
+            }
+        } else if (jlo == 0 && jhi == 32) {
+            // eight lanes store one row's line
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int rl = i * 4 + (lane >> 3), u = lane & 7;
+                const uint4 val = *reinterpret_cast<const uint4 *>(tile + rl * 128 + ((u ^ (rl & 7)) << 4));
+                const int grow = row0 + rl;
+                if (grow < M) *reinterpret_cast<uint4 *>(dst + boff + (long long)grow * out.ld + out.col_off + colbase + 4 * u) = val;
+            }
+        } else if (jlo < jhi) {
+            // sixteen lanes per row, 8 bytes each, inside [jlo, jhi)
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int rl = i * 2 + (lane >> 4), j = (lane & 15) * 2;
+                const uint2 val = *reinterpret_cast<const uint2 *>(tile + rl * 128 + (((j >> 2) ^ (rl & 7)) << 4) + (j & 3) * 4);
+                const int grow = row0 + rl;
+                if (grow < M && j >= jlo && j < jhi) *reinterpret_cast<uint2 *>(dst + boff + (long long)grow * out.ld + out.col_off + colbase + j) = val;
+            }
+        }
+        __syncwarp();  // the tile is rewritten two pieces later
+    }
+}
+
 // Epilogue of one warp for one accumulator tile: NCHUNK pieces of 32 rows (one per lane) x 32 columns.
 //   taddr     tensor-memory address of the warp's lane quarter, first column of the tile's accumulator
 //   row0      first row of the warp's 32 rows, n0 first column of the tile (-4 for the first tile of a product whose
@@ -314,6 +407,10 @@ __device__ __forceinline__ uint16_t hg_to_out16(float x, int out_type) {
 template <int NCHUNK>
 __device__ __forceinline__ void hg_epilogue_tile(const HgOut &out, const CUtensorMap *map_d, uint32_t taddr, int row0, int n0, int batch,
                                                  int M, int N, int rows_vec, unsigned char *staging, int lane, uint32_t &nstores) {
+    if (out.line_shift >= 0) {
+        hg_epilogue_lines<NCHUNK>(out, map_d, taddr, row0, n0, batch, M, N, rows_vec, staging, lane);
+        return;
+    }
     const int row = row0 + lane;
     const long long boff = (long long)batch * out.batch_stride;
 #pragma unroll 1
@@ -934,6 +1031,15 @@ struct HgProblem {
 
 static int out_elem_bytes(int out_type) { return out_type == TB200_OUT_F32 ? 4 : 2; }
 
+// Floats between the 128-byte line below a tile's first column and that column (hg_epilogue_lines), the same for every
+// tile and row when the row pitch and the batch stride are whole lines; -1: that epilogue does not apply.
+static int line_shift_of(const HgOut &out, int n, int nshift, int batches) {
+    if (out.out_type != TB200_OUT_F32 || out.ndst != 1 || !aligned_to(out.dst[0], 8)) return -1;
+    if (out.ld % 32 != 0 || out.col_off % 2 != 0 || n % 2 != 0 || (batches > 1 && out.batch_stride % 32 != 0)) return -1;
+    const long long x0 = (long long)(((uintptr_t)out.dst[0] & 127) / 4) + out.col_off - nshift;
+    return (int)(((x0 % 32) + 32) % 32);
+}
+
 // D = act(alpha * A * B + beta * C + bias) with the tile stores described by `out`.
 static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     const int m = pr.m, n = pr.n, k = pr.k;
@@ -996,7 +1102,10 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
     if (st) return st;
     // finished fp32 pieces of a single dense, 16-byte aligned destination leave as TMA tensor stores (32 x 32 boxes);
     // shifted columns would start the first store at a negative coordinate
-    out.tma_store = out.out_type == TB200_OUT_F32 && out.ndst == 1 && out.col_off == 0 && rows_vec && dst_aligned && n % 4 == 0 && nshift == 0;
+    // -- when the tiles' columns start on the destination's 128-byte lines; off the lines, the stores follow the lines
+    out.line_shift = line_shift_of(out, n, nshift, pr.batches);
+    out.tma_store = out.out_type == TB200_OUT_F32 && out.ndst == 1 && out.col_off == 0 && rows_vec && dst_aligned && n % 4 == 0 && nshift == 0 &&
+                    out.line_shift <= 0;
     if (out.tma_store) {
         st = make_map(&map_d, out.dst[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)n, (uint64_t)m, (uint64_t)pr.batches,
                       (uint64_t)out.batch_stride, 32, 32);
@@ -1005,6 +1114,14 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
         if (out.ld != n) out.tma_store = 0;
     }
     if (!out.tma_store) map_d = CUtensorMap{};  // unused by the kernel
+    if (out.tma_store) out.line_shift = -1;
+    if (out.line_shift >= 0 && out.col_off == 0 && out.ld == n) {
+        // whole lines of the line-following epilogue as TMA stores: a map over the line boundary below the destination,
+        // line_cs floats wider than the row pitch (box columns in front of a row are never stored: such segments are partial)
+        out.line_cs = (int)(((uintptr_t)out.dst[0] & 127) / 4);
+        out.line_tma = make_map(&map_d, reinterpret_cast<float *>(out.dst[0]) - out.line_cs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                                (uint64_t)(n + out.line_cs), (uint64_t)m, (uint64_t)pr.batches, (uint64_t)out.batch_stride, 32, 32, (uint64_t)n) == TB200_OK;
+    }
     // tile rows per band: the band's A panels (rows x k halves) should take about 48 MB of the 126 MB L2
     auto band_rows = [&](int tile_m) {
         long long g = (48ll << 20) / ((long long)tile_m * k * 2);
@@ -1129,8 +1246,15 @@ static int gemm8_launch(int m, int n, int k, const uint8_t *a, const uint8_t *b,
     if (st) return st;
     st = make_map(&map_b, bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)k, (uint64_t)n, 1, 0, 128, (uint32_t)bn);
     if (st) return st;
-    out.tma_store = vec;  // 32-bit results of either kind leave as they are
+    out.line_shift = line_shift_of(out, n, 0, 1);
+    out.tma_store = vec && out.line_shift <= 0;  // 32-bit results of either kind leave as they are
     if (out.tma_store && make_map(&map_d, c, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)n, (uint64_t)m, 1, 0, 32, 32) != TB200_OK) out.tma_store = 0;
+    if (out.tma_store) out.line_shift = -1;
+    if (out.line_shift >= 0) {  // whole lines as TMA stores through a map over the line boundary below c (see hgemm_launch)
+        out.line_cs = (int)(((uintptr_t)c & 127) / 4);
+        out.line_tma = make_map(&map_d, reinterpret_cast<int32_t *>(c) - out.line_cs, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)(n + out.line_cs),
+                                (uint64_t)m, 1, 0, 32, 32, (uint64_t)n) == TB200_OK;
+    }
     // instruction descriptor, both operands K-major: D format at [4,6) (1 = F32, 2 = S32), A and B formats at [7,10) and
     // [10,13) (kind::i8: 1 = signed 8-bit; kind::f8f6f4: 0 = E4M3, 1 = E5M2), N >> 3 at [17,23), M >> 4 at [24,29)
     const uint32_t fmt = KIND == 1 ? 1u : (e5m2 ? 1u : 0u);
