@@ -207,11 +207,20 @@ struct HgOut {
     int plain;      // alpha == 1, beta == 0, no bias, no activation, fp32: the accumulator is stored as it is
 };
 
+// 1 / x by the hardware approximation (1 ulp): the arguments here are 1 + something non-negative.  The IEEE-rounded
+// __frcp_rn carries a slow path for denormals behind a branch, which kept the 32 values of a lane from overlapping
+// (measured on an epilogue-bound product: 320 us with it for gelu, against 74 us without an activation).
+__device__ __forceinline__ float hg_rcp(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
 // erf to about 2e-7 absolute (Abramowitz & Stegun 7.1.26) in a dozen instructions: the library erff costs
 // three times as much, and the epilogue of a tile must finish within the main loop of the next one
 __device__ __forceinline__ float hg_erf(float x) {
     const float ax = fabsf(x);
-    const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.0f));
+    const float t = hg_rcp(fmaf(0.3275911f, ax, 1.0f));
     const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
     const float r = 1.0f - poly * __expf(-ax * ax);
     return copysignf(r, x);
@@ -221,11 +230,11 @@ template <int ACT>
 __device__ __forceinline__ float hg_activate(float x) {
     if (ACT == TB200_ACT_RELU) return fmaxf(x, 0.f);
     if (ACT == TB200_ACT_GELU) return 0.5f * x * (1.0f + hg_erf(x * 0.70710678118654752f));
-    if (ACT == TB200_ACT_SILU) return x * __frcp_rn(1.0f + __expf(-x));
-    if (ACT == TB200_ACT_SIGMOID) return __frcp_rn(1.0f + __expf(-x));
+    if (ACT == TB200_ACT_SILU) return x * hg_rcp(1.0f + __expf(-x));
+    if (ACT == TB200_ACT_SIGMOID) return hg_rcp(1.0f + __expf(-x));
     if (ACT == TB200_ACT_TANH) {
         const float e = __expf(-2.0f * fabsf(x));  // tanh |x| = (1 - e) / (1 + e), no overflow
-        return copysignf((1.0f - e) * __frcp_rn(1.0f + e), x);
+        return copysignf((1.0f - e) * hg_rcp(1.0f + e), x);
     }
     if (ACT == TB200_ACT_HARDSWISH) return x * fminf(fmaxf(x + 3.0f, 0.f), 6.0f) * (1.0f / 6.0f);
     return x;
