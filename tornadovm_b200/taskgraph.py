@@ -162,6 +162,22 @@ class TornadoExecutionPlan:
             arr.data = arr.segment[arr.header:].view(arr.dtype)
             self._buffers[id(arr)] = (self._dev_slab[off:off + n], self._host_slab[off:off + n], off)
         self._arrays = ordered
+        self._host_slab_device_base = self._device_view_of_host_slab()
+
+    def _device_view_of_host_slab(self):
+        """The address at which kernels on this device reach the pinned host slab (cudaHostGetDevicePointer), or None
+        when the runtime does not report one: host segments are then not offered to providers and every output travels
+        by copy."""
+        try:
+            rt = C.CDLL("libcudart.so.12")
+            fn = rt.cudaHostGetDevicePointer
+            fn.argtypes, fn.restype = [C.POINTER(C.c_void_p), C.c_void_p, C.c_uint], C.c_int
+            out = C.c_void_p()
+            if fn(C.byref(out), C.c_void_p(self._host_slab.data_ptr()), 0) != 0 or not out.value:
+                return None
+            return out.value
+        except (OSError, AttributeError):
+            return None
 
     def _buffer(self, arr: TornadoNativeArray):
         return self._buffers[id(arr)]
@@ -189,8 +205,9 @@ class TornadoExecutionPlan:
             d = t.descriptor
             params = d.getParameters()
             ptrs = [self._device_pointer(p) if isinstance(p, TornadoNativeArray) else None for p in params]
-            host = [self._buffer(p)[1].data_ptr() + p.header if isinstance(p, TornadoNativeArray) and id(p) in every_out else None
-                    for p in params]
+            base = self._host_slab_device_base
+            host = [base + self._buffer(p)[2] + p.header if base is not None and isinstance(p, TornadoNativeArray) and id(p) in every_out
+                    else None for p in params]
             inv = LibraryInvocation(params, ptrs, self.context, d.getTuning(), self.device, self.plan_id, host_pointers=host)
             # the interpreter wraps every library dispatch in an NVTX range named library::function
             # (TornadoVMInterpreter.java:1301-1315)
