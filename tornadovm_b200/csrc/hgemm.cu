@@ -1137,10 +1137,12 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
         return (int)(g < 1 ? 1 : (g > 1024 ? 1024 : g));
     };
     const long long tiles256 = (long long)((m + 255) / 256) * ((n + nshift + 255) / 256) * pr.batches;
-    // SM pairs pay off once there are at least two waves of 256 x 256 tiles; smaller products fill the
-    // machine better with 128 x 256 or 128 x 128 tiles on single CTAs (and so does an A 8 bytes off a 16-byte
-    // boundary, whose clearing of the bytes in front of the rows stays inside one CTA there)
-    if (kshift % 8 == 0 && option_value(TB200_OPT_HGEMM_SM_PAIRS) && tiles256 >= 2 * (di->sm_count / 2)) {
+    // SM pairs pay off once the 256 x 256 tiles fill about 85 % of the pairs (measured: 2048 x 2048 results, 64 tiles
+    // on 74 pairs, run alike on both kernels; 3072^3 and 1024 x 8192 x 4096 4 % faster on pairs; 1024^2 results, 16
+    // tiles, 13 % slower); smaller products fill the machine better with 128 x 256 or 128 x 128 tiles on single CTAs
+    // (and so does an A 8 bytes off a 16-byte boundary, whose clearing of the bytes in front of the rows stays
+    // inside one CTA there)
+    if (kshift % 8 == 0 && option_value(TB200_OPT_HGEMM_SM_PAIRS) && tiles256 * 20 >= 17 * (di->sm_count / 2)) {
         st = ensure_smem_optin<hgemm_tc2_kernel>(di);
         if (st) return st;
         CUtensorMap map_a0 = map_a;  // first K block of a shifted A: a map over A itself (see the kernel)
