@@ -388,8 +388,10 @@ int tb200_gemm_ex(int m, int n, int k, int in_type, const void *a, const void *b
  * tornado-api/.../KernelContext.java:703-800; kernel and reference loop in
  * tornado-unittests/.../kernelcontext/matrices/TestMatrixMultiplicationMMAInt8.java:70-172) on
  * tcgen05.mma.kind::i8.  Both operands are fed K-major: B is transposed once per call into `workspace`
- * (tb200_igemm_workspace_bytes(n, k) bytes, 16-byte aligned; provider-owned like the mat-vec workspace).
- * Tensor-core shapes: k % 16 == 0, 16-byte aligned A, a workspace; other cases run a CUDA-core kernel. */
+ * (tb200_igemm_workspace_bytes(n, k) = n * (k + 128) bytes, 16-byte aligned; provider-owned like the mat-vec
+ * workspace: an A behind an array header starts off a 128-byte line, its rows are read from the line boundary below,
+ * and the rows of the transposed B carry as many zero bytes in front).
+ * Tensor-core shapes: k % 16 == 0, 8-byte aligned A, a workspace; other cases run a CUDA-core kernel. */
 size_t tb200_igemm_workspace_bytes(int n, int k);
 int tb200_igemm_s32(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
                     tb200_stream_t stream);

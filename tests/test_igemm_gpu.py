@@ -16,13 +16,16 @@ def _ref(a, b, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(32, 16, 32), (128, 128, 128), (256, 512, 384), (300, 264, 144), (1024, 1024, 1024), (64, 64, 48), (17, 19, 23)])
 @pytest.mark.parametrize("full_range", [False, True])
-def test_igemm_exact(lib, m, n, k, full_range):
+@pytest.mark.parametrize("header", [16, 24, 128])
+def test_igemm_exact(lib, m, n, k, full_range, header):
     r = o.JavaRandom(42)
     if full_range:
         a, b = (r.ints(m * k, 256) - 128).astype(np.int8), (r.ints(k * n, 256) - 128).astype(np.int8)
     else:
         a, b = (r.ints(m * k, 7) - 3).astype(np.int8), (r.ints(k * n, 7) - 3).astype(np.int8)
-    da, db, dc = DevBuf(a), DevBuf(b), out_buf(m * n, np.int32)
+    # every array behind a 16- or 24-byte header (A's rows then start off a 128-byte line, at 24 also off a 16-byte
+    # boundary), or on a line
+    da, db, dc = DevBuf(a, header), DevBuf(b, header), out_buf(m * n, np.int32, header)
     nws = lib.tb200_igemm_workspace_bytes(n, k)
     ws = DevBuf(np.zeros(nws, np.uint8))
     st = lib.tb200_igemm_s32(m, n, k, da.ptr, db.ptr, dc.ptr, ws.ptr, nws, stream_ptr())
@@ -48,8 +51,8 @@ def test_igemm_without_workspace_and_argument_errors(lib):
 FP8_FORMATS = {"e4m3": 0, "e5m2": 1}
 
 
-def _fp8_case(lib, m, n, k, fmt, a, b):
-    da, db, dc = DevBuf(a), DevBuf(b), out_buf(m * n, np.float32)
+def _fp8_case(lib, m, n, k, fmt, a, b, header=16):
+    da, db, dc = DevBuf(a, header), DevBuf(b, header), out_buf(m * n, np.float32, header)
     nws = lib.tb200_igemm_workspace_bytes(n, k)
     ws = DevBuf(np.zeros(max(nws, 16), np.uint8))
     st = lib.tb200_fp8gemm_f32(m, n, k, FP8_FORMATS[fmt], da.ptr, db.ptr, dc.ptr, ws.ptr, nws, stream_ptr())
@@ -61,14 +64,31 @@ def _fp8_case(lib, m, n, k, fmt, a, b):
 
 @pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
 @pytest.mark.parametrize("m,n,k", [(16, 16, 32), (64, 64, 64), (128, 128, 128), (256, 512, 384), (300, 264, 144), (1024, 1024, 1024), (17, 19, 23)])
-def test_fp8_gemm_reference_inputs_exact(lib, m, n, k, fmt):
+@pytest.mark.parametrize("header", [16, 24])
+def test_fp8_gemm_reference_inputs_exact(lib, m, n, k, fmt, header):
     """Inputs of TestMatrixMultiplicationMMAFP8 (multiples of 0.25 in [-2, 2) from Random(42), :433-439): every partial
     sum is exact in fp32, so the result equals the reference loop exactly (its own tolerance is 1e-3, :424)."""
     r = o.JavaRandom(42)
     a = o.fp8_encode_exact((r.ints(m * k, 16) - 8) * 0.25, fmt)
     b = o.fp8_encode_exact((r.ints(k * n, 16) - 8) * 0.25, fmt)
-    got = _fp8_case(lib, m, n, k, fmt, a, b)
+    got = _fp8_case(lib, m, n, k, fmt, a, b, header)
     assert np.array_equal(got.astype(np.float64), o.fp8_gemm_ref(a, b, m, n, k, fmt))
+
+
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+@pytest.mark.parametrize("header", [16, 24, 72])
+@pytest.mark.parametrize("k", [128, 144])
+def test_fp8_gemm_nothing_in_front_of_a_row_reaches_it(lib, fmt, header, k):
+    """A's rows are read from an aligned address below them, so the bytes in front of a row -- the end of the row
+    before -- land in shared memory too.  Row 0 ends in NaNs: they belong in row 0's results and nowhere else."""
+    m, n = 256, 128
+    r = o.JavaRandom(7)
+    a = o.fp8_encode_exact((r.ints(m * k, 16) - 8) * 0.25, fmt).copy()
+    b = o.fp8_encode_exact((r.ints(k * n, 16) - 8) * 0.25, fmt)
+    a.reshape(m, k)[0, k - 16:] = 0x7F  # NaN in both formats
+    got = _fp8_case(lib, m, n, k, fmt, a, b, header)
+    assert np.isnan(got[0]).all()
+    assert np.array_equal(got[1:].astype(np.float64), o.fp8_gemm_ref(a, b, m, n, k, fmt)[1:])
 
 
 def test_fp8_gemm_identity_and_all_halves(lib):

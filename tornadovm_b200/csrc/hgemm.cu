@@ -697,7 +697,8 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         // row r keeps its 16-byte piece j at position j ^ (r % 8) of its 128 bytes (128-byte swizzle);
                         // the first 2 * kshift bytes of the row (whole pieces, then possibly the first 8 bytes of the
                         // next one) are the halves in front of the row
-                        const int zfull = kshift >> 3, zhalf = kshift & 4;
+                        const int zbytes = I8 ? kshift : 2 * kshift;  // kshift counts elements
+                        const int zfull = zbytes >> 4, zhalf = zbytes & 8;
 #pragma unroll
                         for (int r = lane; r < HG_BM; r += 32) {
                             unsigned char *rowp = a_tile + r * 128;
@@ -1179,7 +1180,10 @@ static int hgemm_launch(const HgProblem &pr, HgOut out, tb200_stream_t stream) {
 
 // ---- int8 and fp8 GEMM ---------------------------------------------------------------------------
 // Bt[n][k] = B[k][n], bytes; 32 x 32 tiles through shared memory
-__global__ void __launch_bounds__(256) transpose_bytes_kernel(const int8_t *__restrict__ b, int8_t *__restrict__ bt, int k, int n) {
+// Row n of Bt is `pitch` bytes long and holds column n of B from byte `shift` on; the `shift` bytes in front of it
+// are zeros (an A whose rows start `shift` bytes past the base of its tensor map meets them there).
+__global__ void __launch_bounds__(256) transpose_bytes_kernel(const int8_t *__restrict__ b, int8_t *__restrict__ bt, int k, int n, int pitch,
+                                                              int shift) {
     __shared__ int8_t tile[32][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
@@ -1187,7 +1191,11 @@ __global__ void __launch_bounds__(256) transpose_bytes_kernel(const int8_t *__re
         if (k0 + r < k && n0 + tx < n) tile[r][tx] = b[(size_t)(k0 + r) * n + n0 + tx];
     __syncthreads();
     for (int r = ty; r < 32; r += 8)
-        if (n0 + r < n && k0 + tx < k) bt[(size_t)(n0 + r) * k + k0 + tx] = tile[tx][r];
+        if (n0 + r < n && k0 + tx < k) bt[(size_t)(n0 + r) * pitch + shift + k0 + tx] = tile[tx][r];
+    if (blockIdx.y == 0)
+        for (int r = ty; r < 32; r += 8)
+            for (int j = tx; j < shift; j += 32)
+                if (n0 + r < n) bt[(size_t)(n0 + r) * pitch + j] = 0;
 }
 
 // fp8 byte -> float: E5M2 is the upper byte of an fp16; E4M3 has bias 7, subnormals m * 2^-9 and one NaN (S.1111.111)
@@ -1231,8 +1239,13 @@ static int gemm8_launch(int m, int n, int k, const uint8_t *a, const uint8_t *b,
     const DeviceInfo *di = device_info(&st);
     if (!di) return st;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool tensor = k >= 32 && k % 16 == 0 && aligned_to(a, 16) && (long long)m * n >= 64 * 64 && workspace && aligned_to(workspace, 16) &&
-                        workspace_bytes >= (size_t)n * k;
+    // A off a 128-byte line (an array behind a 16- or 24-byte header): its map lies over the line boundary below
+    // when every row keeps the phase, else over the 16-byte boundary below, and the rows of Bt carry as many zero bytes
+    // in front (see hgemm_tc_kernel)
+    const int kshift = a ? (int)((uintptr_t)a & (k % 128 == 0 ? 127 : 15)) : 0;
+    const int pitch = k + ((kshift + 15) & ~15);
+    const bool tensor = k >= 32 && k % 16 == 0 && aligned_to(a, 8) && (long long)m * n >= 64 * 64 && workspace && aligned_to(workspace, 16) &&
+                        workspace_bytes >= (size_t)n * pitch;
     if (!tensor) {
         st = ensure_kernel<gemm8_generic_kernel<KIND>, 0>(di);
         if (st) return st;
@@ -1243,7 +1256,7 @@ static int gemm8_launch(int m, int n, int k, const uint8_t *a, const uint8_t *b,
     st = ensure_kernel<transpose_bytes_kernel, 0>(di);
     if (st) return st;
     int8_t *bt = reinterpret_cast<int8_t *>(workspace);
-    transpose_bytes_kernel<<<dim3((n + 31) / 32, (k + 31) / 32), 256, 0, s>>>(reinterpret_cast<const int8_t *>(b), bt, k, n);
+    transpose_bytes_kernel<<<dim3((n + 31) / 32, (k + 31) / 32), 256, 0, s>>>(reinterpret_cast<const int8_t *>(b), bt, k, n, pitch, kshift);
     st = check_launch();
     if (st) return st;
     HgOut out{};
@@ -1253,9 +1266,9 @@ static int gemm8_launch(int m, int n, int k, const uint8_t *a, const uint8_t *b,
     const bool wide = 2 * tiles_wide >= di->sm_count;
     const int bn = wide ? 256 : 128;
     CUtensorMap map_a, map_b, map_d{};
-    st = make_map(&map_a, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)k, (uint64_t)m, 1, 0, 128, HG_BM);
+    st = make_map(&map_a, a - kshift, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)(k + kshift), (uint64_t)m, 1, 0, 128, HG_BM, (uint64_t)k);
     if (st) return st;
-    st = make_map(&map_b, bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)k, (uint64_t)n, 1, 0, 128, (uint32_t)bn);
+    st = make_map(&map_b, bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)(k + kshift), (uint64_t)n, 1, 0, 128, (uint32_t)bn, (uint64_t)pitch);
     if (st) return st;
     out.line_shift = line_shift_of(out, n, 0, 1);
     out.tma_store = vec && out.line_shift <= 0;  // 32-bit results of either kind leave as they are
@@ -1277,11 +1290,11 @@ static int gemm8_launch(int m, int n, int k, const uint8_t *a, const uint8_t *b,
     if (wide) {
         st = ensure_smem_optin<hgemm_tc_kernel<256, KIND>>(di);
         if (st) return st;
-        hgemm_tc_kernel<256, KIND><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
+        hgemm_tc_kernel<256, KIND><<<grid, HG_THREADS, HgTile<256>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, kshift, 0);
     } else {
         st = ensure_smem_optin<hgemm_tc_kernel<128, KIND>>(di);
         if (st) return st;
-        hgemm_tc_kernel<128, KIND><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, 0, 0);
+        hgemm_tc_kernel<128, KIND><<<grid, HG_THREADS, HgTile<128>::SMEM_BYTES, s>>>(map_a, map_b, map_d, out, m, n, k, 1, (int)vec, gm, idesc, kshift, 0);
     }
     return check_launch();
 }
@@ -1290,7 +1303,8 @@ static int gemm8_launch(int m, int n, int k, const uint8_t *a, const uint8_t *b,
 
 using namespace tb200;
 
-extern "C" size_t tb200_igemm_workspace_bytes(int n, int k) { return n > 0 && k > 0 ? (size_t)n * k : 0; }
+// room for Bt with up to 128 bytes of zeros in front of every row (an A off a 128-byte line)
+extern "C" size_t tb200_igemm_workspace_bytes(int n, int k) { return n > 0 && k > 0 ? (size_t)n * ((size_t)k + 128) : 0; }
 
 extern "C" int tb200_igemm_s32(int m, int n, int k, const int8_t *a, const int8_t *b, int32_t *c, void *workspace, size_t workspace_bytes,
                                tb200_stream_t stream) {
