@@ -110,3 +110,27 @@ class B200Native:
         v = C.c_int(0)
         cls.check_status(cls.load().tb200_device_status_of(op_classes, C.byref(v)), "tb200_device_status_of")
         return v.value
+
+
+def graph_replayer(cuda_graph, torch_stream, synchronize=True):
+    """A callable that replays an instantiated ``torch.cuda.CUDAGraph`` on ``torch_stream`` with one
+    cudaGraphLaunch (and, with ``synchronize``, one cudaStreamSynchronize) through the CUDA runtime the process has
+    already loaded -- the two calls a JVM host makes per execution -- or None when the runtime library or the
+    graph's handle cannot be reached (callers then replay through torch, which also selects the device and the
+    stream around the launch)."""
+    try:
+        rt = C.CDLL("libcudart.so.12")
+        launch, sync = rt.cudaGraphLaunch, rt.cudaStreamSynchronize
+        launch.argtypes, launch.restype = [C.c_void_p, C.c_void_p], C.c_int
+        sync.argtypes, sync.restype = [C.c_void_p], C.c_int
+        exec_handle = C.c_void_p(cuda_graph.raw_cuda_graph_exec())
+    except (OSError, AttributeError, RuntimeError):
+        return None
+    stream = C.c_void_p(torch_stream.cuda_stream)
+
+    def replay():
+        st = launch(exec_handle, stream) or (sync(stream) if synchronize else 0)
+        if st:
+            raise RuntimeError(f"[ERROR] replay of a captured execution failed with CUDA status {st}")
+    return replay
+

@@ -20,7 +20,7 @@ import ctypes as C
 import torch
 import torch.distributed as dist
 
-from .native import B200Native, TornadoB200Error
+from .native import B200Native, TornadoB200Error, graph_replayer
 from .sharding import shard_range
 
 FLAG_WORDS = 8  # flag array of one rank: one word per peer
@@ -210,10 +210,13 @@ class ShardedGroupedGemv:
                     if download:
                         self.y_host.copy_(y, non_blocking=True)
                 self.steps = steps_before  # capture enqueued nothing; the replay below is the step
-                entry = self._step_graphs[key] = (g, y)
-            g, y = entry
-            with torch.cuda.stream(self.stream):
-                g.replay()
+                entry = self._step_graphs[key] = (g, y, graph_replayer(g, self.stream, synchronize=False))
+            g, y, replay = entry
+            if replay is not None and torch.cuda.current_device() == self.stream.device.index:
+                replay()
+            else:
+                with torch.cuda.stream(self.stream):
+                    g.replay()
             self.steps += 1
         else:
             with torch.cuda.stream(self.stream):

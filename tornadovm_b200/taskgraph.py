@@ -25,6 +25,7 @@ import torch
 
 from .arrays import TornadoNativeArray
 from .descriptor import Access
+from .native import graph_replayer
 from .provider import B200LibraryProvider, LibraryInvocation
 
 
@@ -234,24 +235,8 @@ class TornadoExecutionPlan:
 
     def _bind_replay(self):
         """Replaying an execution is one cudaGraphLaunch on the plan's stream and one stream synchronisation, as in
-        the reference's interpreter (a JNI call each).  Returns a callable that issues exactly those two calls on the
-        instantiated graph, or None when the runtime library or the graph's handle cannot be reached (the plan then
-        replays through torch, which also selects the device and the stream around the launch)."""
-        try:
-            rt = C.CDLL("libcudart.so.12")
-            launch, sync = rt.cudaGraphLaunch, rt.cudaStreamSynchronize
-            launch.argtypes, launch.restype = [C.c_void_p, C.c_void_p], C.c_int
-            sync.argtypes, sync.restype = [C.c_void_p], C.c_int
-            exec_handle = C.c_void_p(self._cuda_graph.raw_cuda_graph_exec())
-        except (OSError, AttributeError, RuntimeError):
-            return None
-        stream = C.c_void_p(self.stream.cuda_stream)
-
-        def replay():
-            st = launch(exec_handle, stream) or sync(stream)
-            if st:
-                raise RuntimeError(f"[ERROR] replay of the captured execution failed with CUDA status {st}")
-        return replay
+        the reference's interpreter (a JNI call each)."""
+        return graph_replayer(self._cuda_graph, self.stream)
 
     def execute(self):
         g = self.graph
