@@ -263,6 +263,15 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             ws = torch.empty(ws_n, dtype=torch.uint8, device=dev)
             t = timeit(lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, 1, P(blocks[i]), P(x), P(yl[i]), P(ws), ws_n, S), 10, period=LAYERS)
             out["q8_blocks_int_b1_one_launch_per_matvec"] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}
+            # the same with 8 activation vectors (the tensor-core mat-vec behind its quantiser kernel), back to back
+            x8 = torch.randn((8, COLS), device=dev)
+            y8 = torch.empty((LAYERS, 8, ROWS), device=dev)
+            ws8_n = lib.tb200_qx_workspace_bytes(COLS, 8)
+            ws8 = torch.empty(ws8_n, dtype=torch.uint8, device=dev)
+            by8 = algorithmic_bytes(ROWS, COLS, 8)
+            t = timeit(lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, 8, P(blocks[i]), P(x8), P(y8[i]), P(ws8), ws8_n, S), 10, period=LAYERS)
+            out["q8_blocks_int_b8_one_launch_per_matvec"] = {"GB/s": by8 / t / 1e9, "frac_hbm": by8 / t / 1e9 / hbm_peak, "us": t * 1e6}
+            del x8, y8, ws8
             for grp in (2, 8):
                 wp = [(C.c_void_p * grp)(*[blocks[c * grp + m].data_ptr() for m in range(grp)]) for c in range(LAYERS // grp)]
                 dp = [(C.c_void_p * 1)(yl[c * grp].data_ptr()) for c in range(LAYERS // grp)]
