@@ -271,6 +271,13 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             by8 = algorithmic_bytes(ROWS, COLS, 8)
             t = timeit(lambda i: lib.tb200_q8b_gemv_i8(ROWS, COLS, 8, P(blocks[i]), P(x8), P(y8[i]), P(ws8), ws8_n, S), 10, period=LAYERS)
             out["q8_blocks_int_b8_one_launch_per_matvec"] = {"GB/s": by8 / t / 1e9, "frac_hbm": by8 / t / 1e9 / hbm_peak, "us": t * 1e6}
+            # ... and 8 matrices per grouped launch: one quantiser kernel, then the tensor-core mat-vecs chained to one another
+            grp = 8
+            wp8 = [(C.c_void_p * grp)(*[blocks[c * grp + m].data_ptr() for m in range(grp)]) for c in range(LAYERS // grp)]
+            dp8 = [(C.c_void_p * 1)(y8[c * grp].data_ptr()) for c in range(LAYERS // grp)]
+            t = timeit(lambda i: lib.tb200_q8b_gemv_i8_grouped(grp, ROWS, COLS, 8, wp8[i], P(x8), dp8[i], 1, 0, None, ROWS, 0, P(ws8), ws8_n, S),
+                       10, period=LAYERS // grp)
+            out["q8_blocks_int_b8_8_per_launch"] = {"GB/s": grp * by8 / t / 1e9, "frac_hbm": grp * by8 / t / 1e9 / hbm_peak, "us": t * 1e6}
             del x8, y8, ws8
             for grp in (2, 8):
                 wp = [(C.c_void_p * grp)(*[blocks[c * grp + m].data_ptr() for m in range(grp)]) for c in range(LAYERS // grp)]
