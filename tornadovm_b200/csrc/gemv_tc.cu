@@ -558,6 +558,18 @@ static bool tc_plan(const QGemvArgs &a, const DeviceInfo *di, TcPlan &p) {
     p.ks = (nch + p.phases - 1) / p.phases;
     const int units = (a.rows + 15) / 16;
     p.grid = units < di->sm_count ? units : di->sm_count;
+    // Every CTA walks ceil(units / grid) units, whole or not: with 896 units on 148 CTAs that is a seventh unit of a
+    // single row each, a full item's latency for 1 % of its bytes.  Among the grids that keep at least four fifths
+    // of the SMs busy, take the one that leaves the fewest unit slots empty (896 units: 128 CTAs of 7 whole units).
+    // Q8_0 blocks only, where the launch is bound by memory (measured at 14336 x 4096: 8 vectors 15.0 -> 14.4 us); the
+    // split layout and Q4_0 are bound by their consumer warps and lose 2-4 % on fewer SMs.
+    if (FMT == FMT_Q8B && units > di->sm_count) {
+        long long best_waste = -1;
+        for (int g = di->sm_count; g >= di->sm_count * 4 / 5; --g) {
+            const long long waste = (long long)((units + g - 1) / g) * g - units;
+            if (best_waste < 0 || waste < best_waste) best_waste = waste, p.grid = g;
+        }
+    }
     const int rows_per_cta = (a.rows + p.grid - 1) / p.grid;
     p.max_units = (rows_per_cta + 15) / 16 + 1;
     const size_t tail = Cfg::PARTIAL + (p.phases > 1 ? (size_t)p.max_units * NT * 512 : 0) + 128;
