@@ -116,8 +116,9 @@ enum tb200_option { TB200_OPT_OVERLAP_LAUNCHES = 1, TB200_OPT_HGEMM_SM_PAIRS = 2
  * TB200_OPT_FLOAT_TENSOR_CORES (default 1): the float-mode quantised mat-vecs (tb200_q8_gemv,
  * tb200_q8b_gemv, tb200_q4b_gemv) feed the tensor cores with the fp32 vector split into two fp16
  * halves (relative representation error 2^-22 of the vector's largest element) when shape and alignment
- * allow.  0 keeps them on the CUDA-core kernels; 1 takes the tensor-core kernel from the batch size
- * where it was measured faster; 2 takes it for every eligible call.
+ * allow.  0 keeps them on the CUDA-core kernels; 1 and 2 take the tensor-core kernel for every eligible
+ * call (it measured faster from one vector on in every layout; the two values are kept for callers that
+ * set them).
  * TB200_OPT_MMA_WARP_RINGS (default 1): diagnostics; 0 selects the older CTA-wide ring of the
  * tensor-core mat-vec kernels.
  * TB200_OPT_HGEMM_LINE_STORES (default 2): the FP16 GEMM's epilogue transposes its tiles through shared memory

@@ -1111,15 +1111,17 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
         path = PATH_RING, a.wshift = ring_phase<FMT>(a.w, a.cols);
     }
     // Tensor-core kernel with the activations in registers (gemv_tc.cu): integer mode from
-    // TB200_OPT_INT_TENSOR_CORE_MIN_BATCH vectors on, float mode from the measured batch on, and every batch
+    // TB200_OPT_INT_TENSOR_CORE_MIN_BATCH vectors on, float mode from one vector on, and every batch
     // when split-layout operands are only 8-byte aligned (arrays behind a 24-byte header), where the alternative
     // is the byte-load kernel.
     const bool overlap = option_value(TB200_OPT_OVERLAP_LAUNCHES) != 0;
     if (option_value(TB200_OPT_TC_REGISTER_KERNEL)) {
         const bool only8 = FMT == FMT_Q8S && (!aligned_to(a.w, 16) || (a.scales && !aligned_to(a.scales, 16)));
         if (MODE == MODE_FLOAT) {
-            const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 from the measured batch on, 2 always
-            const int min_batch = float_tc >= 2 || only8 ? 1 : (FMT == FMT_Q8S ? 1 : 2);
+            const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 / 2 on
+            // measured at 14336 x 4096, one vector: Q8_0 blocks 14.5 us on the tensor cores against 16.6 us on the FFMA ring
+            // kernel, Q4_0 12.6 against 13.9 us; from one vector on in every layout
+            const int min_batch = 1;
             QGemvArgs p = a;
             p.batch = a.batch < 8 ? a.batch : 8;
             if ((float_tc || only8) && a.batch >= min_batch && qtc_eligible(FMT, MODE_FLOAT, p, di)) {
@@ -1173,9 +1175,8 @@ static int qgemv_dispatch(QGemvArgs a, int8_t *xq_ws, float *xs_ws, tb200_stream
             if (qmma_eligible(FMT, a)) return qmma_dispatch(FMT, a, di, s);
         }
         if constexpr (MODE == MODE_FLOAT && !DOTS) {
-            // measured on 14336 x 4096: the split layout gains from one vector on, the block layouts from two
-            const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 from the measured batch on, 2 always
-            const int min_batch = float_tc >= 2 ? 1 : (FMT == FMT_Q8S ? 1 : 2);
+            const int float_tc = option_value(TB200_OPT_FLOAT_TENSOR_CORES);  // 0 off, 1 / 2 on
+            const int min_batch = 1;
             // diagnostics only (TB200_OPT_TC_REGISTER_KERNEL = 0): this older kernel splits x into fp16 pairs without a
             // prescale, so it is accurate only for activations inside the normal fp16 range
             if (float_tc && a.batch >= min_batch && !option_value(TB200_OPT_TC_REGISTER_KERNEL)) {
