@@ -807,12 +807,13 @@ def run_probe(args):
         return raw, C.c_void_p(raw.data_ptr() + at)
     if what[0] == "hgemm":
         n = int(what[1])
-        a = (torch.randn((n, n), device=dev) / n**0.5).half()
-        b = (torch.randn((n, n), device=dev) / n**0.5).half()
+        k = int(what[2]) if len(what) > 2 else n  # hgemm,N,K: an N x N result over K (a small K shows the epilogue)
+        a = (torch.randn((n, k), device=dev) / k**0.5).half()
+        b = (torch.randn((k, n), device=dev) / k**0.5).half()
         c = torch.empty((n, n), device=dev)
         (ka, pa), (kb, pb), (kc, pc) = placed(a), placed(b), placed(c)
         for _ in range(3):
-            B200Native.call("tb200_hgemm_f32", n, n, n, pa, pb, pc, S)
+            B200Native.call("tb200_hgemm_f32", n, n, k, pa, pb, pc, S)
     else:
         fmt, mode, batch = what[0], what[1], int(what[2])
         bb = 18 if fmt == "q4b" else 34
@@ -843,7 +844,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--group", type=int, default=LAYERS, help="matrices per launch (a divisor of the 32 per step)")
     ap.add_argument("--sections", default="", help="run only these secondary kernels (comma list of sgemv,q8,q8layers,q4,sgemm,hgemm; or hgemm_sharded under torch.distributed.run) and print their timings; for profiling")
-    ap.add_argument("--probe", default="q8b,int,8", help="with --sections probe: FMT,MODE,BATCH (q8b|q4b, int|f32) or hgemm,N")
+    ap.add_argument("--probe", default="q8b,int,8", help="with --sections probe: FMT,MODE,BATCH (q8b|q4b, int|f32) or hgemm,N[,K]")
     ap.add_argument("--probe-offset", type=int, default=0, help="with --sections probe: bytes between a 128-byte line and the operands (a multiple of 8)")
     ap.add_argument("--hgemm-sizes", default="2048,4096,8192,16384")
     ap.add_argument("--hgemm-variant", default="pairs", choices=["pairs", "single"],
