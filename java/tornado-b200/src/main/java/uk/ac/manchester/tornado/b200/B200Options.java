@@ -13,6 +13,14 @@ public final class B200Options {
      * mat-vec that reads it.
      */
     public boolean overlapLaunches;
+    /**
+     * Let the grouped and packed mat-vec kernels store their results into the output array's host segment as
+     * well as into its device buffer, so that no device-to-host copy is left for that array. Needs the
+     * segment page-locked and mapped ({@code cuMemHostRegister(..., CU_MEMHOSTREGISTER_DEVICEMAP)}) and an
+     * accessor for its device-visible address on {@code LibraryInvocation}, which the runtime does not have yet;
+     * without them the option is ignored.
+     */
+    public boolean hostResults;
 
     public B200Options exactInt(boolean v) {
         this.exactInt = v;
@@ -21,6 +29,11 @@ public final class B200Options {
 
     public B200Options overlapLaunches(boolean v) {
         this.overlapLaunches = v;
+        return this;
+    }
+
+    public B200Options hostResults(boolean v) {
+        this.hostResults = v;
         return this;
     }
 }

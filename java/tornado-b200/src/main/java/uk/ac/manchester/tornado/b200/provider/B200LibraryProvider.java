@@ -24,6 +24,14 @@ import uk.ac.manchester.tornado.runtime.library.spi.TornadoNativeStreamSupport;
  */
 public final class B200LibraryProvider implements TornadoLibraryProvider {
 
+    /**
+     * B200Options.hostResults needs the device-visible address of the output array's page-locked host segment.
+     * LibraryInvocation has no accessor for it (spi/LibraryInvocation.java:54-97), so the kernels get one
+     * destination; with such an accessor the address would be passed here and the interpreter would skip its
+     * transferToHost copy for the array.
+     */
+    private static final long NO_HOST_SEGMENT = 0L;
+
     private static final class B200Context implements LibraryContext {
         private final long stream;
         private long workspacePtr;
@@ -154,7 +162,7 @@ public final class B200LibraryProvider implements TornadoLibraryProvider {
                     blocks[m] = inv.getDevicePointer(6 + m);
                 }
                 yield B200Native.blockGemvI8Grouped(functionName.startsWith("q8") ? 0 : 1, count, (int) inv.getArg(1), (int) inv.getArg(2), (int) inv.getArg(3), //
-                        blocks, inv.getDevicePointer(4), inv.getDevicePointer(5), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream);
+                        blocks, inv.getDevicePointer(4), inv.getDevicePointer(5), NO_HOST_SEGMENT, ctx.workspacePtr, ctx.workspaceBytes, ctx.stream);
             }
             // (m, n, k, alpha, a, b, beta, c)
             case "sgemm" -> B200Native.sgemm((int) inv.getArg(0), (int) inv.getArg(1), (int) inv.getArg(2), (float) inv.getArg(3), //
@@ -172,7 +180,7 @@ public final class B200LibraryProvider implements TornadoLibraryProvider {
                     blocks[m] = inv.getDevicePointer(4) + m * per;
                 }
                 yield B200Native.blockGemvI8Grouped(kind, count, (int) inv.getArg(1), (int) inv.getArg(2), (int) inv.getArg(3), //
-                        blocks, inv.getDevicePointer(5), inv.getDevicePointer(6), ctx.workspacePtr, ctx.workspaceBytes, ctx.stream);
+                        blocks, inv.getDevicePointer(5), inv.getDevicePointer(6), NO_HOST_SEGMENT, ctx.workspacePtr, ctx.workspaceBytes, ctx.stream);
             }
             // (m, n, k, alpha, a, b, beta, d): 16-bit operands and result, D updated in place
             case "hgemm", "bgemm" -> {

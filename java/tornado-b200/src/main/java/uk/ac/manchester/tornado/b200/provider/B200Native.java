@@ -142,11 +142,18 @@ public final class B200Native {
     }
 
     /** One launch for {@code blocks.length} matrices; the pointer arrays live in a confined arena for the duration of the call only. */
-    public static int blockGemvI8Grouped(int kind, int count, int rows, int cols, int batch, long[] blocks, long x, long y, long workspace, long workspaceBytes, long stream) {
+    /**
+     * yHost: device-visible address of the output array's page-locked host segment, or 0. With it the kernel stores
+     * every result to both destinations (one vector only, where the same kernel runs either way).
+     */
+    public static int blockGemvI8Grouped(int kind, int count, int rows, int cols, int batch, long[] blocks, long x, long y, long yHost, long workspace, long workspaceBytes,
+            long stream) {
         try (Arena arena = Arena.ofConfined()) {
             MemorySegment blockPtrs = arena.allocateFrom(JAVA_LONG, blocks);
-            MemorySegment dst = arena.allocateFrom(JAVA_LONG, y);
-            return (int) (kind == 0 ? q8bGemvI8Grouped : q4bGemvI8Grouped).invokeExact(count, rows, cols, batch, blockPtrs, x, dst, 1, 0L, 0L, rows, 0, workspace, workspaceBytes, stream);
+            boolean both = yHost != 0L && batch == 1;
+            MemorySegment dst = both ? arena.allocateFrom(JAVA_LONG, y, yHost) : arena.allocateFrom(JAVA_LONG, y);
+            return (int) (kind == 0 ? q8bGemvI8Grouped : q4bGemvI8Grouped).invokeExact(count, rows, cols, batch, blockPtrs, x, dst, both ? 2 : 1, 0L, 0L, rows, 0, workspace,
+                    workspaceBytes, stream);
         } catch (Throwable t) {
             throw wrap(t);
         }
