@@ -288,3 +288,28 @@ def test_grouped_rows_of_different_shapes_equal_one_launch_per_matrix(lib, fmt, 
         got = dys[m].numpy()[:batch * r].reshape(batch, r)
         assert np.array_equal(got, want), (m, r)
         assert dys[m].guard_intact()
+
+
+@pytest.mark.parametrize("fmt", ["q8b", "q4b"])
+@pytest.mark.parametrize("rows,cols,batch,count", [(144, 4096, 8, 5), (100, 1024, 2, 3), (16, 2048, 5, 32), (264, 256, 8, 2)])
+def test_matrices_back_to_back_run_as_one_tensor_core_launch(lib, fmt, rows, cols, batch, count):
+    """Equally shaped matrices that lie back to back (the packed task's array) with two to eight vectors are one matrix
+    of count * rows rows to the tensor-core kernel, which writes y[matrix][vector][row].  Bit for bit the results of one
+    launch per matrix (a row's sums do not depend on how rows are dealt to CTAs); rows that are no multiple of 16 make
+    a 16-row unit span two matrices."""
+    mats, x = _case(fmt, rows, cols, batch, count)
+    packed = DevBuf(np.concatenate(mats))
+    per = mats[0].nbytes
+    dx, dy = DevBuf(x), out_buf(count * batch * rows)
+    n = lib.tb200_qx_workspace_bytes(cols, batch)
+    ws = DevBuf(np.zeros(max(n, 16), np.uint8))
+    ptrs = (C.c_void_p * count)(*[packed.ptr.value + m * per for m in range(count)])
+    fn = lib.tb200_q8b_gemv_i8_grouped if fmt == "q8b" else lib.tb200_q4b_gemv_i8_grouped
+    st = fn(count, rows, cols, batch, ptrs, dx.ptr, _ptr_array([dy]), 1, 0, None, rows, 0, ws.ptr, n, stream_ptr())
+    assert st == 0, lib.tb200_status_string(st)
+    sync_and_check(lib)
+    got = dy.numpy().reshape(count, batch, rows)
+    for m in range(count):
+        want = _single(lib, fmt, rows, cols, batch, DevBuf(mats[m]), dx, dp4a=False)
+        assert np.array_equal(got[m], want), (m, np.abs(got[m] - want).max())
+    assert dy.guard_intact() and packed.guard_intact()

@@ -20,6 +20,8 @@ struct QGemvArgs {
     int rows, cols, batch;
     int wshift;              // block-layout ring kernels: byte phase of every row chunk (w modulo 128 or modulo 16)
     int xlayout;             // int mode, tensor-core kernel: 0 = xq[batch][cols], xs[batch][cols/32]; 1 = xq[block][batch][32], xs[block][batch]
+    int group_rows;          // tensor-core kernel: > 0: the rows are those of rows / group_rows equally shaped matrices that lie
+                             // back to back, and y is [matrix][batch][group_rows]
 };
 
 // Several matrices of one shape sharing the activation vectors, and several destinations for every

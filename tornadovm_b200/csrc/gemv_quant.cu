@@ -1344,6 +1344,20 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
             if (st) return st;
             st = quantize_x_layout(cols, batch, x, xq, xs, s, true);
             if (st) return st;
+            // Equally shaped matrices that lie back to back (the packed task's ByteArray) with the standard output
+            // layout are ONE matrix of count * rows rows to the kernel: one launch, the activations loaded once per
+            // CTA, no tail per matrix (measured, 8 matrices of 14336 x 4096, 8 vectors: 12.6 us per matrix as a chain
+            // of launches); the kernel writes y[matrix][vector][row].
+            bool one_launch = count > 1 && total <= 0x7fffffffLL;
+            const size_t per = (size_t)shape.rows[0] * (size_t)(cols / 32) * RingTraits<FMT>::BB;
+            for (int m = 0; m < count && one_launch; ++m)
+                one_launch = shape.rows[m] == shape.rows[0] && shape.row_off[m] == 0 && grp.w[m] == grp.w[0] + (size_t)m * per &&
+                             shape.out_off[m] == (long long)m * batch * shape.rows[0];
+            if (one_launch) {
+                QGemvArgs all{grp.w[0], nullptr, nullptr, xq, xs, dst[0], nullptr, (int)total, cols, batch};
+                all.xlayout = 1, all.group_rows = shape.rows[0];
+                if (qtc_eligible(FMT, MODE_INT, all, di)) return qtc_dispatch(FMT, MODE_INT, all, di, s, true);
+            }
             for (int m = 0; m < count; ++m) {
                 if (shape.rows[m] == 0) continue;
                 QGemvArgs one{grp.w[m], nullptr, nullptr, xq, xs, dst[0] + shape.out_off[m] + shape.row_off[m], nullptr, shape.rows[m], cols, batch};

@@ -517,23 +517,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
                 continue;
             }
             const int r0 = row_begin + u * 16 + g, r1 = r0 + 8;
+            // y[vector][row]; for matrices laid back to back (group_rows > 0) y[matrix][vector][row of the matrix]: a
+            // base per row and the distance between two vectors
+            size_t y0 = (size_t)r0, y1 = (size_t)r1, ystep = (size_t)rows;
+            if (a.group_rows > 0) {
+                const int m0 = r0 / a.group_rows, m1 = r1 / a.group_rows;
+                ystep = (size_t)a.group_rows;
+                y0 = (size_t)m0 * a.batch * ystep + (size_t)(r0 - m0 * a.group_rows);
+                y1 = (size_t)m1 * a.batch * ystep + (size_t)(r1 - m1 * a.group_rows);
+            }
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 if (FLT) {
                     const int n = j * 4 + t;
                     if (n < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n * rows + r0] = sum[j].x;
-                        if (r1 < row_end) a.y[(size_t)n * rows + r1] = sum[j].z;
+                        if (r0 < row_end) a.y[(size_t)n * ystep + y0] = sum[j].x;
+                        if (r1 < row_end) a.y[(size_t)n * ystep + y1] = sum[j].z;
                     }
                 } else {
                     const int n0 = j * 8 + 2 * t, n1 = n0 + 1;
                     if (n0 < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n0 * rows + r0] = sum[j].x;
-                        if (r1 < row_end) a.y[(size_t)n0 * rows + r1] = sum[j].z;
+                        if (r0 < row_end) a.y[(size_t)n0 * ystep + y0] = sum[j].x;
+                        if (r1 < row_end) a.y[(size_t)n0 * ystep + y1] = sum[j].z;
                     }
                     if (n1 < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n1 * rows + r0] = sum[j].y;
-                        if (r1 < row_end) a.y[(size_t)n1 * rows + r1] = sum[j].w;
+                        if (r0 < row_end) a.y[(size_t)n1 * ystep + y0] = sum[j].y;
+                        if (r1 < row_end) a.y[(size_t)n1 * ystep + y1] = sum[j].w;
                     }
                 }
             }
