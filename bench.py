@@ -278,7 +278,16 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
             t = timeit(lambda i: lib.tb200_q8b_gemv_i8_grouped(grp, ROWS, COLS, 8, wp8[i], P(x8), dp8[i], 1, 0, None, ROWS, 0, P(ws8), ws8_n, S),
                        10, period=LAYERS // grp)
             out["q8_blocks_int_b8_8_per_launch"] = {"GB/s": grp * by8 / t / 1e9, "frac_hbm": grp * by8 / t / 1e9 / hbm_peak, "us": t * 1e6}
-            del x8, y8, ws8
+            # the Q4_0 twin: 8 matrices of 14336 x 4096 back to back, 8 vectors, one grouped launch
+            q4per = ROWS * (COLS // 32) * 18
+            q4 = torch.randint(0, 256, (LAYERS, q4per), dtype=torch.uint8, device=dev)
+            q4.view(-1)[1::18] = 0x20  # scales of ordinary size
+            wq4 = [(C.c_void_p * grp)(*[q4[c * grp + m].data_ptr() for m in range(grp)]) for c in range(LAYERS // grp)]
+            by4 = algorithmic_bytes(ROWS, COLS, 8, 18)
+            t = timeit(lambda i: lib.tb200_q4b_gemv_i8_grouped(grp, ROWS, COLS, 8, wq4[i], P(x8), dp8[i], 1, 0, None, ROWS, 0, P(ws8), ws8_n, S),
+                       10, period=LAYERS // grp)
+            out["q4_blocks_int_b8_8_per_launch"] = {"GB/s": grp * by4 / t / 1e9, "frac_hbm": grp * by4 / t / 1e9 / hbm_peak, "us": t * 1e6}
+            del x8, y8, ws8, q4
             for grp in (2, 8):
                 wp = [(C.c_void_p * grp)(*[blocks[c * grp + m].data_ptr() for m in range(grp)]) for c in range(LAYERS // grp)]
                 dp = [(C.c_void_p * 1)(yl[c * grp].data_ptr()) for c in range(LAYERS // grp)]
