@@ -24,6 +24,17 @@ struct QGemvArgs {
                              // back to back, and y is [matrix][batch][group_rows]
 };
 
+// Tensor-core kernel over several matrices that share the column count and the activation vectors: the launch's rows
+// are those of all matrices laid end to end (count = 0: one matrix).  Matrix m holds rows row_start[m] ..
+// row_start[m + 1] and writes its [batch][rows of m] block at y + y_off[m].
+constexpr int kTcMaxGroup = 32;
+struct TcGroup {
+    int count;
+    int row_start[kTcMaxGroup + 1];
+    const uint8_t *w[kTcMaxGroup];
+    long long y_off[kTcMaxGroup];
+};
+
 // Several matrices of one shape sharing the activation vectors, and several destinations for every
 // output value (this GPU's buffer and, peer-mapped, the other GPUs' buffers).
 // rows a warp of the grouped kernel collects before it stores them (128-byte stores to every destination;
@@ -135,6 +146,8 @@ int qmma_float_dispatch(int fmt, const QGemvArgs &a, const DeviceInfo *di, cudaS
 // a.dots set (batch 1, MODE_INT) writes the int32 block dots instead of y.
 bool qtc_eligible(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di);
 int qtc_dispatch(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap);
+// block formats, MODE_INT, 1..8 vectors: a.rows = rows of all matrices of grp, a.w = grp.w[0] (all at one 16-byte phase)
+int qtc_dispatch_group(int fmt, const QGemvArgs &a, const TcGroup &grp, const DeviceInfo *di, cudaStream_t s, bool overlap);
 
 // ---- helpers of gemv_quant.cu used by the allocation-free entry point ----
 int split_workspace(int cols, int batch, void *workspace, size_t workspace_bytes, int8_t **xq, float **xs);

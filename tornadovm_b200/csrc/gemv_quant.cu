@@ -1358,6 +1358,20 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
                 all.xlayout = 1, all.group_rows = shape.rows[0];
                 if (qtc_eligible(FMT, MODE_INT, all, di)) return qtc_dispatch(FMT, MODE_INT, all, di, s, true);
             }
+            // Any other group whose matrices share the 16-byte phase: still one launch, with a table of the matrices'
+            // first rows, addresses and output blocks in the kernel's parameters (a row's matrix is looked up where
+            // the row is requested and where its sums are stored).
+            bool table = count > 1 && total <= 0x7fffffffLL;
+            for (int m = 0; m < count && table; ++m) table = aligned_to(grp.w[m], 8) && (((uintptr_t)grp.w[m] ^ (uintptr_t)grp.w[0]) & 15) == 0;
+            if (table) {
+                TcGroup tg{};
+                tg.count = count;
+                for (int m = 0; m < count; ++m) tg.row_start[m] = grp.row_start[m], tg.w[m] = grp.w[m], tg.y_off[m] = shape.out_off[m] + shape.row_off[m];
+                tg.row_start[count] = (int)total;
+                QGemvArgs all{grp.w[0], nullptr, nullptr, xq, xs, dst[0], nullptr, (int)total, cols, batch};
+                all.xlayout = 1;
+                if (qtc_eligible(FMT, MODE_INT, all, di)) return qtc_dispatch_group(FMT, all, tg, di, s, true);
+            }
             for (int m = 0; m < count; ++m) {
                 if (shape.rows[m] == 0) continue;
                 QGemvArgs one{grp.w[m], nullptr, nullptr, xq, xs, dst[0] + shape.out_off[m] + shape.row_off[m], nullptr, shape.rows[m], cols, batch};

@@ -61,7 +61,15 @@ struct TcArgs {
     int stages;    // stages of the CTA-wide ring
     int wshift;    // 0, or 8 when the weights sit 8 bytes past a 16-byte boundary (an array behind a 24-byte header)
     int sshift;    // the same for the scale array of the split layout
+    TcGroup grp;   // count > 0: the rows of several matrices laid end to end (block formats)
 };
+
+// matrix of row r of a grouped launch (r < row_start[count])
+__device__ __forceinline__ int tc_matrix_of(const TcGroup &grp, int r) {
+    int m = 0;
+    while (r >= grp.row_start[m + 1]) ++m;
+    return m;
+}
 
 __device__ __forceinline__ float4 ldg_f4(const float *p, bool vec) {
     if (vec) return __ldg(reinterpret_cast<const float4 *>(p));
@@ -407,8 +415,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
             __syncwarp();
             // lanes 0..15: the 16-byte aligned part of row `lane`, at the same phase in shared memory as in global
             // memory; lanes 16..31: the scales of row lane - 16 (split layout)
+            // first byte of row `r` of the unit in this phase; grouped: the row's matrix is looked up (a unit may span two)
+            auto row_src = [&](int r) -> const unsigned char * {
+                if (args.grp.count == 0) return src + (size_t)r * row_bytes;
+                const int vr = row_first + r, m = tc_matrix_of(args.grp, vr);
+                return args.grp.w[m] + (size_t)(vr - args.grp.row_start[m]) * row_bytes + (size_t)p * KS * T::WROW;
+            };
             if (lane < nrows)
-                bulk_g2s_stream(dst + (size_t)lane * wpitch + wcut, src + (size_t)lane * row_bytes + (wcut >> 1), wbytes - wcut, &full_bar[st], policy);
+                bulk_g2s_stream(dst + (size_t)lane * wpitch + wcut, row_src(lane) + (wcut >> 1), wbytes - wcut, &full_bar[st], policy);
             if (sbytes && lane >= 16 && lane - 16 < nrows)
                 bulk_g2s_stream(dst + 16 * (size_t)wpitch + (size_t)(lane - 16) * spitch + scut, ssrc + (size_t)(lane - 16) * bpr * 2 + (scut >> 1), sbytes - scut,
                                 &full_bar[st], policy);
@@ -418,7 +432,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
                 if (r < nrows) {
                     if (args.wshift) {
                         const uint32_t off = last ? wbytes - 8 : 0u;  // relative to the row's first byte
-                        cp_async_8(smem_u32(dst + (size_t)r * wpitch + 8 + off), src + (size_t)r * row_bytes + off);
+                        cp_async_8(smem_u32(dst + (size_t)r * wpitch + 8 + off), row_src(r) + off);
                     }
                     if (args.sshift && sbytes) {
                         const uint32_t off = last ? sbytes - 8 : 0u;
@@ -519,30 +533,43 @@ __global__ void __launch_bounds__(TC_THREADS, 1) qtc_gemv_kernel(const __grid_co
             const int r0 = row_begin + u * 16 + g, r1 = r0 + 8;
             // y[vector][row]; for matrices laid back to back (group_rows > 0) y[matrix][vector][row of the matrix]: a
             // base per row and the distance between two vectors
-            size_t y0 = (size_t)r0, y1 = (size_t)r1, ystep = (size_t)rows;
+            long long y0 = r0, y1 = r1;
+            size_t ystep0 = (size_t)rows, ystep1 = (size_t)rows;
             if (a.group_rows > 0) {
                 const int m0 = r0 / a.group_rows, m1 = r1 / a.group_rows;
-                ystep = (size_t)a.group_rows;
-                y0 = (size_t)m0 * a.batch * ystep + (size_t)(r0 - m0 * a.group_rows);
-                y1 = (size_t)m1 * a.batch * ystep + (size_t)(r1 - m1 * a.group_rows);
+                ystep0 = ystep1 = (size_t)a.group_rows;
+                y0 = (long long)m0 * a.batch * a.group_rows + (r0 - m0 * a.group_rows);
+                y1 = (long long)m1 * a.batch * a.group_rows + (r1 - m1 * a.group_rows);
+            } else if (args.grp.count > 0) {
+                // the table of a grouped launch: matrix m writes its [batch][rows of m] block at y + y_off[m]
+                if (r0 < row_end) {
+                    const int m0 = tc_matrix_of(args.grp, r0);
+                    ystep0 = (size_t)(args.grp.row_start[m0 + 1] - args.grp.row_start[m0]);
+                    y0 = args.grp.y_off[m0] + (r0 - args.grp.row_start[m0]);
+                }
+                if (r1 < row_end) {
+                    const int m1 = tc_matrix_of(args.grp, r1);
+                    ystep1 = (size_t)(args.grp.row_start[m1 + 1] - args.grp.row_start[m1]);
+                    y1 = args.grp.y_off[m1] + (r1 - args.grp.row_start[m1]);
+                }
             }
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
                 if (FLT) {
                     const int n = j * 4 + t;
                     if (n < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n * ystep + y0] = sum[j].x;
-                        if (r1 < row_end) a.y[(size_t)n * ystep + y1] = sum[j].z;
+                        if (r0 < row_end) a.y[(long long)(n * ystep0) + y0] = sum[j].x;
+                        if (r1 < row_end) a.y[(long long)(n * ystep1) + y1] = sum[j].z;
                     }
                 } else {
                     const int n0 = j * 8 + 2 * t, n1 = n0 + 1;
                     if (n0 < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n0 * ystep + y0] = sum[j].x;
-                        if (r1 < row_end) a.y[(size_t)n0 * ystep + y1] = sum[j].z;
+                        if (r0 < row_end) a.y[(long long)(n0 * ystep0) + y0] = sum[j].x;
+                        if (r1 < row_end) a.y[(long long)(n0 * ystep1) + y1] = sum[j].z;
                     }
                     if (n1 < a.batch) {
-                        if (r0 < row_end) a.y[(size_t)n1 * ystep + y0] = sum[j].y;
-                        if (r1 < row_end) a.y[(size_t)n1 * ystep + y1] = sum[j].w;
+                        if (r0 < row_end) a.y[(long long)(n1 * ystep0) + y0] = sum[j].y;
+                        if (r1 < row_end) a.y[(long long)(n1 * ystep1) + y1] = sum[j].w;
                     }
                 }
             }
@@ -592,12 +619,13 @@ static bool tc_plan(const QGemvArgs &a, const DeviceInfo *di, TcPlan &p) {
 }
 
 template <int FMT, int NT, int XSRC, bool DOTS>
-static int tc_launch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
+static int tc_launch(const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap, const TcGroup *grp = nullptr) {
     TcPlan p;
     if (!tc_plan<FMT, NT>(a, di, p)) return TB200_ERR_INVALID_ARG;
     // pointers are 0 or 8 modulo 16 here (tc_eligible)
     const int wshift = (int)((uintptr_t)a.w & 15), sshift = (FMT == FMT_Q8S && a.scales) ? (int)((uintptr_t)a.scales & 15) : 0;
     TcArgs args{a, p.ks, p.phases, p.max_units, p.stages, wshift, sshift};
+    if (grp) args.grp = *grp;
     constexpr auto kernel = qtc_gemv_kernel<FMT, NT, XSRC, DOTS>;
     const int st = ensure_smem_optin<kernel>(di);
     if (st) return st;
@@ -639,6 +667,11 @@ bool qtc_eligible(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di) {
 int qtc_dispatch(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap) {
     return fmt == FMT_Q8S ? tc_dispatch<FMT_Q8S>(mode, a, di, s, overlap)
                           : fmt == FMT_Q8B ? tc_dispatch<FMT_Q8B>(mode, a, di, s, overlap) : tc_dispatch<FMT_Q4B>(mode, a, di, s, overlap);
+}
+
+int qtc_dispatch_group(int fmt, const QGemvArgs &a, const TcGroup &grp, const DeviceInfo *di, cudaStream_t s, bool overlap) {
+    if (fmt == FMT_Q8S || a.batch > 8 || grp.count < 1 || grp.count > kTcMaxGroup) return TB200_ERR_INVALID_ARG;
+    return fmt == FMT_Q8B ? tc_launch<FMT_Q8B, 1, X_INT_WS, false>(a, di, s, overlap, &grp) : tc_launch<FMT_Q4B, 1, X_INT_WS, false>(a, di, s, overlap, &grp);
 }
 
 }  // namespace tb200
