@@ -53,6 +53,11 @@ __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *m
                  : "memory");
 }
 
+// fetch a tensor map (a kernel parameter) into the descriptor cache before the first copy needs it
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void *dst_smem, const CUtensorMap *map, int x, int y, int z, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
                      smem_u32(dst_smem)),
@@ -602,6 +607,11 @@ hgemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int edge_cols = (N + nshift) - (tiles_n - 1) * BN;  // columns of the last tile column
     const bool edge_last = !I8 && batches == 1 && tiles_n > 1 && edge_cols <= BN / 2;
 
+    if (threadIdx.x == 32) {  // descriptor fetches overlap the set-up below
+        tma_prefetch_map(&map_a);
+        tma_prefetch_map(&map_b);
+        if (out.tma_store || out.line_tma) tma_prefetch_map(&map_d);
+    }
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
@@ -844,6 +854,12 @@ hgemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int k_blocks = (K + kshift + HG_BK - 1) / HG_BK;
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
+    if (threadIdx.x == 32) {  // descriptor fetches overlap the set-up below
+        tma_prefetch_map(&map_a);
+        if (kshift) tma_prefetch_map(&map_a0);
+        tma_prefetch_map(&map_b);
+        if (out.tma_store || out.line_tma) tma_prefetch_map(&map_d);
+    }
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < H2_STAGES; ++s) {
