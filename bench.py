@@ -349,8 +349,7 @@ def secondary_metrics(torch, lib, stream, hbm_peak, tensor_peak, sections=("sgem
                     for rows_a, w_a, y_a, n, c in garg[i & 1]:
                         lib.tb200_q4b_gemv_i8_grouped_rows(n, rows_a, c, batch, w_a, P(xs[c]), y_a, P(ws), ws_n, S)
                 runs = [(f"q4_layer_sweep_f32_b{batch}", sweep_f), (f"q4_layer_sweep_int_b{batch}", sweep_i)]
-                if batch <= 4:
-                    runs.append((f"q4_layer_sweep_int_grouped_b{batch}", sweep_g))
+                runs.append((f"q4_layer_sweep_int_grouped_b{batch}", sweep_g))
                 for name, fn in runs:
                     t = timeit(fn, 3, period=2)
                     out[name] = {"GB/s": by / t / 1e9, "frac_hbm": by / t / 1e9 / hbm_peak, "us": t * 1e6}

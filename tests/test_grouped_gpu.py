@@ -263,7 +263,7 @@ def test_grouped_sync_announces_waits_and_rotates_slots(lib):
 
 
 @pytest.mark.parametrize("fmt", ["q8b", "q4b"])
-@pytest.mark.parametrize("cols,batch", [(1024, 1), (4096, 2), (96, 1), (14336, 4)])
+@pytest.mark.parametrize("cols,batch", [(1024, 1), (4096, 2), (96, 1), (14336, 4), (4096, 8), (2048, 16), (4096, 9)])
 def test_grouped_rows_of_different_shapes_equal_one_launch_per_matrix(lib, fmt, cols, batch):
     """The projections that read one vector (different row counts, one of them empty), each with its own output array."""
     rows = [300, 64, 0, 64, 1000, 17] if cols < 8192 else [40, 9, 0, 33]
@@ -291,7 +291,8 @@ def test_grouped_rows_of_different_shapes_equal_one_launch_per_matrix(lib, fmt, 
 
 
 @pytest.mark.parametrize("fmt", ["q8b", "q4b"])
-@pytest.mark.parametrize("rows,cols,batch,count", [(144, 4096, 8, 5), (100, 1024, 2, 3), (16, 2048, 5, 32), (264, 256, 8, 2)])
+@pytest.mark.parametrize("rows,cols,batch,count", [(144, 4096, 8, 5), (100, 1024, 2, 3), (16, 2048, 5, 32), (264, 256, 8, 2), (80, 4096, 16, 3),
+                                                   (24, 1024, 11, 4)])
 def test_matrices_back_to_back_run_as_one_tensor_core_launch(lib, fmt, rows, cols, batch, count):
     """Equally shaped matrices that lie back to back (the packed task's array) with two to eight vectors are one matrix
     of count * rows rows to the tensor-core kernel, which writes y[matrix][vector][row].  Bit for bit the results of one

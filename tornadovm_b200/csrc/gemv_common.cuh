@@ -146,7 +146,7 @@ int qmma_float_dispatch(int fmt, const QGemvArgs &a, const DeviceInfo *di, cudaS
 // a.dots set (batch 1, MODE_INT) writes the int32 block dots instead of y.
 bool qtc_eligible(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di);
 int qtc_dispatch(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di, cudaStream_t s, bool overlap);
-// block formats, MODE_INT, 1..8 vectors: a.rows = rows of all matrices of grp, a.w = grp.w[0] (all at one 16-byte phase)
+// block formats, MODE_INT, 1..16 vectors: a.rows = rows of all matrices of grp, a.w = grp.w[0] (all at one 16-byte phase)
 int qtc_dispatch_group(int fmt, const QGemvArgs &a, const TcGroup &grp, const DeviceInfo *di, cudaStream_t s, bool overlap);
 
 // ---- helpers of gemv_quant.cu used by the allocation-free entry point ----

@@ -1329,6 +1329,9 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
     // Two to eight vectors into one local buffer: the tensor-core mat-vec per matrix (it outruns the dp4a ring kernel
     // from two vectors on), all behind ONE quantiser launch and chained to one another, so that each starts
     // requesting its weights while its predecessor drains.
+    // Up to 8 vectors (one column tile).  With 9 to 16 the kernel that reads quantised activations from the workspace is
+    // the slower one (Q4_0 layer sweep at 16 vectors: 311 us as one launch per column count against 259 us as one launch
+    // per matrix with the quantiser inside the kernel), so those groups take the per-matrix path below.
     if (batch >= option_value(TB200_OPT_INT_TENSOR_CORE_MIN_BATCH) && batch <= 8 && npeers == 1 && !epoch && !gs.flags &&
         option_value(TB200_OPT_TC_REGISTER_KERNEL) && workspace) {
         bool tc = true;
@@ -1337,7 +1340,14 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
                           cols, batch};
             tc = shape.ld[m] == shape.rows[m] && qtc_eligible(FMT, MODE_INT, one, di);
         }
-        if (tc) {
+        // one launch over all rows: possible when the matrices share the 16-byte phase and the kernel takes that many rows
+        bool table = tc && count > 1 && total <= 0x7fffffffLL;
+        for (int m = 0; m < count && table; ++m) table = aligned_to(grp.w[m], 8) && (((uintptr_t)grp.w[m] ^ (uintptr_t)grp.w[0]) & 15) == 0;
+        if (table) {
+            QGemvArgs probe{grp.w[0], nullptr, nullptr, reinterpret_cast<const int8_t *>(workspace), nullptr, dst[0], nullptr, (int)total, cols, batch};
+            table = qtc_eligible(FMT, MODE_INT, probe, di);
+        }
+        if (tc && (batch <= 8 || table)) {
             int8_t *xq;
             float *xs;
             st = split_workspace(cols, batch, workspace, workspace_bytes, &xq, &xs);
@@ -1348,7 +1358,7 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
             // layout are ONE matrix of count * rows rows to the kernel: one launch, the activations loaded once per
             // CTA, no tail per matrix (measured, 8 matrices of 14336 x 4096, 8 vectors: 12.6 us per matrix as a chain
             // of launches); the kernel writes y[matrix][vector][row].
-            bool one_launch = count > 1 && total <= 0x7fffffffLL;
+            bool one_launch = table;
             const size_t per = (size_t)shape.rows[0] * (size_t)(cols / 32) * RingTraits<FMT>::BB;
             for (int m = 0; m < count && one_launch; ++m)
                 one_launch = shape.rows[m] == shape.rows[0] && shape.row_off[m] == 0 && grp.w[m] == grp.w[0] + (size_t)m * per &&
@@ -1361,8 +1371,6 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
             // Any other group whose matrices share the 16-byte phase: still one launch, with a table of the matrices'
             // first rows, addresses and output blocks in the kernel's parameters (a row's matrix is looked up where
             // the row is requested and where its sums are stored).
-            bool table = count > 1 && total <= 0x7fffffffLL;
-            for (int m = 0; m < count && table; ++m) table = aligned_to(grp.w[m], 8) && (((uintptr_t)grp.w[m] ^ (uintptr_t)grp.w[0]) & 15) == 0;
             if (table) {
                 TcGroup tg{};
                 tg.count = count;
@@ -1370,7 +1378,7 @@ static int qgemv_i8_grouped_shape(int count, const GroupShape &shape, int cols, 
                 tg.row_start[count] = (int)total;
                 QGemvArgs all{grp.w[0], nullptr, nullptr, xq, xs, dst[0], nullptr, (int)total, cols, batch};
                 all.xlayout = 1;
-                if (qtc_eligible(FMT, MODE_INT, all, di)) return qtc_dispatch_group(FMT, all, tg, di, s, true);
+                return qtc_dispatch_group(FMT, all, tg, di, s, true);
             }
             for (int m = 0; m < count; ++m) {
                 if (shape.rows[m] == 0) continue;

@@ -670,7 +670,8 @@ int qtc_dispatch(int fmt, int mode, const QGemvArgs &a, const DeviceInfo *di, cu
 }
 
 int qtc_dispatch_group(int fmt, const QGemvArgs &a, const TcGroup &grp, const DeviceInfo *di, cudaStream_t s, bool overlap) {
-    if (fmt == FMT_Q8S || a.batch > 8 || grp.count < 1 || grp.count > kTcMaxGroup) return TB200_ERR_INVALID_ARG;
+    if (fmt == FMT_Q8S || a.batch > kMaxBatch || grp.count < 1 || grp.count > kTcMaxGroup) return TB200_ERR_INVALID_ARG;
+    if (a.batch > 8) return fmt == FMT_Q8B ? tc_launch<FMT_Q8B, 2, X_INT_WS, false>(a, di, s, overlap, &grp) : tc_launch<FMT_Q4B, 2, X_INT_WS, false>(a, di, s, overlap, &grp);
     return fmt == FMT_Q8B ? tc_launch<FMT_Q8B, 1, X_INT_WS, false>(a, di, s, overlap, &grp) : tc_launch<FMT_Q4B, 1, X_INT_WS, false>(a, di, s, overlap, &grp);
 }
 
