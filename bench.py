@@ -592,12 +592,15 @@ def run_gpu_arm(args):
         from tornadovm_b200.taskgraph import CudaDevice, DataTransferMode, TaskGraph, TornadoExecutionPlan
         # one ByteArray per task holds the task's `group` matrices back to back (7 task arguments whatever the count:
         # a library task carries at most 20, TaskGraph.java:886)
-        wa = [ByteArray(blocks[c * group:(c + 1) * group].cpu().numpy().ravel()) for c in range(LAYERS // group)]
-        xa = FloatArray(op.x_dev.cpu().numpy())
-        ya = [FloatArray(group * ROWS * BATCH) for _ in range(LAYERS // group)]
+        w_host = [blocks[c * group:(c + 1) * group].cpu().numpy().ravel() for c in range(LAYERS // group)]
+        x_host = op.x_dev.cpu().numpy()
 
-        def plan_seconds(host_results):
-            """Seconds per execute() of the step as one task graph; the outputs of the last execution."""
+        def plan_seconds(host_results, header=16):
+            """Seconds per execute() of the step as one task graph; the outputs of the last execution.  `header`: bytes
+            in front of every array's payload (16, or 24 as with the reference launcher's default JVM flags)."""
+            wa = [ByteArray(w, header) for w in w_host]
+            xa = FloatArray(x_host, header)
+            ya = [FloatArray(group * ROWS * BATCH, header) for _ in range(LAYERS // group)]
             opts = B200Options(exact_int=True, overlap_launches=True, host_results=host_results)
             tg = TaskGraph("q8decode").transferToDevice(DataTransferMode.FIRST_EXECUTION, *wa) \
                 .transferToDevice(DataTransferMode.EVERY_EXECUTION, xa)
@@ -621,9 +624,10 @@ def run_gpu_arm(args):
         # the output arrays' pinned host segments themselves (B200Options.host_results); the second is the e2e figure
         copy_s, _, _, copy_out = plan_seconds(False)
         e2e_s, h2d, d2h, host_out = plan_seconds(True)
-        if not all(np.array_equal(a, b) for a, b in zip(copy_out, host_out)):
+        h24_s, _, _, h24_out = plan_seconds(True, header=24)
+        if not all(np.array_equal(a, b) and np.array_equal(a, c) for a, b, c in zip(copy_out, host_out, h24_out)):
             raise SystemExit("e2e: the host-stored results differ from the copied ones")
-        del copy_out, host_out
+        del copy_out, host_out, h24_out, w_host
         e2e_s *= e2e_steps
         api = ("TaskGraph.libraryTask(B200.q8GemvBytesPacked, B200Options(host_results=True)) + "
                "TornadoExecutionPlan.withCUDAGraph().execute()")
@@ -666,7 +670,8 @@ def run_gpu_arm(args):
                    "launch": f"{LAYERS // group} grouped launch(es) per step, programmatic dependent launches" + (", timed steps replayed from one CUDA graph" if world > 1 else "")},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / e2e_steps * 1e3, "api": api,
-                **({"copy_back_ms_per_step": copy_s * 1e3, "copy_back_value": total_bytes / copy_s / 1e9} if world == 1 else {})},
+                **({"copy_back_ms_per_step": copy_s * 1e3, "copy_back_value": total_bytes / copy_s / 1e9,
+                    "header24_ms_per_step": h24_s * 1e3, "header24_value": total_bytes / h24_s / 1e9} if world == 1 else {})},
         "gpu_launches": gpu_launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": NCU_TRAFFIC_BYTES_PER_GEMV * group if world == 1 else None,
