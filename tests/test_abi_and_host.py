@@ -100,3 +100,34 @@ def test_provider_rejects_devices_without_native_stream():
         def getNativeStream(self, plan):  # noqa: N802
             return 0
     assert p.canHandle(Dev())
+
+
+def test_invocation_host_segments_and_delivery_marks():
+    """The extension of LibraryInvocation that B200Options.host_results uses: the device-visible address of an output
+    array's host segment (None unless the plan offers one) and the marks a dispatch leaves for the arrays whose
+    results its kernel stored on the host itself."""
+    from tornadovm_b200.provider import LibraryInvocation
+    x, y = FloatArray(8), FloatArray(8)
+    inv = LibraryInvocation([4, x, y], [None, 0x1000, 0x2000], context=None)
+    assert inv.getHostPointer(1) is None and inv.getHostPointer(2) is None and inv.hostDelivered() == frozenset()
+    inv = LibraryInvocation([4, x, y], [None, 0x1000, 0x2000], context=None, host_pointers=[None, None, 0x7F0000002010])
+    assert inv.getHostPointer(2) == 0x7F0000002010 and inv.getHostPointer(1) is None
+    inv.markHostDelivered(2)
+    assert inv.hostDelivered() == frozenset({2})
+    assert B200Options().host_results is False and B200Options(host_results=True).host_results is True
+
+
+def test_graph_replayer_declines_what_is_not_a_captured_graph():
+    """Without an instantiated CUDA graph (no GPU here) the replayer reports that it cannot bind, and callers replay
+    through torch instead."""
+    from tornadovm_b200.native import graph_replayer
+
+    class NoGraph:
+        pass
+    assert graph_replayer(NoGraph(), NoGraph()) is None
+
+
+def test_igemm_workspace_covers_the_padded_transpose(lib):
+    """B transposed with up to 128 zero bytes in front of every row (an A off a 128-byte line)."""
+    assert lib.tb200_igemm_workspace_bytes(264, 144) == 264 * (144 + 128)
+    assert lib.tb200_igemm_workspace_bytes(0, 144) == 0
